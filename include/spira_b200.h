@@ -1,0 +1,190 @@
+/*
+ * spira_b200 -- C ABI of the B200-native sparse-convolution hot path.
+ *
+ * Every entry point replaces one function of the reference's pybind module
+ * `spira.nn.functional._C` (SPIN-Research-Group/Spira); the reference interface each one
+ * stands in for is cited as  file:line  relative to the reference's `source/` directory.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; all data pointers are DEVICE pointers unless the name
+ *     starts with `host_`;
+ *   - every call is stream-ordered on `stream` (a cudaStream_t passed as void*) and never
+ *     synchronises, allocates or frees device memory: outputs and scratch are caller-owned;
+ *   - return value 0 = success, negative = error; spira_b200_last_error() returns the
+ *     message of the last failing call made by the calling thread;
+ *   - `key_bytes` is 4 (x12|y12|z8) or 8 (x24|y24|z16), z in the low bits
+ *     (csrc/spira/compress_layout.h:12-44).
+ */
+#ifndef SPIRA_B200_H_
+#define SPIRA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPIRA_B200_OK 0
+#define SPIRA_B200_ERR_ARGUMENT (-1)
+#define SPIRA_B200_ERR_CUDA (-2)
+#define SPIRA_B200_ERR_UNSUPPORTED (-3)
+#define SPIRA_B200_ERR_WORKSPACE (-4)
+
+#define SPIRA_B200_LAYOUT_OS 0 /* map[T_al][K], column iz*nxy + o   (kernels/query_sorted.cuh:150,159) */
+#define SPIRA_B200_LAYOUT_WS 1 /* map[K][T_al], row kz*o + iz       (kernels/query_sorted.cuh:42,52)   */
+
+#define SPIRA_B200_MAX_MAPS 16   /* maps per batched search launch */
+#define SPIRA_B200_MAX_LEVELS 8  /* levels per batched downsample  */
+
+int spira_b200_version(void);
+const char *spira_b200_last_error(void);
+/* Clears the sticky CUDA error of the calling thread's device, like
+ * cuda_reset_error (csrc/spira/torch/cuda_memory_buffer.cu:15-16). */
+int spira_b200_reset_error(void);
+
+/* ---- packed keys ------------------------------------------------------------------------- */
+
+/* coords[n][3] int32 -> keys[n]; replaces the Compress kernel (csrc/spira/cuda/kernels/compress.cuh:8-24). */
+int spira_b200_pack(const int32_t *coords, int64_t n, int key_bytes, void *keys, void *stream);
+
+/* keys[n] -> coords[n][3]; replaces cuda_unflatten (csrc/spira/torch/cuda_arg_sort_coordinates.cu:41-66). */
+int spira_b200_unpack(const void *keys, int64_t n, int key_bytes, int32_t *coords, void *stream);
+
+/* Scratch bytes needed by spira_b200_flatten_sort for n keys. */
+int spira_b200_flatten_sort_workspace(int64_t n, int key_bytes, size_t *bytes);
+
+/* pack + ascending unsigned sort + permutation; replaces cuda_flatten_sort
+ * (csrc/spira/torch/cuda_arg_sort_coordinates.cu:11-39, cuda/functions/arg_sort_coodrinates.cu:35-88).
+ * sorted_keys[n], perm[n] (int32, perm[i] = original row of sorted item i). */
+int spira_b200_flatten_sort(const int32_t *coords, int64_t n, int key_bytes, void *sorted_keys, int32_t *perm,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
+/* rows_out[i][:] = rows_in[perm[i]][:], row_bytes a multiple of 2; the feature permutation of
+ * SparseTensor.order (spira/tensors.py:55-65). */
+int spira_b200_permute_rows(const void *rows_in, const int32_t *perm, int64_t n, int64_t row_bytes, void *rows_out,
+                            void *stream);
+
+/* Scratch bytes for spira_b200_downsample with n input keys and n_levels levels. */
+int spira_b200_downsample_workspace(int64_t n, int key_bytes, int n_levels, size_t *bytes);
+
+/* For each level l: out_keys[l][0 .. counts[l]) = unique(sort(keys & mask(strides[l]))).
+ * Replaces cuda_downsample and cuda_streamed_output_generate
+ * (csrc/spira/torch/cuda_arg_sort_coordinates.cu:68-200).  host_strides is [n_levels][3]
+ * (powers of two), host_out_keys holds n_levels device buffers of n keys each, counts is a
+ * device int32[n_levels] written by the call (the caller copies it back to size its views). */
+int spira_b200_downsample(const void *keys, int64_t n, int key_bytes, int n_levels, const int32_t *host_strides,
+                          void *const *host_out_keys, int32_t *counts, void *workspace, size_t workspace_bytes,
+                          void *stream);
+
+/* ---- kernel-map search -------------------------------------------------------------------- */
+
+typedef struct spira_b200_kmap_desc {
+  const void *sources;     /* sorted unique keys [num_sources] */
+  const void *targets;     /* sorted unique keys [num_targets] */
+  int64_t num_sources;
+  int64_t num_targets;
+  int32_t kernel_size[3];  /* kx, ky, kz (odd: [-k/2, k/2], even: [-k/2+1, k/2]) */
+  int32_t source_stride[3];
+  int32_t layout;          /* SPIRA_B200_LAYOUT_OS / _WS */
+  int32_t reserved;
+  int32_t *map;            /* dense int32 map, T_al = ceil(T/128)*128 rows/columns, -1 = no neighbour */
+  int32_t *tile_counts;    /* optional [K][T_al/128] (row order as LAYOUT_WS): hits per 128 targets, or NULL */
+} spira_b200_kmap_desc;
+
+/* Builds up to SPIRA_B200_MAX_MAPS kernel maps in ONE launch.  Replaces cuda_binary_search and
+ * cuda_binary_search_streamed (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:211-892,
+ * 894-1645) and the search kernels (csrc/spira/cuda/kernels/query_sorted.cuh:8-163).
+ * Result: exact lookup of tgt[t] + offset (wrapping packed arithmetic) in sources. */
+int spira_b200_kmap_search(const spira_b200_kmap_desc *host_descs, int n_maps, int key_bytes, void *stream);
+
+/* Weight-stationary post-processing, phase 1 (sizes).  From tile_counts[K][n_tiles] of the first
+ * `rows` rows: nbsizes[rows], naddrs[rows+1], qnaddrs[rows+1] (sizes rounded up to 128),
+ * tile_base[rows][n_tiles] (exclusive position of each tile inside its row's list) and
+ * sizes[2] = {mapsize, qmapsize}.  Replaces the ReduceByKey + prefix-sum part of
+ * BinarySearch_Streamed_Ws[_Half] (csrc/spira/cuda/functions/query_sorted_index.cu:146-209,
+ * csrc/spira/cuda/kernels/quantifier_wstat.cuh:8-44). */
+int spira_b200_kmap_ws_sizes(const int32_t *tile_counts, int rows, int64_t n_tiles, int32_t *nbsizes,
+                             int32_t *naddrs, int32_t *qnaddrs, int32_t *tile_base, int32_t *sizes, void *stream);
+
+/* Phase 2 (pairs): compacts rows [0, rows) of a LAYOUT_WS map into in_idx / out_idx, ordered by
+ * (row, target).  Replaces the DeviceSelect::If compaction (query_sorted_index.cu:170-188). */
+int spira_b200_kmap_ws_pairs(const int32_t *map_ws, int rows, int64_t aligned_targets, const int32_t *naddrs,
+                             const int32_t *tile_base, int32_t *in_idx, int32_t *out_idx, void *stream);
+
+/* source_masks[K][S], target_masks[K][T] (rank of each pair inside its row, -1 elsewhere) from a
+ * LAYOUT_WS map; both outputs are fully written.  Replaces GenerateMasksFromKernelMap
+ * (csrc/spira/cuda/kernels/generate_masks_from_kernel_map.cuh:9-62). */
+int spira_b200_kmap_masks(const int32_t *map_ws, int rows_total, int64_t num_sources, int64_t num_targets,
+                          int64_t aligned_targets, const int32_t *tile_base, int32_t *source_masks,
+                          int32_t *target_masks, void *stream);
+
+/* out[S_al][K] (fully written) = inverse of map_os[T_al][K] per column; replaces
+ * cuda_convert_transposed_os (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:1809-1830). */
+int spira_b200_convert_transposed_os(const int32_t *map_os, int64_t aligned_targets, int K, int32_t *out,
+                                     int64_t aligned_sources, void *stream);
+
+/* in-place [rows][cols] -> [cols][rows] transpose of an int32 map into `out` (the
+ * `.T.contiguous()` of KernelMapCache.get_kernel_map, spira/nn/conv.py:80-83). */
+int spira_b200_transpose_map(const int32_t *in, int64_t rows, int64_t cols, int32_t *out, void *stream);
+
+/* ---- feature compute (fp16 in/out, fp32 accumulate) ---------------------------------------- */
+
+/* Optional per-channel affine + residual + ReLU applied to the fp32 accumulator before the single
+ * rounding to fp16:  y = relu?( (acc + bias) * scale + shift + residual ).  Any pointer may be NULL.
+ * (The reference applies bias, BatchNorm, the residual add and ReLU as separate passes:
+ * spira/nn/conv.py:415-416, spira/nn/normalizations.py:8-10, spira/nn/activations.py:8-18.) */
+typedef struct spira_b200_epilogue {
+  const void *bias;      /* fp16 [c_out] */
+  const float *scale;    /* fp32 [c_out] */
+  const float *shift;    /* fp32 [c_out] */
+  const void *residual;  /* fp16 [num_targets][c_out] */
+  int32_t relu;
+  int32_t reserved;
+} spira_b200_epilogue;
+
+#define SPIRA_B200_PACK_OS 0 /* reduction index r = k*c_in + c, 64-wide chunks over the whole r range */
+#define SPIRA_B200_PACK_WS 1 /* every offset padded to ceil(c_in/64) chunks of its own */
+
+/* 1 if (c_in, c_out, K) can run on the tcgen05 tensor-core kernels, else 0 (SIMT kernels are used). */
+int spira_b200_tensor_core_eligible(int K, int c_in, int c_out);
+
+/* Bytes of the pre-packed weight image for spira_b200_conv_*. */
+int spira_b200_packed_weight_bytes(int K, int c_in, int c_out, int pack_mode, size_t *bytes);
+
+/* weights[K][c_in][c_out] fp16 -> tensor-core operand image: per 64-wide reduction chunk one
+ * 128-byte-swizzled K-major tile of c_out rows, so that one bulk copy lands a ready MMA operand
+ * in shared memory.  Done once per layer (weights are constant at inference). */
+int spira_b200_pack_weights(const void *weights, int K, int c_in, int c_out, int pack_mode, void *packed,
+                            void *stream);
+
+/* Output-stationary implicit GEMM: out[t][:] = sum_c feats[map[t][c]][:] @ W[c], map is
+ * LAYOUT_OS [T_al][K].  Replaces cuda_sparse_convolution_forward_os
+ * (csrc/spira/torch/cuda_sparse_convolution_forward.cu:11-80, cuda/kernels/output_stat.cuh:20-644).
+ * `packed` (PACK_OS image) selects the tensor-core kernel; with packed == NULL the SIMT kernel
+ * reads `weights` directly.  `epilogue` may be NULL.  `status` is a device int32 the kernel sets
+ * non-zero if one of its bounded internal waits expired (it never spins forever). */
+int spira_b200_conv_os(const void *feats, const void *weights, const void *packed,
+                       const spira_b200_epilogue *epilogue, const int32_t *map_os, int64_t num_sources,
+                       int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status, void *stream);
+
+/* Weight-stationary gather-GEMM-scatter over compacted pair lists: for row k and pair p in
+ * [naddrs[k], naddrs[k+1]):  accum[out_idx[p]][:] += feats[in_idx[p]][:] @ W[k].  With
+ * `mirror` != 0 (submanifold, odd K, rows == (K+1)/2) every row k < rows-1 is also applied with
+ * in/out swapped and weight K-1-k (csrc/spira/cuda/kernels/weight_stat.cuh:786-798).  With
+ * `swap` != 0 the roles of in_idx and out_idx are exchanged (transposed layer on the map of its
+ * non-transposed twin, spira/nn/conv.py:341-348).  accum is fp32 [num_targets][c_out] scratch,
+ * zeroed by the call; out is fp16 [num_targets][c_out].  `qnaddrs` holds the 128-rounded prefix
+ * sums and `num_tiles128` = qnaddrs[rows] / 128 (the caller learned it when it sized the lists).
+ * Replaces cuda_sparse_convolution_forward_ws_merged
+ * (csrc/spira/torch/cuda_sparse_convolution_forward.cu:183-246). */
+int spira_b200_conv_ws(const void *feats, const void *weights, const void *packed,
+                       const spira_b200_epilogue *epilogue, const int32_t *in_idx, const int32_t *out_idx,
+                       const int32_t *naddrs, const int32_t *qnaddrs, int rows, int64_t num_tiles128, int mirror,
+                       int swap, int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out, float *accum,
+                       void *out, int32_t *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPIRA_B200_H_ */

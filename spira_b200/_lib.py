@@ -1,0 +1,96 @@
+"""ctypes binding of ``libspira_b200.so`` -- the only route from Python to the CUDA kernels.
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libspira_b200.so"
+
+c_void_p, c_int, c_int32, c_int64, c_size_t = C.c_void_p, C.c_int, C.c_int32, C.c_int64, C.c_size_t
+
+
+class KmapDesc(C.Structure):
+    """Mirror of ``spira_b200_kmap_desc`` (include/spira_b200.h)."""
+    _fields_ = [
+        ("sources", c_void_p), ("targets", c_void_p),
+        ("num_sources", c_int64), ("num_targets", c_int64),
+        ("kernel_size", c_int32 * 3), ("source_stride", c_int32 * 3),
+        ("layout", c_int32), ("reserved", c_int32),
+        ("map", c_void_p), ("tile_counts", c_void_p),
+    ]
+
+
+class Epilogue(C.Structure):
+    """Mirror of ``spira_b200_epilogue`` (include/spira_b200.h)."""
+    _fields_ = [("bias", c_void_p), ("scale", c_void_p), ("shift", c_void_p), ("residual", c_void_p),
+                ("relu", c_int32), ("reserved", c_int32)]
+
+
+LAYOUT_OS, LAYOUT_WS = 0, 1
+PACK_OS, PACK_WS = 0, 1
+MAX_MAPS, MAX_LEVELS = 16, 8
+
+# name -> argument types (every function returns int except the two noted below)
+SIGNATURES = {
+    "spira_b200_version": [],
+    "spira_b200_reset_error": [],
+    "spira_b200_pack": [c_void_p, c_int64, c_int, c_void_p, c_void_p],
+    "spira_b200_unpack": [c_void_p, c_int64, c_int, c_void_p, c_void_p],
+    "spira_b200_flatten_sort_workspace": [c_int64, c_int, C.POINTER(c_size_t)],
+    "spira_b200_flatten_sort": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p],
+    "spira_b200_permute_rows": [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p],
+    "spira_b200_downsample_workspace": [c_int64, c_int, c_int, C.POINTER(c_size_t)],
+    "spira_b200_downsample": [c_void_p, c_int64, c_int, c_int, C.POINTER(c_int32), C.POINTER(c_void_p), c_void_p,
+                              c_void_p, c_size_t, c_void_p],
+    "spira_b200_kmap_search": [C.POINTER(KmapDesc), c_int, c_int, c_void_p],
+    "spira_b200_kmap_ws_sizes": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "spira_b200_kmap_ws_pairs": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "spira_b200_kmap_masks": [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
+    "spira_b200_convert_transposed_os": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p],
+    "spira_b200_transpose_map": [c_void_p, c_int64, c_int64, c_void_p, c_void_p],
+    "spira_b200_tensor_core_eligible": [c_int, c_int, c_int],
+    "spira_b200_packed_weight_bytes": [c_int, c_int, c_int, c_int, C.POINTER(c_size_t)],
+    "spira_b200_pack_weights": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "spira_b200_conv_os": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_int64, c_int64, c_int, c_int,
+                           c_int, c_void_p, c_void_p, c_void_p],
+    "spira_b200_conv_ws": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
+                           c_void_p, c_void_p],
+}
+EXPORTS = sorted(list(SIGNATURES) + ["spira_b200_last_error"])
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the library once; raises if it has not been built (``python -m spira_b200.build``)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m spira_b200.build` "
+                               "(the CUDA library is the only implementation; there is no fallback)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, args in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        lib.spira_b200_last_error.argtypes = []
+        lib.spira_b200_last_error.restype = C.c_char_p
+        _lib = lib
+    return _lib
+
+
+def check(code: int) -> None:
+    """Turns a non-zero return code into ``RuntimeError('[spira_b200] ...')`` like the reference's
+    ``SpiraException`` -> ``RuntimeError`` (csrc/spira/common/exception.h:9-28)."""
+    if code != 0:
+        msg = load().spira_b200_last_error().decode(errors="replace")
+        raise RuntimeError(f"[spira_b200] {msg} (code {code})")
+
+
+def call(name: str, *args) -> None:
+    check(getattr(load(), name)(*args))

@@ -1,0 +1,680 @@
+// Sparse-convolution feature compute: fp16 in/out, fp32 accumulate.
+//
+// Two dataflows share one persistent, warp-specialised tcgen05 kernel (conv_tc_kernel):
+//
+//   output-stationary (OS): a tile is 128 consecutive targets.  The reduction runs over all
+//     (offset, channel) pairs in 64-wide chunks; chunks whose offsets have no neighbour in the tile
+//     are skipped.  The accumulator lives in tensor memory for the whole tile and is stored once,
+//     so there are no atomics and the result is deterministic.
+//   weight-stationary (WS): a tile is 128 compacted (in, out) pairs of ONE offset, so every MMA
+//     row is a real pair.  The 128 x c_out product is added into an fp32 scratch with vector
+//     reductions; a second small kernel applies the epilogue and rounds to fp16.
+//
+// Roles inside a CTA (288 threads, one CTA per SM):
+//   warps 0-3  producers: gather feature rows with 16-byte cp.async (zero-fill for missing rows)
+//              into a 128-byte-swizzled K-major A tile; one thread bulk-copies the matching
+//              pre-packed weight chunk (already an MMA-ready image) and posts its byte count;
+//   warp  8    one elected thread issues tcgen05.mma (M=128, N=c_out, K=16) into one of two
+//              TMEM accumulator buffers and commits stage / accumulator barriers;
+//   warps 4-7  epilogue: tcgen05.ld the finished accumulator (one row per thread), apply the
+//              fused epilogue, store fp16 rows (OS) or issue fp32 vector reductions (WS) while the
+//              next tile is already being multiplied.
+// All mbarrier waits are bounded; on expiry the kernel raises a status word and drains.
+//
+// Channel counts the tensor-core path cannot tile (c_in % 8 != 0, c_out % 16 != 0, c_out > 256)
+// run on simple SIMT kernels (conv_os_simt_kernel / conv_ws_simt_kernel) -- those layers
+// (3-5 input channels) are bandwidth-bound and tiny.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace sb {
+
+using namespace sb::ptx;
+
+constexpr int kRows = 128;              // MMA M / rows per tile
+constexpr int kChunk = 64;              // fp16 elements of the reduction per pipeline stage (128 bytes)
+constexpr int kABytes = kRows * 128;    // one A stage
+constexpr int kProducers = 128;
+constexpr int kConvThreads = 288;
+constexpr int kMaxStages = 6;
+constexpr int kSmemBudget = 220 * 1024;
+constexpr int kScatterRing = 16;        // WS: scatter-row lists kept for tiles in flight (>= stages + 2)
+
+struct Epilogue {
+  const __half *bias;
+  const float *scale;
+  const float *shift;
+  const __half *residual;
+  int relu;
+};
+
+struct ConvParams {
+  const __half *feats;
+  const unsigned char *packed;
+  __half *out;      // OS
+  float *accum;     // WS
+  Epilogue ep;
+  int32_t *status;
+  // OS
+  const int32_t *map;  // [T_al][K]
+  // WS
+  const int32_t *in_idx, *out_idx, *naddrs, *qnaddrs;
+  int rows, mirror, n_tiles_plain;
+  // common
+  int T, n_tiles, K, c_in, c_out, R, n_chunks;  // n_chunks: OS = ceil(R/64); WS = ceil(c_in/64) per offset
+  int stages, slab_bufs, b_bytes, acc_stride, tmem_cols;
+  int off_b, off_slab, off_flags, off_cm, off_meta, off_bar;
+};
+
+__device__ __forceinline__ float epilogue_apply(float v, int c, const Epilogue &ep) {
+  if (ep.bias) v += __half2float(ep.bias[c]);
+  if (ep.scale) v = v * ep.scale[c] + ep.shift[c];
+  return v;
+}
+
+template <bool kWS>
+__global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_constant__ ConvParams P) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char *smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  const uint32_t sbase = smem_u32(smem);
+
+  int32_t *slab = reinterpret_cast<int32_t *>(smem + P.off_slab);
+  int32_t *flags = reinterpret_cast<int32_t *>(smem + P.off_flags);
+  uint32_t *cmask = reinterpret_cast<uint32_t *>(smem + P.off_cm);
+  int32_t *meta = reinterpret_cast<int32_t *>(smem + P.off_meta);
+  const uint32_t bar0 = sbase + P.off_bar;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
+  auto bar_acc_full = [&](int b) { return bar0 + 8u * (2 * kMaxStages + b); };
+  auto bar_acc_empty = [&](int b) { return bar0 + 8u * (2 * kMaxStages + 2 + b); };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + P.off_bar + 8 * (2 * kMaxStages + 4));
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + P.off_bar + 8 * (2 * kMaxStages + 4) + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int stages = P.stages;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar_full(s), kProducers + 1);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), 128);
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(tmem_slot), P.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    // =========================== producers ===========================
+    const int piece = tid & 7, row0 = tid >> 3;
+    const int lag = stages - 1;
+    int stage = 0, phase = 0, arr_stage = 0, unarrived = 0, groups_since_prefetch = 0;
+    bool ok = true;
+    int tile_i = 0;
+    for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+      const int buf = (P.slab_bufs == 2) ? (tile_i & 1) : 0;
+      int32_t *my_slab;
+      int w_row = 0, n_chunks_tile;
+      if constexpr (kWS) {
+        // tile -> (row k, first pair, count)
+        int tt = tile;
+        const bool mirrored = tt >= P.n_tiles_plain;
+        if (mirrored) tt -= P.n_tiles_plain;
+        const int q0 = tt * kRows;
+        int k = 0;
+        while (k + 1 < P.rows && P.qnaddrs[k + 1] <= q0) ++k;
+        const int p0 = P.naddrs[k] + (q0 - P.qnaddrs[k]);
+        const int n = min(kRows, P.naddrs[k + 1] - p0);
+        w_row = mirrored ? (P.K - 1 - k) : k;
+        // rows to gather (first 128 ints) and rows to scatter to.  The producers run at most
+        // stages + 2 tiles ahead of the epilogue, so a ring of kScatterRing lists is never overwritten early.
+        my_slab = slab;
+        int32_t *scatter = slab + kRows + (tile_i & (kScatterRing - 1)) * kRows;
+        named_bar_sync(1, kProducers);  // previous tile's gathers have read the row list
+        const int32_t *g = mirrored ? P.out_idx : P.in_idx;
+        const int32_t *s = mirrored ? P.in_idx : P.out_idx;
+        my_slab[tid] = tid < n ? g[p0 + tid] : -1;
+        scatter[tid] = tid < n ? s[p0 + tid] : -1;
+        named_bar_sync(1, kProducers);
+        n_chunks_tile = P.n_chunks;
+      } else {
+        my_slab = slab + buf * kRows * P.K;
+        const int4 *src4 = reinterpret_cast<const int4 *>(P.map + static_cast<int64_t>(tile) * kRows * P.K);
+        if (P.slab_bufs == 1 || tile_i == 0) {
+          named_bar_sync(1, kProducers);
+          int4 *dst4 = reinterpret_cast<int4 *>(my_slab);
+          for (int i = tid; i < (kRows / 4) * P.K; i += kProducers) dst4[i] = src4[i];
+        } else {
+          cp_async_wait_dyn(groups_since_prefetch);  // the group that carried this slab has landed
+        }
+        named_bar_sync(1, kProducers);
+        // which offsets have at least one neighbour in this tile
+        for (int k = warp; k < P.K; k += 4) {
+          bool any = false;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) any |= my_slab[(lane + 32 * j) * P.K + k] >= 0;
+          unsigned m = __ballot_sync(0xffffffffu, any);
+          if (lane == 0) flags[k] = m != 0;
+        }
+        named_bar_sync(1, kProducers);
+        // which 64-wide reduction chunks touch a non-empty offset
+        const int n_words = (P.n_chunks + 31) >> 5;
+        for (int j = tid; j < n_words * 32; j += kProducers) {
+          bool ne = false;
+          if (j < P.n_chunks) {
+            int k_lo = (j * kChunk) / P.c_in;
+            int k_hi = min((j * kChunk + kChunk - 1) / P.c_in, P.K - 1);
+            for (int k = k_lo; k <= k_hi; ++k) ne |= flags[k] != 0;
+          }
+          unsigned m = __ballot_sync(0xffffffffu, ne);
+          if (lane == 0) cmask[j >> 5] = m;
+        }
+        named_bar_sync(1, kProducers);
+        n_chunks_tile = 0;
+        for (int w = 0; w < n_words; ++w) n_chunks_tile += __popc(cmask[w]);
+      }
+
+      const bool force_first = (n_chunks_tile == 0);  // a tile always sends at least one chunk
+      if (force_first) n_chunks_tile = 1;
+      int sent = 0;
+      const int n_words = kWS ? 1 : ((P.n_chunks + 31) >> 5);
+      for (int w = 0; ok && w < n_words; ++w) {
+        uint32_t bits;
+        if constexpr (kWS) bits = 0; else bits = cmask[w];
+        if (force_first && w == 0) bits = 1u;
+        int ws_j = 0;
+        while (ok) {
+          int j;
+          if constexpr (kWS) {
+            if (ws_j >= P.n_chunks) break;
+            j = ws_j++;
+          } else {
+            if (bits == 0) break;
+            j = (w << 5) + __ffs(bits) - 1;
+            bits &= bits - 1;
+          }
+          ++sent;
+          if (!mbar_wait(bar_empty(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+          // ---- A: 128 rows x 8 pieces of 16 bytes, this thread owns piece `piece` of 8 rows
+          const uint32_t a_stage = sbase + stage * kABytes;
+          int k, c;
+          bool piece_valid;
+          if constexpr (kWS) {
+            c = j * kChunk + piece * 8;
+            k = 0;
+            piece_valid = c < P.c_in;
+          } else {
+            const int r = j * kChunk + piece * 8;
+            k = r / P.c_in;
+            c = r - k * P.c_in;
+            piece_valid = r < P.R;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int m = row0 + 16 * i;
+            int idx = -1;
+            if (piece_valid) idx = kWS ? my_slab[m] : my_slab[m * P.K + k];
+            const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
+            cp_async_16(a_stage + m * 128 + ((piece ^ (m & 7)) << 4), src, idx >= 0 ? 16u : 0u);
+          }
+          if (tid == 0) {
+            // ---- B: one bulk copy of the pre-packed chunk; meta word for the MMA thread
+            const int chunk_id = kWS ? (w_row * P.n_chunks + j) : j;
+            const int valid = kWS ? min(kChunk, P.c_in - j * kChunk) : min(kChunk, P.R - j * kChunk);
+            const int nk = (valid + 15) >> 4;
+            meta[stage] = nk | ((sent == 1) << 8) | ((sent == n_chunks_tile) << 9);
+            mbar_arrive_expect_tx(bar_full(stage), P.b_bytes);
+            bulk_g2s(sbase + P.off_b + stage * P.b_bytes, P.packed + static_cast<int64_t>(chunk_id) * P.b_bytes,
+                     P.b_bytes, bar_full(stage));
+          }
+          if constexpr (!kWS) {
+            // the next tile's slab rides in the commit group of this tile's first chunk
+            if (sent == 1 && P.slab_bufs == 2) {
+              const int next = tile + gridDim.x;
+              groups_since_prefetch = 0;
+              if (next < P.n_tiles) {
+                const int4 *n4 = reinterpret_cast<const int4 *>(P.map + static_cast<int64_t>(next) * kRows * P.K);
+                const uint32_t dst = sbase + P.off_slab + (buf ^ 1) * kRows * P.K * 4;
+                for (int i = tid; i < (kRows / 4) * P.K; i += kProducers) cp_async_16(dst + i * 16, n4 + i, 16u);
+              }
+            } else {
+              ++groups_since_prefetch;
+            }
+          }
+          cp_async_commit();
+          ++unarrived;
+          if (unarrived > lag) {
+            cp_async_wait_dyn(lag);
+            fence_proxy_async();
+            mbar_arrive(bar_full(arr_stage));
+            arr_stage = (arr_stage + 1 == stages) ? 0 : arr_stage + 1;
+            --unarrived;
+          }
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    // drain: everything issued has landed, then post the outstanding arrivals
+    cp_async_wait<0>();
+    fence_proxy_async();
+    while (unarrived > 0) {
+      mbar_arrive(bar_full(arr_stage));
+      arr_stage = (arr_stage + 1 == stages) ? 0 : arr_stage + 1;
+      --unarrived;
+    }
+  } else if (warp == 8) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      const uint32_t idesc = idesc_f16_m128(P.c_out);
+      int stage = 0, phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      bool ok = true;
+      int tile_i = 0;
+      for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+        const int b = tile_i & 1;
+        if (!mbar_wait(bar_acc_empty(b), acc_phase[b] ^ 1, abort_flag)) break;
+        acc_phase[b] ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + b * P.acc_stride;
+        while (true) {
+          if (!mbar_wait(bar_full(stage), phase, abort_flag)) { ok = false; break; }
+          fence_proxy_async();
+          tc_fence_after();
+          const int m = meta[stage];
+          const int nk = m & 0xff;
+          const bool first = (m >> 8) & 1, last = (m >> 9) & 1;
+          const uint32_t a_addr = sbase + stage * kABytes;
+          const uint32_t b_addr = sbase + P.off_b + stage * P.b_bytes;
+          for (int ks = 0; ks < nk; ++ks)
+            mma_f16_ss(d_tmem, smem_desc_k_sw128(a_addr + ks * 32), smem_desc_k_sw128(b_addr + ks * 32), idesc,
+                       (first && ks == 0) ? 0u : 1u);
+          mma_commit(bar_empty(stage));
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+          if (last) {
+            mma_commit(bar_acc_full(b));
+            break;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // =========================== epilogue ===========================
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    uint32_t acc_phase[2] = {0, 0};
+    int tile_i = 0;
+    for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+      const int b = tile_i & 1;
+      if (!mbar_wait(bar_acc_full(b), acc_phase[b], abort_flag)) break;
+      acc_phase[b] ^= 1;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + b * P.acc_stride + (static_cast<uint32_t>(q * 32) << 16);
+      int64_t out_row;
+      if constexpr (kWS) {
+        out_row = slab[kRows + (tile_i & (kScatterRing - 1)) * kRows + row];
+      } else {
+        const int64_t t = static_cast<int64_t>(tile) * kRows + row;
+        out_row = t < P.T ? t : -1;
+      }
+      for (int c0 = 0; c0 < P.c_out; c0 += 32) {
+        uint32_t r[32];
+        const bool full = c0 + 32 <= P.c_out;
+        if (full) {
+          tmem_ld_32x32(taddr + c0, r);
+        } else {
+          uint32_t h[16];
+          tmem_ld_32x16(taddr + c0, h);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { r[i] = h[i]; r[16 + i] = 0; }
+        }
+        tmem_ld_wait();
+        const int width = full ? 32 : 16;
+        if (out_row >= 0) {
+          if constexpr (kWS) {
+            float *dst = P.accum + out_row * P.c_out + c0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              if (i < width)
+                red_add_v4_f32(dst + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                               __uint_as_float(r[i + 3]));
+          } else {
+            __half *dst = P.out + out_row * P.c_out + c0;
+            const __half *res = P.ep.residual ? P.ep.residual + out_row * P.c_out + c0 : nullptr;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (i < width) {
+                uint4 pack;
+                uint32_t *pw = reinterpret_cast<uint32_t *>(&pack);
+                uint4 rv = make_uint4(0, 0, 0, 0);
+                if (res) rv = *reinterpret_cast<const uint4 *>(res + i);
+                const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float v0 = epilogue_apply(__uint_as_float(r[i + 2 * e]), c0 + i + 2 * e, P.ep);
+                  float v1 = epilogue_apply(__uint_as_float(r[i + 2 * e + 1]), c0 + i + 2 * e + 1, P.ep);
+                  if (res) { v0 += __low2float(rh[e]); v1 += __high2float(rh[e]); }
+                  if (P.ep.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
+                  __half2 hv = __floats2half2_rn(v0, v1);
+                  pw[e] = *reinterpret_cast<uint32_t *>(&hv);
+                }
+                *reinterpret_cast<uint4 *>(dst + i) = pack;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_acc_empty(b));
+    }
+  }
+
+  // =========================== teardown ===========================
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // a bounded wait expired: report, give copies in flight time to land, then release TMEM
+    if (tid == 0 && P.status) atomicExch(P.status, 1);
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) { }
+    __syncthreads();
+  }
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, P.tmem_cols);
+  }
+}
+
+// ---- weight image ---------------------------------------------------------------------------
+
+// one thread per 16-byte piece of the image: chunk j, row n (output channel), piece p
+__global__ void __launch_bounds__(256) pack_weights_kernel(const __half *__restrict__ w, int K, int c_in, int c_out,
+                                                            int ws_mode, int chunks_per_offset, int64_t n_pieces,
+                                                            unsigned char *__restrict__ packed) {
+  int64_t g = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  if (g >= n_pieces) return;
+  const int p = static_cast<int>(g & 7);
+  const int n = static_cast<int>((g >> 3) % c_out);
+  const int64_t j = (g >> 3) / c_out;
+  __align__(16) __half v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    int k, c;
+    bool valid;
+    if (ws_mode) {
+      k = static_cast<int>(j / chunks_per_offset);
+      c = static_cast<int>(j % chunks_per_offset) * kChunk + p * 8 + e;
+      valid = c < c_in;
+    } else {
+      int64_t r = j * kChunk + p * 8 + e;
+      k = static_cast<int>(r / c_in);
+      c = static_cast<int>(r % c_in);
+      valid = k < K;
+    }
+    v[e] = valid ? w[(static_cast<int64_t>(k) * c_in + c) * c_out + n] : __float2half(0.f);
+  }
+  unsigned char *dst = packed + j * (static_cast<int64_t>(c_out) * 128) + n * 128 + ((p ^ (n & 7)) << 4);
+  *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(v);
+}
+
+// ---- SIMT kernels (any channel count) -----------------------------------------------------------
+
+// one warp per target row; lanes over output channels
+__global__ void __launch_bounds__(128) conv_os_simt_kernel(const __half *__restrict__ feats,
+                                                            const __half *__restrict__ w, Epilogue ep,
+                                                            const int32_t *__restrict__ map, int64_t T, int K, int c_in,
+                                                            int c_out, __half *__restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = blockIdx.x * int64_t(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  for (int co = lane; co < c_out; co += 32) {
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int m = map[t * K + k];
+      if (m < 0) continue;
+      const __half *f = feats + static_cast<int64_t>(m) * c_in;
+      const __half *wk = w + static_cast<int64_t>(k) * c_in * c_out + co;
+      for (int ci = 0; ci < c_in; ++ci) acc = fmaf(__half2float(f[ci]), __half2float(wk[static_cast<int64_t>(ci) * c_out]), acc);
+    }
+    float v = epilogue_apply(acc, co, ep);
+    if (ep.residual) v += __half2float(ep.residual[t * c_out + co]);
+    if (ep.relu) v = fmaxf(v, 0.f);
+    out[t * c_out + co] = __float2half_rn(v);
+  }
+}
+
+// one warp per pair; grid.y = list rows (doubled when mirrored)
+__global__ void __launch_bounds__(128) conv_ws_simt_kernel(const __half *__restrict__ feats,
+                                                            const __half *__restrict__ w,
+                                                            const int32_t *__restrict__ in_idx,
+                                                            const int32_t *__restrict__ out_idx,
+                                                            const int32_t *__restrict__ naddrs, int rows, int K,
+                                                            int c_in, int c_out, float *__restrict__ accum) {
+  const int lane = threadIdx.x & 31;
+  int k = blockIdx.y;
+  const bool mirrored = k >= rows;
+  if (mirrored) k -= rows;
+  const int begin = naddrs[k], end = naddrs[k + 1];
+  const int wk_row = mirrored ? (K - 1 - k) : k;
+  for (int p = begin + blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < end; p += gridDim.x * (blockDim.x >> 5)) {
+    const int i = mirrored ? out_idx[p] : in_idx[p];
+    const int o = mirrored ? in_idx[p] : out_idx[p];
+    const __half *f = feats + static_cast<int64_t>(i) * c_in;
+    for (int co = lane; co < c_out; co += 32) {
+      const __half *wk = w + static_cast<int64_t>(wk_row) * c_in * c_out + co;
+      float acc = 0.f;
+      for (int ci = 0; ci < c_in; ++ci) acc = fmaf(__half2float(f[ci]), __half2float(wk[static_cast<int64_t>(ci) * c_out]), acc);
+      atomicAdd(accum + static_cast<int64_t>(o) * c_out + co, acc);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) finalize_kernel(const float *__restrict__ accum, Epilogue ep, int64_t n,
+                                                        int c_out, __half *__restrict__ out) {
+  int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  const int c = static_cast<int>(i % c_out);
+  float v = epilogue_apply(accum[i], c, ep);
+  if (ep.residual) v += __half2float(ep.residual[i]);
+  if (ep.relu) v = fmaxf(v, 0.f);
+  out[i] = __float2half_rn(v);
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+
+static bool tc_eligible(int K, int c_in, int c_out) {
+  return K >= 1 && c_in >= 8 && c_in % 8 == 0 && c_out >= 16 && c_out % 16 == 0 && c_out <= 256;
+}
+
+static Epilogue make_epilogue(const spira_b200_epilogue *e) {
+  Epilogue ep{nullptr, nullptr, nullptr, nullptr, 0};
+  if (e) {
+    ep.bias = static_cast<const __half *>(e->bias);
+    ep.scale = e->scale;
+    ep.shift = e->shift;
+    ep.residual = static_cast<const __half *>(e->residual);
+    ep.relu = e->relu;
+  }
+  return ep;
+}
+
+static int round16(int x) { return (x + 15) / 16 * 16; }
+
+// Fills the shared-memory plan of ConvParams; returns the dynamic shared memory size or 0 if it does not fit.
+static size_t plan_smem(ConvParams &P, bool ws) {
+  P.b_bytes = P.c_out * 128;
+  int acc = 32;
+  while (acc < P.c_out) acc <<= 1;
+  P.acc_stride = acc;
+  P.tmem_cols = 2 * acc;
+  int slab_one = ws ? (1 + kScatterRing) * kRows * 4 : kRows * P.K * 4;
+  P.slab_bufs = (!ws && 2 * slab_one <= 32 * 1024) ? 2 : 1;
+  int slab_bytes = ws ? slab_one : P.slab_bufs * slab_one;
+  int n_words = ws ? 1 : (P.n_chunks + 31) / 32;
+  int fixed = slab_bytes + round16(P.K * 4) + round16(n_words * 4) + round16(kMaxStages * 4) + 8 * (2 * kMaxStages + 4) + 16;
+  int per_stage = kABytes + P.b_bytes;
+  int stages = (kSmemBudget - fixed) / per_stage;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return 0;
+  P.stages = stages;
+  P.off_b = stages * kABytes;
+  P.off_slab = P.off_b + stages * P.b_bytes;
+  P.off_flags = P.off_slab + slab_bytes;
+  P.off_cm = P.off_flags + round16(P.K * 4);
+  P.off_meta = P.off_cm + round16(n_words * 4);
+  P.off_bar = P.off_meta + round16(kMaxStages * 4);
+  return static_cast<size_t>(P.off_bar) + 8 * (2 * kMaxStages + 4) + 16 + 1024;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int spira_b200_tensor_core_eligible(int K, int c_in, int c_out) { return tc_eligible(K, c_in, c_out) ? 1 : 0; }
+
+extern "C" int spira_b200_packed_weight_bytes(int K, int c_in, int c_out, int pack_mode, size_t *bytes) {
+  SB_CHECK_ARG(bytes != nullptr, "packed_weight_bytes: null output");
+  SB_CHECK_ARG(tc_eligible(K, c_in, c_out), "packed_weight_bytes: (K=%d, c_in=%d, c_out=%d) is not tensor-core eligible", K,
+               c_in, c_out);
+  int64_t chunks = pack_mode == SPIRA_B200_PACK_WS ? static_cast<int64_t>(K) * div_up(c_in, kChunk)
+                                                   : div_up(static_cast<int64_t>(K) * c_in, kChunk);
+  *bytes = static_cast<size_t>(chunks) * c_out * 128;
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_pack_weights(const void *weights, int K, int c_in, int c_out, int pack_mode, void *packed,
+                                       void *stream) {
+  SB_CHECK_ARG(weights && packed, "pack_weights: null pointer");
+  SB_CHECK_ARG(tc_eligible(K, c_in, c_out), "pack_weights: (K=%d, c_in=%d, c_out=%d) is not tensor-core eligible", K, c_in,
+               c_out);
+  SB_CHECK_ARG(reinterpret_cast<uintptr_t>(packed) % 16 == 0, "pack_weights: packed image must be 16-byte aligned");
+  const bool ws = pack_mode == SPIRA_B200_PACK_WS;
+  int cpo = static_cast<int>(div_up(c_in, kChunk));
+  int64_t chunks = ws ? static_cast<int64_t>(K) * cpo : div_up(static_cast<int64_t>(K) * c_in, kChunk);
+  int64_t pieces = chunks * c_out * 8;
+  pack_weights_kernel<<<static_cast<unsigned>(div_up(pieces, 256)), 256, 0, as_stream(stream)>>>(
+      static_cast<const __half *>(weights), K, c_in, c_out, ws ? 1 : 0, cpo, pieces, static_cast<unsigned char *>(packed));
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const void *packed,
+                                  const spira_b200_epilogue *epilogue, const int32_t *map_os, int64_t num_sources,
+                                  int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status,
+                                  void *stream) {
+  SB_CHECK_ARG(num_sources >= 0 && num_targets >= 0 && num_targets < (int64_t(1) << 31) - 128 &&
+                   num_sources < (int64_t(1) << 31),
+               "conv_os: sizes out of range");
+  SB_CHECK_ARG(K >= 1 && c_in >= 1 && c_out >= 1, "conv_os: K=%d c_in=%d c_out=%d", K, c_in, c_out);
+  if (num_targets == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(map_os && out && (feats || num_sources == 0), "conv_os: null pointer");
+  Epilogue ep = make_epilogue(epilogue);
+  SB_CHECK_ARG((ep.scale == nullptr) == (ep.shift == nullptr), "conv_os: scale and shift must be given together");
+  if (packed == nullptr) {
+    SB_CHECK_ARG(weights != nullptr, "conv_os: neither weights nor a packed image given");
+    conv_os_simt_kernel<<<static_cast<unsigned>(div_up(num_targets, 4)), 128, 0, as_stream(stream)>>>(
+        static_cast<const __half *>(feats), static_cast<const __half *>(weights), ep, map_os, num_targets, K, c_in, c_out,
+        static_cast<__half *>(out));
+    SB_CHECK_LAUNCH();
+    return SPIRA_B200_OK;
+  }
+  SB_CHECK_ARG(tc_eligible(K, c_in, c_out), "conv_os: (K=%d, c_in=%d, c_out=%d) is not tensor-core eligible", K, c_in, c_out);
+  SB_CHECK_ARG(reinterpret_cast<uintptr_t>(feats) % 16 == 0 && reinterpret_cast<uintptr_t>(packed) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(map_os) % 16 == 0 &&
+                   (ep.residual == nullptr || reinterpret_cast<uintptr_t>(ep.residual) % 16 == 0),
+               "conv_os: feats, packed, out, map and residual must be 16-byte aligned");
+  ConvParams P{};
+  P.feats = static_cast<const __half *>(feats);
+  P.packed = static_cast<const unsigned char *>(packed);
+  P.out = static_cast<__half *>(out);
+  P.ep = ep;
+  P.status = status;
+  P.map = map_os;
+  P.T = static_cast<int>(num_targets);
+  P.n_tiles = static_cast<int>(align128(num_targets) / kRows);
+  P.K = K; P.c_in = c_in; P.c_out = c_out;
+  P.R = K * c_in;
+  P.n_chunks = static_cast<int>(div_up(P.R, kChunk));
+  size_t smem = plan_smem(P, false);
+  if (smem == 0) return fail(SPIRA_B200_ERR_UNSUPPORTED, "conv_os: K=%d c_out=%d does not fit the shared-memory plan", K, c_out);
+  SB_CHECK_CUDA(cudaFuncSetAttribute(conv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  int grid = P.n_tiles < sm_count() ? P.n_tiles : sm_count();
+  conv_tc_kernel<false><<<grid, kConvThreads, smem, as_stream(stream)>>>(P);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const void *packed,
+                                  const spira_b200_epilogue *epilogue, const int32_t *in_idx, const int32_t *out_idx,
+                                  const int32_t *naddrs, const int32_t *qnaddrs, int rows, int64_t num_tiles128,
+                                  int mirror, int swap, int64_t num_sources, int64_t num_targets, int K, int c_in,
+                                  int c_out, float *accum, void *out, int32_t *status, void *stream) {
+  SB_CHECK_ARG(num_sources >= 0 && num_targets >= 0 && num_targets < (int64_t(1) << 31) && num_sources < (int64_t(1) << 31),
+               "conv_ws: sizes out of range");
+  SB_CHECK_ARG(K >= 1 && c_in >= 1 && c_out >= 1 && rows >= 1 && rows <= K, "conv_ws: K=%d c_in=%d c_out=%d rows=%d", K, c_in,
+               c_out, rows);
+  SB_CHECK_ARG(!mirror || (rows == (K + 1) / 2 && K % 2 == 1 && !swap), "conv_ws: mirror needs odd K, rows == (K+1)/2 and no swap");
+  SB_CHECK_ARG(num_tiles128 >= 0 && num_tiles128 < (int64_t(1) << 30), "conv_ws: num_tiles128 out of range");
+  if (num_targets == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(accum && out && naddrs, "conv_ws: null pointer");
+  Epilogue ep = make_epilogue(epilogue);
+  SB_CHECK_ARG((ep.scale == nullptr) == (ep.shift == nullptr), "conv_ws: scale and shift must be given together");
+  cudaStream_t st = as_stream(stream);
+  const int64_t n_out = num_targets * c_out;
+  SB_CHECK_CUDA(cudaMemsetAsync(accum, 0, sizeof(float) * n_out, st));
+  const int32_t *gi = swap ? out_idx : in_idx;
+  const int32_t *go = swap ? in_idx : out_idx;
+  if (num_tiles128 > 0) {
+    SB_CHECK_ARG(gi && go && feats, "conv_ws: null pointer");
+    if (packed == nullptr) {
+      SB_CHECK_ARG(weights != nullptr, "conv_ws: neither weights nor a packed image given");
+      dim3 grid(static_cast<unsigned>(sm_count() * 2), static_cast<unsigned>(mirror ? 2 * rows - 1 : rows));
+      conv_ws_simt_kernel<<<grid, 128, 0, st>>>(static_cast<const __half *>(feats), static_cast<const __half *>(weights), gi,
+                                                go, naddrs, rows, K, c_in, c_out, accum);
+      SB_CHECK_LAUNCH();
+    } else {
+      SB_CHECK_ARG(tc_eligible(K, c_in, c_out), "conv_ws: (K=%d, c_in=%d, c_out=%d) is not tensor-core eligible", K, c_in, c_out);
+      SB_CHECK_ARG(qnaddrs != nullptr, "conv_ws: null qnaddrs");
+      SB_CHECK_ARG(reinterpret_cast<uintptr_t>(feats) % 16 == 0 && reinterpret_cast<uintptr_t>(packed) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(accum) % 16 == 0,
+                   "conv_ws: feats, packed and accum must be 16-byte aligned");
+      ConvParams P{};
+      P.feats = static_cast<const __half *>(feats);
+      P.packed = static_cast<const unsigned char *>(packed);
+      P.accum = accum;
+      P.status = status;
+      P.in_idx = gi; P.out_idx = go; P.naddrs = naddrs; P.qnaddrs = qnaddrs;
+      P.rows = rows; P.mirror = mirror;
+      P.n_tiles_plain = static_cast<int>(num_tiles128);
+      // the centre row (last of the half list) is its own mirror image: its tiles are not repeated
+      int64_t centre_tiles = mirror ? div_up(num_targets, kRows) : 0;
+      P.n_tiles = static_cast<int>(mirror ? 2 * num_tiles128 - centre_tiles : num_tiles128);
+      P.T = static_cast<int>(num_targets);
+      P.K = K; P.c_in = c_in; P.c_out = c_out;
+      P.R = c_in;
+      P.n_chunks = static_cast<int>(div_up(c_in, kChunk));
+      size_t smem = plan_smem(P, true);
+      if (smem == 0) return fail(SPIRA_B200_ERR_UNSUPPORTED, "conv_ws: c_out=%d does not fit the shared-memory plan", c_out);
+      SB_CHECK_CUDA(cudaFuncSetAttribute(conv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      int grid = P.n_tiles < sm_count() ? P.n_tiles : sm_count();
+      if (grid > 0) {
+        conv_tc_kernel<true><<<grid, kConvThreads, smem, st>>>(P);
+        SB_CHECK_LAUNCH();
+      }
+    }
+  }
+  finalize_kernel<<<static_cast<unsigned>(div_up(n_out, 256)), 256, 0, st>>>(accum, ep, n_out, c_out, static_cast<__half *>(out));
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}

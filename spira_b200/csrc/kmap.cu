@@ -1,0 +1,455 @@
+// Kernel-map construction: one launch builds the (input, output, weight-offset) maps of every
+// sparse-convolution layer of a network.
+//
+// Work decomposition: one CTA of 128 threads per tile of 128 consecutive sorted targets of one map.
+// For an xy offset o the queries tgt[t] + off[o] of a tile are monotone in t, so every match lies
+// in one contiguous window of the sorted source keys.  The CTA finds the window bounds with
+// warp-cooperative 32-ary searches (4 dependent loads instead of 17 for 120k keys), stages the
+// windows of as many offsets as fit into shared memory with coalesced loads, and every thread then
+// resolves its queries by a binary search + z walk entirely in shared memory.  Results are
+//   - written as a dense int32 map, either [K][T_al] with coalesced rows, or [T_al][K] through a
+//     shared-memory slab that is stored with 16-byte vectors, and
+//   - counted per (offset, 128-target tile) with warp ballots, which is what the compaction into
+//     weight-stationary pair lists, the mask format and the dataflow selector consume.
+// A query equals an exact lookup of the wrapped packed key; windows that would be too large (or
+// offsets whose queries wrap inside the tile) fall back to per-thread searches in global memory.
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int kTile = 128;          // targets per CTA == threads per CTA
+constexpr int kMaxXY = 64;          // kx*ky
+constexpr int kMaxK = 512;          // kx*ky*kz
+constexpr int kWindowCap = 3072;    // keys staged per offset group
+constexpr int kStageMaxBytes = 96 * 1024;
+
+template <typename KeyT>
+struct MapDesc {
+  const KeyT *src;
+  const KeyT *tgt;
+  int32_t *map;
+  int32_t *tile_counts;
+  int32_t S, T, T_al, n_tiles;
+  int32_t kx, ky, kz, nxy, K;
+  int32_t x0, y0, z0;  // lowest offset per axis, in units of the source stride
+  int32_t sx, sy, sz;
+  int32_t layout, staged;
+  int32_t tile_begin;
+};
+
+template <typename KeyT>
+struct SearchParams {
+  MapDesc<KeyT> m[SPIRA_B200_MAX_MAPS];
+  int32_t n_maps;
+};
+
+template <typename KeyT>
+__device__ __forceinline__ KeyT xy_offset(const MapDesc<KeyT> &D, int o) {
+  int ix = o / D.ky + D.x0;
+  int iy = o % D.ky + D.y0;
+  // wrapping arithmetic on purpose: identical to adding signed multiples of the field units
+  return static_cast<KeyT>(static_cast<int64_t>(ix) * D.sx) * (KeyT(1) << KeyShift<KeyT>::X) +
+         static_cast<KeyT>(static_cast<int64_t>(iy) * D.sy) * (KeyT(1) << KeyShift<KeyT>::Y) +
+         static_cast<KeyT>(static_cast<int64_t>(D.z0) * D.sz);
+}
+
+// lower_bound over global memory by a whole warp: 32 probes per round.
+template <typename KeyT>
+__device__ __forceinline__ int warp_lower_bound(const KeyT *__restrict__ a, int n, KeyT q, int lane) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    int len = hi - lo;
+    int step = (len + 31) >> 5;
+    int pos = lo + lane * step;
+    bool less = (pos < hi) && (a[pos] < q);
+    int c = __popc(__ballot_sync(0xffffffffu, less));
+    if (c == 0) {
+      hi = lo;
+    } else {
+      int nhi = lo + c * step;
+      lo = lo + (c - 1) * step + 1;
+      hi = nhi < hi ? nhi : hi;
+    }
+  }
+  return lo;
+}
+
+template <typename KeyT>
+__device__ __forceinline__ int lower_bound(const KeyT *a, int n, KeyT q) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (a[mid] < q) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+template <typename KeyT>
+__global__ void __launch_bounds__(kTile) kmap_search_kernel(const __grid_constant__ SearchParams<KeyT> P,
+                                                             int stage_bytes) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int s_lo[kMaxXY], s_hi[kMaxXY], s_irregular[kMaxXY];
+  __shared__ int s_cnt[kMaxK];
+
+  int32_t *stage = reinterpret_cast<int32_t *>(smem_raw);
+  KeyT *win = reinterpret_cast<KeyT *>(smem_raw + stage_bytes);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int mi = 0;
+  while (mi + 1 < P.n_maps && static_cast<int>(blockIdx.x) >= P.m[mi + 1].tile_begin) ++mi;
+  const MapDesc<KeyT> &D = P.m[mi];
+  const int lt = blockIdx.x - D.tile_begin;
+  const int t0 = lt * kTile;
+  const int t = t0 + tid;
+  const int nvalid = min(kTile, D.T - t0);
+  const bool valid = tid < nvalid;
+  const KeyT *__restrict__ src = D.src;
+  const KeyT my = valid ? D.tgt[t] : KeyT(0);
+  const KeyT first = D.tgt[t0], last = D.tgt[t0 + nvalid - 1];
+  const KeyT sz = static_cast<KeyT>(D.sz);
+  const int K = D.K, nxy = D.nxy, kz = D.kz;
+  const bool count = D.tile_counts != nullptr;
+
+  for (int k = tid; k < K; k += kTile) s_cnt[k] = 0;
+
+  // ---- window bounds: 2*nxy warp-cooperative searches --------------------------------------
+  for (int b = warp; b < 2 * nxy; b += kTile / 32) {
+    int o = b >> 1;
+    KeyT off = xy_offset(D, o);
+    KeyT qf = first + off, ql = last + off;
+    KeyT qmax = ql + static_cast<KeyT>(kz - 1) * sz;
+    bool irregular = !(qf <= ql && ql <= qmax) || D.S == 0;
+    int r;
+    if (irregular) {
+      r = (b & 1) ? D.S : 0;
+    } else if (b & 1) {
+      r = (qmax == ~KeyT(0)) ? D.S : warp_lower_bound(src, D.S, static_cast<KeyT>(qmax + 1), lane);
+    } else {
+      r = warp_lower_bound(src, D.S, qf, lane);
+    }
+    if (lane == 0) {
+      if (b & 1) s_hi[o] = r; else { s_lo[o] = r; s_irregular[o] = irregular; }
+    }
+  }
+  __syncthreads();
+
+  // ---- offsets in groups whose windows fit into shared memory ------------------------------
+  int o_begin = 0;
+  while (o_begin < nxy) {
+    int used = 0, o_end = o_begin;
+    while (o_end < nxy) {
+      int len = s_hi[o_end] - s_lo[o_end];
+      int need = len <= kWindowCap ? len : 0;  // oversized windows are searched in global memory
+      if (used + need > kWindowCap) break;
+      used += need;
+      ++o_end;
+    }
+    // stage
+    int base = 0;
+    for (int o = o_begin; o < o_end; ++o) {
+      int lo = s_lo[o], len = s_hi[o] - lo;
+      if (len <= kWindowCap) {
+        for (int i = tid; i < len; i += kTile) win[base + i] = src[lo + i];
+        base += len;
+      }
+    }
+    __syncthreads();
+    // search
+    base = 0;
+    for (int o = o_begin; o < o_end; ++o) {
+      const int lo = s_lo[o], len = s_hi[o] - lo;
+      const bool in_smem = len <= kWindowCap;
+      const bool irregular = s_irregular[o] != 0;
+      const KeyT *W = in_smem ? (win + base) : (src + lo);
+      if (in_smem) base += len;
+      KeyT q = my + xy_offset(D, o);
+      int i = 0;
+      if (valid && !irregular && in_smem) i = lower_bound(W, len, q);
+#pragma unroll 1
+      for (int iz = 0; iz < kz; ++iz) {
+        int r = -1;
+        if (valid) {
+          if (irregular || !in_smem) {
+            i = lower_bound(W, len, q);
+          } else {
+            while (i < len && W[i] < q) ++i;
+          }
+          if (i < len && W[i] == q) r = lo + i;
+        }
+        const int k_ws = kz * o + iz;
+        if (count) {
+          unsigned m = __ballot_sync(0xffffffffu, r >= 0);
+          if (lane == 0 && m) atomicAdd(&s_cnt[k_ws], __popc(m));
+        }
+        if (D.layout == SPIRA_B200_LAYOUT_WS) {
+          D.map[static_cast<int64_t>(k_ws) * D.T_al + t] = r;
+        } else if (D.staged) {
+          stage[tid * K + iz * nxy + o] = r;
+        } else {
+          D.map[static_cast<int64_t>(t) * K + iz * nxy + o] = r;
+        }
+        q += sz;
+      }
+    }
+    __syncthreads();
+    o_begin = o_end;
+  }
+
+  if (D.layout == SPIRA_B200_LAYOUT_OS && D.staged) {
+    const int4 *s4 = reinterpret_cast<const int4 *>(stage);
+    int4 *d4 = reinterpret_cast<int4 *>(D.map + static_cast<int64_t>(t0) * K);
+    for (int i = tid; i < (kTile / 4) * K; i += kTile) d4[i] = s4[i];
+  }
+  if (count)
+    for (int k = tid; k < K; k += kTile) D.tile_counts[static_cast<int64_t>(k) * D.n_tiles + lt] = s_cnt[k];
+}
+
+// ---- weight-stationary post-processing ------------------------------------------------------
+
+// One CTA per map row: exclusive scan of the row's per-tile counts.
+__global__ void __launch_bounds__(256) ws_row_scan_kernel(const int32_t *__restrict__ tile_counts, int64_t n_tiles,
+                                                           int32_t *__restrict__ tile_base,
+                                                           int32_t *__restrict__ nbsizes) {
+  __shared__ int s_warp[8];
+  __shared__ int s_carry;
+  const int k = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) s_carry = 0;
+  __syncthreads();
+  for (int64_t b = 0; b < n_tiles; b += 256) {
+    int64_t i = b + tid;
+    int v = i < n_tiles ? tile_counts[k * n_tiles + i] : 0;
+    int x = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    if (lane == 31) s_warp[warp] = x;
+    __syncthreads();
+    int wp = 0;
+    for (int w = 0; w < warp; ++w) wp += s_warp[w];
+    int carry = s_carry;
+    if (i < n_tiles) tile_base[k * n_tiles + i] = carry + wp + x - v;
+    __syncthreads();
+    if (tid == 255) s_carry = carry + wp + x;
+    __syncthreads();
+  }
+  if (tid == 0) nbsizes[k] = s_carry;
+}
+
+__global__ void ws_addr_kernel(const int32_t *__restrict__ nbsizes, int rows, int32_t *__restrict__ naddrs,
+                               int32_t *__restrict__ qnaddrs, int32_t *__restrict__ sizes) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int acc = 0, qacc = 0;
+  for (int k = 0; k < rows; ++k) {
+    naddrs[k] = acc;
+    qnaddrs[k] = qacc;
+    int v = nbsizes[k];
+    acc += v;
+    qacc += (v + 127) / 128 * 128;
+  }
+  naddrs[rows] = acc;
+  qnaddrs[rows] = qacc;
+  sizes[0] = acc;
+  sizes[1] = qacc;
+}
+
+// grid (n_tiles, rows): compaction of one 128-target tile of one row, order preserved.
+__global__ void __launch_bounds__(kTile) ws_pairs_kernel(const int32_t *__restrict__ map_ws, int64_t T_al,
+                                                          int64_t n_tiles, const int32_t *__restrict__ naddrs,
+                                                          const int32_t *__restrict__ tile_base,
+                                                          int32_t *__restrict__ in_idx, int32_t *__restrict__ out_idx) {
+  __shared__ int s_warp[kTile / 32];
+  const int tile = blockIdx.x, k = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t t = static_cast<int64_t>(tile) * kTile + tid;
+  const int v = map_ws[k * T_al + t];
+  const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
+  if (lane == 0) s_warp[warp] = __popc(m);
+  __syncthreads();
+  if (v < 0) return;
+  int rank = __popc(m & ((1u << lane) - 1));
+  for (int w = 0; w < warp; ++w) rank += s_warp[w];
+  const int64_t pos = static_cast<int64_t>(naddrs[k]) + tile_base[k * n_tiles + tile] + rank;
+  in_idx[pos] = v;
+  out_idx[pos] = static_cast<int32_t>(t);
+}
+
+__global__ void __launch_bounds__(kTile) masks_kernel(const int32_t *__restrict__ map_ws, int64_t S, int64_t T,
+                                                       int64_t T_al, int64_t n_tiles,
+                                                       const int32_t *__restrict__ tile_base,
+                                                       int32_t *__restrict__ source_masks,
+                                                       int32_t *__restrict__ target_masks) {
+  __shared__ int s_warp[kTile / 32];
+  const int tile = blockIdx.x, k = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t t = static_cast<int64_t>(tile) * kTile + tid;
+  const int v = map_ws[k * T_al + t];
+  const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
+  if (lane == 0) s_warp[warp] = __popc(m);
+  __syncthreads();
+  if (v < 0) return;
+  int rank = __popc(m & ((1u << lane) - 1)) + tile_base[k * n_tiles + tile];
+  for (int w = 0; w < warp; ++w) rank += s_warp[w];
+  source_masks[k * S + v] = rank;
+  target_masks[k * T + t] = rank;
+}
+
+__global__ void __launch_bounds__(256) invert_os_kernel(const int32_t *__restrict__ map_os, int64_t n, int K,
+                                                         int32_t *__restrict__ out) {
+  int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  int v = map_os[i];
+  if (v < 0) return;
+  out[static_cast<int64_t>(v) * K + (i % K)] = static_cast<int32_t>(i / K);
+}
+
+__global__ void __launch_bounds__(256) transpose_kernel(const int32_t *__restrict__ in, int64_t rows, int64_t cols,
+                                                         int32_t *__restrict__ out) {
+  __shared__ int32_t tile[32][33];
+  int64_t c0 = blockIdx.x * 32ll, r0 = blockIdx.y * 32ll;
+  int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int j = ty; j < 32; j += 8) {
+    int64_t r = r0 + j, c = c0 + tx;
+    if (r < rows && c < cols) tile[j][tx] = in[r * cols + c];
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    int64_t c = c0 + j, r = r0 + tx;
+    if (r < rows && c < cols) out[c * rows + r] = tile[tx][j];
+  }
+}
+
+template <typename KeyT>
+int search_impl(const spira_b200_kmap_desc *descs, int n_maps, cudaStream_t stream) {
+  SearchParams<KeyT> P;
+  P.n_maps = 0;
+  int tiles = 0, stage_bytes = 0;
+  for (int i = 0; i < n_maps; ++i) {
+    const spira_b200_kmap_desc &d = descs[i];
+    SB_CHECK_ARG(d.num_sources >= 0 && d.num_sources < (int64_t(1) << 31) && d.num_targets >= 0 &&
+                     d.num_targets < (int64_t(1) << 31) - 128,
+                 "kmap_search: map %d has sizes out of range", i);
+    const int kx = d.kernel_size[0], ky = d.kernel_size[1], kz = d.kernel_size[2];
+    SB_CHECK_ARG(kx >= 1 && ky >= 1 && kz >= 1, "kmap_search: map %d has a non-positive kernel size", i);
+    SB_CHECK_ARG(kx * ky <= kMaxXY && kx * ky * kz <= kMaxK, "kmap_search: map %d kernel %dx%dx%d exceeds %d xy / %d total offsets",
+                 i, kx, ky, kz, kMaxXY, kMaxK);
+    SB_CHECK_ARG(d.source_stride[0] >= 1 && d.source_stride[1] >= 1 && d.source_stride[2] >= 1,
+                 "kmap_search: map %d has a non-positive stride", i);
+    SB_CHECK_ARG(d.layout == SPIRA_B200_LAYOUT_OS || d.layout == SPIRA_B200_LAYOUT_WS, "kmap_search: map %d layout %d", i,
+                 d.layout);
+    if (d.num_targets == 0) continue;
+    SB_CHECK_ARG(d.targets && d.map && (d.sources || d.num_sources == 0), "kmap_search: map %d has a null pointer", i);
+    MapDesc<KeyT> &m = P.m[P.n_maps++];
+    m.src = static_cast<const KeyT *>(d.sources);
+    m.tgt = static_cast<const KeyT *>(d.targets);
+    m.map = d.map;
+    m.tile_counts = d.tile_counts;
+    m.S = static_cast<int32_t>(d.num_sources);
+    m.T = static_cast<int32_t>(d.num_targets);
+    m.T_al = static_cast<int32_t>(align128(d.num_targets));
+    m.n_tiles = m.T_al / kTile;
+    m.kx = kx; m.ky = ky; m.kz = kz; m.nxy = kx * ky; m.K = kx * ky * kz;
+    m.x0 = (kx % 2 == 1) ? -(kx / 2) : -(kx / 2) + 1;
+    m.y0 = (ky % 2 == 1) ? -(ky / 2) : -(ky / 2) + 1;
+    m.z0 = (kz % 2 == 1) ? -(kz / 2) : -(kz / 2) + 1;
+    m.sx = d.source_stride[0]; m.sy = d.source_stride[1]; m.sz = d.source_stride[2];
+    m.layout = d.layout;
+    int sb = m.K * kTile * 4;
+    m.staged = (d.layout == SPIRA_B200_LAYOUT_OS && sb <= kStageMaxBytes) ? 1 : 0;
+    if (m.staged && sb > stage_bytes) stage_bytes = sb;
+    m.tile_begin = tiles;
+    tiles += m.n_tiles;
+  }
+  if (tiles == 0) return SPIRA_B200_OK;
+  size_t smem = static_cast<size_t>(stage_bytes) + kWindowCap * sizeof(KeyT);
+  SB_CHECK_CUDA(cudaFuncSetAttribute(kmap_search_kernel<KeyT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)));
+  kmap_search_kernel<KeyT><<<tiles, kTile, smem, stream>>>(P, stage_bytes);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int spira_b200_kmap_search(const spira_b200_kmap_desc *host_descs, int n_maps, int key_bytes,
+                                      void *stream) {
+  SB_CHECK_ARG(n_maps >= 0 && n_maps <= SPIRA_B200_MAX_MAPS, "kmap_search: n_maps=%d not in [0,%d]", n_maps,
+               SPIRA_B200_MAX_MAPS);
+  if (n_maps == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(host_descs != nullptr, "kmap_search: null descriptor array");
+  if (key_bytes == 4) return search_impl<uint32_t>(host_descs, n_maps, as_stream(stream));
+  if (key_bytes == 8) return search_impl<uint64_t>(host_descs, n_maps, as_stream(stream));
+  return fail(SPIRA_B200_ERR_ARGUMENT, "key_bytes must be 4 or 8, got %d", key_bytes);
+}
+
+extern "C" int spira_b200_kmap_ws_sizes(const int32_t *tile_counts, int rows, int64_t n_tiles, int32_t *nbsizes,
+                                        int32_t *naddrs, int32_t *qnaddrs, int32_t *tile_base, int32_t *sizes,
+                                        void *stream) {
+  SB_CHECK_ARG(rows >= 1 && rows <= kMaxK && n_tiles >= 0, "kmap_ws_sizes: rows=%d n_tiles=%lld", rows, (long long)n_tiles);
+  SB_CHECK_ARG(nbsizes && naddrs && qnaddrs && sizes && (n_tiles == 0 || (tile_counts && tile_base)),
+               "kmap_ws_sizes: null pointer");
+  ws_row_scan_kernel<<<rows, 256, 0, as_stream(stream)>>>(tile_counts, n_tiles, tile_base, nbsizes);
+  SB_CHECK_LAUNCH();
+  ws_addr_kernel<<<1, 32, 0, as_stream(stream)>>>(nbsizes, rows, naddrs, qnaddrs, sizes);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_kmap_ws_pairs(const int32_t *map_ws, int rows, int64_t aligned_targets,
+                                        const int32_t *naddrs, const int32_t *tile_base, int32_t *in_idx,
+                                        int32_t *out_idx, void *stream) {
+  SB_CHECK_ARG(rows >= 1 && rows <= kMaxK && aligned_targets >= 0 && aligned_targets % 128 == 0,
+               "kmap_ws_pairs: rows=%d aligned_targets=%lld", rows, (long long)aligned_targets);
+  if (aligned_targets == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(map_ws && naddrs && tile_base && in_idx && out_idx, "kmap_ws_pairs: null pointer");
+  int64_t n_tiles = aligned_targets / kTile;
+  dim3 grid(static_cast<unsigned>(n_tiles), static_cast<unsigned>(rows));
+  ws_pairs_kernel<<<grid, kTile, 0, as_stream(stream)>>>(map_ws, aligned_targets, n_tiles, naddrs, tile_base, in_idx,
+                                                         out_idx);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_kmap_masks(const int32_t *map_ws, int rows_total, int64_t num_sources, int64_t num_targets,
+                                     int64_t aligned_targets, const int32_t *tile_base, int32_t *source_masks,
+                                     int32_t *target_masks, void *stream) {
+  SB_CHECK_ARG(rows_total >= 1 && rows_total <= kMaxK && aligned_targets % 128 == 0 && num_targets <= aligned_targets,
+               "kmap_masks: bad sizes");
+  SB_CHECK_ARG(source_masks && target_masks, "kmap_masks: null pointer");
+  SB_CHECK_CUDA(cudaMemsetAsync(source_masks, 0xFF, sizeof(int32_t) * rows_total * num_sources, as_stream(stream)));
+  SB_CHECK_CUDA(cudaMemsetAsync(target_masks, 0xFF, sizeof(int32_t) * rows_total * num_targets, as_stream(stream)));
+  if (aligned_targets == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(map_ws && tile_base, "kmap_masks: null pointer");
+  int64_t n_tiles = aligned_targets / kTile;
+  dim3 grid(static_cast<unsigned>(n_tiles), static_cast<unsigned>(rows_total));
+  masks_kernel<<<grid, kTile, 0, as_stream(stream)>>>(map_ws, num_sources, num_targets, aligned_targets, n_tiles,
+                                                      tile_base, source_masks, target_masks);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_convert_transposed_os(const int32_t *map_os, int64_t aligned_targets, int K, int32_t *out,
+                                                int64_t aligned_sources, void *stream) {
+  SB_CHECK_ARG(K >= 1 && aligned_targets >= 0 && aligned_sources >= 0, "convert_transposed_os: bad sizes");
+  if (aligned_sources > 0) {
+    SB_CHECK_ARG(out != nullptr, "convert_transposed_os: null output");
+    SB_CHECK_CUDA(cudaMemsetAsync(out, 0xFF, sizeof(int32_t) * aligned_sources * K, as_stream(stream)));
+  }
+  int64_t n = aligned_targets * K;
+  if (n == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(map_os != nullptr, "convert_transposed_os: null input");
+  invert_os_kernel<<<static_cast<unsigned>(div_up(n, 256)), 256, 0, as_stream(stream)>>>(map_os, n, K, out);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_transpose_map(const int32_t *in, int64_t rows, int64_t cols, int32_t *out, void *stream) {
+  SB_CHECK_ARG(rows >= 0 && cols >= 0, "transpose_map: bad sizes");
+  if (rows == 0 || cols == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(in && out, "transpose_map: null pointer");
+  dim3 grid(static_cast<unsigned>(div_up(cols, 32)), static_cast<unsigned>(div_up(rows, 32)));
+  transpose_kernel<<<grid, 256, 0, as_stream(stream)>>>(in, rows, cols, out);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}

@@ -1,0 +1,233 @@
+"""``KernelMapCache`` and ``SparseConv`` -- same public surface as the reference module
+(spira/nn/conv.py:17-151 and :153-419): constructor arguments, ``kernel`` parameter of shape
+``[K, c_in, c_out]``, ``_tunable_config`` keys, cache keys ``(source_stride, target_stride, kernel_size)`` and the
+rule that a transposed layer reuses the map of its non-transposed twin.
+
+Underneath there are two dataflows.  ``map_dataflow == 0`` (or ``force_os``) runs the output-stationary
+implicit GEMM; every other value runs the weight-stationary gather-GEMM-scatter over compacted pair lists
+(odd values through the reference's ``ws_merged`` slots, even values through its mask slots).
+"""
+__all__ = ['SparseConv', 'KernelMapCache', 'Conv3d']
+
+import contextlib
+import operator
+from typing import Any, Dict, List, Optional, Tuple, Union
+
+import numpy as np
+import torch
+from torch.nn import Module
+
+from spira_b200.nn import functional as F
+from spira_b200.nn.functional import _C
+from spira_b200.tensors import SparseTensor
+from spira_b200.utils.helpers import as_tuple
+from spira_b200.utils.typing import ScalarOrTuple
+
+
+class KernelMapCache(object):
+    """Coordinates per stride and kernel maps per ``(source_stride, target_stride, kernel_size)``."""
+
+    def __init__(self):
+        self._kernel_maps_cache = dict()
+        self._coordinates_cache = dict()
+        self._derived = dict()   # maps derived from cached ones (transposed / inverted), built once
+
+    def reset(self):
+        self._coordinates_cache.clear()
+        self._kernel_maps_cache.clear()
+        self._derived.clear()
+
+    def get_target_coordinates(self, source_coordinates: torch.Tensor, source_stride: ScalarOrTuple[int],
+                               target_stride: ScalarOrTuple[int], transposed: bool = False):
+        source_stride = as_tuple(source_stride, size=3, name="source_stride")
+        if source_stride not in self._coordinates_cache:
+            self._coordinates_cache[source_stride] = source_coordinates
+        if target_stride in self._coordinates_cache:
+            return self._coordinates_cache[target_stride]
+        if transposed:
+            raise RuntimeError("Layer must transpose=True must have its corresponding "
+                               "non-transposed layer before its execution")
+        target_coordinates = F.downsample(source_coordinates, target_stride)
+        self._coordinates_cache[target_stride] = target_coordinates
+        return target_coordinates
+
+    def get_kernel_map(self, source_coordinates: torch.Tensor, source_stride: ScalarOrTuple[int],
+                       target_coordinates: torch.Tensor, target_stride: ScalarOrTuple[int],
+                       kernel_size: ScalarOrTuple[int], map_dataflow: int, force_os: bool = False,
+                       transposed: bool = False):
+        source_stride = as_tuple(source_stride, size=3, name="source_stride")
+        target_stride = as_tuple(target_stride, size=3, name="target_stride")
+        kernel_size = as_tuple(kernel_size, size=3, name="kernel_size")
+        key = (target_stride, source_stride, kernel_size) if transposed else (source_stride, target_stride, kernel_size)
+
+        if key not in self._kernel_maps_cache:
+            if transposed:
+                raise RuntimeError("Layer must transpose=True must have its corresponding "
+                                   "non-transposed layer before its execution")
+            kernel_map = F.build_kmap(source_coordinates, target_coordinates, kernel_size, source_stride, map_dataflow)
+            self._kernel_maps_cache[key] = [False, *kernel_map]
+        entry = self._kernel_maps_cache[key]  # [flipped_flag, *tuple9]
+
+        if force_os and not entry[0]:
+            # a [K, T_al] map used output-stationary: transpose it once (reference: conv.py:80-83)
+            sb = getattr(entry[3], "_sb", None)
+            if sb is None or sb.get("layout") == _C.LAYOUT_WS:
+                flipped = _C.transpose_map(entry[3])
+                if sb is not None:
+                    flipped._sb = dict(sb, layout=_C.LAYOUT_OS)
+                entry[3] = flipped
+            entry[0] = True
+
+        if (map_dataflow == 0 or force_os) and transposed:
+            # output-stationary map of the transposed layer = inverse of the cached one.  The reference
+            # rebuilds it on every forward (conv.py:85-89); it depends only on the cached map, so it is kept.
+            dkey = (key, "inverted")
+            if dkey not in self._derived:
+                self._derived[dkey] = F.convert_transposed_os(entry[3], entry[1])
+            new_entry = list(entry[1:])
+            new_entry[2] = self._derived[dkey]
+            return new_entry
+        return entry[1:]
+
+    def add_all_kernel_maps(self, source_coordinates: torch.Tensor, kernel_sizes: List[ScalarOrTuple[int]],
+                            source_strides: List[ScalarOrTuple[int]], target_strides: List[ScalarOrTuple[int]],
+                            init_stride: Union[int, Tuple[int, ...]], dataflow: List[int]):
+        """Network-wide precompute: all down-sampled coordinate sets, then all kernel maps in one batched
+        search (reference: conv.py:116-151)."""
+        output = F.streamed_output_generate(source_coordinates, target_strides) if len(target_strides) else []
+        voxels: List[torch.Tensor] = [source_coordinates] + output
+
+        s_stride = as_tuple(init_stride, size=3)
+        self._coordinates_cache[s_stride] = voxels[0]
+        for i, t_stride in enumerate(target_strides):
+            self._coordinates_cache[as_tuple(t_stride, size=3)] = voxels[i + 1]
+
+        kmaps = F.build_kmap_streamed(voxels, kernel_sizes, source_strides[:-1], dataflow)
+
+        for i in range(len(kernel_sizes)):
+            t_stride = as_tuple(source_strides[i + 1], size=3)
+            key = (s_stride, t_stride, as_tuple(kernel_sizes[i], size=3))
+            self._kernel_maps_cache[key] = [False, *kmaps[i]]
+            s_stride = t_stride
+        return self
+
+
+class SparseConv(Module):
+
+    __AVAILABLE_THRESHOLD__ = [-1, *list(np.linspace(0, 2, num=50)), None]
+    __NUM_TUNING_ROUNDS__ = 5
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: ScalarOrTuple[int],
+                 stride: ScalarOrTuple[int] = 1, bias: bool = False, transposed: bool = False, dilation: int = 1):
+        super().__init__()
+        if dilation != 1 and tuple(as_tuple(dilation, size=3)) != (1, 1, 1):
+            raise ValueError("dilation other than 1 is not supported (the reference layer has no dilation argument)")
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.kernel_size = as_tuple(kernel_size, size=3, name="kernel_size")
+        self.stride = as_tuple(stride, size=3, name="stride")
+        self.transposed = transposed
+
+        kernel_volume = int(np.prod(self.kernel_size).item())
+        self.kernel = torch.nn.Parameter(torch.empty(kernel_volume, in_channels, out_channels))
+        if bias:
+            self.bias = torch.nn.Parameter(torch.empty(out_channels))
+        else:
+            self.register_parameter('bias', None)
+        self.reset_parameters()
+
+        self._kernel_map_cache: Optional[KernelMapCache] = None
+        self._tunable_config = {
+            'threshold': -1,
+            'gather_tile_size': min(in_channels, 16),
+            'scatter_tile_size': min(out_channels, 16),
+            'map_dataflow': 2,
+            'force_os': False,
+        }
+        self._tuning_data = None
+
+    @property
+    def tunable_config(self) -> Dict[str, Any]:
+        return self._tunable_config
+
+    def reset_parameters(self):
+        std = (self.out_channels if self.transposed else self.in_channels)
+        std = 1. / np.sqrt(std * len(self.kernel))
+        self.kernel.data.uniform_(-std, std)
+        if self.bias is not None:
+            self.bias.data.uniform_(-std, std)
+
+    def set_kernel_map_cache(self, cache: KernelMapCache):
+        self._kernel_map_cache = cache
+
+    @property
+    def is_trivial(self):
+        return all(x == 1 for x in self.stride) and all(x == 1 for x in self.kernel_size)
+
+    @contextlib.contextmanager
+    def tune_gs(self, free_buffers: bool = True):
+        """Kept for interface compatibility (reference: conv.py:217-307).  The gather / GEMM / scatter tile
+        sizes and the padding threshold it searched belong to the reference's three-kernel pipeline; the fused
+        weight-stationary kernel has none of them, so the context only records the calls."""
+        try:
+            self._tuning_data = list()
+            yield
+        finally:
+            self._tuning_data = None
+
+    def forward(self, inputs: SparseTensor):
+        source_features = inputs._features
+        if self.is_trivial:
+            kernel = self.kernel.view(self.in_channels, self.out_channels)
+            target_features = torch.mm(source_features, kernel)
+            target_coordinates = inputs._coordinates
+            target_stride = inputs._stride
+        else:
+            if self._kernel_map_cache is None:
+                raise ValueError("Kernel map cache must be specified")
+            op = operator.floordiv if self.transposed else operator.mul
+            target_stride = tuple(op(a, b) for a, b in zip(inputs._stride, self.stride))
+            cache = self._kernel_map_cache
+            target_coordinates = cache.get_target_coordinates(inputs._coordinates, inputs._stride, target_stride, self.transposed)
+
+            map_dataflow = self._tunable_config['map_dataflow']
+            force_os = self._tunable_config['force_os']
+            m = cache.get_kernel_map(inputs._coordinates, inputs._stride, target_coordinates, target_stride,
+                                     self.kernel_size, map_dataflow, force_os, self.transposed)
+            # m = (num_sources, num_targets, map, slot3, slot4, slot5, slot6, mapsize, qmapsize) of the
+            # NON-transposed twin; a transposed layer exchanges the roles of sources and targets
+            n_src, n_tgt = (m[1], m[0]) if self.transposed else (m[0], m[1])
+
+            if map_dataflow == 0 or force_os:
+                target_features = F.sparse_convolution_forward_os(n_src, n_tgt, m[2], source_features, self.kernel)
+            elif map_dataflow % 2 == 1:
+                if map_dataflow == 1:
+                    target_features = F.sparse_convolution_forward_ws_merged(
+                        n_src, n_tgt, source_features, self.kernel, m[5], m[6], m[3], m[7], m[8], self.transposed)
+                else:
+                    target_features = F.sparse_convolution_forward_hs_merged(
+                        n_src, n_tgt, source_features, self.kernel, m[5], m[6], m[3],
+                        None if map_dataflow == 3 else m[2], m[7], m[8], self.transposed)
+            else:
+                masks = (m[4], m[3]) if self.transposed else (m[3], m[4])
+                if self._tuning_data is not None:
+                    self._tuning_data.append((masks[0], masks[1], m[5]))
+                if map_dataflow == 2:
+                    target_features = F.sparse_convolution_forward_ws(
+                        n_src, n_tgt, source_features, self.kernel, masks[0], masks[1], m[5],
+                        self._tunable_config['gather_tile_size'], self._tunable_config['scatter_tile_size'],
+                        None, self._tunable_config['threshold'])
+                else:
+                    target_features = F.sparse_convolution_forward_hs(
+                        n_src, n_tgt, source_features, self.kernel, masks[0], masks[1], m[5],
+                        None if map_dataflow == 4 else m[2],
+                        self._tunable_config['gather_tile_size'], self._tunable_config['scatter_tile_size'],
+                        None, self._tunable_config['threshold'])
+
+        if self.bias is not None:
+            target_features += self.bias
+        return SparseTensor(features=target_features, coordinates=target_coordinates, stride=target_stride)
+
+
+# TorchSparse's name for the same layer (the reference's comparison scripts use it, scripts/correctness.py:79-80)
+Conv3d = SparseConv

@@ -1,0 +1,498 @@
+"""Drop-in for the reference's pybind module ``spira.nn.functional._C``.
+
+Same 18 function names, argument order and return structures as the reference registers
+(``csrc/spira/torch/cuda_arg_sort_coordinates.cu:202-208``,
+``csrc/spira/torch/cuda_sparse_convolution_mapping.cu:1832-1838``,
+``csrc/spira/torch/cuda_sparse_convolution_forward.cu:500-507``,
+``csrc/spira/torch/cuda_memory_buffer.cu:15-16``), implemented by calls into the C-ABI library
+``libspira_b200.so``.  torch is used for device memory and the current stream only.
+
+Kernel maps are returned as the reference's 9-tuple
+``(num_sources, num_targets, map, opt, opt, opt, opt, mapsize, qmapsize)``; the tensors in it
+additionally carry the engine's own structures in a ``_sb`` attribute so that the forward calls do
+not have to rebuild them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from spira_b200 import _lib
+from spira_b200._lib import KmapDesc, Epilogue, LAYOUT_OS, LAYOUT_WS, PACK_OS, PACK_WS, MAX_MAPS, MAX_LEVELS
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise NotImplementedError("spira_b200 runs on CUDA tensors only")
+
+
+def _key_bytes(keys: torch.Tensor) -> int:
+    if keys.dtype == torch.int32:
+        return 4
+    if keys.dtype == torch.int64:
+        return 8
+    raise RuntimeError(f"[spira_b200] packed keys must be int32 or int64, got {keys.dtype}")
+
+
+def _aligned(n: int) -> int:
+    return (n + 127) // 128 * 128
+
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 the tensor-core kernels raise when one of their bounded waits expires."""
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status[idx]
+
+
+def check_status(device=None) -> None:
+    """Synchronises and raises if any kernel launched so far reported an expired wait."""
+    for idx, t in list(_status.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        if int(t.item()) != 0:
+            t.zero_()
+            raise RuntimeError("[spira_b200] a tensor-core kernel gave up on an internal wait (status word set)")
+
+
+# ------------------------------------------------------------------------------------------------
+# coordinates
+# ------------------------------------------------------------------------------------------------
+def cuda_flatten_sort(coordinates: torch.Tensor, is_double: bool = False):
+    """``[N,3] int32`` -> ``(sorted packed keys [N] int32|int64, permutation [N] int32)``.
+    Reference: ``CUDAFlattenSort`` (csrc/spira/torch/cuda_arg_sort_coordinates.cu:11-39)."""
+    _require_cuda(coordinates)
+    if coordinates.dim() != 2 or coordinates.shape[1] != 3 or coordinates.dtype != torch.int32:
+        raise RuntimeError("[spira_b200] Tensor coordinates is expected to be int32 of shape [N, 3]")
+    coordinates = coordinates.contiguous()
+    n = coordinates.shape[0]
+    kb = 8 if is_double else 4
+    keys = torch.empty(n, dtype=torch.int64 if is_double else torch.int32, device=coordinates.device)
+    perm = torch.empty(n, dtype=torch.int32, device=coordinates.device)
+    need = C.c_size_t()
+    _lib.call("spira_b200_flatten_sort_workspace", n, kb, C.byref(need))
+    ws = torch.empty(need.value, dtype=torch.uint8, device=coordinates.device)
+    _lib.call("spira_b200_flatten_sort", _ptr(coordinates), n, kb, _ptr(keys), _ptr(perm), _ptr(ws), need.value,
+              _stream(coordinates.device))
+    return keys, perm
+
+
+def cuda_unflatten(coordinates: torch.Tensor) -> torch.Tensor:
+    """Packed keys ``[N]`` -> ``[N,3] int32`` (csrc/spira/torch/cuda_arg_sort_coordinates.cu:41-66)."""
+    _require_cuda(coordinates)
+    if coordinates.dim() != 1:
+        raise RuntimeError("[spira_b200] Tensor coordinates is expected to have 1 dimension(s)")
+    coordinates = coordinates.contiguous()
+    n = coordinates.shape[0]
+    out = torch.empty((n, 3), dtype=torch.int32, device=coordinates.device)
+    _lib.call("spira_b200_unpack", _ptr(coordinates), n, _key_bytes(coordinates), _ptr(out), _stream(coordinates.device))
+    return out
+
+
+def permute_rows(rows: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
+    """``rows[perm]`` for a 2-D tensor and an int32 permutation (the feature shuffle of ``SparseTensor.order``)."""
+    _require_cuda(rows, perm)
+    rows = rows.contiguous()
+    row_bytes = rows.shape[1] * rows.element_size() if rows.dim() == 2 else 0
+    if rows.dim() != 2 or perm.dtype != torch.int32 or row_bytes % 2 != 0 or row_bytes == 0:
+        return rows[perm.long()]
+    out = torch.empty_like(rows)
+    _lib.call("spira_b200_permute_rows", _ptr(rows), _ptr(perm.contiguous()), rows.shape[0], row_bytes, _ptr(out),
+              _stream(rows.device))
+    return out
+
+
+def cuda_streamed_output_generate(coordinates: torch.Tensor, target_strides: Sequence[Tuple[int, int, int]]) -> List[torch.Tensor]:
+    """Down-sampled key sets of all levels from the level-0 keys; one host read of the level sizes.
+    Reference: ``CUDAStreamedOutputGenerate`` (csrc/spira/torch/cuda_arg_sort_coordinates.cu:107-200)."""
+    _require_cuda(coordinates)
+    if coordinates.dim() != 1:
+        raise RuntimeError("[spira_b200] Tensor coordinates is expected to have 1 dimension(s)")
+    coordinates = coordinates.contiguous()
+    strides = [tuple(int(v) for v in s) for s in target_strides]
+    outputs: List[torch.Tensor] = []
+    n, kb, dev = coordinates.shape[0], _key_bytes(coordinates), coordinates.device
+    for first in range(0, len(strides), MAX_LEVELS):
+        group = strides[first:first + MAX_LEVELS]
+        L = len(group)
+        bufs = torch.empty((L, n), dtype=coordinates.dtype, device=dev)
+        counts = torch.empty(L, dtype=torch.int32, device=dev)
+        need = C.c_size_t()
+        _lib.call("spira_b200_downsample_workspace", n, kb, L, C.byref(need))
+        ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
+        host_strides = (C.c_int32 * (3 * L))(*[v for s in group for v in s])
+        host_out = (C.c_void_p * L)(*[bufs[l].data_ptr() for l in range(L)])
+        _lib.call("spira_b200_downsample", _ptr(coordinates), n, kb, L, host_strides, host_out, _ptr(counts), _ptr(ws),
+                  need.value, _stream(dev))
+        host_counts = counts.cpu().tolist()
+        outputs += [bufs[l, :host_counts[l]] for l in range(L)]
+    return outputs
+
+
+def cuda_downsample(coordinates: torch.Tensor, stride_x: int, stride_y: int, stride_z: int) -> torch.Tensor:
+    """``unique(sort(keys & mask))`` (csrc/spira/torch/cuda_arg_sort_coordinates.cu:68-105)."""
+    return cuda_streamed_output_generate(coordinates, [(stride_x, stride_y, stride_z)])[0]
+
+
+# ------------------------------------------------------------------------------------------------
+# kernel maps
+# ------------------------------------------------------------------------------------------------
+class WsLists:
+    """Compacted pair lists of a weight-stationary map (engine-native form of the reference's
+    ``nbmaps / nbsizes / naddrs / qnaddrs`` slots)."""
+    __slots__ = ("in_idx", "out_idx", "nbsizes", "naddrs", "qnaddrs", "rows", "mirror", "mapsize", "qmapsize", "nbmaps")
+
+
+def _dataflow_layout(dataflow: int) -> int:
+    return LAYOUT_OS if dataflow == 0 else LAYOUT_WS
+
+
+def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows):
+    """Shared implementation of the serial and the network-wide builders.
+
+    ``voxel_pairs[i] = (sources, targets)``.  One search launch per group of <= 16 maps, one
+    size scan per weight-stationary map, ONE host read of all list sizes, then the compactions.
+    """
+    n = len(voxel_pairs)
+    dev = voxel_pairs[0][0].device
+    kb = _key_bytes(voxel_pairs[0][0])
+    stream = _stream(dev)
+    info = []
+    for i in range(n):
+        src, tgt = voxel_pairs[i]
+        _require_cuda(src, tgt)
+        if _key_bytes(src) != kb or _key_bytes(tgt) != kb:
+            raise RuntimeError("[spira_b200] all coordinate tensors of one call must share a key width")
+        ks = tuple(int(v) for v in kernel_sizes[i])
+        st = tuple(int(v) for v in source_strides[i])
+        df = int(dataflows[i])
+        if df < 0 or df > 8:
+            raise RuntimeError(f"[spira_b200] unknown map dataflow {df}")
+        S, T = src.shape[0], tgt.shape[0]
+        K = ks[0] * ks[1] * ks[2]
+        Tal = _aligned(T)
+        layout = _dataflow_layout(df)
+        shape = (Tal, K) if layout == LAYOUT_OS else (K, Tal)
+        dense = torch.empty(shape, dtype=torch.int32, device=dev)
+        counts = torch.empty((K, Tal // 128), dtype=torch.int32, device=dev)
+        info.append(dict(src=src, tgt=tgt, S=S, T=T, K=K, Tal=Tal, ks=ks, st=st, df=df, layout=layout, dense=dense,
+                         counts=counts))
+    for first in range(0, n, MAX_MAPS):
+        group = info[first:first + MAX_MAPS]
+        descs = (KmapDesc * len(group))()
+        for d, m in zip(descs, group):
+            d.sources, d.targets = m["src"].data_ptr(), m["tgt"].data_ptr()
+            d.num_sources, d.num_targets = m["S"], m["T"]
+            d.kernel_size[:] = m["ks"]
+            d.source_stride[:] = m["st"]
+            d.layout = m["layout"]
+            d.map, d.tile_counts = m["dense"].data_ptr(), m["counts"].data_ptr()
+        _lib.call("spira_b200_kmap_search", descs, len(group), kb, stream)
+
+    # weight-stationary post-processing: sizes for every such map, one host read, then the pairs
+    ws_maps = [m for m in info if m["layout"] == LAYOUT_WS]
+    if ws_maps:
+        sizes = torch.empty((len(ws_maps), 2), dtype=torch.int32, device=dev)
+        for j, m in enumerate(ws_maps):
+            K, nt = m["K"], m["Tal"] // 128
+            # submanifold map with an odd kernel volume: only the first (K+1)/2 rows are listed, the rest is
+            # applied by symmetry (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:269)
+            half = (m["S"] == m["T"]) and (K % 2 == 1)
+            rows = (K + 1) // 2 if half else K
+            m["rows"], m["half"] = rows, half
+            m["nbsizes"] = torch.empty(K, dtype=torch.int32, device=dev)
+            m["naddrs"] = torch.empty(K + 1, dtype=torch.int32, device=dev)
+            m["qnaddrs"] = torch.empty(K + 1, dtype=torch.int32, device=dev)
+            m["tile_base"] = torch.empty((K, max(nt, 1)), dtype=torch.int32, device=dev)
+            # tile_base / nbsizes are produced for all K rows (the mask format needs them); the
+            # prefix sums below cover the `rows` rows the pair lists hold
+            if nt > 0:
+                if rows == K or m["df"] % 2 == 0:
+                    _lib.call("spira_b200_kmap_ws_sizes", _ptr(m["counts"]), K, nt, _ptr(m["nbsizes"]), _ptr(m["naddrs"]),
+                              _ptr(m["qnaddrs"]), _ptr(m["tile_base"]), _ptr(sizes[j]), stream)
+                if rows != K:
+                    _lib.call("spira_b200_kmap_ws_sizes", _ptr(m["counts"]), rows, nt, _ptr(m["nbsizes"]),
+                              _ptr(m["naddrs"]), _ptr(m["qnaddrs"]), _ptr(m["tile_base"]), _ptr(sizes[j]), stream)
+            else:
+                m["nbsizes"].zero_(); m["naddrs"].zero_(); m["qnaddrs"].zero_(); sizes[j].zero_()
+        host_sizes = sizes.cpu().tolist()
+        for j, m in enumerate(ws_maps):
+            mapsize, qmapsize = host_sizes[j]
+            rows = m["rows"]
+            nbmaps = torch.empty((2, mapsize), dtype=torch.int32, device=dev)
+            if mapsize > 0:
+                _lib.call("spira_b200_kmap_ws_pairs", _ptr(m["dense"]), rows, m["Tal"], _ptr(m["naddrs"]),
+                          _ptr(m["tile_base"]), _ptr(nbmaps[0]), _ptr(nbmaps[1]), stream)
+            w = WsLists()
+            w.nbmaps, w.in_idx, w.out_idx = nbmaps, nbmaps[0], nbmaps[1]
+            w.nbsizes, w.naddrs, w.qnaddrs = m["nbsizes"][:rows], m["naddrs"][:rows + 1], m["qnaddrs"][:rows + 1]
+            w.rows, w.mirror, w.mapsize, w.qmapsize = rows, bool(m["half"]), int(mapsize), int(qmapsize)
+            m["ws"] = w
+
+    results = []
+    for m in info:
+        df, dense = m["df"], m["dense"]
+        dense._sb = dict(counts=m["counts"], ws=m.get("ws"), kernel_size=m["ks"], layout=m["layout"])
+        if df == 0:
+            results.append((m["S"], m["T"], dense, None, None, None, None, None, None))
+        elif df in (1, 3, 5, 7):
+            w = m["ws"]
+            w.nbmaps._sb = dense._sb
+            results.append((m["S"], m["T"], dense, w.nbmaps, w.nbsizes, w.naddrs, w.qnaddrs, w.mapsize, w.qmapsize))
+        else:
+            w = m["ws"]
+            K = m["K"]
+            sm = torch.empty((K, m["S"]), dtype=torch.int32, device=dev)
+            tm = torch.empty((K, m["T"]), dtype=torch.int32, device=dev)
+            _lib.call("spira_b200_kmap_masks", _ptr(dense), K, m["S"], m["T"], m["Tal"], _ptr(m["tile_base"]), _ptr(sm),
+                      _ptr(tm), stream)
+            sm._sb, sm._sb_role = dense._sb, "source"
+            tm._sb, tm._sb_role = dense._sb, "target"
+            results.append((m["S"], m["T"], dense, sm, tm, w.nbsizes, None, None, None))
+    return results
+
+
+def cuda_binary_search(sources, targets, kernel_size, source_stride, dataflow: int = 0):
+    """One kernel map.  Reference: ``BinarySearch`` (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:211-892)."""
+    return _build_maps([(sources.contiguous(), targets.contiguous())], [kernel_size], [source_stride], [dataflow])[0]
+
+
+def cuda_binary_search_streamed(voxels, kernel_sizes, source_strides, dataflow):
+    """All kernel maps of a network in one go; map ``i`` uses ``voxels[i // 2]`` as sources and
+    ``voxels[(i + 1) // 2]`` as targets (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:894-1645, :945-946)."""
+    if not (len(kernel_sizes) == len(source_strides) == len(dataflow)):
+        raise RuntimeError("[spira_b200] kernel_sizes, source_strides and dataflow must have the same length")
+    voxels = [v.contiguous() for v in voxels]
+    pairs = [(voxels[i // 2], voxels[(i + 1) // 2]) for i in range(len(kernel_sizes))]
+    return _build_maps(pairs, kernel_sizes, source_strides, dataflow)
+
+
+def cuda_binary_search_no_small_z(sources, targets, kernel_size, source_stride):
+    """Ablation entry of the reference (full search for every offset, natural column order,
+    csrc/spira/cuda/kernels/query_sorted.cuh:165-201): same result as the natural-order map, ``[T_al, K]``."""
+    S, T, dense_ws, *_ = _build_maps([(sources.contiguous(), targets.contiguous())], [kernel_size], [source_stride], [1])[0]
+    out = torch.empty((dense_ws.shape[1], dense_ws.shape[0]), dtype=torch.int32, device=dense_ws.device)
+    _lib.call("spira_b200_transpose_map", _ptr(dense_ws), dense_ws.shape[0], dense_ws.shape[1], _ptr(out), _stream(out.device))
+    return (S, T, out, None, None, None, None, None, None)
+
+
+def transpose_map(m: torch.Tensor) -> torch.Tensor:
+    """``m.T.contiguous()`` for an int32 map."""
+    m = m.contiguous()
+    out = torch.empty((m.shape[1], m.shape[0]), dtype=torch.int32, device=m.device)
+    _lib.call("spira_b200_transpose_map", _ptr(m), m.shape[0], m.shape[1], _ptr(out), _stream(m.device))
+    return out
+
+
+def cuda_convert_transposed_os(out_in_map: torch.Tensor, num_sources: int) -> torch.Tensor:
+    """Inverse of a ``[T_al, K]`` map: ``[S_al, K]`` (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:1809-1830)."""
+    _require_cuda(out_in_map)
+    out_in_map = out_in_map.contiguous()
+    Tal, K = out_in_map.shape
+    Sal = _aligned(int(num_sources))
+    out = torch.empty((Sal, K), dtype=torch.int32, device=out_in_map.device)
+    _lib.call("spira_b200_convert_transposed_os", _ptr(out_in_map), Tal, K, _ptr(out), Sal, _stream(out.device))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# feature compute
+# ------------------------------------------------------------------------------------------------
+_packed_cache = {}
+
+
+def packed_weights(weights: torch.Tensor, mode: int) -> Optional[torch.Tensor]:
+    """Tensor-core operand image of ``weights [K, c_in, c_out]`` (cached until the tensor changes)."""
+    K, cin, cout = weights.shape
+    if weights.dtype != torch.float16 or not _lib.load().spira_b200_tensor_core_eligible(K, cin, cout):
+        return None
+    key = (weights.data_ptr(), weights._version, tuple(weights.shape), mode, weights.device.index)
+    hit = _packed_cache.get(key)
+    if hit is not None:
+        return hit
+    if len(_packed_cache) > 512:
+        _packed_cache.clear()
+    need = C.c_size_t()
+    _lib.call("spira_b200_packed_weight_bytes", K, cin, cout, mode, C.byref(need))
+    packed = torch.empty(need.value, dtype=torch.uint8, device=weights.device)
+    _lib.call("spira_b200_pack_weights", _ptr(weights), K, cin, cout, mode, _ptr(packed), _stream(weights.device))
+    _packed_cache[key] = packed
+    return packed
+
+
+def _epilogue(bias=None, scale=None, shift=None, residual=None, relu=False):
+    if bias is None and scale is None and residual is None and not relu:
+        return None, ()
+    e = Epilogue()
+    keep = []
+    for name, t, dt in (("bias", bias, torch.float16), ("scale", scale, torch.float32), ("shift", shift, torch.float32),
+                        ("residual", residual, torch.float16)):
+        if t is not None:
+            t = t.to(dt).contiguous()
+            keep.append(t)
+            setattr(e, name, t.data_ptr())
+    e.relu = 1 if relu else 0
+    return e, keep
+
+
+def _check_feats(sources, weights):
+    _require_cuda(sources, weights)
+    if sources.dim() != 2:
+        raise RuntimeError("[spira_b200] Tensor sources is expected to have 2 dimension(s)")
+    if weights.dim() != 3:
+        raise RuntimeError("[spira_b200] Tensor weights is expected to have 3 dimension(s)")
+    if sources.shape[1] != weights.shape[1]:
+        raise RuntimeError(f"[spira_b200] The dimension 1 of Tensor sources is expected to be {weights.shape[1]} but found {sources.shape[1]}")
+    if sources.dtype != torch.float16 or weights.dtype != torch.float16:
+        raise RuntimeError("[spira_b200] features and weights must be float16 (fp16 in/out, fp32 accumulate)")
+
+
+def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None, scale=None, shift=None, residual=None,
+            relu=False, force_simt=False) -> torch.Tensor:
+    """Output-stationary forward with the optional fused epilogue."""
+    _check_feats(sources, weights)
+    sources, weights, out_in_map = sources.contiguous(), weights.contiguous(), out_in_map.contiguous()
+    K, cin, cout = weights.shape
+    if out_in_map.dim() != 2 or out_in_map.shape[1] != K or out_in_map.shape[0] < num_targets:
+        raise RuntimeError(f"[spira_b200] out_in_map must be [T_al, {K}] with T_al >= {num_targets}, got {tuple(out_in_map.shape)}")
+    out = torch.empty((num_targets, cout), dtype=torch.float16, device=sources.device)
+    packed = None if force_simt else packed_weights(weights, PACK_OS)
+    if packed is not None and out_in_map.shape[0] != _aligned(num_targets):
+        packed = None
+    ep, keep = _epilogue(bias, scale, shift, residual, relu)
+    _lib.call("spira_b200_conv_os", _ptr(sources), _ptr(weights), _ptr(packed), C.byref(ep) if ep is not None else None,
+              _ptr(out_in_map), int(num_sources), int(num_targets), K, cin, cout, _ptr(out), _ptr(status_word(sources.device)),
+              _stream(sources.device))
+    return out
+
+
+def conv_ws(num_sources, num_targets, sources, weights, lists: WsLists, *, swap=False, bias=None, scale=None, shift=None,
+            residual=None, relu=False, force_simt=False) -> torch.Tensor:
+    """Weight-stationary forward over compacted pair lists with the optional fused epilogue."""
+    _check_feats(sources, weights)
+    sources, weights = sources.contiguous(), weights.contiguous()
+    K, cin, cout = weights.shape
+    out = torch.empty((num_targets, cout), dtype=torch.float16, device=sources.device)
+    accum = torch.empty((num_targets, cout), dtype=torch.float32, device=sources.device)
+    packed = None if force_simt else packed_weights(weights, PACK_WS)
+    mirror = bool(lists.mirror)
+    if mirror and swap:
+        raise RuntimeError("[spira_b200] a mirrored (submanifold) list cannot be used transposed")
+    ep, keep = _epilogue(bias, scale, shift, residual, relu)
+    _lib.call("spira_b200_conv_ws", _ptr(sources), _ptr(weights), _ptr(packed), C.byref(ep) if ep is not None else None,
+              _ptr(lists.in_idx), _ptr(lists.out_idx), _ptr(lists.naddrs), _ptr(lists.qnaddrs), lists.rows,
+              lists.qmapsize // 128, 1 if mirror else 0, 1 if swap else 0, int(num_sources), int(num_targets), K, cin, cout,
+              _ptr(accum), _ptr(out), _ptr(status_word(sources.device)), _stream(sources.device))
+    return out
+
+
+def cuda_sparse_convolution_forward_os(num_sources, num_targets, out_in_map, sources, weights):
+    """Reference: ``cuda_sparse_convolution_forward_os`` (csrc/spira/torch/cuda_sparse_convolution_forward.cu:11-80)."""
+    return conv_os(num_sources, num_targets, out_in_map, sources, weights)
+
+
+def _lists_from_reference_slots(naddrs, qnaddrs, nbmaps, mapsize, qmapsize, num_sources, num_targets, K) -> WsLists:
+    w = WsLists()
+    nbmaps = nbmaps.contiguous()
+    w.nbmaps, w.in_idx, w.out_idx = nbmaps, nbmaps[0], nbmaps[1]
+    w.naddrs, w.qnaddrs = naddrs.contiguous(), qnaddrs.contiguous()
+    w.rows = naddrs.shape[0] - 1
+    w.nbsizes = None
+    w.mirror = (w.rows == (K + 1) // 2) and K % 2 == 1 and num_sources == num_targets and w.rows != K
+    w.mapsize, w.qmapsize = int(mapsize), int(qmapsize)
+    return w
+
+
+def cuda_sparse_convolution_forward_ws_merged(num_sources, num_targets, sources, weights, naddrs, qnaddrs, nbmaps, mapsize,
+                                              qmapsize, transpose=False):
+    """Reference: ``cuda_sparse_convolution_forward_ws_merged`` (csrc/spira/torch/cuda_sparse_convolution_forward.cu:183-246)."""
+    K = weights.shape[0]
+    lists = _lists_from_reference_slots(naddrs, qnaddrs, nbmaps, mapsize, qmapsize, num_sources, num_targets, K)
+    return conv_ws(num_sources, num_targets, sources, weights, lists, swap=bool(transpose))
+
+
+def cuda_sparse_convolution_forward_ws(num_sources, num_targets, gather_tile_size, scatter_tile_size, parallel, threshold,
+                                       sources, weights, source_masks, target_masks, kernel_map_sizes):
+    """Mask-format weight-stationary call (csrc/spira/torch/cuda_sparse_convolution_forward.cu:82-181).  The tile
+    sizes, GEMM parallelism and padding threshold tune the reference's gather / cuBLAS / scatter
+    pipeline and have no counterpart in the fused kernel; they are accepted and ignored."""
+    sb = getattr(source_masks, "_sb", None) or getattr(target_masks, "_sb", None)
+    if sb is None or sb.get("ws") is None:
+        raise RuntimeError("[spira_b200] mask tensors must come from this engine's build_kmap(dataflow=2)")
+    lists = sb["ws"]
+    # the masks of a transposed layer arrive exchanged (spira/nn/conv.py:353-360)
+    swap = getattr(source_masks, "_sb_role", "source") == "target"
+    return conv_ws(num_sources, num_targets, sources, weights, lists, swap=swap)
+
+
+def cuda_sparse_convolution_forward_hs_merged(num_sources, num_targets, sources, weights, naddrs, qnaddrs, nbmaps, out_in_map,
+                                              mapsize, qmapsize, transpose=False):
+    """Hybrid call of the reference (csrc/spira/torch/cuda_sparse_convolution_forward.cu:338-420): maps built by this
+    engine for dataflows 3/5/7 hold the complete pair lists, so the call reduces to the weight-stationary one."""
+    return cuda_sparse_convolution_forward_ws_merged(num_sources, num_targets, sources, weights, naddrs, qnaddrs, nbmaps,
+                                                     mapsize, qmapsize, transpose)
+
+
+def cuda_sparse_convolution_forward_hs(num_sources, num_targets, gather_tile_size, scatter_tile_size, parallel, threshold,
+                                       sources, weights, source_masks, target_masks, kernel_map_sizes, out_in_map):
+    """Hybrid mask-format call (csrc/spira/torch/cuda_sparse_convolution_forward.cu:248-336); see ``..._hs_merged``."""
+    return cuda_sparse_convolution_forward_ws(num_sources, num_targets, gather_tile_size, scatter_tile_size, parallel,
+                                              threshold, sources, weights, source_masks, target_masks, kernel_map_sizes)
+
+
+def _time_ws(weights, source_masks, target_masks) -> float:
+    sb = getattr(source_masks, "_sb", None)
+    if sb is None or sb.get("ws") is None:
+        raise RuntimeError("[spira_b200] mask tensors must come from this engine's build_kmap(dataflow=2)")
+    S, T = source_masks.shape[1], target_masks.shape[1]
+    feats = torch.zeros((S, weights.shape[1]), dtype=weights.dtype, device=weights.device)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    conv_ws(S, T, feats, weights, sb["ws"])
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b)
+
+
+def cuda_time_gemm(parallel, threshold, is_hybrid, weights, source_masks, target_masks, kernel_map_sizes) -> float:
+    """Timing probe used by the reference tuner (csrc/spira/torch/cuda_sparse_convolution_forward.cu:422-498).  The fused
+    kernel has no separate GEMM stage: the time of the whole weight-stationary layer is returned."""
+    return _time_ws(weights, source_masks, target_masks)
+
+
+def cuda_time_gather(tile_size, threshold, is_hybrid, weights, source_masks, target_masks, kernel_map_sizes) -> float:
+    """See :func:`cuda_time_gemm`."""
+    return _time_ws(weights, source_masks, target_masks)
+
+
+def cuda_time_scatter(tile_size, threshold, is_hybrid, weights, source_masks, target_masks, kernel_map_sizes) -> float:
+    """See :func:`cuda_time_gemm`."""
+    return _time_ws(weights, source_masks, target_masks)
+
+
+def cuda_free_buffers() -> None:
+    """The reference releases its private stack allocator here (csrc/spira/torch/cuda_memory_buffer.cu:7-16).  This
+    engine holds no pool of its own (scratch comes from torch's caching allocator); only the packed-weight cache is dropped."""
+    _packed_cache.clear()
+
+
+def cuda_reset_error() -> None:
+    """Clears a sticky CUDA error (csrc/spira/torch/cuda_memory_buffer.cu:11-16)."""
+    _lib.call("spira_b200_reset_error")

@@ -1,0 +1,220 @@
+"""``as_tuple``, ``set_kernel_map_cache`` and ``tune`` with the reference's signatures
+(spira/utils/helpers.py:20-47, 388-618).
+
+``tune`` keeps the reference's entry point, grouping rule (layers grouped by
+``(effective_stride, kernel_size, stride)``), return value and ``.pt`` result file, but chooses the
+dataflow of each group from MEASURED layer shape and map density instead of timing nine
+dataflows: the engine has two dataflows (output-stationary = reference dataflow 0, weight-stationary
+= reference dataflow 1) and a cost model over the hit counts the map search already produced.
+With ``verify=True`` the model-level timing of the reference (``helpers.py:122-143``) cross-checks
+the choice.
+"""
+__all__ = ['as_tuple', 'make_divisible', 'tune', 'set_kernel_map_cache', 'DataflowConfig', 'choose_dataflow']
+
+import functools
+import itertools
+import os.path
+from collections import defaultdict
+from typing import Dict, Iterable, List, Optional, Tuple, Union
+
+import torch
+from torch.nn import Module
+
+from spira_b200.utils.typing import ScalarOrTuple
+
+
+def set_kernel_map_cache(module: Module, cache):
+    if hasattr(module, "set_kernel_map_cache"):
+        module.set_kernel_map_cache(cache)
+    for submodule in module.children():
+        set_kernel_map_cache(submodule, cache=cache)
+    return module
+
+
+def as_tuple(value: ScalarOrTuple, *, size: int = 3, name: Optional[str] = None):
+    name = name or "Value"
+    if not isinstance(value, Iterable):
+        return tuple(value for _ in range(size))
+    value = tuple(value)
+    if len(value) != size:
+        raise ValueError(f"{name} must be a scalar or a iterable of size {size} but found {len(value)} elements")
+    return value
+
+
+def make_divisible(value: int, divisor: int) -> int:
+    return (value + divisor - 1) // divisor * divisor
+
+
+class DataflowConfig:
+    """Per-group choice, same fields as the reference's record (helpers.py:81-93)."""
+
+    def __init__(self, map_dataflow: int = 0, force_os: bool = False):
+        self.map_dataflow = map_dataflow
+        self.force_os = force_os
+
+    def __repr__(self):
+        return f"DataflowConfig(map_dataflow={self.map_dataflow}, force_os={self.force_os})"
+
+    def to_dict(self):
+        return {"map_dataflow": self.map_dataflow, "force_os": self.force_os}
+
+
+def choose_dataflow(c_in: int, c_out: int, kernel_volume: int, num_targets: int, nnz: int, nonempty_tile_offsets: int,
+                    transposed_or_strided: bool = False) -> int:
+    """Cost model of the selector: returns 0 (output-stationary) or 1 (weight-stationary).
+
+    Both kernels are gather-bound, so the cost is the number of 128-row operand tiles they
+    move.  OS moves one tile per (128-target tile, offset) that has at least one neighbour
+    (``nonempty_tile_offsets``) and writes each output once.  WS moves ``ceil(nnz_k / 128)`` tiles
+    per offset -- about ``nnz / 128 + K / 2`` -- but pays an fp32 read-modify-write of the
+    output per pair (4 bytes x c_out x 2 against 2 bytes x c_in gathered) and a final conversion
+    pass.  Channel counts the tensor-core kernels cannot tile run output-stationary on the SIMT kernel.
+    """
+    if c_in % 8 != 0 or c_out % 16 != 0 or c_out > 256 or num_targets == 0:
+        return 0
+    os_tiles = float(max(nonempty_tile_offsets, 1))
+    ws_tiles = nnz / 128.0 + kernel_volume / 2.0
+    gather = 2.0 * c_in
+    scatter = 8.0 * c_out
+    os_cost = os_tiles * gather + (num_targets / 128.0) * 2.0 * c_out
+    ws_cost = ws_tiles * (gather + scatter) + (num_targets / 128.0) * 10.0 * c_out
+    return 1 if ws_cost < 0.8 * os_cost else 0
+
+
+def _map_statistics(cache, conv, inputs_stride):
+    """(num_targets, nnz, non-empty (tile, offset) count) of the layer's map from the search's hit counters."""
+    from spira_b200.utils.helpers import as_tuple as _t
+    s = _t(inputs_stride, size=3)
+    if conv.transposed:
+        key = (tuple(a // b for a, b in zip(s, conv.stride)), s, conv.kernel_size)
+    else:
+        key = (s, tuple(a * b for a, b in zip(s, conv.stride)), conv.kernel_size)
+    entry = cache._kernel_maps_cache.get(key)
+    if entry is None:
+        return None
+    sb = getattr(entry[3], "_sb", None)
+    if sb is None:
+        return None
+    counts = sb["counts"]
+    nnz = int(counts.sum().item())
+    nonempty = int((counts > 0).sum().item())
+    return int(entry[2]), nnz, nonempty
+
+
+def _time_model(model, samples, cache, skip: int = 1) -> float:
+    times = []
+    for i, x in enumerate(samples):
+        if cache is not None:
+            cache.reset()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        with torch.no_grad():
+            model(x)
+        b.record()
+        b.synchronize()
+        if i >= skip:
+            times.append(a.elapsed_time(b))
+    return sum(times) / max(len(times), 1)
+
+
+def tune(model: Module, data_loader: Iterable, kernel_map_cache=None, map_dataflow_options: List[int] = None,
+         test_force_os: bool = True, n_samples: int = 10, n_samples_for_gs: int = 1, save_dir: str = ".tune_configs",
+         tune_tag: str = "default", force_retune: bool = False, allow_gs_tuning: bool = True, verbose: bool = False,
+         return_dataflows: bool = False, verify: bool = False) -> Union[Module, Tuple[Module, Dict]]:
+    """Chooses a dataflow per layer group and stores it in every layer's ``_tunable_config``.
+
+    Result file ``<save_dir>/<tune_tag>.pt`` holds ``{name_to_group, best_configs, layer_configs}`` like the
+    reference's (helpers.py:340-365) and is reloaded unless ``force_retune``.
+    """
+    from spira_b200.nn import SparseConv
+
+    allowed = set(map_dataflow_options) if map_dataflow_options is not None else {0, 1}
+    samples = list(itertools.islice(data_loader, max(1, min(n_samples, 4))))
+    save_path = os.path.join(save_dir, f"{tune_tag}.pt")
+    convs = {name: m for name, m in model.named_modules() if isinstance(m, SparseConv)}
+
+    def apply(name_to_group, best):
+        for name, m in convs.items():
+            g = name_to_group.get(name)
+            if g is not None and g in best:
+                m._tunable_config['map_dataflow'] = best[g].map_dataflow
+                m._tunable_config['force_os'] = best[g].force_os
+
+    if os.path.exists(save_path) and not force_retune:
+        try:
+            blob = torch.load(save_path, weights_only=False)
+            best = {g: DataflowConfig(**c) for g, c in blob["best_configs"].items()}
+            apply(blob["name_to_group"], best)
+            out = {g: c.map_dataflow for g, c in best.items()}
+            return (model, out) if return_dataflows else model
+        except Exception as e:  # unreadable cache -> tune again
+            if verbose:
+                print(f"could not load {save_path} ({e}); tuning again")
+
+    # ---- one forward pass with hooks: group the layers and read the density of their maps
+    name_to_group, group_to_name, stats = {}, defaultdict(list), defaultdict(list)
+
+    def hook(module, inputs, outputs, name):
+        x = inputs[0]
+        stride = x._stride
+        eff = tuple(stride[k] // module.stride[k] for k in range(3)) if module.transposed else stride
+        g = (eff, module.kernel_size, module.stride)
+        name_to_group[name] = g
+        group_to_name[g].append(name)
+        if not module.is_trivial and kernel_map_cache is not None:
+            st = _map_statistics(kernel_map_cache, module, stride)
+            if st is not None:
+                stats[g].append((module.in_channels, module.out_channels, module.transposed) + st)
+
+    handles = [m.register_forward_hook(functools.partial(hook, name=n)) for n, m in convs.items()]
+    for m in convs.values():
+        m._tunable_config['map_dataflow'] = 1  # weight-stationary maps carry every statistic the model needs
+        m._tunable_config['force_os'] = False
+    if kernel_map_cache is not None:
+        kernel_map_cache.reset()
+    with torch.no_grad():
+        model(samples[0])
+    for h in handles:
+        h.remove()
+
+    best: Dict[Tuple, DataflowConfig] = {}
+    for g, names in group_to_name.items():
+        votes = []
+        for (cin, cout, transposed, T, nnz, nonempty) in stats.get(g, []):
+            kv = g[1][0] * g[1][1] * g[1][2]
+            votes.append(choose_dataflow(cin, cout, kv, T, nnz, nonempty, transposed or any(v != 1 for v in g[2])))
+        df = 1 if votes and sum(votes) * 2 > len(votes) else 0
+        if df not in allowed:
+            df = 0 if 0 in allowed else min(allowed)
+        best[g] = DataflowConfig(map_dataflow=df, force_os=False)
+        if verbose:
+            print(f"group {g}: {len(names)} layer(s) -> map_dataflow={df}")
+    apply(name_to_group, best)
+
+    if verify and len(best) > 0:
+        base = _time_model(model, samples, kernel_map_cache)
+        for g in list(best):
+            if len(stats.get(g, [])) == 0:
+                continue
+            flipped = DataflowConfig(map_dataflow=1 - best[g].map_dataflow, force_os=False)
+            if flipped.map_dataflow not in allowed:
+                continue
+            trial = dict(best)
+            trial[g] = flipped
+            apply(name_to_group, trial)
+            t = _time_model(model, samples, kernel_map_cache)
+            if t < 0.97 * base:
+                best, base = trial, t
+                if verbose:
+                    print(f"group {g}: timing overrides the model -> map_dataflow={flipped.map_dataflow} ({t:.3f} ms)")
+            apply(name_to_group, best)
+
+    os.makedirs(save_dir, exist_ok=True)
+    torch.save({"name_to_group": name_to_group,
+                "best_configs": {g: c.to_dict() for g, c in best.items()},
+                "layer_configs": {n: dict(m._tunable_config) for n, m in convs.items()}}, save_path)
+    if kernel_map_cache is not None:
+        kernel_map_cache.reset()
+    out = {g: c.map_dataflow for g, c in best.items()}
+    return (model, out) if return_dataflows else model

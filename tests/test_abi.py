@@ -1,0 +1,53 @@
+"""CPU: the C-ABI library builds, loads and exports every symbol the header declares (no compute calls)."""
+import ctypes
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "spira_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(spira_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_surface():
+    names = declared_symbols()
+    for must in ("spira_b200_flatten_sort", "spira_b200_downsample", "spira_b200_kmap_search", "spira_b200_conv_os",
+                 "spira_b200_conv_ws", "spira_b200_convert_transposed_os", "spira_b200_last_error"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol(lib):
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared in include/spira_b200.h but not exported"
+
+
+def test_python_binding_covers_the_header(lib):
+    from spira_b200 import _lib
+    assert sorted(_lib.EXPORTS) == declared_symbols()
+
+
+def test_struct_layouts_match_the_header():
+    from spira_b200 import _lib
+    assert ctypes.sizeof(_lib.KmapDesc) == 8 * 4 + 4 * 8 + 8 * 2      # 2 ptr, 2 i64, 8 i32, 2 ptr
+    assert ctypes.sizeof(_lib.Epilogue) == 4 * 8 + 8
+
+
+def test_argument_errors_without_a_gpu(lib):
+    """Validation happens on the host before any CUDA call."""
+    from spira_b200 import _lib
+    import pytest
+    n = ctypes.c_size_t()
+    assert lib.spira_b200_flatten_sort_workspace(10, 5, ctypes.byref(n)) != 0
+    assert b"key_bytes" in lib.spira_b200_last_error()
+    assert lib.spira_b200_downsample_workspace(10, 4, 99, ctypes.byref(n)) != 0
+    assert lib.spira_b200_tensor_core_eligible(27, 64, 64) == 1
+    assert lib.spira_b200_tensor_core_eligible(27, 4, 32) == 0
+    assert lib.spira_b200_tensor_core_eligible(27, 64, 19) == 0
+    assert lib.spira_b200_packed_weight_bytes(27, 64, 64, 0, ctypes.byref(n)) == 0 and n.value == 27 * 64 * 128
+    assert lib.spira_b200_packed_weight_bytes(27, 32, 64, 0, ctypes.byref(n)) == 0 and n.value == 14 * 64 * 128
+    assert lib.spira_b200_packed_weight_bytes(27, 32, 64, 1, ctypes.byref(n)) == 0 and n.value == 27 * 64 * 128
+    with pytest.raises(RuntimeError, match="spira_b200"):
+        _lib.call("spira_b200_kmap_search", None, 99, 4, None)

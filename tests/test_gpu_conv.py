@@ -1,0 +1,199 @@
+"""GPU parity: feature compute through the C-ABI vs the torch-CPU oracle.
+
+Tolerance: 1e-2 relative / 1e-3 absolute (fp16 in/out, fp32 accumulate, one rounding)."""
+import numpy as np
+import pytest
+import torch
+
+import spira_oracle as O
+from helpers import surface, cloud, dev, keys_to_torch, assert_features_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C(lib):
+    from spira_b200.nn.functional import _C
+    yield _C
+    _C.check_status()
+
+
+@pytest.fixture(scope="module")
+def scene():
+    c = surface(21, 24000)
+    keys, _ = O.flat_sort(c)
+    down = O.downsample(keys, (2, 2, 2))
+    return keys, down
+
+
+def tensors(n, cin, cout, K, seed):
+    rng = np.random.default_rng(seed)
+    f = rng.normal(size=(n, cin)).astype(np.float16)
+    w = (rng.normal(size=(K, cin, cout)) / np.sqrt(K * cin)).astype(np.float16)
+    return torch.from_numpy(f), torch.from_numpy(w)
+
+
+CHANNELS = [(16, 16), (32, 32), (64, 64), (32, 64), (96, 96), (128, 128), (192, 96), (256, 256), (384, 256), (64, 48),
+            (24, 16), (4, 32), (3, 32), (5, 16), (32, 19)]
+
+
+@pytest.mark.parametrize("cin,cout", CHANNELS)
+def test_output_stationary_submanifold(C, scene, cin, cout):
+    keys, _ = scene
+    n = len(keys)
+    m = C.cuda_binary_search(keys_to_torch(keys), keys_to_torch(keys), (3, 3, 3), (1, 1, 1), 0)
+    f, w = tensors(n, cin, cout, 27, cin * 1000 + cout)
+    got = C.cuda_sparse_convolution_forward_os(n, n, m[2], f.cuda(), w.cuda())
+    want = O.conv_os(f, w, m[2].cpu().numpy(), n)
+    assert_features_close(got, want)
+    C.check_status()
+
+
+@pytest.mark.parametrize("cin,cout", [(64, 64), (4, 32)])
+def test_simt_kernel_agrees(C, scene, cin, cout):
+    keys, _ = scene
+    n = len(keys)
+    m = C.cuda_binary_search(keys_to_torch(keys), keys_to_torch(keys), (3, 3, 3), (1, 1, 1), 0)
+    f, w = tensors(n, cin, cout, 27, 5)
+    got = C.conv_os(n, n, m[2], f.cuda(), w.cuda(), force_simt=True)
+    assert_features_close(got, O.conv_os(f, w, m[2].cpu().numpy(), n))
+
+
+@pytest.mark.parametrize("cin,cout", [(16, 16), (32, 32), (64, 64), (128, 64), (96, 128), (256, 256), (4, 32), (24, 48)])
+def test_weight_stationary_submanifold_mirrored(C, scene, cin, cout):
+    keys, _ = scene
+    n = len(keys)
+    m = C.cuda_binary_search(keys_to_torch(keys), keys_to_torch(keys), (3, 3, 3), (1, 1, 1), 1)
+    f, w = tensors(n, cin, cout, 27, cin * 7 + cout)
+    got = C.cuda_sparse_convolution_forward_ws_merged(n, n, f.cuda(), w.cuda(), m[5], m[6], m[3], m[7], m[8], False)
+    want = O.conv_ws(f, w, m[2].cpu().numpy(), n)
+    assert_features_close(got, want)
+    C.check_status()
+
+
+@pytest.mark.parametrize("ks", [(3, 3, 3), (2, 2, 2)])
+@pytest.mark.parametrize("cin,cout", [(32, 64), (64, 64), (4, 16)])
+def test_strided_and_transposed(C, scene, ks, cin, cout):
+    keys, down = scene
+    S, T = len(keys), len(down)
+    K = ks[0] * ks[1] * ks[2]
+    tk, td = keys_to_torch(keys), keys_to_torch(down)
+    f, w = tensors(S, cin, cout, K, 31)
+    m_os = C.cuda_binary_search(tk, td, ks, (1, 1, 1), 0)
+    m_ws = C.cuda_binary_search(tk, td, ks, (1, 1, 1), 1)
+    dense_ws = m_ws[2].cpu().numpy()
+    want = O.conv_ws(f, w, dense_ws, T)
+    # the z-major map pairs column c with weight row c: permute natural weights to z-major for the OS call
+    nxy, kz = O.n_offsets(ks)
+    perm = [(col % nxy) * kz + col // nxy for col in range(K)]
+    got_os = C.cuda_sparse_convolution_forward_os(S, T, m_os[2], f.cuda(), w[perm].contiguous().cuda())
+    assert_features_close(got_os, want)
+    got_ws = C.cuda_sparse_convolution_forward_ws_merged(S, T, f.cuda(), w.cuda(), m_ws[5], m_ws[6], m_ws[3], m_ws[7], m_ws[8], False)
+    assert_features_close(got_ws, want)
+    # transposed layer on the same maps: coarse -> fine
+    g, wt = tensors(T, cout, cin, K, 32)
+    want_t = O.conv_ws_transposed(g, wt, dense_ws, S)
+    got_t = C.cuda_sparse_convolution_forward_ws_merged(T, S, g.cuda(), wt.cuda(), m_ws[5], m_ws[6], m_ws[3], m_ws[7], m_ws[8], True)
+    assert_features_close(got_t, want_t)
+    inv = C.cuda_convert_transposed_os(m_os[2], S)
+    got_t_os = C.cuda_sparse_convolution_forward_os(T, S, inv, g.cuda(), wt[perm].contiguous().cuda())
+    assert_features_close(got_t_os, want_t)
+    C.check_status()
+
+
+def test_large_kernel_volume(C):
+    """5^3 = 125 offsets: the map slab is single-buffered and chunks straddle offsets (c_in = 32)."""
+    c = surface(22, 6000)
+    keys, _ = O.flat_sort(c)
+    n = len(keys)
+    tk = keys_to_torch(keys)
+    f, w = tensors(n, 32, 32, 125, 33)
+    m = C.cuda_binary_search(tk, tk, (5, 5, 5), (1, 1, 1), 0)
+    assert_features_close(C.cuda_sparse_convolution_forward_os(n, n, m[2], f.cuda(), w.cuda()), O.conv_os(f, w, m[2].cpu().numpy(), n))
+    m1 = C.cuda_binary_search(tk, tk, (5, 5, 5), (1, 1, 1), 1)
+    got = C.cuda_sparse_convolution_forward_ws_merged(n, n, f.cuda(), w.cuda(), m1[5], m1[6], m1[3], m1[7], m1[8], False)
+    assert_features_close(got, O.conv_ws(f, w, m1[2].cpu().numpy(), n))
+    C.check_status()
+
+
+@pytest.mark.parametrize("n", [1, 100, 128, 129, 257])
+def test_ragged_tiles(C, n):
+    c = cloud(n + 40, n, 32, 38)
+    keys, _ = O.flat_sort(c)
+    n = len(keys)
+    tk = keys_to_torch(keys)
+    f, w = tensors(n, 64, 64, 27, 34)
+    m = C.cuda_binary_search(tk, tk, (3, 3, 3), (1, 1, 1), 0)
+    assert_features_close(C.cuda_sparse_convolution_forward_os(n, n, m[2], f.cuda(), w.cuda()), O.conv_os(f, w, m[2].cpu().numpy(), n))
+    m1 = C.cuda_binary_search(tk, tk, (3, 3, 3), (1, 1, 1), 1)
+    got = C.cuda_sparse_convolution_forward_ws_merged(n, n, f.cuda(), w.cuda(), m1[5], m1[6], m1[3], m1[7], m1[8], False)
+    assert_features_close(got, O.conv_ws(f, w, m1[2].cpu().numpy(), n))
+    C.check_status()
+
+
+def test_isolated_voxels_have_only_the_centre(C):
+    """No neighbours at all: every tile still produces its (centre-only) output; empty offsets are skipped."""
+    c = (np.stack(np.meshgrid(np.arange(12), np.arange(12), np.arange(6), indexing="ij"), -1).reshape(-1, 3) * 4 + 32).astype(np.int32)
+    keys, _ = O.flat_sort(c)
+    n = len(keys)
+    f, w = tensors(n, 64, 64, 27, 35)
+    m = C.cuda_binary_search(keys_to_torch(keys), keys_to_torch(keys), (3, 3, 3), (1, 1, 1), 0)
+    got = C.cuda_sparse_convolution_forward_os(n, n, m[2], f.cuda(), w.cuda())
+    want = (f.float() @ w[13].float()).half()          # z-major column 13 is still the centre
+    assert_features_close(got, want)
+
+
+@pytest.mark.parametrize("mode", ["os", "ws"])
+def test_fused_epilogue(C, scene, mode):
+    keys, _ = scene
+    n = len(keys)
+    tk = keys_to_torch(keys)
+    f, w = tensors(n, 64, 64, 27, 36)
+    rng = np.random.default_rng(36)
+    bias = torch.from_numpy(rng.normal(size=64).astype(np.float16))
+    scale = torch.from_numpy(rng.uniform(0.5, 1.5, 64).astype(np.float32))
+    shift = torch.from_numpy(rng.normal(size=64).astype(np.float32))
+    res = torch.from_numpy(rng.normal(size=(n, 64)).astype(np.float16))
+    kw = dict(bias=bias.cuda(), scale=scale.cuda(), shift=shift.cuda(), residual=res.cuda(), relu=True)
+    if mode == "os":
+        m = C.cuda_binary_search(tk, tk, (3, 3, 3), (1, 1, 1), 0)
+        got = C.conv_os(n, n, m[2], f.cuda(), w.cuda(), **kw)
+        acc = O.conv_from_pairs(f.float(), w.float(), *_pairs_os(m[2].cpu().numpy(), n), n)
+    else:
+        m = C.cuda_binary_search(tk, tk, (3, 3, 3), (1, 1, 1), 1)
+        got = C.conv_ws(n, n, f.cuda(), w.cuda(), m[3]._sb["ws"], **kw)
+        d = m[2].cpu().numpy()
+        k, t = np.nonzero(d[:, :n] >= 0)
+        acc = O.conv_from_pairs(f.float(), w.float(), d[k, t], t, k, n)
+    want = torch.relu((acc + bias.float()) * scale + shift + res.float()).half()
+    assert_features_close(got, want)
+
+
+def _pairs_os(m, n):
+    t, c = np.nonzero(m[:n] >= 0)
+    return m[t, c], t, c
+
+
+def test_module_level_dataflows_agree(C, scene):
+    """SparseConv through the cache: dataflow 0, 1, 2 and force_os give the same features (weights permuted to
+    the order each map implies), stride-2 and transposed included."""
+    import spira_b200 as sp
+    from spira_b200 import nn as spnn
+    keys, _ = scene
+    n = len(keys)
+    f, _ = tensors(n, 32, 32, 27, 37)
+    x = sp.SparseTensor(keys_to_torch(keys), f.cuda())
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(spnn.SparseConv(32, 64, 3), spnn.SparseConv(64, 64, 3, stride=2), spnn.SparseConv(64, 32, 3, stride=2, transposed=True)).cuda().half()
+    outs = {}
+    for df, force_os in ((1, False), (2, False), (1, True), (5, False), (4, False)):
+        cache = spnn.KernelMapCache()
+        sp.set_kernel_map_cache(net, cache)
+        for layer in net:
+            layer._tunable_config["map_dataflow"], layer._tunable_config["force_os"] = df, force_os
+        with torch.no_grad():
+            outs[(df, force_os)] = net(x)._features
+    base = outs[(1, False)]
+    for k, v in outs.items():
+        assert_features_close(v, base)
+    C.check_status()

@@ -1,0 +1,85 @@
+"""GPU: whole networks through the public API -- network-wide map precompute, both dataflows, the selector."""
+import numpy as np
+import pytest
+import torch
+
+import spira_oracle as O
+from helpers import assert_features_close
+
+pytestmark = pytest.mark.gpu
+
+
+def run(model, cache, coords, feats, schedule, dataflow):
+    import spira_b200 as sp
+    x = sp.SparseTensor(coords.clone(), feats.clone()).order()
+    ks, ss, ts = schedule
+    cache.reset()
+    cache.add_all_kernel_maps(x._coordinates, ks, ss, ts, (1, 1, 1), [dataflow] * len(ks))
+    for m in model.modules():
+        if hasattr(m, "_tunable_config"):
+            m._tunable_config["map_dataflow"] = dataflow
+    with torch.no_grad():
+        return model(x), x
+
+
+@pytest.mark.parametrize("resample_kernel", [3, 2])
+def test_minkunet_dataflows_agree(lib, resample_kernel):
+    import spira_b200 as sp
+    from spira_b200 import models, scenes, nn as spnn
+    from spira_b200.nn.functional import _C
+    torch.manual_seed(0)
+    c = scenes.lidar_scene(3)[:60000]
+    coords = torch.from_numpy(c).cuda()
+    feats = torch.from_numpy(scenes.features(len(c), 4, 3)).cuda()
+    model = models.minkunet18(4, 19, resample_kernel).cuda().half().eval()
+    cache = spnn.KernelMapCache()
+    sp.set_kernel_map_cache(model, cache)
+    sched = models.map_schedule(4, 3, resample_kernel)
+    y0, x0 = run(model, cache, coords, feats, sched, 0)
+    assert y0._features.shape == (len(c), 19) and torch.isfinite(y0._features).all()
+    # dataflow 0 reads the kernel parameter in z-major order, dataflow 1 in natural order: permute once so that
+    # both runs use the same mathematical weights
+    nxy, kz = (resample_kernel ** 2, resample_kernel)
+    for m in model.modules():
+        if isinstance(m, spnn.SparseConv) and not m.is_trivial:
+            nxy, kz = m.kernel_size[0] * m.kernel_size[1], m.kernel_size[2]
+            K = nxy * kz
+            nat_of_col = torch.tensor([(col % nxy) * kz + col // nxy for col in range(K)], device="cuda")
+            w_nat = torch.empty_like(m.kernel.data)
+            w_nat[nat_of_col] = m.kernel.data
+            m.kernel.data = w_nat
+    y1, _ = run(model, cache, coords, feats, sched, 1)
+    scale = y0._features.float().abs().max().item()
+    assert (y0._features.float() - y1._features.float()).abs().max().item() <= 2e-2 * max(scale, 1.0)
+    _C.check_status()
+    # the first stem layer against the torch-CPU oracle
+    stem = model.stem[0][0]
+    keys = x0._coordinates.cpu().numpy().view(np.uint32)
+    dense = O.kernel_map(keys, keys, (3, 3, 3), (1, 1, 1), "ws")
+    want = O.conv_ws(x0._features.cpu(), stem.kernel.data.cpu(), dense, len(keys))
+    got = stem(x0)._features
+    assert_features_close(got, want)
+
+
+def test_selector_and_backbone(lib, tmp_path):
+    import spira_b200 as sp
+    from spira_b200 import models, scenes, nn as spnn
+    c = scenes.lidar_scene(4)[:50000]
+    model = models.second_backbone(5).cuda().half().eval()
+    cache = spnn.KernelMapCache()
+    sp.set_kernel_map_cache(model, cache)
+
+    def loader():
+        for s in range(3):
+            yield sp.SparseTensor(torch.from_numpy(c).cuda(), torch.from_numpy(scenes.features(len(c), 5, s)).cuda()).order()
+
+    model, chosen = sp.tune(model, loader(), cache, n_samples=2, save_dir=str(tmp_path), tune_tag="t", force_retune=True,
+                            return_dataflows=True, verify=True)
+    assert len(chosen) >= 4 and all(v in (0, 1) for v in chosen.values())
+    x = next(loader())
+    with torch.no_grad():
+        y = model(x)
+    assert torch.isfinite(y._features).all() and y._stride == (8, 8, 8)
+    # reload from the stored file
+    model2, chosen2 = sp.tune(model, loader(), cache, save_dir=str(tmp_path), tune_tag="t", return_dataflows=True)
+    assert chosen2 == chosen
