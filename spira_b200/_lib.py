@@ -92,5 +92,22 @@ def check(code: int) -> None:
         raise RuntimeError(f"[spira_b200] {msg} (code {code})")
 
 
+# kernels of this library launched per successful call (library kernels such as the radix sort are not counted)
+KERNELS_PER_CALL = {
+    "spira_b200_pack": 1, "spira_b200_unpack": 1, "spira_b200_flatten_sort": 1, "spira_b200_permute_rows": 1,
+    "spira_b200_downsample": 1, "spira_b200_kmap_search": 1, "spira_b200_kmap_ws_sizes": 2, "spira_b200_kmap_ws_pairs": 1,
+    "spira_b200_kmap_masks": 1, "spira_b200_convert_transposed_os": 1, "spira_b200_transpose_map": 1,
+    "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_ws": 2,
+}
+launch_count = 0          # kernels launched through `call` since import (or since it was last reset by the caller)
+profile_hook = None       # optional callable(name, args, run) -> None used by the benchmark to time single calls
+
+
 def call(name: str, *args) -> None:
-    check(getattr(load(), name)(*args))
+    global launch_count
+    fn = getattr(load(), name)
+    if profile_hook is not None:
+        profile_hook(name, args, lambda: check(fn(*args)))
+    else:
+        check(fn(*args))
+    launch_count += KERNELS_PER_CALL.get(name, 0)

@@ -82,7 +82,7 @@ class KernelMapCache(object):
             # output-stationary map of the transposed layer = inverse of the cached one.  The reference
             # rebuilds it on every forward (conv.py:85-89); it depends only on the cached map, so it is kept.
             dkey = (key, "inverted")
-            if dkey not in self._derived:
+            if dkey not in self._derived or not getattr(_C, "CACHE_DERIVED", True):
                 self._derived[dkey] = F.convert_transposed_os(entry[3], entry[1])
             new_entry = list(entry[1:])
             new_entry[2] = self._derived[dkey]

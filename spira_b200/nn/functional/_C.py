@@ -315,25 +315,28 @@ def cuda_convert_transposed_os(out_in_map: torch.Tensor, num_sources: int) -> to
 # ------------------------------------------------------------------------------------------------
 # feature compute
 # ------------------------------------------------------------------------------------------------
-_packed_cache = {}
-
-
 def packed_weights(weights: torch.Tensor, mode: int) -> Optional[torch.Tensor]:
-    """Tensor-core operand image of ``weights [K, c_in, c_out]`` (cached until the tensor changes)."""
+    """Tensor-core operand image of ``weights [K, c_in, c_out]``.
+
+    The image is kept ON the weight tensor object (so it lives exactly as long as the tensor and can never be
+    matched to a different tensor that happens to reuse the same address) and is rebuilt when the tensor's
+    version counter or storage changes."""
     K, cin, cout = weights.shape
     if weights.dtype != torch.float16 or not _lib.load().spira_b200_tensor_core_eligible(K, cin, cout):
         return None
-    key = (weights.data_ptr(), weights._version, tuple(weights.shape), mode, weights.device.index)
-    hit = _packed_cache.get(key)
-    if hit is not None:
-        return hit
-    if len(_packed_cache) > 512:
-        _packed_cache.clear()
+    stamp = (weights.data_ptr(), weights._version)
+    store = getattr(weights, "_sb_packed", None)
+    if store is None:
+        store = {}
+        weights._sb_packed = store
+    hit = store.get(mode)
+    if hit is not None and hit[0] == stamp:
+        return hit[1]
     need = C.c_size_t()
     _lib.call("spira_b200_packed_weight_bytes", K, cin, cout, mode, C.byref(need))
     packed = torch.empty(need.value, dtype=torch.uint8, device=weights.device)
     _lib.call("spira_b200_pack_weights", _ptr(weights), K, cin, cout, mode, _ptr(packed), _stream(weights.device))
-    _packed_cache[key] = packed
+    store[mode] = (stamp, packed)
     return packed
 
 
@@ -489,8 +492,8 @@ def cuda_time_scatter(tile_size, threshold, is_hybrid, weights, source_masks, ta
 
 def cuda_free_buffers() -> None:
     """The reference releases its private stack allocator here (csrc/spira/torch/cuda_memory_buffer.cu:7-16).  This
-    engine holds no pool of its own (scratch comes from torch's caching allocator); only the packed-weight cache is dropped."""
-    _packed_cache.clear()
+    engine holds no pool of its own: scratch comes from torch's caching allocator, so there is nothing to release."""
+    return None
 
 
 def cuda_reset_error() -> None:
