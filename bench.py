@@ -367,8 +367,14 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second"])
+    ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap"])
+    ap.add_argument("--gather", default="default", choices=["default", "tma", "cpasync"], help="row-gather engine of the tensor-core kernels")
+    ap.add_argument("--cin", type=int, default=64)
+    ap.add_argument("--cout", type=int, default=64)
+    ap.add_argument("--scene", default="c0", choices=["c0", "lidar"], help="layer workload: 50k-voxel plane/sphere scene or a LiDAR scene")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dataflow", default="auto", choices=["auto", "0", "1"], help="auto = per-group selector (tune); 0/1 = uniform")
+    ap.add_argument("--dump-layers", default=None, help="write the per-layer timing table of the profiled step to this JSON file")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -383,9 +389,25 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=device)
     n_gpus = world
 
+    pk, pk_kind = peaks()
+    if args.impl == "ours" and args.gather != "default":
+        from spira_b200 import build
+        build.build()
+        from spira_b200.nn.functional import _C as native
+        native.set_option("gather_tma", 1 if args.gather == "tma" else 0)
+    if args.workload in ("layer", "kmap"):
+        from spira_b200 import build, _lib
+        build.build()
+        _lib.load()
+        line = run_layer(args, device, pk, pk_kind) if args.workload == "layer" else run_kmap(args, device, pk, pk_kind)
+        line["n_gpus"] = n_gpus
+        if rank == 0:
+            print(json.dumps(line))
+        if dist_ctx:
+            torch.distributed.destroy_process_group()
+        return
     wl = make_workload(args.workload)
     from spira_b200 import scenes as sc
-    pk, pk_kind = peaks()
 
     ref_mod = None
     if args.impl == "reference":
@@ -415,7 +437,10 @@ def main():
 
     engine = Engine(wl, device)
     chosen_note = None
-    if args.impl == "ours":
+    if args.impl == "ours" and args.dataflow != "auto":
+        engine.set_uniform_dataflow(int(args.dataflow))
+        chosen_note = {"uniform_map_dataflow": int(args.dataflow)}
+    elif args.impl == "ours":
         import spira_b200 as sp
 
         def loader():
@@ -507,6 +532,9 @@ def main():
         # roofline of the dominant kernel class + secondary metrics, measured live with CUDA events
         per_call, layers = profile_kernels(engine, dev[0])
         line["roofline"] = roofline_from_layers(layers, pk, pk_kind)
+        if args.dump_layers and rank == 0:
+            Path(args.dump_layers).parent.mkdir(parents=True, exist_ok=True)
+            Path(args.dump_layers).write_text(json.dumps([{k: (list(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in layers], indent=0))
         km = per_call.get("spira_b200_kmap_search")
         if km:
             maps_bytes = 0
@@ -527,6 +555,127 @@ def main():
         print(json.dumps(line))
     if dist_ctx:
         torch.distributed.destroy_process_group()
+
+
+def _time_calls(fn, steps, warmup, l2buf):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(steps):
+        flush_l2(l2buf)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    t = [a.elapsed_time(b) for a, b in evs]
+    return sum(t) / len(t), min(t)
+
+
+def run_layer(args, device, pk, pk_kind):
+    """BASELINE.json configs[0]: one submanifold 3^3 layer, c_in -> c_out, 50,000 voxels in a 512^3 grid (64-bit keys)."""
+    from spira_b200 import scenes as sc
+    from spira_b200.nn.functional import _C
+    if args.scene == "c0":
+        c, double = sc.planes_and_spheres(0), True
+    else:
+        c, double = sc.lidar_scene(1), False
+    n = len(c)
+    keys, perm = _C.cuda_flatten_sort(torch.from_numpy(c).to(device), double)
+    feats = torch.from_numpy(sc.features(n, args.cin, 0)).to(device)
+    rng = np.random.default_rng(0)
+    w = torch.from_numpy((rng.normal(size=(27, args.cin, args.cout)) / np.sqrt(27 * args.cin)).astype(np.float16)).to(device)
+    df = 1 if args.dataflow == "1" else 0
+    m = _C.cuda_binary_search(keys, keys, (3, 3, 3), (1, 1, 1), df)
+    nnz = int(m[2]._sb["counts"].sum().item())
+    l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+    if df == 0:
+        fn = lambda: _C.conv_os(n, n, m[2], feats, w)
+    else:
+        fn = lambda: _C.conv_ws(n, n, feats, w, m[3]._sb["ws"])
+    mean_ms, min_ms = _time_calls(fn, args.steps, args.warmup, l2buf)
+    _C.check_status()
+    map_ms, _ = _time_calls(lambda: _C.cuda_binary_search(keys, keys, (3, 3, 3), (1, 1, 1), df), args.steps, args.warmup, l2buf)
+    flops = 2.0 * nnz * args.cin * args.cout
+    byts = n * args.cin * 2 + 27 * args.cin * args.cout * 2 + n * args.cout * 2 + (27 * n * 4 if df == 0 else nnz * 8)
+    t_tensor, t_hbm = flops / (pk["bf16_tflops"] * 1e12), byts / (pk["hbm_gbs"] * 1e9)
+    if t_hbm >= t_tensor:
+        ach = byts / (mean_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(ach / pk["hbm_gbs"], 4), "traffic": None}
+    else:
+        ach = flops / (mean_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": round(ach, 2), "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": round(ach / pk["bf16_tflops"], 4), "traffic": None}
+    roof.update(kernel="conv_tc_kernel<%s>" % ("WS" if df else "OS"), peak_source=f"of {pk_kind}", algorithmic_bytes=int(byts), algorithmic_flops=int(flops))
+    return {"metric": "SpC layer TFLOP/s (FLOPs = 2*nnz*c_in*c_out)", "value": round(flops / (mean_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s",
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(mean_ms, 5), "min_ms": round(min_ms, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"single submanifold 3^3 layer {args.cin}->{args.cout}, {n} voxels ({args.scene}), dataflow {'WS' if df else 'OS'}",
+                       "nnz": nnz, "nnz_per_voxel": round(nnz / n, 2), "l2": "256 MiB buffer rewritten between timed steps"},
+            "kernel_map_build_ms": round(map_ms, 5), "roofline": roof, "gpu_launches": args.steps * (2 if df else 1)}
+
+
+def run_kmap(args, device, pk, pk_kind):
+    """BASELINE.json configs[1]: kernel maps only, 4 LiDAR-like scenes: 3^3, 5^3, stride-2 down-sampling + transposed reuse."""
+    from spira_b200 import scenes as sc
+    from spira_b200.nn.functional import _C
+    scenes_k = []
+    for seed in (1, 2, 3, 4):
+        keys, _ = _C.cuda_flatten_sort(torch.from_numpy(sc.lidar_scene(seed)).to(device), False)
+        scenes_k.append((keys, _C.cuda_downsample(keys, 2, 2, 2)))
+    l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+    out = {}
+    byts_all = 0
+
+    def search_only(keys, tgt, ks, layout):
+        return _C.cuda_binary_search(keys, tgt, ks, (1, 1, 1), layout)
+
+    for name, ks, strided, df in (("3x3x3_os", (3, 3, 3), False, 0), ("3x3x3_ws", (3, 3, 3), False, 1), ("5x5x5_os", (5, 5, 5), False, 0),
+                                  ("down_3x3x3_os", (3, 3, 3), True, 0), ("down_3x3x3_ws", (3, 3, 3), True, 1)):
+        def fn():
+            for keys, down in scenes_k:
+                search_only(keys, down if strided else keys, ks, df)
+        mean_ms, min_ms = _time_calls(fn, args.steps, args.warmup, l2buf)
+        K = ks[0] * ks[1] * ks[2]
+        byts = sum((k.numel() + (d.numel() if strided else k.numel())) * 4 + K * ((((d.numel() if strided else k.numel()) + 127) // 128) * 128) * 4
+                   for k, d in scenes_k)
+        out[name] = {"ms_per_scene": round(mean_ms / 4, 5), "min_ms_per_scene": round(min_ms / 4, 5), "algorithmic_bytes_per_scene": byts // 4,
+                     "gbs": round(byts / (mean_ms * 1e-3) / 1e9, 1)}
+    # the whole config per scene: 3^3 + 5^3 submanifold, 3^3 stride-2 map, inverse for the transposed layer
+    def all_maps():
+        for keys, down in scenes_k:
+            maps = _C.cuda_binary_search_streamed([keys, down], [(3, 3, 3), (3, 3, 3)], [(1, 1, 1), (1, 1, 1)], [0, 0])
+            _C.cuda_binary_search(keys, keys, (5, 5, 5), (1, 1, 1), 0)
+            _C.cuda_convert_transposed_os(maps[1][2], keys.numel())
+    mean_ms, min_ms = _time_calls(all_maps, args.steps, args.warmup, l2buf)
+    # roofline of the search kernel alone on the 5^3 map of scene 0 (the largest single launch)
+    from spira_b200 import _lib
+    keys = scenes_k[0][0]
+    n = keys.numel()
+    Tal = (n + 127) // 128 * 128
+    dense = torch.empty((Tal, 125), dtype=torch.int32, device=device)
+    import ctypes as C
+    d = (_lib.KmapDesc * 1)()
+    d[0].sources = d[0].targets = keys.data_ptr()
+    d[0].num_sources = d[0].num_targets = n
+    d[0].kernel_size[:] = (5, 5, 5)
+    d[0].source_stride[:] = (1, 1, 1)
+    d[0].layout = 0
+    d[0].map = dense.data_ptr()
+    d[0].tile_counts = None
+    stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    k_ms, k_min = _time_calls(lambda: _lib.call("spira_b200_kmap_search", d, 1, 4, stream), max(args.steps, 10), args.warmup, l2buf)
+    byts5 = 2 * n * 4 + 125 * Tal * 4
+    ach = byts5 / (k_ms * 1e-3) / 1e9
+    return {"metric": "kernel-map build (3^3 + 5^3 + stride-2 + transposed inverse)", "value": round(4 / (mean_ms * 1e-3), 2), "unit": "scenes/s",
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(mean_ms, 5), "ms_per_scene": round(mean_ms / 4, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+            "config": {"workload": "kernel maps only, 4 LiDAR-like scenes ~125k voxels each", "voxels": [k.numel() for k, _ in scenes_k],
+                       "l2": "256 MiB buffer rewritten between timed steps"},
+            "maps": out,
+            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(ach / pk["hbm_gbs"], 4),
+                         "traffic": None, "kernel": "kmap_search_kernel<u32>, 5^3 map of scene 0", "peak_source": f"of {pk_kind}",
+                         "algorithmic_bytes": byts5, "kernel_ms": round(k_ms, 5), "kernel_min_ms": round(k_min, 5)},
+            "gpu_launches": args.steps * 4 * 4}
 
 
 def run_reference_port(args, wl, n_gpus):

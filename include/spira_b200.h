@@ -43,6 +43,13 @@ const char *spira_b200_last_error(void);
  * cuda_reset_error (csrc/spira/torch/cuda_memory_buffer.cu:15-16). */
 int spira_b200_reset_error(void);
 
+/* Run-time options of the calling process (not thread safe; set them before launching work):
+ *   "gather_tma"        1: the tensor-core kernels fetch feature rows with TMA gather4, 0: with 16-byte cp.async
+ * get_option additionally answers "os_pack_mode": the SPIRA_B200_PACK_* image spira_b200_conv_os expects under
+ * the current options.  Unknown names: set_option fails, get_option returns -1. */
+int spira_b200_set_option(const char *name, int value);
+int spira_b200_get_option(const char *name);
+
 /* ---- packed keys ------------------------------------------------------------------------- */
 
 /* coords[n][3] int32 -> keys[n]; replaces the Compress kernel (csrc/spira/cuda/kernels/compress.cuh:8-24). */

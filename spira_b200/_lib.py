@@ -38,6 +38,8 @@ MAX_MAPS, MAX_LEVELS = 16, 8
 SIGNATURES = {
     "spira_b200_version": [],
     "spira_b200_reset_error": [],
+    "spira_b200_set_option": [C.c_char_p, c_int],
+    "spira_b200_get_option": [C.c_char_p],
     "spira_b200_pack": [c_void_p, c_int64, c_int, c_void_p, c_void_p],
     "spira_b200_unpack": [c_void_p, c_int64, c_int, c_void_p, c_void_p],
     "spira_b200_flatten_sort_workspace": [c_int64, c_int, C.POINTER(c_size_t)],

@@ -10,13 +10,14 @@
 //     row is a real pair.  The 128 x c_out product is added into an fp32 scratch with vector
 //     reductions; a second small kernel applies the epilogue and rounds to fp16.
 //
-// Roles inside a CTA (288 threads, one CTA per SM):
-//   warps 0-3  producers: gather feature rows with 16-byte cp.async (zero-fill for missing rows)
-//              into a 128-byte-swizzled K-major A tile; one thread bulk-copies the matching
-//              pre-packed weight chunk (already an MMA-ready image) and posts its byte count;
-//   warp  8    one elected thread issues tcgen05.mma (M=128, N=c_out, K=16) into one of two
+// Roles inside a CTA (416 threads, one CTA per SM):
+//   warps 0-7  producers: gather feature rows with 16-byte cp.async (zero-fill for missing rows)
+//              into a 128-byte-swizzled K-major A tile and let the copies arrive on the stage's
+//              mbarrier asynchronously (no thread waits for its own data); one thread bulk-copies
+//              the matching pre-packed weight chunk (already an MMA-ready image) and posts its bytes;
+//   warp  12   one elected thread issues tcgen05.mma (M=128, N=c_out, K=16) into one of two
 //              TMEM accumulator buffers and commits stage / accumulator barriers;
-//   warps 4-7  epilogue: tcgen05.ld the finished accumulator (one row per thread), apply the
+//   warps 8-11 epilogue: tcgen05.ld the finished accumulator (one row per thread), apply the
 //              fused epilogue, store fp16 rows (OS) or issue fp32 vector reductions (WS) while the
 //              next tile is already being multiplied.
 // All mbarrier waits are bounded; on expiry the kernel raises a status word and drains.
@@ -24,6 +25,10 @@
 // Channel counts the tensor-core path cannot tile (c_in % 8 != 0, c_out % 16 != 0, c_out > 256)
 // run on simple SIMT kernels (conv_os_simt_kernel / conv_ws_simt_kernel) -- those layers
 // (3-5 input channels) are bandwidth-bound and tiny.
+#include <cuda.h>
+
+#include <cstring>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -34,8 +39,11 @@ using namespace sb::ptx;
 constexpr int kRows = 128;              // MMA M / rows per tile
 constexpr int kChunk = 64;              // fp16 elements of the reduction per pipeline stage (128 bytes)
 constexpr int kABytes = kRows * 128;    // one A stage
-constexpr int kProducers = 128;
-constexpr int kConvThreads = 288;
+constexpr int kProducers = 256;          // cp.async producers: 2 threads per tile row, 4 x 16 bytes each per stage
+constexpr int kProducerWarps = kProducers / 32;
+constexpr int kMmaWarp = kProducerWarps + 4;         // warps kProducerWarps .. +3 are the epilogue (warp % 4 = TMEM lane quarter)
+static_assert(kProducerWarps % 4 == 0, "epilogue warps must start at a multiple of 4");
+constexpr int kConvThreads = (kMmaWarp + 1) * 32;
 constexpr int kMaxStages = 6;
 constexpr int kSmemBudget = 220 * 1024;
 constexpr int kScatterRing = 16;        // WS: scatter-row lists kept for tiles in flight (>= stages + 2)
@@ -72,8 +80,11 @@ __device__ __forceinline__ float epilogue_apply(float v, int c, const Epilogue &
   return v;
 }
 
-template <bool kWS>
-__global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_constant__ ConvParams P) {
+// kTma: the producers are ONE warp whose lanes each issue a TMA gather4 (4 feature rows x 128 bytes, zero fill for
+// row index -1) per pipeline stage; otherwise 128 threads gather with 16-byte cp.async.
+template <bool kWS, bool kTma>
+__global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_constant__ ConvParams P,
+                                                                   const __grid_constant__ CUtensorMap tmap_feats) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char *smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
@@ -96,7 +107,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(bar_full(s), kProducers + 1);
+      mbar_init(bar_full(s), kTma ? 1 : kProducers + 1);
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -106,7 +117,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     *abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(tmem_slot), P.tmem_cols);
     tmem_relinquish();
   }
@@ -115,11 +126,122 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 4) {
-    // =========================== producers ===========================
-    const int piece = tid & 7, row0 = tid >> 3;
-    const int lag = stages - 1;
-    int stage = 0, phase = 0, arr_stage = 0, unarrived = 0, groups_since_prefetch = 0;
+  if (kTma && warp < kProducerWarps) {
+    // =========================== producer (TMA gather4): warp 0 only ===========================
+    if (warp == 0) {
+      const uint64_t tmap = reinterpret_cast<uint64_t>(&tmap_feats);
+      const int cpo = P.n_chunks;  // 64-wide chunks per offset
+      int stage = 0, phase = 0;
+      bool ok = true;
+      int tile_i = 0;
+      const int slab_int4 = (kRows / 4) * P.K;
+      if constexpr (!kWS) {
+        if (static_cast<int>(blockIdx.x) < P.n_tiles) {
+          const int4 *s4 = reinterpret_cast<const int4 *>(P.map + static_cast<int64_t>(blockIdx.x) * kRows * P.K);
+          for (int i = lane; i < slab_int4; i += 32) cp_async_16(sbase + P.off_slab + i * 16, s4 + i, 16u);
+        }
+        cp_async_commit();
+      }
+      for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+        int idx[4] = {-1, -1, -1, -1};
+        int w_row = 0, n_offsets = 1;
+        uint32_t kmask[16];
+        const int32_t *my_slab = slab;
+        if constexpr (kWS) {
+          int tt = tile;
+          const bool mirrored = tt >= P.n_tiles_plain;
+          if (mirrored) tt -= P.n_tiles_plain;
+          const int q0 = tt * kRows;
+          int k = 0;
+          while (k + 1 < P.rows && P.qnaddrs[k + 1] <= q0) ++k;
+          const int p0 = P.naddrs[k] + (q0 - P.qnaddrs[k]);
+          const int n = min(kRows, P.naddrs[k + 1] - p0);
+          w_row = mirrored ? (P.K - 1 - k) : k;
+          const int32_t *g = mirrored ? P.out_idx : P.in_idx;
+          const int32_t *sc = mirrored ? P.in_idx : P.out_idx;
+          int32_t *scatter = slab + kRows + (tile_i & (kScatterRing - 1)) * kRows;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int m = 4 * lane + r;
+            idx[r] = m < n ? g[p0 + m] : -1;
+            scatter[m] = m < n ? sc[p0 + m] : -1;
+          }
+        } else {
+          const int buf = (P.slab_bufs == 2) ? (tile_i & 1) : 0;
+          my_slab = slab + buf * kRows * P.K;
+          if (P.slab_bufs == 1 && tile_i > 0) {
+            __syncwarp();
+            const int4 *s4 = reinterpret_cast<const int4 *>(P.map + static_cast<int64_t>(tile) * kRows * P.K);
+            for (int i = lane; i < slab_int4; i += 32) cp_async_16(sbase + P.off_slab + i * 16, s4 + i, 16u);
+            cp_async_commit();
+          }
+          cp_async_wait<0>();
+          __syncwarp();
+          if (P.slab_bufs == 2) {
+            const int next = tile + gridDim.x;
+            if (next < P.n_tiles) {
+              const int4 *n4 = reinterpret_cast<const int4 *>(P.map + static_cast<int64_t>(next) * kRows * P.K);
+              const uint32_t dst = sbase + P.off_slab + (buf ^ 1) * kRows * P.K * 4;
+              for (int i = lane; i < slab_int4; i += 32) cp_async_16(dst + i * 16, n4 + i, 16u);
+            }
+            cp_async_commit();
+          }
+          // offsets with at least one neighbour in this tile
+#pragma unroll
+          for (int w = 0; w < 16; ++w) kmask[w] = 0;
+          n_offsets = 0;
+          for (int k = 0; k < P.K; ++k) {
+            int v = -1;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) v = max(v, my_slab[(4 * lane + r) * P.K + k]);
+            if (__ballot_sync(0xffffffffu, v >= 0)) {
+              kmask[k >> 5] |= 1u << (k & 31);
+              ++n_offsets;
+            }
+          }
+          if (n_offsets == 0) { kmask[0] = 1u; n_offsets = 1; }   // a tile always sends at least one offset
+        }
+        const int total = n_offsets * cpo;
+        int sent = 0;
+        for (int kw = 0; ok && kw < (kWS ? 1 : ((P.K + 31) >> 5)); ++kw) {
+          uint32_t bits = kWS ? 1u : kmask[kw];
+          while (ok && bits) {
+            const int k = (kw << 5) + __ffs(bits) - 1;
+            bits &= bits - 1;
+            if constexpr (!kWS) {
+              w_row = k;
+#pragma unroll
+              for (int r = 0; r < 4; ++r) idx[r] = my_slab[(4 * lane + r) * P.K + k];
+            }
+            for (int jj = 0; jj < cpo; ++jj) {
+              ++sent;
+              if (!mbar_wait(bar_empty(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+              if (lane == 0) {
+                const int valid = min(kChunk, P.c_in - jj * kChunk);
+                meta[stage] = ((valid + 15) >> 4) | ((sent == 1) << 8) | ((sent == total) << 9);
+                mbar_arrive_expect_tx(bar_full(stage), kABytes + P.b_bytes);
+                bulk_g2s(sbase + P.off_b + stage * P.b_bytes,
+                         P.packed + static_cast<int64_t>(w_row * cpo + jj) * P.b_bytes, P.b_bytes, bar_full(stage));
+              }
+              __syncwarp();
+              tma_gather4(sbase + stage * kABytes + lane * 512, tmap, jj * kChunk, idx[0], idx[1], idx[2], idx[3],
+                          bar_full(stage));
+              if (++stage == stages) { stage = 0; phase ^= 1; }
+            }
+          }
+        }
+      }
+      cp_async_wait<0>();
+    }
+  } else if (warp < kProducerWarps) {
+    // =========================== producers (cp.async) ===========================
+    const int row = tid >> 1, half = tid & 1;
+    uint32_t dst_off[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) dst_off[p] = row * 128 + (((half * 4 + p) ^ (row & 7)) << 4);
+    const bool whole_half = (P.c_in & 31) == 0;   // a 32-channel half row never straddles two offsets
+    const float inv_c_in = 1.0f / static_cast<float>(P.c_in);
+    int stage = 0, phase = 0, groups_since_prefetch = 0;
     bool ok = true;
     int tile_i = 0;
     for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
@@ -144,8 +266,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         named_bar_sync(1, kProducers);  // previous tile's gathers have read the row list
         const int32_t *g = mirrored ? P.out_idx : P.in_idx;
         const int32_t *s = mirrored ? P.in_idx : P.out_idx;
-        my_slab[tid] = tid < n ? g[p0 + tid] : -1;
-        scatter[tid] = tid < n ? s[p0 + tid] : -1;
+        if (tid < kRows) {
+          my_slab[tid] = tid < n ? g[p0 + tid] : -1;
+          scatter[tid] = tid < n ? s[p0 + tid] : -1;
+        }
         named_bar_sync(1, kProducers);
         n_chunks_tile = P.n_chunks;
       } else {
@@ -160,7 +284,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         }
         named_bar_sync(1, kProducers);
         // which offsets have at least one neighbour in this tile
-        for (int k = warp; k < P.K; k += 4) {
+        for (int k = warp; k < P.K; k += kProducerWarps) {
           bool any = false;
 #pragma unroll
           for (int j = 0; j < 4; ++j) any |= my_slab[(lane + 32 * j) * P.K + k] >= 0;
@@ -206,27 +330,45 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           }
           ++sent;
           if (!mbar_wait(bar_empty(stage), phase ^ 1, abort_flag)) { ok = false; break; }
-          // ---- A: 128 rows x 8 pieces of 16 bytes, this thread owns piece `piece` of 8 rows
+          // ---- A: this thread owns half a row (4 pieces of 16 bytes = 32 channels) of the 128 x 64 tile
           const uint32_t a_stage = sbase + stage * kABytes;
-          int k, c;
-          bool piece_valid;
-          if constexpr (kWS) {
-            c = j * kChunk + piece * 8;
-            k = 0;
-            piece_valid = c < P.c_in;
-          } else {
-            const int r = j * kChunk + piece * 8;
-            k = r / P.c_in;
-            c = r - k * P.c_in;
-            piece_valid = r < P.R;
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = row0 + 16 * i;
+          if (whole_half) {
+            int k = 0, c;
+            bool valid;
+            if constexpr (kWS) {
+              c = j * kChunk + half * 32;
+              valid = c < P.c_in;
+            } else {
+              const int r = j * kChunk + half * 32;
+              k = __float2int_rd((static_cast<float>(r) + 0.5f) * inv_c_in);
+              c = r - k * P.c_in;
+              valid = r < P.R;
+            }
             int idx = -1;
-            if (piece_valid) idx = kWS ? my_slab[m] : my_slab[m * P.K + k];
+            if (valid) idx = kWS ? my_slab[row] : my_slab[row * P.K + k];
             const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
-            cp_async_16(a_stage + m * 128 + ((piece ^ (m & 7)) << 4), src, idx >= 0 ? 16u : 0u);
+            const uint32_t bytes = idx >= 0 ? 16u : 0u;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) cp_async_16(a_stage + dst_off[p], idx >= 0 ? src + 8 * p : src, bytes);
+          } else {
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              int k = 0, c;
+              bool valid;
+              if constexpr (kWS) {
+                c = j * kChunk + (half * 4 + p) * 8;
+                valid = c < P.c_in;
+              } else {
+                const int r = j * kChunk + (half * 4 + p) * 8;
+                k = __float2int_rd((static_cast<float>(r) + 0.5f) * inv_c_in);
+                c = r - k * P.c_in;
+                valid = r < P.R;
+              }
+              int idx = -1;
+              if (valid) idx = kWS ? my_slab[row] : my_slab[row * P.K + k];
+              const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
+              cp_async_16(a_stage + dst_off[p], src, idx >= 0 ? 16u : 0u);
+            }
           }
           if (tid == 0) {
             // ---- B: one bulk copy of the pre-packed chunk; meta word for the MMA thread
@@ -252,28 +394,17 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
               ++groups_since_prefetch;
             }
           }
+          // this thread's share of the stage is complete when its copies land: asynchronous arrival, the
+          // thread itself never waits for data (the commit group only tracks the slab prefetch)
+          cp_async_mbar_arrive_noinc(bar_full(stage));
           cp_async_commit();
-          ++unarrived;
-          if (unarrived > lag) {
-            cp_async_wait_dyn(lag);
-            fence_proxy_async();
-            mbar_arrive(bar_full(arr_stage));
-            arr_stage = (arr_stage + 1 == stages) ? 0 : arr_stage + 1;
-            --unarrived;
-          }
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
       }
     }
-    // drain: everything issued has landed, then post the outstanding arrivals
+    // nothing of this thread may still be in flight when the CTA tears down
     cp_async_wait<0>();
-    fence_proxy_async();
-    while (unarrived > 0) {
-      mbar_arrive(bar_full(arr_stage));
-      arr_stage = (arr_stage + 1 == stages) ? 0 : arr_stage + 1;
-      --unarrived;
-    }
-  } else if (warp == 8) {
+  } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
       const uint32_t idesc = idesc_f16_m128(P.c_out);
@@ -294,11 +425,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           const int m = meta[stage];
           const int nk = m & 0xff;
           const bool first = (m >> 8) & 1, last = (m >> 9) & 1;
-          const uint32_t a_addr = sbase + stage * kABytes;
-          const uint32_t b_addr = sbase + P.off_b + stage * P.b_bytes;
+          // descriptors of the first 16-wide K step; each further step is 32 bytes (2 units of 16 bytes) on
+          const uint64_t a_desc = smem_desc_k_sw128(sbase + stage * kABytes);
+          const uint64_t b_desc = smem_desc_k_sw128(sbase + P.off_b + stage * P.b_bytes);
           for (int ks = 0; ks < nk; ++ks)
-            mma_f16_ss(d_tmem, smem_desc_k_sw128(a_addr + ks * 32), smem_desc_k_sw128(b_addr + ks * 32), idesc,
-                       (first && ks == 0) ? 0u : 1u);
+            mma_f16_ss(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (first && ks == 0) ? 0u : 1u);
           mma_commit(bar_empty(stage));
           if (++stage == stages) { stage = 0; phase ^= 1; }
           if (last) {
@@ -390,7 +521,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     while (global_timer_ns() - t0 < 200000ull) { }
     __syncthreads();
   }
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, P.tmem_cols);
   }
@@ -511,6 +642,58 @@ static Epilogue make_epilogue(const spira_b200_epilogue *e) {
 
 static int round16(int x) { return (x + 15) / 16 * 16; }
 
+// ---- run-time options -----------------------------------------------------------------------------
+static int g_gather_tma = 0;      // 1: producers use TMA gather4, 0: cp.async
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D map over feats[num_rows][c_in] (fp16), box = 64 channels x 1 row, 128-byte swizzle, zero fill out of bounds.
+static int make_feats_tensor_map(CUtensorMap *map, const void *feats, int64_t num_rows, int c_in) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return fail(SPIRA_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(c_in), static_cast<cuuint64_t>(num_rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(c_in) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kChunk), 1};   // gather4 takes ONE row per index (a 4-row box is rejected by the hardware)
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(feats), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SPIRA_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return SPIRA_B200_OK;
+}
+
+template <bool kWS>
+static int launch_conv_tc(ConvParams &P, bool tma, size_t smem, int64_t num_sources, cudaStream_t st) {
+  alignas(64) CUtensorMap tmap;
+  std::memset(&tmap, 0, sizeof(tmap));
+  int grid = P.n_tiles < sm_count() ? P.n_tiles : sm_count();
+  if (grid <= 0) return SPIRA_B200_OK;
+  if (tma) {
+    int rc = make_feats_tensor_map(&tmap, P.feats, num_sources, P.c_in);
+    if (rc != SPIRA_B200_OK) return rc;
+    SB_CHECK_CUDA(cudaFuncSetAttribute(conv_tc_kernel<kWS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    conv_tc_kernel<kWS, true><<<grid, kConvThreads, smem, st>>>(P, tmap);
+  } else {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(conv_tc_kernel<kWS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    conv_tc_kernel<kWS, false><<<grid, kConvThreads, smem, st>>>(P, tmap);
+  }
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
 // Fills the shared-memory plan of ConvParams; returns the dynamic shared memory size or 0 if it does not fit.
 static size_t plan_smem(ConvParams &P, bool ws) {
   P.b_bytes = P.c_out * 128;
@@ -604,15 +787,13 @@ extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const 
   P.T = static_cast<int>(num_targets);
   P.n_tiles = static_cast<int>(align128(num_targets) / kRows);
   P.K = K; P.c_in = c_in; P.c_out = c_out;
+  const bool tma = g_gather_tma != 0 && num_sources > 0 && K <= 512;
   P.R = K * c_in;
-  P.n_chunks = static_cast<int>(div_up(P.R, kChunk));
+  // TMA gather: every offset owns ceil(c_in/64) chunks (PACK_WS image); cp.async: 64-wide chunks over the whole reduction
+  P.n_chunks = tma ? static_cast<int>(div_up(c_in, kChunk)) : static_cast<int>(div_up(P.R, kChunk));
   size_t smem = plan_smem(P, false);
   if (smem == 0) return fail(SPIRA_B200_ERR_UNSUPPORTED, "conv_os: K=%d c_out=%d does not fit the shared-memory plan", K, c_out);
-  SB_CHECK_CUDA(cudaFuncSetAttribute(conv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  int grid = P.n_tiles < sm_count() ? P.n_tiles : sm_count();
-  conv_tc_kernel<false><<<grid, kConvThreads, smem, as_stream(stream)>>>(P);
-  SB_CHECK_LAUNCH();
-  return SPIRA_B200_OK;
+  return launch_conv_tc<false>(P, tma, smem, num_sources, as_stream(stream));
 }
 
 extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const void *packed,
@@ -666,15 +847,24 @@ extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const 
       P.n_chunks = static_cast<int>(div_up(c_in, kChunk));
       size_t smem = plan_smem(P, true);
       if (smem == 0) return fail(SPIRA_B200_ERR_UNSUPPORTED, "conv_ws: c_out=%d does not fit the shared-memory plan", c_out);
-      SB_CHECK_CUDA(cudaFuncSetAttribute(conv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      int grid = P.n_tiles < sm_count() ? P.n_tiles : sm_count();
-      if (grid > 0) {
-        conv_tc_kernel<true><<<grid, kConvThreads, smem, st>>>(P);
-        SB_CHECK_LAUNCH();
-      }
+      int rc = launch_conv_tc<true>(P, g_gather_tma != 0 && num_sources > 0, smem, num_sources, st);
+      if (rc != SPIRA_B200_OK) return rc;
     }
   }
   finalize_kernel<<<static_cast<unsigned>(div_up(n_out, 256)), 256, 0, st>>>(accum, ep, n_out, c_out, static_cast<__half *>(out));
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_set_option(const char *name, int value) {
+  SB_CHECK_ARG(name != nullptr, "set_option: null name");
+  if (std::strcmp(name, "gather_tma") == 0) { g_gather_tma = value ? 1 : 0; return SPIRA_B200_OK; }
+  return fail(SPIRA_B200_ERR_ARGUMENT, "set_option: unknown option '%s'", name);
+}
+
+extern "C" int spira_b200_get_option(const char *name) {
+  if (name == nullptr) return -1;
+  if (std::strcmp(name, "gather_tma") == 0) return g_gather_tma;
+  if (std::strcmp(name, "os_pack_mode") == 0) return g_gather_tma ? SPIRA_B200_PACK_WS : SPIRA_B200_PACK_OS;
+  return -1;
 }

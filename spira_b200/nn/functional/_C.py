@@ -376,7 +376,7 @@ def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None
     if out_in_map.dim() != 2 or out_in_map.shape[1] != K or out_in_map.shape[0] < num_targets:
         raise RuntimeError(f"[spira_b200] out_in_map must be [T_al, {K}] with T_al >= {num_targets}, got {tuple(out_in_map.shape)}")
     out = torch.empty((num_targets, cout), dtype=torch.float16, device=sources.device)
-    packed = None if force_simt else packed_weights(weights, PACK_OS)
+    packed = None if force_simt else packed_weights(weights, _lib.load().spira_b200_get_option(b"os_pack_mode"))
     if packed is not None and out_in_map.shape[0] != _aligned(num_targets):
         packed = None
     ep, keep = _epilogue(bias, scale, shift, residual, relu)
@@ -488,6 +488,15 @@ def cuda_time_gather(tile_size, threshold, is_hybrid, weights, source_masks, tar
 def cuda_time_scatter(tile_size, threshold, is_hybrid, weights, source_masks, target_masks, kernel_map_sizes) -> float:
     """See :func:`cuda_time_gemm`."""
     return _time_ws(weights, source_masks, target_masks)
+
+
+def set_option(name: str, value: int) -> None:
+    """Process-wide kernel options, e.g. ``set_option("gather_tma", 1)`` (see include/spira_b200.h)."""
+    _lib.call("spira_b200_set_option", name.encode(), int(value))
+
+
+def get_option(name: str) -> int:
+    return int(_lib.load().spira_b200_get_option(name.encode()))
 
 
 def cuda_free_buffers() -> None:
