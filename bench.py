@@ -234,11 +234,8 @@ def timed_loop(step_fn, n_steps, warmup, l2buf, dist_ctx):
     wall = time.perf_counter() - wall0
     if dist_ctx:
         torch.distributed.barrier()
-    total_ms = sum(a.elapsed_time(b) for a, b in evs)
-    if dist_ctx:
-        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        total_ms = float(t.item())
+    from spira_b200 import sharding
+    total_ms = sharding.max_over_ranks(sum(a.elapsed_time(b) for a, b in evs), torch.device("cuda"))
     return total_ms, wall
 
 
@@ -374,6 +371,7 @@ def main():
     ap.add_argument("--scene", default="c0", choices=["c0", "lidar"], help="layer workload: 50k-voxel plane/sphere scene or a LiDAR scene")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dataflow", default="auto", choices=["auto", "0", "1"], help="auto = per-group selector (tune); 0/1 = uniform")
+    ap.add_argument("--no-fuse", action="store_true", help="keep BatchNorm / ReLU / residual adds as separate passes (ours arm)")
     ap.add_argument("--dump-layers", default=None, help="write the per-layer timing table of the profiled step to this JSON file")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -436,6 +434,9 @@ def main():
     n_vox = [len(h[0]) for h in host]
 
     engine = Engine(wl, device)
+    if args.impl == "ours" and not args.no_fuse:
+        import spira_b200 as sp_
+        sp_.fuse(engine.model)
     chosen_note = None
     if args.impl == "ours" and args.dataflow != "auto":
         engine.set_uniform_dataflow(int(args.dataflow))
@@ -518,7 +519,8 @@ def main():
         "dtype": "f16 (fp32 accumulate); u32 packed keys", "data": "synthetic",
         "config": {"workload": wl["label"], "voxels_per_scene": n_vox, "scenes_per_rank": len(dev),
                    "timed_region": "order() + add_all_kernel_maps() + model forward, per scene",
-                   "l2": "256 MiB buffer rewritten between timed steps", "dataflows": chosen_note, "sharding": "independent scenes per GPU, no collective"},
+                   "l2": "256 MiB buffer rewritten between timed steps", "dataflows": chosen_note, "sharding": "independent scenes per GPU, no collective",
+                   "fused_epilogue": bool(args.impl == "ours" and not args.no_fuse)},
         "e2e": {"value": round(e2e_value, 3), "unit": "scenes/s", "ms_per_step": round(e2e_ms / args.steps, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches if args.impl == "ours" else 0,

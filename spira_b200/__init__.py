@@ -13,5 +13,6 @@ from . import nn
 from . import utils
 from .operators import *
 from .compat import install_as_spira
+from .fusion import fuse
 
 __version__ = "0.1.0"

@@ -10,14 +10,14 @@
 //     row is a real pair.  The 128 x c_out product is added into an fp32 scratch with vector
 //     reductions; a second small kernel applies the epilogue and rounds to fp16.
 //
-// Roles inside a CTA (416 threads, one CTA per SM):
-//   warps 0-7  producers: gather feature rows with 16-byte cp.async (zero-fill for missing rows)
+// Roles inside a CTA (672 threads, one CTA per SM):
+//   warps 0-15 producers: gather feature rows with 16-byte cp.async (zero-fill for missing rows)
 //              into a 128-byte-swizzled K-major A tile and let the copies arrive on the stage's
 //              mbarrier asynchronously (no thread waits for its own data); one thread bulk-copies
 //              the matching pre-packed weight chunk (already an MMA-ready image) and posts its bytes;
-//   warp  12   one elected thread issues tcgen05.mma (M=128, N=c_out, K=16) into one of two
+//   warp  20   one elected thread issues tcgen05.mma (M=128, N=c_out, K=16) into one of two
 //              TMEM accumulator buffers and commits stage / accumulator barriers;
-//   warps 8-11 epilogue: tcgen05.ld the finished accumulator (one row per thread), apply the
+//   warps 16-19 epilogue: tcgen05.ld the finished accumulator (one row per thread), apply the
 //              fused epilogue, store fp16 rows (OS) or issue fp32 vector reductions (WS) while the
 //              next tile is already being multiplied.
 // All mbarrier waits are bounded; on expiry the kernel raises a status word and drains.
@@ -39,14 +39,14 @@ using namespace sb::ptx;
 constexpr int kRows = 128;              // MMA M / rows per tile
 constexpr int kChunk = 64;              // fp16 elements of the reduction per pipeline stage (128 bytes)
 constexpr int kABytes = kRows * 128;    // one A stage
-constexpr int kProducers = 256;          // cp.async producers: 2 threads per tile row, 4 x 16 bytes each per stage
+constexpr int kProducers = 512;          // cp.async producers: up to 4 teams of 128 threads (thread <-> tile row)
 constexpr int kProducerWarps = kProducers / 32;
 constexpr int kMmaWarp = kProducerWarps + 4;         // warps kProducerWarps .. +3 are the epilogue (warp % 4 = TMEM lane quarter)
 static_assert(kProducerWarps % 4 == 0, "epilogue warps must start at a multiple of 4");
 constexpr int kConvThreads = (kMmaWarp + 1) * 32;
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 220 * 1024;
-constexpr int kScatterRing = 16;        // WS: scatter-row lists kept for tiles in flight (>= stages + 2)
+constexpr int kScatterRing = 32;        // WS: scatter-row lists kept for tiles in flight (producers run < 16 tiles ahead)
 
 struct Epilogue {
   const __half *bias;
@@ -70,7 +70,7 @@ struct ConvParams {
   int rows, mirror, n_tiles_plain;
   // common
   int T, n_tiles, K, c_in, c_out, R, n_chunks;  // n_chunks: OS = ceil(R/64); WS = ceil(c_in/64) per offset
-  int stages, slab_bufs, b_bytes, acc_stride, tmem_cols;
+  int stages, teams, slab_bufs, b_bytes, acc_stride, tmem_cols;
   int off_b, off_slab, off_flags, off_cm, off_meta, off_bar;
 };
 
@@ -91,7 +91,6 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
   const uint32_t sbase = smem_u32(smem);
 
   int32_t *slab = reinterpret_cast<int32_t *>(smem + P.off_slab);
-  int32_t *flags = reinterpret_cast<int32_t *>(smem + P.off_flags);
   uint32_t *cmask = reinterpret_cast<uint32_t *>(smem + P.off_cm);
   int32_t *meta = reinterpret_cast<int32_t *>(smem + P.off_meta);
   const uint32_t bar0 = sbase + P.off_bar;
@@ -107,13 +106,15 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(bar_full(s), kTma ? 1 : kProducers + 1);
+      mbar_init(bar_full(s), kTma ? 1 : kRows + 1);
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full(b), 1);
       mbar_init(bar_acc_empty(b), 128);
     }
+    mbar_init(bar0 + 8u * (2 * kMaxStages + 6), 1);   // map slab buffers (bulk copies)
+    mbar_init(bar0 + 8u * (2 * kMaxStages + 7), 1);
     *abort_flag = 0;
     mbar_init_fence();
   }
@@ -235,175 +236,189 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     }
   } else if (warp < kProducerWarps) {
     // =========================== producers (cp.async) ===========================
-    const int row = tid >> 1, half = tid & 1;
-    uint32_t dst_off[4];
+    // The producer warps form teams of 4 warps (128 threads, thread r <-> tile row r).  A team fills a whole
+    // pipeline stage: every thread copies the eight 16-byte pieces of its row (zero fill when the row has no
+    // neighbour) and its copies arrive on the stage's mbarrier asynchronously; thread 0 of the team also posts the
+    // weight chunk.  Teams work on different stages concurrently.  Stage s is ALWAYS filled by team s % teams: a
+    // parity wait can only tell two consecutive phases of an mbarrier apart, so the waiter must have taken part in
+    // every earlier phase of that barrier itself (stages is a multiple of teams).
+    const int team = warp >> 2, r = tid & 127;
+    const int teams = P.teams;
+    const bool active = team < teams;
+    const uint32_t row_off = r * 128;
+    uint32_t dsw[8];
 #pragma unroll
-    for (int p = 0; p < 4; ++p) dst_off[p] = row * 128 + (((half * 4 + p) ^ (row & 7)) << 4);
-    const bool whole_half = (P.c_in & 31) == 0;   // a 32-channel half row never straddles two offsets
-    const float inv_c_in = 1.0f / static_cast<float>(P.c_in);
-    int stage = 0, phase = 0, groups_since_prefetch = 0;
+    for (int p = 0; p < 8; ++p) dsw[p] = ((p ^ (r & 7)) << 4);
     bool ok = true;
     int tile_i = 0;
-    for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
-      const int buf = (P.slab_bufs == 2) ? (tile_i & 1) : 0;
-      int32_t *my_slab;
-      int w_row = 0, n_chunks_tile;
-      if constexpr (kWS) {
-        // tile -> (row k, first pair, count)
-        int tt = tile;
-        const bool mirrored = tt >= P.n_tiles_plain;
-        if (mirrored) tt -= P.n_tiles_plain;
-        const int q0 = tt * kRows;
-        int k = 0;
-        while (k + 1 < P.rows && P.qnaddrs[k + 1] <= q0) ++k;
-        const int p0 = P.naddrs[k] + (q0 - P.qnaddrs[k]);
-        const int n = min(kRows, P.naddrs[k + 1] - p0);
-        w_row = mirrored ? (P.K - 1 - k) : k;
-        // rows to gather (first 128 ints) and rows to scatter to.  The producers run at most
-        // stages + 2 tiles ahead of the epilogue, so a ring of kScatterRing lists is never overwritten early.
-        my_slab = slab;
-        int32_t *scatter = slab + kRows + (tile_i & (kScatterRing - 1)) * kRows;
-        named_bar_sync(1, kProducers);  // previous tile's gathers have read the row list
-        const int32_t *g = mirrored ? P.out_idx : P.in_idx;
-        const int32_t *s = mirrored ? P.in_idx : P.out_idx;
-        if (tid < kRows) {
-          my_slab[tid] = tid < n ? g[p0 + tid] : -1;
-          scatter[tid] = tid < n ? s[p0 + tid] : -1;
+    auto post_weights = [&](int stage, int chunk_id, int valid, bool first, bool last) {
+      meta[stage] = ((valid + 15) >> 4) | (first << 8) | (last << 9);
+      mbar_arrive_expect_tx(bar_full(stage), P.b_bytes);
+      bulk_g2s(sbase + P.off_b + stage * P.b_bytes, P.packed + static_cast<int64_t>(chunk_id) * P.b_bytes, P.b_bytes,
+               bar_full(stage));
+    };
+    if constexpr (kWS) {
+      // ---- weight-stationary: a tile is 128 pairs of one offset; no CTA-level barriers
+      // Pipeline item q = (CTA-local tile number) * cpo + (chunk of the tile) goes to stage q % stages; this team
+      // owns the items with q % teams == team.  Tile number, chunk, stage and phase are advanced incrementally.
+      const int cpo = P.n_chunks;
+      int jj = team;
+      while (jj >= cpo) { jj -= cpo; ++tile_i; }
+      int my_stage = team;
+      uint32_t my_phase = 0;
+      int loaded_tile = -1, k_hint = 0, idx = -1, w_row = 0;
+      bool hint_mirrored = false;
+      const __half *src_row = P.feats;
+      while (active && ok) {
+        const int tile = blockIdx.x + tile_i * gridDim.x;
+        if (tile >= P.n_tiles) break;
+        if (tile_i != loaded_tile) {
+          loaded_tile = tile_i;
+          int tt = tile;
+          const bool mirrored = tt >= P.n_tiles_plain;
+          if (mirrored) tt -= P.n_tiles_plain;
+          const int q0 = tt * kRows;
+          int k = (mirrored == hint_mirrored) ? k_hint : 0;     // tiles arrive in increasing order
+          while (k + 1 < P.rows && P.qnaddrs[k + 1] <= q0) ++k;
+          k_hint = k;
+          hint_mirrored = mirrored;
+          const int p0 = P.naddrs[k] + (q0 - P.qnaddrs[k]);
+          const int n = min(kRows, P.naddrs[k + 1] - p0);
+          w_row = mirrored ? (P.K - 1 - k) : k;
+          idx = r < n ? (mirrored ? P.out_idx : P.in_idx)[p0 + r] : -1;
+          src_row = P.feats + (idx >= 0 ? static_cast<int64_t>(idx) * P.c_in : 0);
+          // the scatter list (written by the team of the tile's first chunk) is read by the epilogue at most
+          // kScatterRing - 1 tiles later
+          if (jj == 0)
+            slab[kRows + (tile_i & (kScatterRing - 1)) * kRows + r] = r < n ? (mirrored ? P.in_idx : P.out_idx)[p0 + r] : -1;
         }
-        named_bar_sync(1, kProducers);
-        n_chunks_tile = P.n_chunks;
-      } else {
-        my_slab = slab + buf * kRows * P.K;
-        const int4 *src4 = reinterpret_cast<const int4 *>(P.map + static_cast<int64_t>(tile) * kRows * P.K);
-        if (P.slab_bufs == 1 || tile_i == 0) {
-          named_bar_sync(1, kProducers);
-          int4 *dst4 = reinterpret_cast<int4 *>(my_slab);
-          for (int i = tid; i < (kRows / 4) * P.K; i += kProducers) dst4[i] = src4[i];
-        } else {
-          cp_async_wait_dyn(groups_since_prefetch);  // the group that carried this slab has landed
-        }
-        named_bar_sync(1, kProducers);
-        // which offsets have at least one neighbour in this tile
-        for (int k = warp; k < P.K; k += kProducerWarps) {
-          bool any = false;
+        const int stage = my_stage;
+        if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
+        if (r == 0) post_weights(stage, w_row * cpo + jj, min(kChunk, P.c_in - jj * kChunk), jj == 0, jj == cpo - 1);
+        const uint32_t dst = sbase + stage * kABytes + row_off;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) any |= my_slab[(lane + 32 * j) * P.K + k] >= 0;
-          unsigned m = __ballot_sync(0xffffffffu, any);
-          if (lane == 0) flags[k] = m != 0;
+        for (int p = 0; p < 8; ++p) {
+          const int c = jj * kChunk + p * 8;
+          const bool take = idx >= 0 && c < P.c_in;
+          cp_async_16_ca(dst + dsw[p], take ? src_row + c : P.feats, take ? 16u : 0u);
         }
-        named_bar_sync(1, kProducers);
-        // which 64-wide reduction chunks touch a non-empty offset
-        const int n_words = (P.n_chunks + 31) >> 5;
-        for (int j = tid; j < n_words * 32; j += kProducers) {
-          bool ne = false;
-          if (j < P.n_chunks) {
-            int k_lo = (j * kChunk) / P.c_in;
-            int k_hi = min((j * kChunk + kChunk - 1) / P.c_in, P.K - 1);
-            for (int k = k_lo; k <= k_hi; ++k) ne |= flags[k] != 0;
-          }
-          unsigned m = __ballot_sync(0xffffffffu, ne);
-          if (lane == 0) cmask[j >> 5] = m;
-        }
-        named_bar_sync(1, kProducers);
-        n_chunks_tile = 0;
-        for (int w = 0; w < n_words; ++w) n_chunks_tile += __popc(cmask[w]);
+        cp_async_mbar_arrive_noinc(bar_full(stage));
+        my_stage += teams;
+        if (my_stage >= stages) { my_stage -= stages; my_phase ^= 1; }
+        jj += teams;
+        while (jj >= cpo) { jj -= cpo; ++tile_i; }
       }
-
-      const bool force_first = (n_chunks_tile == 0);  // a tile always sends at least one chunk
-      if (force_first) n_chunks_tile = 1;
-      int sent = 0;
-      const int n_words = kWS ? 1 : ((P.n_chunks + 31) >> 5);
-      for (int w = 0; ok && w < n_words; ++w) {
-        uint32_t bits;
-        if constexpr (kWS) bits = 0; else bits = cmask[w];
-        if (force_first && w == 0) bits = 1u;
-        int ws_j = 0;
-        while (ok) {
-          int j;
-          if constexpr (kWS) {
-            if (ws_j >= P.n_chunks) break;
-            j = ws_j++;
-          } else {
-            if (bits == 0) break;
-            j = (w << 5) + __ffs(bits) - 1;
-            bits &= bits - 1;
+    } else {
+      // ---- output-stationary: all producer warps prepare a tile together, the teams then take its non-empty
+      // chunks in turn
+      const float inv_c_in = 1.0f / static_cast<float>(P.c_in);
+      const int n_words = (P.n_chunks + 31) >> 5;
+      const uint32_t slab_bytes = kRows * P.K * 4;
+      const uint32_t bar_slab0 = bar0 + 8u * (2 * kMaxStages + 6);
+      const bool one_offset_per_chunk = (P.c_in % kChunk) == 0;
+      uint32_t q_base = 0;
+      int q_mod_teams = 0;            // q_base % teams
+      int my_stage = team;            // stage of this team's next item (items of a team advance by `teams` stages)
+      uint32_t my_phase = 0;
+      if (tid == 0 && P.slab_bufs == 2 && static_cast<int>(blockIdx.x) < P.n_tiles) {
+        mbar_arrive_expect_tx(bar_slab0, slab_bytes);
+        bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(blockIdx.x) * kRows * P.K, slab_bytes, bar_slab0);
+      }
+      for (int w = tid; w < 2 * n_words; w += kProducers) cmask[w] = 0;
+      // Every thread runs the same sequence of named barriers; a failed wait only takes effect through the
+      // OR-reduction of those barriers, so that all producer warps leave the loop in the same iteration.
+      for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+        const int buf = (P.slab_bufs == 2) ? (tile_i & 1) : 0;
+        const int32_t *my_slab = slab + buf * kRows * P.K;
+        uint32_t *my_cmask = cmask + (tile_i & 1) * n_words;
+        if (P.slab_bufs == 2) {
+          if (!mbar_wait(bar_slab0 + 8u * buf, (tile_i >> 1) & 1, abort_flag)) ok = false;
+          // all warps have issued their share of the previous tile: the other slab and chunk mask are free
+          if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
+          const int next = tile + gridDim.x;
+          if (tid == 0 && next < P.n_tiles) {
+            mbar_arrive_expect_tx(bar_slab0 + 8u * (buf ^ 1), slab_bytes);
+            bulk_g2s(sbase + P.off_slab + (buf ^ 1) * slab_bytes, P.map + static_cast<int64_t>(next) * kRows * P.K, slab_bytes,
+                     bar_slab0 + 8u * (buf ^ 1));
           }
-          ++sent;
-          if (!mbar_wait(bar_empty(stage), phase ^ 1, abort_flag)) { ok = false; break; }
-          // ---- A: this thread owns half a row (4 pieces of 16 bytes = 32 channels) of the 128 x 64 tile
-          const uint32_t a_stage = sbase + stage * kABytes;
-          if (whole_half) {
-            int k = 0, c;
-            bool valid;
-            if constexpr (kWS) {
-              c = j * kChunk + half * 32;
-              valid = c < P.c_in;
-            } else {
-              const int r = j * kChunk + half * 32;
-              k = __float2int_rd((static_cast<float>(r) + 0.5f) * inv_c_in);
-              c = r - k * P.c_in;
-              valid = r < P.R;
-            }
-            int idx = -1;
-            if (valid) idx = kWS ? my_slab[row] : my_slab[row * P.K + k];
-            const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
+        } else {
+          if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
+          if (tid == 0) {
+            mbar_arrive_expect_tx(bar_slab0, slab_bytes);
+            bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(tile) * kRows * P.K, slab_bytes, bar_slab0);
+          }
+          if (!mbar_wait(bar_slab0, tile_i & 1, abort_flag)) ok = false;
+        }
+        // which 64-wide reduction chunks touch at least one neighbour of this tile: one bit per chunk, the
+        // chunks are spread over the warps
+        for (int j = warp; j < P.n_chunks; j += kProducerWarps) {
+          const int k_lo = __float2int_rd((static_cast<float>(j * kChunk) + 0.5f) * inv_c_in);
+          const int k_hi = min(__float2int_rd((static_cast<float>(j * kChunk + kChunk - 8) + 0.5f) * inv_c_in), P.K - 1);
+          int v = -1;
+          for (int k = k_lo; k <= k_hi; ++k)
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd) v = max(v, my_slab[(lane + 32 * qd) * P.K + k]);
+          if (__ballot_sync(0xffffffffu, v >= 0) && lane == 0) atomicOr(&my_cmask[j >> 5], 1u << (j & 31));
+        }
+        if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
+        // the mask of the NEXT tile starts from zero (its previous user, tile_i - 1, is finished for all warps)
+        for (int w = tid; w < n_words; w += kProducers) cmask[((tile_i + 1) & 1) * n_words + w] = 0;
+        int n_chunks_tile = 0;
+        for (int w = 0; w < n_words; ++w) n_chunks_tile += __popc(my_cmask[w]);
+        const bool force_first = (n_chunks_tile == 0);   // a tile always sends at least one chunk
+        if (force_first) n_chunks_tile = 1;
+        // Chunk number e (0-based, in increasing j) of the tile is pipeline item q = q_base + e and goes to stage
+        // q % stages; this team owns the items with q % teams == team (teams divides stages).  All of it is tracked
+        // incrementally: an integer division per chunk would dominate this latency-bound instruction stream.
+        int word = 0, before = 0;                        // position inside the mask for the n-th set bit
+        int e = team - q_mod_teams;
+        if (e < 0) e += teams;
+        for (; active && ok && e < n_chunks_tile; e += teams) {
+          int j = 0;
+          if (!force_first) {
+            while (before + __popc(my_cmask[word]) <= e) { before += __popc(my_cmask[word]); ++word; }
+            j = (word << 5) + __fns(my_cmask[word], 0, e - before + 1);
+          }
+          const int stage = my_stage;
+          if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
+          my_stage += teams;
+          if (my_stage >= stages) { my_stage -= stages; my_phase ^= 1; }
+          if (r == 0) post_weights(stage, j, min(kChunk, P.R - j * kChunk), e == 0, e == n_chunks_tile - 1);
+          const uint32_t dst = sbase + stage * kABytes + row_off;
+          if (one_offset_per_chunk) {
+            const int rr = j * kChunk;
+            const int k = __float2int_rd((static_cast<float>(rr) + 0.5f) * inv_c_in);
+            const int idx = my_slab[r * P.K + k];
+            const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + (rr - k * P.c_in)) : 0);
             const uint32_t bytes = idx >= 0 ? 16u : 0u;
 #pragma unroll
-            for (int p = 0; p < 4; ++p) cp_async_16(a_stage + dst_off[p], idx >= 0 ? src + 8 * p : src, bytes);
+            for (int p = 0; p < 8; ++p)
+              cp_async_16_ca(dst + dsw[p], idx >= 0 ? src + 8 * p : src, bytes);
           } else {
+            int cur_k = -1, idx = -1;
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              int k = 0, c;
-              bool valid;
-              if constexpr (kWS) {
-                c = j * kChunk + (half * 4 + p) * 8;
-                valid = c < P.c_in;
-              } else {
-                const int r = j * kChunk + (half * 4 + p) * 8;
-                k = __float2int_rd((static_cast<float>(r) + 0.5f) * inv_c_in);
-                c = r - k * P.c_in;
-                valid = r < P.R;
+            for (int p = 0; p < 8; ++p) {
+              const int rr = j * kChunk + p * 8;
+              int k = __float2int_rd((static_cast<float>(rr) + 0.5f) * inv_c_in);
+              const int c = rr - k * P.c_in;
+              if (rr >= P.R) k = -2;                                  // zero padding behind the last offset
+              if (k != cur_k) {
+                cur_k = k;
+                idx = k >= 0 ? my_slab[r * P.K + k] : -1;
               }
-              int idx = -1;
-              if (valid) idx = kWS ? my_slab[row] : my_slab[row * P.K + k];
               const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
-              cp_async_16(a_stage + dst_off[p], src, idx >= 0 ? 16u : 0u);
+              cp_async_16_ca(dst + dsw[p], src, idx >= 0 ? 16u : 0u);
             }
           }
-          if (tid == 0) {
-            // ---- B: one bulk copy of the pre-packed chunk; meta word for the MMA thread
-            const int chunk_id = kWS ? (w_row * P.n_chunks + j) : j;
-            const int valid = kWS ? min(kChunk, P.c_in - j * kChunk) : min(kChunk, P.R - j * kChunk);
-            const int nk = (valid + 15) >> 4;
-            meta[stage] = nk | ((sent == 1) << 8) | ((sent == n_chunks_tile) << 9);
-            mbar_arrive_expect_tx(bar_full(stage), P.b_bytes);
-            bulk_g2s(sbase + P.off_b + stage * P.b_bytes, P.packed + static_cast<int64_t>(chunk_id) * P.b_bytes,
-                     P.b_bytes, bar_full(stage));
-          }
-          if constexpr (!kWS) {
-            // the next tile's slab rides in the commit group of this tile's first chunk
-            if (sent == 1 && P.slab_bufs == 2) {
-              const int next = tile + gridDim.x;
-              groups_since_prefetch = 0;
-              if (next < P.n_tiles) {
-                const int4 *n4 = reinterpret_cast<const int4 *>(P.map + static_cast<int64_t>(next) * kRows * P.K);
-                const uint32_t dst = sbase + P.off_slab + (buf ^ 1) * kRows * P.K * 4;
-                for (int i = tid; i < (kRows / 4) * P.K; i += kProducers) cp_async_16(dst + i * 16, n4 + i, 16u);
-              }
-            } else {
-              ++groups_since_prefetch;
-            }
-          }
-          // this thread's share of the stage is complete when its copies land: asynchronous arrival, the
-          // thread itself never waits for data (the commit group only tracks the slab prefetch)
           cp_async_mbar_arrive_noinc(bar_full(stage));
-          cp_async_commit();
-          if (++stage == stages) { stage = 0; phase ^= 1; }
         }
+        q_base += n_chunks_tile;
+        q_mod_teams += n_chunks_tile % teams;
+        if (q_mod_teams >= teams) q_mod_teams -= teams;
       }
     }
     // nothing of this thread may still be in flight when the CTA tears down
-    cp_async_wait<0>();
+    cp_async_wait_all();
   } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
@@ -420,7 +435,6 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         const uint32_t d_tmem = tmem_base + b * P.acc_stride;
         while (true) {
           if (!mbar_wait(bar_full(stage), phase, abort_flag)) { ok = false; break; }
-          fence_proxy_async();
           tc_fence_after();
           const int m = meta[stage];
           const int nk = m & 0xff;
@@ -705,19 +719,23 @@ static size_t plan_smem(ConvParams &P, bool ws) {
   P.slab_bufs = (!ws && 2 * slab_one <= 32 * 1024) ? 2 : 1;
   int slab_bytes = ws ? slab_one : P.slab_bufs * slab_one;
   int n_words = ws ? 1 : (P.n_chunks + 31) / 32;
-  int fixed = slab_bytes + round16(P.K * 4) + round16(n_words * 4) + round16(kMaxStages * 4) + 8 * (2 * kMaxStages + 4) + 16;
+  int fixed = slab_bytes + round16(P.K * 4) + round16(2 * n_words * 4) + round16(kMaxStages * 4) + 8 * (2 * kMaxStages + 8) + 16;
   int per_stage = kABytes + P.b_bytes;
   int stages = (kSmemBudget - fixed) / per_stage;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return 0;
+  // producer teams: stage s is filled by team s % teams, so the stage count is a multiple of the team count
+  if (stages == 7) stages = 6;
+  if (stages == 5) stages = 4;
+  P.teams = (stages % 4 == 0) ? 4 : (stages % 3 == 0) ? 3 : 2;
   P.stages = stages;
   P.off_b = stages * kABytes;
   P.off_slab = P.off_b + stages * P.b_bytes;
   P.off_flags = P.off_slab + slab_bytes;
   P.off_cm = P.off_flags + round16(P.K * 4);
-  P.off_meta = P.off_cm + round16(n_words * 4);
+  P.off_meta = P.off_cm + round16(2 * n_words * 4);
   P.off_bar = P.off_meta + round16(kMaxStages * 4);
-  return static_cast<size_t>(P.off_bar) + 8 * (2 * kMaxStages + 4) + 16 + 1024;
+  return static_cast<size_t>(P.off_bar) + 8 * (2 * kMaxStages + 8) + 16 + 1024;
 }
 
 }  // namespace sb
@@ -868,3 +886,4 @@ extern "C" int spira_b200_get_option(const char *name) {
   if (std::strcmp(name, "os_pack_mode") == 0) return g_gather_tma ? SPIRA_B200_PACK_WS : SPIRA_B200_PACK_OS;
   return -1;
 }
+

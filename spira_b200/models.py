@@ -24,14 +24,29 @@ def _conv_bn_relu(cin, cout, k, stride=1, transposed=False):
 
 
 class ResBlock(nn.Module):
+    """``relu(main(x) + shortcut(x))`` with ``main = conv-bn-relu-conv-bn`` (the reference's ``SparseResBlock``,
+    scripts/models/spira/modules/blocks.py:51-84)."""
+
     def __init__(self, cin: int, cout: int, k: int = 3):
         super().__init__()
         self.main = nn.Sequential(spnn.SparseConv(cin, cout, k), spnn.BatchNorm(cout), spnn.ReLU(True),
                                   spnn.SparseConv(cout, cout, k), spnn.BatchNorm(cout))
         self.shortcut = nn.Identity() if cin == cout else nn.Sequential(spnn.SparseConv(cin, cout, 1), spnn.BatchNorm(cout))
         self.relu = spnn.ReLU(True)
+        self._residual_fused = False
+
+    def fuse_residual(self):
+        """After ``spira_b200.fuse``: the add and the final ReLU run in the epilogue of the last main convolution."""
+        last = self.main[3]
+        if isinstance(last, spnn.SparseConv) and last._fused is not None and isinstance(self.main[4], nn.Identity):
+            last._fused["relu"] = True
+            self._residual_fused = True
 
     def forward(self, x):
+        if self._residual_fused:
+            s = self.shortcut(x)
+            h = self.main[2](self.main[1](self.main[0](x)))
+            return self.main[3](h, residual=s._features)
         return self.relu(self.main(x) + self.shortcut(x))
 
 

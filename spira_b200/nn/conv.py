@@ -145,6 +145,16 @@ class SparseConv(Module):
             'force_os': False,
         }
         self._tuning_data = None
+        # optional fused epilogue (set by spira_b200.fuse): per-channel fp32 scale / shift and a ReLU flag that the
+        # kernels apply to the fp32 accumulator before the single rounding to fp16
+        self._fused = None
+
+    def set_fused_epilogue(self, scale: Optional[torch.Tensor], shift: Optional[torch.Tensor], relu: bool):
+        """``y = relu?((conv(x) + bias) * scale + shift [+ residual])`` inside the convolution kernel."""
+        if self.is_trivial:
+            raise ValueError("the 1x1x1 stride-1 layer is a plain matrix product and has no fused epilogue")
+        self._fused = dict(scale=None if scale is None else scale.detach().float().contiguous(),
+                           shift=None if shift is None else shift.detach().float().contiguous(), relu=bool(relu))
 
     @property
     def tunable_config(self) -> Dict[str, Any]:
@@ -175,7 +185,7 @@ class SparseConv(Module):
         finally:
             self._tuning_data = None
 
-    def forward(self, inputs: SparseTensor):
+    def forward(self, inputs: SparseTensor, residual: Optional[torch.Tensor] = None):
         source_features = inputs._features
         if self.is_trivial:
             kernel = self.kernel.view(self.in_channels, self.out_channels)
@@ -198,6 +208,18 @@ class SparseConv(Module):
             # NON-transposed twin; a transposed layer exchanges the roles of sources and targets
             n_src, n_tgt = (m[1], m[0]) if self.transposed else (m[0], m[1])
 
+            if self._fused is not None or residual is not None:
+                # engine-native call: bias / BatchNorm affine / residual / ReLU are applied in the kernel epilogue
+                fz = self._fused or dict(scale=None, shift=None, relu=False)
+                kw = dict(bias=self.bias, scale=fz["scale"], shift=fz["shift"], residual=residual, relu=fz["relu"])
+                if map_dataflow == 0 or force_os:
+                    target_features = _C.conv_os(n_src, n_tgt, m[2], source_features, self.kernel, **kw)
+                else:
+                    lists = (getattr(m[3], "_sb", None) or {}).get("ws")
+                    if lists is None:
+                        raise RuntimeError("[spira_b200] the fused epilogue needs kernel maps built by this engine")
+                    target_features = _C.conv_ws(n_src, n_tgt, source_features, self.kernel, lists, swap=self.transposed, **kw)
+                return SparseTensor(features=target_features, coordinates=target_coordinates, stride=target_stride)
             if map_dataflow == 0 or force_os:
                 target_features = F.sparse_convolution_forward_os(n_src, n_tgt, m[2], source_features, self.kernel)
             elif map_dataflow % 2 == 1:

@@ -83,3 +83,36 @@ def test_selector_and_backbone(lib, tmp_path):
     # reload from the stored file
     model2, chosen2 = sp.tune(model, loader(), cache, save_dir=str(tmp_path), tune_tag="t", return_dataflows=True)
     assert chosen2 == chosen
+
+
+def test_fused_epilogues_match_the_module_by_module_result(lib):
+    """spira_b200.fuse(): BatchNorm(eval) + ReLU + residual add inside the convolution kernels vs separate passes."""
+    import copy
+    import spira_b200 as sp
+    from spira_b200 import models, scenes, nn as spnn
+    from spira_b200.nn.functional import _C
+    torch.manual_seed(1)
+    c = scenes.lidar_scene(2)[:40000]
+    coords = torch.from_numpy(c).cuda()
+    feats = torch.from_numpy(scenes.features(len(c), 4, 5)).cuda()
+    model = models.minkunet18(4, 19, 3).cuda().half().eval()
+    for m in model.modules():                      # non-trivial BatchNorm statistics
+        if isinstance(m, spnn.BatchNorm):
+            m.running_mean.normal_(0, 0.2)
+            m.running_var.uniform_(0.5, 1.5)
+            m.weight.data.uniform_(0.8, 1.2)
+            m.bias.data.normal_(0, 0.1)
+    sched = models.map_schedule(4, 3, 3)
+    for dataflow in (0, 1):
+        cache = spnn.KernelMapCache()
+        sp.set_kernel_map_cache(model, cache)
+        y_ref, _ = run(model, cache, coords, feats, sched, dataflow)
+        fused = sp.fuse(copy.deepcopy(model))
+        n_fused = sum(1 for m in fused.modules() if isinstance(m, spnn.SparseConv) and m._fused is not None)
+        assert n_fused == 42
+        cache2 = spnn.KernelMapCache()
+        sp.set_kernel_map_cache(fused, cache2)
+        y_fused, _ = run(fused, cache2, coords, feats, sched, dataflow)
+        scale = y_ref._features.float().abs().max().item()
+        assert (y_ref._features.float() - y_fused._features.float()).abs().max().item() <= 3e-2 * max(scale, 1.0)
+    _C.check_status()
