@@ -191,6 +191,26 @@ int spira_b200_conv_ws(const void *feats, const void *weights, const void *packe
                        int swap, int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out, float *accum,
                        void *out, int32_t *status, void *stream);
 
+/* Capacity, in floats, of the scratch array built into the library for spira_b200_conv_ws_static (16 MiB per GPU). */
+#define SPIRA_B200_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)
+
+/* Same computation and arguments as spira_b200_conv_ws, minus `accum`: the fp32 accumulation scratch is a fixed
+ * device array inside the library, so the call needs no memory beyond its inputs and outputs and performs no
+ * allocation of any kind.  It has no counterpart in the reference.  It is meant for hosts that must not allocate on
+ * the request path: an inference server that carves up device memory once at start-up and treats any later
+ * allocation as a fault, or a plain C / C++ embedder that has no caching allocator to borrow scratch from.
+ *   - limit: num_targets * c_out <= SPIRA_B200_STATIC_SCRATCH_FLOATS, otherwise the call fails with
+ *     SPIRA_B200_ERR_ARGUMENT and a message naming the limit (use spira_b200_conv_ws then);
+ *   - the first call on a device looks up the array's device address; make that call before capturing a stream;
+ *   - all calls on a GPU share the one array (it is cleared at the start of every call and keeps the last call's
+ *     partial sums afterwards), so two calls that overlap on the GPU -- different streams, or different host threads
+ *     -- race with each other: serialise them. */
+int spira_b200_conv_ws_static(const void *feats, const void *weights, const void *packed,
+                              const spira_b200_epilogue *epilogue, const int32_t *in_idx, const int32_t *out_idx,
+                              const int32_t *naddrs, const int32_t *qnaddrs, int rows, int64_t num_tiles128, int mirror,
+                              int swap, int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out, void *out,
+                              int32_t *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

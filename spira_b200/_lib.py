@@ -62,7 +62,11 @@ SIGNATURES = {
     "spira_b200_conv_ws": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                            c_void_p, c_void_p],
+    "spira_b200_conv_ws_static": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_void_p],
 }
+STATIC_SCRATCH_FLOATS = 4 * 1024 * 1024
 EXPORTS = sorted(list(SIGNATURES) + ["spira_b200_last_error"])
 
 _lib = None
@@ -99,7 +103,7 @@ KERNELS_PER_CALL = {
     "spira_b200_pack": 1, "spira_b200_unpack": 1, "spira_b200_flatten_sort": 1, "spira_b200_permute_rows": 1,
     "spira_b200_downsample": 1, "spira_b200_kmap_search": 1, "spira_b200_kmap_ws_sizes": 2, "spira_b200_kmap_ws_pairs": 1,
     "spira_b200_kmap_masks": 1, "spira_b200_convert_transposed_os": 1, "spira_b200_transpose_map": 1,
-    "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_ws": 2,
+    "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_ws": 2, "spira_b200_conv_ws_static": 2,
 }
 launch_count = 0          # kernels launched through `call` since import (or since it was last reset by the caller)
 profile_hook = None       # optional callable(name, args, run) -> None used by the benchmark to time single calls

@@ -887,3 +887,36 @@ extern "C" int spira_b200_get_option(const char *name) {
   return -1;
 }
 
+
+// ---- weight-stationary convolution without any caller-provided scratch ------------------------------------------
+// Scratch for the fp32 accumulation lives in this file-scope device array.  Every GPU that loads the library keeps
+// its own copy (16 MiB) until the process exits.  In host code the array's name is only a handle: the device address
+// is obtained once per device with cudaGetSymbolAddress while that device is current, and that pointer is what the
+// kernels receive.
+static __device__ __align__(256) float g_static_accum[SPIRA_B200_STATIC_SCRATCH_FLOATS];
+static float *g_static_accum_ptr[64] = {nullptr};
+
+extern "C" int spira_b200_conv_ws_static(const void *feats, const void *weights, const void *packed,
+                                         const spira_b200_epilogue *epilogue, const int32_t *in_idx,
+                                         const int32_t *out_idx, const int32_t *naddrs, const int32_t *qnaddrs, int rows,
+                                         int64_t num_tiles128, int mirror, int swap, int64_t num_sources,
+                                         int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status,
+                                         void *stream) {
+  SB_CHECK_ARG(num_targets >= 0 && c_out >= 1, "conv_ws_static: bad sizes");
+  SB_CHECK_ARG(num_targets * static_cast<int64_t>(c_out) <= static_cast<int64_t>(SPIRA_B200_STATIC_SCRATCH_FLOATS),
+               "conv_ws_static: num_targets * c_out = %lld exceeds the built-in scratch of %lld floats; use spira_b200_conv_ws "
+               "with caller-provided scratch",
+               static_cast<long long>(num_targets * static_cast<int64_t>(c_out)),
+               static_cast<long long>(SPIRA_B200_STATIC_SCRATCH_FLOATS));
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  SB_CHECK_ARG(dev >= 0 && dev < 64, "conv_ws_static: device index %d out of range", dev);
+  if (g_static_accum_ptr[dev] == nullptr) {
+    // first call on this device: resolve the device address of the array (do this before any stream capture)
+    float *p = nullptr;
+    SB_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_accum));
+    g_static_accum_ptr[dev] = p;
+  }
+  return spira_b200_conv_ws(feats, weights, packed, epilogue, in_idx, out_idx, naddrs, qnaddrs, rows, num_tiles128, mirror,
+                            swap, num_sources, num_targets, K, c_in, c_out, g_static_accum_ptr[dev], out, status, stream);
+}
