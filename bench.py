@@ -145,6 +145,7 @@ class Engine:
         self.layer_strides = []
         for i in range(len(self.ks)):
             self.layer_strides.append(tuple(b // a for a, b in zip(self.ss[i], self.ss[i + 1])))
+        self.compiled = None
         self.set_uniform_dataflow(0)
         if dataflows is not None:
             self.dataflows = dataflows
@@ -165,8 +166,17 @@ class Engine:
         x = self.sp.SparseTensor(coords, feats).order()
         self.cache.reset()
         self.cache.add_all_kernel_maps(x._coordinates, self.ks, self.ss, self.ts, (1, 1, 1), self.dataflows)
+        if self.compiled is not None:
+            return self.compiled(x)._features
         with torch.no_grad():
             return self.model(x)._features
+
+    def compile(self, coords, feats):
+        """Records the operator tape once (spira_b200.compile_model); later steps replay it."""
+        x = self.sp.SparseTensor(coords, feats).order()
+        self.cache.reset()
+        self.cache.add_all_kernel_maps(x._coordinates, self.ks, self.ss, self.ts, (1, 1, 1), self.dataflows)
+        self.compiled = self.sp.compile_model(self.model, x, self.cache)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -223,15 +233,18 @@ def timed_loop(step_fn, n_steps, warmup, l2buf, dist_ctx):
         torch.distributed.barrier()
     evs = []
     wall0 = time.perf_counter()
+    enqueue = 0.0
     for i in range(n_steps):
         flush_l2(l2buf)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
+        c0 = time.perf_counter()
         step_fn(warmup + i)
+        enqueue += time.perf_counter() - c0
         b.record()
         evs.append((a, b))
     torch.cuda.synchronize()
-    wall = time.perf_counter() - wall0
+    wall = (time.perf_counter() - wall0, enqueue)
     if dist_ctx:
         torch.distributed.barrier()
     from spira_b200 import sharding
@@ -264,10 +277,12 @@ def profile_kernels(engine, scene):
     from spira_b200.nn import SparseConv
     handles = [m.register_forward_hook(fwd_hook) for m in engine.model.modules() if isinstance(m, SparseConv)]
     _lib.profile_hook = hook
+    compiled, engine.compiled = engine.compiled, None      # module hooks only fire on the eager path
     try:
         engine.step(*scene)
         torch.cuda.synchronize()
     finally:
+        engine.compiled = compiled
         _lib.profile_hook = None
         for h in handles:
             h.remove()
@@ -371,6 +386,7 @@ def main():
     ap.add_argument("--scene", default="c0", choices=["c0", "lidar"], help="layer workload: 50k-voxel plane/sphere scene or a LiDAR scene")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dataflow", default="auto", choices=["auto", "0", "1"], help="auto = per-group selector (tune); 0/1 = uniform")
+    ap.add_argument("--no-compile", action="store_true", help="run the eager module path instead of the recorded tape (ours arm)")
     ap.add_argument("--no-fuse", action="store_true", help="keep BatchNorm / ReLU / residual adds as separate passes (ours arm)")
     ap.add_argument("--dump-layers", default=None, help="write the per-layer timing table of the profiled step to this JSON file")
     args = ap.parse_args()
@@ -448,7 +464,7 @@ def main():
             for c, f in dev:
                 yield sp.SparseTensor(c, f).order()
         _, chosen = sp.tune(engine.model, loader(), engine.cache, n_samples=2, save_dir=str(ROOT / "gpurun_out" / ".tune"),
-                            tune_tag=f"{args.workload}_r{rank}", force_retune=True, return_dataflows=True, verify=True)
+                            tune_tag=f"{args.workload}_r{rank}", force_retune=True, return_dataflows=True, verify=False)
         engine.apply_groups(chosen)
         chosen_note = {str(k): v for k, v in chosen.items()}
     else:
@@ -474,6 +490,8 @@ def main():
         engine.set_uniform_dataflow(best[0])
         chosen_note = {"uniform_map_dataflow": best[0]}
 
+    if args.impl == "ours" and not args.no_compile:
+        engine.compile(*dev[0])
     l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
     from spira_b200 import _lib
 
@@ -520,10 +538,12 @@ def main():
         "config": {"workload": wl["label"], "voxels_per_scene": n_vox, "scenes_per_rank": len(dev),
                    "timed_region": "order() + add_all_kernel_maps() + model forward, per scene",
                    "l2": "256 MiB buffer rewritten between timed steps", "dataflows": chosen_note, "sharding": "independent scenes per GPU, no collective",
-                   "fused_epilogue": bool(args.impl == "ours" and not args.no_fuse)},
+                   "fused_epilogue": bool(args.impl == "ours" and not args.no_fuse),
+                   "recorded_tape": bool(args.impl == "ours" and not args.no_compile)},
         "e2e": {"value": round(e2e_value, 3), "unit": "scenes/s", "ms_per_step": round(e2e_ms / args.steps, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches if args.impl == "ours" else 0,
+        "host_enqueue_ms_per_step": round(wall[1] * 1e3 / args.steps, 4),
         "clocks": clocks,
     }
     if args.impl == "reference":

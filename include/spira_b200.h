@@ -182,7 +182,8 @@ int spira_b200_conv_os(const void *feats, const void *weights, const void *packe
  * `swap` != 0 the roles of in_idx and out_idx are exchanged (transposed layer on the map of its
  * non-transposed twin, spira/nn/conv.py:341-348).  accum is fp32 [num_targets][c_out] scratch,
  * zeroed by the call; out is fp16 [num_targets][c_out].  `qnaddrs` holds the 128-rounded prefix
- * sums and `num_tiles128` = qnaddrs[rows] / 128 (the caller learned it when it sized the lists).
+ * sums and `num_tiles128` = qnaddrs[rows] / 128 if the caller knows it, or -1: the kernels then read it from
+ * `qnaddrs` on the device, so list sizes never have to travel to the host.
  * Replaces cuda_sparse_convolution_forward_ws_merged
  * (csrc/spira/torch/cuda_sparse_convolution_forward.cu:183-246). */
 int spira_b200_conv_ws(const void *feats, const void *weights, const void *packed,

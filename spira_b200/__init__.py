@@ -14,5 +14,6 @@ from . import utils
 from .operators import *
 from .compat import install_as_spira
 from .fusion import fuse
+from .compile import compile_model, CompiledModel
 
 __version__ = "0.1.0"

@@ -67,7 +67,7 @@ struct ConvParams {
   const int32_t *map;  // [T_al][K]
   // WS
   const int32_t *in_idx, *out_idx, *naddrs, *qnaddrs;
-  int rows, mirror, n_tiles_plain;
+  int rows, mirror, n_tiles_plain, centre_tiles;
   // common
   int T, n_tiles, K, c_in, c_out, R, n_chunks;  // n_chunks: OS = ceil(R/64); WS = ceil(c_in/64) per offset
   int stages, teams, slab_bufs, b_bytes, acc_stride, tmem_cols;
@@ -103,6 +103,14 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int stages = P.stages;
+  // tile counts: given by the host, or (weight-stationary lists whose sizes never left the device) read here
+  int n_tiles = P.n_tiles, n_tiles_plain = P.n_tiles_plain;
+  if constexpr (kWS) {
+    if (P.n_tiles < 0) {
+      n_tiles_plain = P.qnaddrs[P.rows] >> 7;
+      n_tiles = P.mirror ? 2 * n_tiles_plain - P.centre_tiles : n_tiles_plain;
+    }
+  }
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -137,21 +145,21 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       int tile_i = 0;
       const int slab_int4 = (kRows / 4) * P.K;
       if constexpr (!kWS) {
-        if (static_cast<int>(blockIdx.x) < P.n_tiles) {
+        if (static_cast<int>(blockIdx.x) < n_tiles) {
           const int4 *s4 = reinterpret_cast<const int4 *>(P.map + static_cast<int64_t>(blockIdx.x) * kRows * P.K);
           for (int i = lane; i < slab_int4; i += 32) cp_async_16(sbase + P.off_slab + i * 16, s4 + i, 16u);
         }
         cp_async_commit();
       }
-      for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++tile_i) {
         int idx[4] = {-1, -1, -1, -1};
         int w_row = 0, n_offsets = 1;
         uint32_t kmask[16];
         const int32_t *my_slab = slab;
         if constexpr (kWS) {
           int tt = tile;
-          const bool mirrored = tt >= P.n_tiles_plain;
-          if (mirrored) tt -= P.n_tiles_plain;
+          const bool mirrored = tt >= n_tiles_plain;
+          if (mirrored) tt -= n_tiles_plain;
           const int q0 = tt * kRows;
           int k = 0;
           while (k + 1 < P.rows && P.qnaddrs[k + 1] <= q0) ++k;
@@ -180,7 +188,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           __syncwarp();
           if (P.slab_bufs == 2) {
             const int next = tile + gridDim.x;
-            if (next < P.n_tiles) {
+            if (next < n_tiles) {
               const int4 *n4 = reinterpret_cast<const int4 *>(P.map + static_cast<int64_t>(next) * kRows * P.K);
               const uint32_t dst = sbase + P.off_slab + (buf ^ 1) * kRows * P.K * 4;
               for (int i = lane; i < slab_int4; i += 32) cp_async_16(dst + i * 16, n4 + i, 16u);
@@ -236,19 +244,19 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     }
   } else if (warp < kProducerWarps) {
     // =========================== producers (cp.async) ===========================
-    // The producer warps form teams of 4 warps (128 threads, thread r <-> tile row r).  A team fills a whole
-    // pipeline stage: every thread copies the eight 16-byte pieces of its row (zero fill when the row has no
-    // neighbour) and its copies arrive on the stage's mbarrier asynchronously; thread 0 of the team also posts the
-    // weight chunk.  Teams work on different stages concurrently.  Stage s is ALWAYS filled by team s % teams: a
+    // The producer warps form teams of 4 warps (128 threads).  A team fills a whole pipeline stage: thread r copies
+    // ONE 16-byte piece (r & 7) of 8 rows (r >> 3, +16, ...), zero-filling rows without a neighbour, so that the eight
+    // lanes sharing a row read 128 contiguous bytes (a warp-level copy touches 4 rows; with one row per lane it would
+    // touch 32 cache lines and the L1, which handles one line per cycle, becomes the limit).  The copies arrive on the
+    // stage's mbarrier asynchronously; thread 0 of the team also posts the weight chunk.  Teams work on different
+    // stages concurrently.  Stage s is ALWAYS filled by team s % teams: a
     // parity wait can only tell two consecutive phases of an mbarrier apart, so the waiter must have taken part in
     // every earlier phase of that barrier itself (stages is a multiple of teams).
     const int team = warp >> 2, r = tid & 127;
     const int teams = P.teams;
     const bool active = team < teams;
-    const uint32_t row_off = r * 128;
-    uint32_t dsw[8];
-#pragma unroll
-    for (int p = 0; p < 8; ++p) dsw[p] = ((p ^ (r & 7)) << 4);
+    const int piece = r & 7, rowbase = r >> 3;
+    const uint32_t dst_off = rowbase * 128 + ((piece ^ (rowbase & 7)) << 4);   // (row & 7) == (rowbase & 7) for all 8 rows
     bool ok = true;
     int tile_i = 0;
     auto post_weights = [&](int stage, int chunk_id, int valid, bool first, bool last) {
@@ -266,17 +274,17 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       while (jj >= cpo) { jj -= cpo; ++tile_i; }
       int my_stage = team;
       uint32_t my_phase = 0;
-      int loaded_tile = -1, k_hint = 0, idx = -1, w_row = 0;
+      int loaded_tile = -1, k_hint = 0, w_row = 0;
+      int idx[8];
       bool hint_mirrored = false;
-      const __half *src_row = P.feats;
       while (active && ok) {
         const int tile = blockIdx.x + tile_i * gridDim.x;
-        if (tile >= P.n_tiles) break;
+        if (tile >= n_tiles) break;
         if (tile_i != loaded_tile) {
           loaded_tile = tile_i;
           int tt = tile;
-          const bool mirrored = tt >= P.n_tiles_plain;
-          if (mirrored) tt -= P.n_tiles_plain;
+          const bool mirrored = tt >= n_tiles_plain;
+          if (mirrored) tt -= n_tiles_plain;
           const int q0 = tt * kRows;
           int k = (mirrored == hint_mirrored) ? k_hint : 0;     // tiles arrive in increasing order
           while (k + 1 < P.rows && P.qnaddrs[k + 1] <= q0) ++k;
@@ -285,8 +293,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           const int p0 = P.naddrs[k] + (q0 - P.qnaddrs[k]);
           const int n = min(kRows, P.naddrs[k + 1] - p0);
           w_row = mirrored ? (P.K - 1 - k) : k;
-          idx = r < n ? (mirrored ? P.out_idx : P.in_idx)[p0 + r] : -1;
-          src_row = P.feats + (idx >= 0 ? static_cast<int64_t>(idx) * P.c_in : 0);
+          const int32_t *g = mirrored ? P.out_idx : P.in_idx;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) idx[i] = (rowbase + 16 * i) < n ? g[p0 + rowbase + 16 * i] : -1;
           // the scatter list (written by the team of the tile's first chunk) is read by the epilogue at most
           // kScatterRing - 1 tiles later
           if (jj == 0)
@@ -295,12 +304,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         const int stage = my_stage;
         if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
         if (r == 0) post_weights(stage, w_row * cpo + jj, min(kChunk, P.c_in - jj * kChunk), jj == 0, jj == cpo - 1);
-        const uint32_t dst = sbase + stage * kABytes + row_off;
+        const uint32_t dst = sbase + stage * kABytes + dst_off;
+        const int c = jj * kChunk + piece * 8;
 #pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          const int c = jj * kChunk + p * 8;
-          const bool take = idx >= 0 && c < P.c_in;
-          cp_async_16_ca(dst + dsw[p], take ? src_row + c : P.feats, take ? 16u : 0u);
+        for (int i = 0; i < 8; ++i) {
+          const bool take = idx[i] >= 0 && c < P.c_in;
+          cp_async_16(dst + i * 2048, take ? P.feats + static_cast<int64_t>(idx[i]) * P.c_in + c : P.feats, take ? 16u : 0u);
         }
         cp_async_mbar_arrive_noinc(bar_full(stage));
         my_stage += teams;
@@ -315,19 +324,18 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       const int n_words = (P.n_chunks + 31) >> 5;
       const uint32_t slab_bytes = kRows * P.K * 4;
       const uint32_t bar_slab0 = bar0 + 8u * (2 * kMaxStages + 6);
-      const bool one_offset_per_chunk = (P.c_in % kChunk) == 0;
       uint32_t q_base = 0;
       int q_mod_teams = 0;            // q_base % teams
       int my_stage = team;            // stage of this team's next item (items of a team advance by `teams` stages)
       uint32_t my_phase = 0;
-      if (tid == 0 && P.slab_bufs == 2 && static_cast<int>(blockIdx.x) < P.n_tiles) {
+      if (tid == 0 && P.slab_bufs == 2 && static_cast<int>(blockIdx.x) < n_tiles) {
         mbar_arrive_expect_tx(bar_slab0, slab_bytes);
         bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(blockIdx.x) * kRows * P.K, slab_bytes, bar_slab0);
       }
       for (int w = tid; w < 2 * n_words; w += kProducers) cmask[w] = 0;
       // Every thread runs the same sequence of named barriers; a failed wait only takes effect through the
       // OR-reduction of those barriers, so that all producer warps leave the loop in the same iteration.
-      for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
         const int buf = (P.slab_bufs == 2) ? (tile_i & 1) : 0;
         const int32_t *my_slab = slab + buf * kRows * P.K;
         uint32_t *my_cmask = cmask + (tile_i & 1) * n_words;
@@ -336,7 +344,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           // all warps have issued their share of the previous tile: the other slab and chunk mask are free
           if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
           const int next = tile + gridDim.x;
-          if (tid == 0 && next < P.n_tiles) {
+          if (tid == 0 && next < n_tiles) {
             mbar_arrive_expect_tx(bar_slab0 + 8u * (buf ^ 1), slab_bytes);
             bulk_g2s(sbase + P.off_slab + (buf ^ 1) * slab_bytes, P.map + static_cast<int64_t>(next) * kRows * P.K, slab_bytes,
                      bar_slab0 + 8u * (buf ^ 1));
@@ -384,31 +392,18 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           my_stage += teams;
           if (my_stage >= stages) { my_stage -= stages; my_phase ^= 1; }
           if (r == 0) post_weights(stage, j, min(kChunk, P.R - j * kChunk), e == 0, e == n_chunks_tile - 1);
-          const uint32_t dst = sbase + stage * kABytes + row_off;
-          if (one_offset_per_chunk) {
-            const int rr = j * kChunk;
-            const int k = __float2int_rd((static_cast<float>(rr) + 0.5f) * inv_c_in);
-            const int idx = my_slab[r * P.K + k];
-            const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + (rr - k * P.c_in)) : 0);
-            const uint32_t bytes = idx >= 0 ? 16u : 0u;
+          // this thread's piece belongs to one offset k and starts at channel c of it
+          const int rr = j * kChunk + piece * 8;
+          const int k = __float2int_rd((static_cast<float>(rr) + 0.5f) * inv_c_in);
+          const int c = rr - k * P.c_in;
+          const bool piece_valid = rr < P.R;
+          const uint32_t dst = sbase + stage * kABytes + dst_off;
+          const int32_t *col = my_slab + rowbase * P.K + k;
 #pragma unroll
-            for (int p = 0; p < 8; ++p)
-              cp_async_16_ca(dst + dsw[p], idx >= 0 ? src + 8 * p : src, bytes);
-          } else {
-            int cur_k = -1, idx = -1;
-#pragma unroll
-            for (int p = 0; p < 8; ++p) {
-              const int rr = j * kChunk + p * 8;
-              int k = __float2int_rd((static_cast<float>(rr) + 0.5f) * inv_c_in);
-              const int c = rr - k * P.c_in;
-              if (rr >= P.R) k = -2;                                  // zero padding behind the last offset
-              if (k != cur_k) {
-                cur_k = k;
-                idx = k >= 0 ? my_slab[r * P.K + k] : -1;
-              }
-              const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
-              cp_async_16_ca(dst + dsw[p], src, idx >= 0 ? 16u : 0u);
-            }
+          for (int i = 0; i < 8; ++i) {
+            const int idx = piece_valid ? col[i * 16 * P.K] : -1;
+            const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
+            cp_async_16(dst + i * 2048, src, idx >= 0 ? 16u : 0u);
           }
           cp_async_mbar_arrive_noinc(bar_full(stage));
         }
@@ -427,7 +422,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       uint32_t acc_phase[2] = {0, 0};
       bool ok = true;
       int tile_i = 0;
-      for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++tile_i) {
         const int b = tile_i & 1;
         if (!mbar_wait(bar_acc_empty(b), acc_phase[b] ^ 1, abort_flag)) break;
         acc_phase[b] ^= 1;
@@ -460,7 +455,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     const int row = q * 32 + lane;
     uint32_t acc_phase[2] = {0, 0};
     int tile_i = 0;
-    for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
       const int b = tile_i & 1;
       if (!mbar_wait(bar_acc_full(b), acc_phase[b], abort_flag)) break;
       acc_phase[b] ^= 1;
@@ -541,6 +536,282 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
   }
 }
 
+// =====================================================================================================================
+// Output-stationary kernel for c_out <= 128: the operand roles are exchanged.  The tensor pipe spends ~128 cycles on an
+// M=128, K=16 MMA whatever N <= 256 is, so a narrow layer (N = c_out = 32..128) wastes most of it.  Here the WEIGHTS are
+// the M operand (c_out rows padded to 128; the padding rows read whatever follows in shared memory and produce
+// accumulator rows nobody reads) and 256 TARGETS are the N operand: one MMA covers two 128-target tiles.
+// Accumulator: TMEM lane = output channel, column = target.  Epilogue thread c owns channel c, so bias / scale / shift
+// are per-thread constants, and for a fixed target the 32 lanes of a warp store 32 consecutive channels (64 bytes).
+// =====================================================================================================================
+constexpr int kN2Rows = 256;                 // targets per tile (MMA N)
+constexpr int kN2FeatBytes = kN2Rows * 128;  // one feature stage
+constexpr int kN2TeamThreads = 128;          // a team: 8 lanes per row, 16 rows per thread
+
+struct ConvN2Params {
+  const __half *feats;
+  const unsigned char *packed;
+  __half *out;
+  Epilogue ep;
+  int32_t *status;
+  const int32_t *map;  // [T_al][K]
+  int T, T_al, n_tiles, K, c_in, c_out, R, n_chunks;
+  int stages, w_bytes, w_stride;
+  int off_feat, off_slab, off_tr, off_cm, off_meta, off_bar;
+};
+
+__global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __grid_constant__ ConvN2Params P) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char *smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  const uint32_t sbase = smem_u32(smem);
+  int32_t *slab = reinterpret_cast<int32_t *>(smem + P.off_slab);
+  uint32_t *cmask = reinterpret_cast<uint32_t *>(smem + P.off_cm);
+  int32_t *meta = reinterpret_cast<int32_t *>(smem + P.off_meta);
+  const uint32_t bar0 = sbase + P.off_bar;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
+  auto bar_acc_full = [&](int b) { return bar0 + 8u * (2 * kMaxStages + b); };
+  auto bar_acc_empty = [&](int b) { return bar0 + 8u * (2 * kMaxStages + 2 + b); };
+  const uint32_t bar_slab = bar0 + 8u * (2 * kMaxStages + 6);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + P.off_bar + 8 * (2 * kMaxStages + 4));
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + P.off_bar + 8 * (2 * kMaxStages + 4) + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int stages = P.stages;
+  constexpr int kTeams = kProducers / kN2TeamThreads;   // 4
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar_full(s), kN2TeamThreads + 1);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), 128);
+    }
+    mbar_init(bar_slab, 1);
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < kProducerWarps) {
+    // =========================== producers: 4 teams of 128 threads, stage s is filled by team s % 4 ===========
+    // Thread r of a team owns ONE 16-byte piece (r & 7) of 16 rows (r >> 3, +16, ...): the eight lanes that share a row
+    // read 128 contiguous bytes, so a warp-level copy touches 4 rows instead of 32 different cache lines (the L1
+    // processes one line per cycle: a thread-per-row mapping is bound by that, not by bandwidth).
+    const int team = warp >> 2, r = tid & 127;
+    const int piece = r & 7, rowbase = r >> 3;
+    const uint32_t dst_off = rowbase * 128 + ((piece ^ (rowbase & 7)) << 4);   // (row & 7) == (rowbase & 7) for all 16 rows
+    const float inv_c_in = 1.0f / static_cast<float>(P.c_in);
+    const int n_words = (P.n_chunks + 31) >> 5;
+    bool ok = true;
+    int tile_i = 0, q_mod_teams = 0, my_stage = team;
+    uint32_t my_phase = 0;
+    for (int w = tid; w < 2 * n_words; w += kProducers) cmask[w] = 0;
+    for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+      uint32_t *my_cmask = cmask + (tile_i & 1) * n_words;
+      // every warp has issued its share of the previous tile: the slab may be overwritten
+      if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
+      const int t0 = tile * kN2Rows;
+      const int rows_here = min(kN2Rows, P.T_al - t0);          // the map has T_al rows (a multiple of 128)
+      if (tid == 0) {
+        const uint32_t bytes = static_cast<uint32_t>(rows_here) * P.K * 4;
+        mbar_arrive_expect_tx(bar_slab, bytes);
+        bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(t0) * P.K, bytes, bar_slab);
+      }
+      for (int i = rows_here * P.K + tid; i < kN2Rows * P.K; i += kProducers) slab[i] = -1;
+      if (!mbar_wait(bar_slab, tile_i & 1, abort_flag)) ok = false;
+      if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
+      // non-empty 64-wide reduction chunks of this tile (one bit per chunk), spread over the warps
+      for (int j = warp; j < P.n_chunks; j += kProducerWarps) {
+        const int k_lo = __float2int_rd((static_cast<float>(j * kChunk) + 0.5f) * inv_c_in);
+        const int k_hi = min(__float2int_rd((static_cast<float>(j * kChunk + kChunk - 8) + 0.5f) * inv_c_in), P.K - 1);
+        int v = -1;
+        for (int k = k_lo; k <= k_hi; ++k)
+#pragma unroll
+          for (int qd = 0; qd < 8; ++qd) v = max(v, slab[(lane + 32 * qd) * P.K + k]);
+        if (__ballot_sync(0xffffffffu, v >= 0) && lane == 0) atomicOr(&my_cmask[j >> 5], 1u << (j & 31));
+      }
+      if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
+      for (int w = tid; w < n_words; w += kProducers) cmask[((tile_i + 1) & 1) * n_words + w] = 0;
+      int n_chunks_tile = 0;
+      for (int w = 0; w < n_words; ++w) n_chunks_tile += __popc(my_cmask[w]);
+      const bool force_first = (n_chunks_tile == 0);
+      if (force_first) n_chunks_tile = 1;
+      int word = 0, before = 0;
+      int e = team - q_mod_teams;
+      if (e < 0) e += kTeams;
+      for (; ok && e < n_chunks_tile; e += kTeams) {
+        int j = 0;
+        if (!force_first) {
+          while (before + __popc(my_cmask[word]) <= e) { before += __popc(my_cmask[word]); ++word; }
+          j = (word << 5) + __fns(my_cmask[word], 0, e - before + 1);
+        }
+        const int stage = my_stage;
+        if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
+        my_stage += kTeams;
+        if (my_stage >= stages) { my_stage -= stages; my_phase ^= 1; }
+        if (r == 0) {
+          const int valid = min(kChunk, P.R - j * kChunk);
+          meta[stage] = ((valid + 15) >> 4) | ((e == 0) << 8) | ((e == n_chunks_tile - 1) << 9);
+          mbar_arrive_expect_tx(bar_full(stage), P.w_bytes);
+          bulk_g2s(sbase + stage * P.w_stride, P.packed + static_cast<int64_t>(j) * P.w_bytes, P.w_bytes, bar_full(stage));
+        }
+        // this thread's piece belongs to one offset k and starts at channel c of it
+        const int rr = j * kChunk + piece * 8;
+        const int k = __float2int_rd((static_cast<float>(rr) + 0.5f) * inv_c_in);
+        const int c = rr - k * P.c_in;
+        const bool piece_valid = rr < P.R;
+        const uint32_t dst = sbase + P.off_feat + stage * kN2FeatBytes + dst_off;
+        const int32_t *col = slab + rowbase * P.K + k;
+#pragma unroll
+        for (int i = 0; i < kN2Rows / 16; ++i) {
+          const int idx = piece_valid ? col[i * 16 * P.K] : -1;
+          const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
+          cp_async_16(dst + i * 2048, src, idx >= 0 ? 16u : 0u);
+        }
+        cp_async_mbar_arrive_noinc(bar_full(stage));
+      }
+      q_mod_teams += n_chunks_tile % kTeams;
+      if (q_mod_teams >= kTeams) q_mod_teams -= kTeams;
+    }
+    cp_async_wait_all();
+  } else if (warp == kMmaWarp) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      // fp16 x fp16 -> fp32, both K-major, M = 128 (channels), N = 256 (targets)
+      const uint32_t idesc = (1u << 4) | ((static_cast<uint32_t>(kN2Rows) >> 3) << 17) | ((128u >> 4) << 24);
+      int stage = 0, phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      bool ok = true;
+      int tile_i = 0;
+      for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+        const int b = tile_i & 1;
+        if (!mbar_wait(bar_acc_empty(b), acc_phase[b] ^ 1, abort_flag)) break;
+        acc_phase[b] ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + b * kN2Rows;
+        while (true) {
+          if (!mbar_wait(bar_full(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const int m = meta[stage];
+          const int nk = m & 0xff;
+          const bool first = (m >> 8) & 1, last = (m >> 9) & 1;
+          const uint64_t w_desc = smem_desc_k_sw128(sbase + stage * P.w_stride);
+          const uint64_t f_desc = smem_desc_k_sw128(sbase + P.off_feat + stage * kN2FeatBytes);
+          for (int ks = 0; ks < nk; ++ks)
+            mma_f16_ss(d_tmem, w_desc + 2 * ks, f_desc + 2 * ks, idesc, (first && ks == 0) ? 0u : 1u);
+          mma_commit(bar_empty(stage));
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+          if (last) {
+            mma_commit(bar_acc_full(b));
+            break;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // =========================== epilogue ===========================
+    // Accumulator lane = output channel, column = target.  Thread c applies the per-channel affine (its own constants)
+    // to 32 targets, rounds to fp16 and parks the values in a small per-warp tile; the warp then reads the tile
+    // transposed, so that thread t holds the 32 channels of ONE target: residual add and ReLU in fp16 pairs, four
+    // 16-byte stores per target row instead of 32 two-byte ones.
+    const int q = warp & 3;
+    const int c = q * 32 + lane;
+    const bool has_channel = c < P.c_out;
+    const int n_valid = min(32, P.c_out - q * 32);          // channels of this warp that exist (a multiple of 16)
+    const float bias = (has_channel && P.ep.bias) ? __half2float(P.ep.bias[c]) : 0.f;
+    const float scale = (has_channel && P.ep.scale) ? P.ep.scale[c] : 1.f;
+    const float shift = (has_channel && P.ep.shift) ? P.ep.shift[c] : 0.f;
+    uint32_t *tr = reinterpret_cast<uint32_t *>(smem + P.off_tr) + q * (32 * 17);
+    uint32_t acc_phase[2] = {0, 0};
+    int tile_i = 0;
+    for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+      const int b = tile_i & 1;
+      if (!mbar_wait(bar_acc_full(b), acc_phase[b], abort_flag)) break;
+      acc_phase[b] ^= 1;
+      tc_fence_after();
+      if (n_valid > 0) {
+        const uint32_t taddr = tmem_base + b * kN2Rows + (static_cast<uint32_t>(q * 32) << 16);
+        const int64_t t0 = static_cast<int64_t>(tile) * kN2Rows;
+        for (int jb = 0; jb < kN2Rows / 32; ++jb) {
+          if (t0 + jb * 32 >= P.T) break;                       // warp-uniform: no target left in this block
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + jb * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float x0 = (__uint_as_float(v[2 * i]) + bias) * scale + shift;
+            const float x1 = (__uint_as_float(v[2 * i + 1]) + bias) * scale + shift;
+            const __half2 h = __floats2half2_rn(x0, x1);            // targets 2i, 2i+1 of channel `lane`
+            tr[lane * 17 + i] = *reinterpret_cast<const uint32_t *>(&h);
+          }
+          __syncwarp();
+          // thread `lane` = target jb*32 + lane: channel cc sits in word (lane >> 1) of row cc, low or high half
+          const int64_t t = t0 + jb * 32 + lane;
+          const uint32_t sel = (lane & 1) ? 0x7632u : 0x5410u;      // PRMT: take the high / low halves of two words
+          uint32_t y[16];
+#pragma unroll
+          for (int m2 = 0; m2 < 16; ++m2) {
+            const uint32_t w0 = tr[(2 * m2) * 17 + (lane >> 1)];
+            const uint32_t w1 = tr[(2 * m2 + 1) * 17 + (lane >> 1)];
+            y[m2] = __byte_perm(w0, w1, sel);                       // (channel 2*m2, channel 2*m2+1) of this target
+          }
+          __syncwarp();
+          if (t < P.T) {
+            __half *dst = P.out + t * P.c_out + q * 32;
+            const __half *res = P.ep.residual ? P.ep.residual + t * P.c_out + q * 32 : nullptr;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (g * 8 < n_valid) {
+                uint4 o = make_uint4(y[4 * g], y[4 * g + 1], y[4 * g + 2], y[4 * g + 3]);
+                __half2 *oh = reinterpret_cast<__half2 *>(&o);
+                if (res) {
+                  const uint4 rv = *reinterpret_cast<const uint4 *>(res + g * 8);
+                  const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+                  for (int e2 = 0; e2 < 4; ++e2) oh[e2] = __hadd2(oh[e2], rh[e2]);
+                }
+                if (P.ep.relu) {
+                  const __half2 zero = __float2half2_rn(0.f);
+#pragma unroll
+                  for (int e2 = 0; e2 < 4; ++e2) oh[e2] = __hmax2(oh[e2], zero);
+                }
+                *reinterpret_cast<uint4 *>(dst + g * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_acc_empty(b));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    if (tid == 0 && P.status) atomicExch(P.status, 1);
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) { }
+    __syncthreads();
+  }
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ---- weight image ---------------------------------------------------------------------------
 
 // one thread per 16-byte piece of the image: chunk j, row n (output channel), piece p
@@ -596,6 +867,67 @@ __global__ void __launch_bounds__(128) conv_os_simt_kernel(const __half *__restr
     if (ep.residual) v += __half2float(ep.residual[t * c_out + co]);
     if (ep.relu) v = fmaxf(v, 0.f);
     out[t * c_out + co] = __float2half_rn(v);
+  }
+}
+
+
+// Output-stationary kernel for the network stems (3-8 input channels, 16/32/64 output channels): far too little
+// arithmetic for the tensor cores and rows too short for 16-byte gathers.  One thread per target keeps all COUT
+// accumulators in registers; the weights sit in shared memory as fp32 and are read as broadcast float4; the tile's map
+// slab is staged with coalesced 16-byte loads.
+template <int COUT>
+__global__ void __launch_bounds__(128) conv_os_stem_kernel(const __half *__restrict__ feats, const __half *__restrict__ w,
+                                                            Epilogue ep, const int32_t *__restrict__ map, int64_t T, int K,
+                                                            int c_in, __half *__restrict__ out) {
+  extern __shared__ __align__(16) unsigned char stem_smem[];
+  float *ws = reinterpret_cast<float *>(stem_smem);                              // [K][c_in][COUT]
+  int32_t *slab = reinterpret_cast<int32_t *>(stem_smem + static_cast<size_t>(K) * c_in * COUT * 4);   // [128][K]
+  const int tid = threadIdx.x;
+  for (int i = tid; i < K * c_in * COUT; i += 128) ws[i] = __half2float(w[i]);
+  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * 128;
+  const int4 *s4 = reinterpret_cast<const int4 *>(map + t0 * K);                 // the map has T_al rows: always in range
+  for (int i = tid; i < 32 * K; i += 128) reinterpret_cast<int4 *>(slab)[i] = s4[i];
+  __syncthreads();
+  const int64_t t = t0 + tid;
+  float acc[COUT];
+#pragma unroll
+  for (int co = 0; co < COUT; ++co) acc[co] = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int idx = slab[tid * K + k];
+    if (idx < 0) continue;
+    const __half *f = feats + static_cast<int64_t>(idx) * c_in;
+    const float4 *wk = reinterpret_cast<const float4 *>(ws + static_cast<size_t>(k) * c_in * COUT);
+    for (int ci = 0; ci < c_in; ++ci) {
+      const float x = __half2float(f[ci]);
+#pragma unroll
+      for (int c4 = 0; c4 < COUT / 4; ++c4) {
+        const float4 wv = wk[ci * (COUT / 4) + c4];
+        acc[4 * c4 + 0] = fmaf(x, wv.x, acc[4 * c4 + 0]);
+        acc[4 * c4 + 1] = fmaf(x, wv.y, acc[4 * c4 + 1]);
+        acc[4 * c4 + 2] = fmaf(x, wv.z, acc[4 * c4 + 2]);
+        acc[4 * c4 + 3] = fmaf(x, wv.w, acc[4 * c4 + 3]);
+      }
+    }
+  }
+  if (t >= T) return;
+  __half *dst = out + t * COUT;
+  const __half *res = ep.residual ? ep.residual + t * COUT : nullptr;
+#pragma unroll
+  for (int c8 = 0; c8 < COUT / 8; ++c8) {
+    uint4 pack, rv = make_uint4(0, 0, 0, 0);
+    if (res) rv = *reinterpret_cast<const uint4 *>(res + 8 * c8);
+    const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+    uint32_t *pw = reinterpret_cast<uint32_t *>(&pack);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int co = 8 * c8 + 2 * e;
+      float v0 = epilogue_apply(acc[co], co, ep), v1 = epilogue_apply(acc[co + 1], co + 1, ep);
+      if (res) { v0 += __low2float(rh[e]); v1 += __high2float(rh[e]); }
+      if (ep.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
+      const __half2 hv = __floats2half2_rn(v0, v1);
+      pw[e] = *reinterpret_cast<const uint32_t *>(&hv);
+    }
+    *reinterpret_cast<uint4 *>(dst + 8 * c8) = pack;
   }
 }
 
@@ -693,7 +1025,7 @@ template <bool kWS>
 static int launch_conv_tc(ConvParams &P, bool tma, size_t smem, int64_t num_sources, cudaStream_t st) {
   alignas(64) CUtensorMap tmap;
   std::memset(&tmap, 0, sizeof(tmap));
-  int grid = P.n_tiles < sm_count() ? P.n_tiles : sm_count();
+  int grid = (P.n_tiles >= 0 && P.n_tiles < sm_count()) ? P.n_tiles : sm_count();
   if (grid <= 0) return SPIRA_B200_OK;
   if (tma) {
     int rc = make_feats_tensor_map(&tmap, P.feats, num_sources, P.c_in);
@@ -737,6 +1069,31 @@ static size_t plan_smem(ConvParams &P, bool ws) {
   P.off_bar = P.off_meta + round16(kMaxStages * 4);
   return static_cast<size_t>(P.off_bar) + 8 * (2 * kMaxStages + 8) + 16 + 1024;
 }
+
+// Shared-memory plan of conv_os_n256_kernel; returns the dynamic shared memory size or 0 if it does not fit.
+static size_t plan_smem_n256(ConvN2Params &P) {
+  P.w_bytes = P.c_out * 128;
+  P.w_stride = (P.w_bytes + 1023) / 1024 * 1024;
+  const int slab_bytes = kN2Rows * P.K * 4;
+  const int n_words = (P.n_chunks + 31) / 32;
+  const int tr_bytes = 4 * 32 * 17 * 4;             // per epilogue warp: 32 channels x 16 fp16 pairs, padded rows
+  const int fixed = slab_bytes + tr_bytes + round16(2 * n_words * 4) + round16(kMaxStages * 4) + 8 * (2 * kMaxStages + 8) + 16;
+  const int per_stage = P.w_stride + kN2FeatBytes;
+  int stages = (kSmemBudget - fixed) / per_stage;
+  if (stages > kMaxStages) stages = kMaxStages;
+  stages &= ~3;                       // four producer teams: stage s is filled by team s % 4
+  if (stages < 4) return 0;
+  P.stages = stages;
+  P.off_feat = stages * P.w_stride;   // the weight stages come first: an M=128 descriptor may read past a short one
+  P.off_slab = P.off_feat + stages * kN2FeatBytes;
+  P.off_tr = P.off_slab + slab_bytes;
+  P.off_cm = P.off_tr + tr_bytes;
+  P.off_meta = P.off_cm + round16(2 * n_words * 4);
+  P.off_bar = P.off_meta + round16(kMaxStages * 4);
+  return static_cast<size_t>(P.off_bar) + 8 * (2 * kMaxStages + 8) + 16 + 1024;
+}
+
+static int g_os_n256 = 1;          // 1: layers with c_out <= 128 use the exchanged-operand kernel
 
 }  // namespace sb
 
@@ -784,6 +1141,22 @@ extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const 
   SB_CHECK_ARG((ep.scale == nullptr) == (ep.shift == nullptr), "conv_os: scale and shift must be given together");
   if (packed == nullptr) {
     SB_CHECK_ARG(weights != nullptr, "conv_os: neither weights nor a packed image given");
+    const size_t stem_smem = static_cast<size_t>(K) * c_in * c_out * 4 + static_cast<size_t>(128) * K * 4;
+    const bool aligned16 = reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(map_os) % 16 == 0 &&
+                           (ep.residual == nullptr || reinterpret_cast<uintptr_t>(ep.residual) % 16 == 0);
+    if (c_in <= 8 && (c_out == 16 || c_out == 32 || c_out == 64) && stem_smem <= 96 * 1024 && aligned16) {
+      const unsigned grid = static_cast<unsigned>(div_up(num_targets, 128));
+      auto launch = [&](auto kernel) -> int {
+        SB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(stem_smem)));
+        kernel<<<grid, 128, stem_smem, as_stream(stream)>>>(static_cast<const __half *>(feats), static_cast<const __half *>(weights),
+                                                            ep, map_os, num_targets, K, c_in, static_cast<__half *>(out));
+        SB_CHECK_LAUNCH();
+        return SPIRA_B200_OK;
+      };
+      if (c_out == 16) return launch(conv_os_stem_kernel<16>);
+      if (c_out == 32) return launch(conv_os_stem_kernel<32>);
+      return launch(conv_os_stem_kernel<64>);
+    }
     conv_os_simt_kernel<<<static_cast<unsigned>(div_up(num_targets, 4)), 128, 0, as_stream(stream)>>>(
         static_cast<const __half *>(feats), static_cast<const __half *>(weights), ep, map_os, num_targets, K, c_in, c_out,
         static_cast<__half *>(out));
@@ -795,6 +1168,29 @@ extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const 
                    reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(map_os) % 16 == 0 &&
                    (ep.residual == nullptr || reinterpret_cast<uintptr_t>(ep.residual) % 16 == 0),
                "conv_os: feats, packed, out, map and residual must be 16-byte aligned");
+  if (g_os_n256 && !g_gather_tma && c_out <= 128 && K <= 32) {
+    ConvN2Params Q{};
+    Q.feats = static_cast<const __half *>(feats);
+    Q.packed = static_cast<const unsigned char *>(packed);
+    Q.out = static_cast<__half *>(out);
+    Q.ep = ep;
+    Q.status = status;
+    Q.map = map_os;
+    Q.T = static_cast<int>(num_targets);
+    Q.T_al = static_cast<int>(align128(num_targets));
+    Q.n_tiles = static_cast<int>(div_up(num_targets, kN2Rows));
+    Q.K = K; Q.c_in = c_in; Q.c_out = c_out;
+    Q.R = K * c_in;
+    Q.n_chunks = static_cast<int>(div_up(Q.R, kChunk));
+    size_t smem2 = plan_smem_n256(Q);
+    if (smem2 != 0) {
+      SB_CHECK_CUDA(cudaFuncSetAttribute(conv_os_n256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
+      int grid = Q.n_tiles < sm_count() ? Q.n_tiles : sm_count();
+      conv_os_n256_kernel<<<grid, kConvThreads, smem2, as_stream(stream)>>>(Q);
+      SB_CHECK_LAUNCH();
+      return SPIRA_B200_OK;
+    }
+  }
   ConvParams P{};
   P.feats = static_cast<const __half *>(feats);
   P.packed = static_cast<const unsigned char *>(packed);
@@ -824,7 +1220,7 @@ extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const 
   SB_CHECK_ARG(K >= 1 && c_in >= 1 && c_out >= 1 && rows >= 1 && rows <= K, "conv_ws: K=%d c_in=%d c_out=%d rows=%d", K, c_in,
                c_out, rows);
   SB_CHECK_ARG(!mirror || (rows == (K + 1) / 2 && K % 2 == 1 && !swap), "conv_ws: mirror needs odd K, rows == (K+1)/2 and no swap");
-  SB_CHECK_ARG(num_tiles128 >= 0 && num_tiles128 < (int64_t(1) << 30), "conv_ws: num_tiles128 out of range");
+  SB_CHECK_ARG(num_tiles128 >= -1 && num_tiles128 < (int64_t(1) << 30), "conv_ws: num_tiles128 out of range");
   if (num_targets == 0) return SPIRA_B200_OK;
   SB_CHECK_ARG(accum && out && naddrs, "conv_ws: null pointer");
   Epilogue ep = make_epilogue(epilogue);
@@ -834,7 +1230,7 @@ extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const 
   SB_CHECK_CUDA(cudaMemsetAsync(accum, 0, sizeof(float) * n_out, st));
   const int32_t *gi = swap ? out_idx : in_idx;
   const int32_t *go = swap ? in_idx : out_idx;
-  if (num_tiles128 > 0) {
+  if (num_tiles128 != 0) {
     SB_CHECK_ARG(gi && go && feats, "conv_ws: null pointer");
     if (packed == nullptr) {
       SB_CHECK_ARG(weights != nullptr, "conv_ws: neither weights nor a packed image given");
@@ -855,10 +1251,15 @@ extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const 
       P.status = status;
       P.in_idx = gi; P.out_idx = go; P.naddrs = naddrs; P.qnaddrs = qnaddrs;
       P.rows = rows; P.mirror = mirror;
-      P.n_tiles_plain = static_cast<int>(num_tiles128);
       // the centre row (last of the half list) is its own mirror image: its tiles are not repeated
-      int64_t centre_tiles = mirror ? div_up(num_targets, kRows) : 0;
-      P.n_tiles = static_cast<int>(mirror ? 2 * num_tiles128 - centre_tiles : num_tiles128);
+      P.centre_tiles = static_cast<int>(div_up(num_targets, kRows));
+      if (num_tiles128 < 0) {
+        P.n_tiles_plain = -1;      // the kernel reads qnaddrs[rows] itself
+        P.n_tiles = -1;
+      } else {
+        P.n_tiles_plain = static_cast<int>(num_tiles128);
+        P.n_tiles = static_cast<int>(mirror ? 2 * num_tiles128 - P.centre_tiles : num_tiles128);
+      }
       P.T = static_cast<int>(num_targets);
       P.K = K; P.c_in = c_in; P.c_out = c_out;
       P.R = c_in;
@@ -877,12 +1278,14 @@ extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const 
 extern "C" int spira_b200_set_option(const char *name, int value) {
   SB_CHECK_ARG(name != nullptr, "set_option: null name");
   if (std::strcmp(name, "gather_tma") == 0) { g_gather_tma = value ? 1 : 0; return SPIRA_B200_OK; }
+  if (std::strcmp(name, "os_n256") == 0) { g_os_n256 = value ? 1 : 0; return SPIRA_B200_OK; }
   return fail(SPIRA_B200_ERR_ARGUMENT, "set_option: unknown option '%s'", name);
 }
 
 extern "C" int spira_b200_get_option(const char *name) {
   if (name == nullptr) return -1;
   if (std::strcmp(name, "gather_tma") == 0) return g_gather_tma;
+  if (std::strcmp(name, "os_n256") == 0) return g_os_n256;
   if (std::strcmp(name, "os_pack_mode") == 0) return g_gather_tma ? SPIRA_B200_PACK_WS : SPIRA_B200_PACK_OS;
   return -1;
 }
@@ -920,3 +1323,4 @@ extern "C" int spira_b200_conv_ws_static(const void *feats, const void *weights,
   return spira_b200_conv_ws(feats, weights, packed, epilogue, in_idx, out_idx, naddrs, qnaddrs, rows, num_tiles128, mirror,
                             swap, num_sources, num_targets, K, c_in, c_out, g_static_accum_ptr[dev], out, status, stream);
 }
+

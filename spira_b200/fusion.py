@@ -36,6 +36,18 @@ def _fuse_sequential(seq: nn.Sequential) -> int:
     i = 0
     while i < len(mods):
         name, m = mods[i]
+        if isinstance(m, SparseConv) and m.is_trivial and m._folded is None and i + 1 < len(mods):
+            bn_name, bn = mods[i + 1]
+            if isinstance(bn, BatchNorm) and not bn.training and bn.track_running_stats:
+                # a 1x1x1 stride-1 layer is a matrix product: the BatchNorm affine folds into its weight and bias
+                scale, shift = bn_affine(bn)
+                w = m.kernel.detach().view(m.in_channels, m.out_channels).float() * scale[None, :]
+                b = shift if m.bias is None else m.bias.detach().float() * scale + shift
+                m._folded = (w.to(m.kernel.dtype).contiguous(), b.to(m.kernel.dtype).contiguous())
+                setattr(seq, bn_name, nn.Identity())
+                fused += 1
+                i += 2
+                continue
         if isinstance(m, SparseConv) and not m.is_trivial and m._fused is None and i + 1 < len(mods):
             bn_name, bn = mods[i + 1]
             if isinstance(bn, BatchNorm) and not bn.training and bn.track_running_stats:

@@ -20,6 +20,7 @@ from torch.nn import Module
 from spira_b200.nn import functional as F
 from spira_b200.nn.functional import _C
 from spira_b200.tensors import SparseTensor
+from spira_b200 import compile as _compile
 from spira_b200.utils.helpers import as_tuple
 from spira_b200.utils.typing import ScalarOrTuple
 
@@ -39,7 +40,8 @@ class KernelMapCache(object):
 
     def get_target_coordinates(self, source_coordinates: torch.Tensor, source_stride: ScalarOrTuple[int],
                                target_stride: ScalarOrTuple[int], transposed: bool = False):
-        source_stride = as_tuple(source_stride, size=3, name="source_stride")
+        if type(source_stride) is not tuple:
+            source_stride = as_tuple(source_stride, size=3, name="source_stride")
         if source_stride not in self._coordinates_cache:
             self._coordinates_cache[source_stride] = source_coordinates
         if target_stride in self._coordinates_cache:
@@ -55,9 +57,12 @@ class KernelMapCache(object):
                        target_coordinates: torch.Tensor, target_stride: ScalarOrTuple[int],
                        kernel_size: ScalarOrTuple[int], map_dataflow: int, force_os: bool = False,
                        transposed: bool = False):
-        source_stride = as_tuple(source_stride, size=3, name="source_stride")
-        target_stride = as_tuple(target_stride, size=3, name="target_stride")
-        kernel_size = as_tuple(kernel_size, size=3, name="kernel_size")
+        if type(source_stride) is not tuple:
+            source_stride = as_tuple(source_stride, size=3, name="source_stride")
+        if type(target_stride) is not tuple:
+            target_stride = as_tuple(target_stride, size=3, name="target_stride")
+        if type(kernel_size) is not tuple:
+            kernel_size = as_tuple(kernel_size, size=3, name="kernel_size")
         key = (target_stride, source_stride, kernel_size) if transposed else (source_stride, target_stride, kernel_size)
 
         if key not in self._kernel_maps_cache:
@@ -83,7 +88,11 @@ class KernelMapCache(object):
             # rebuilds it on every forward (conv.py:85-89); it depends only on the cached map, so it is kept.
             dkey = (key, "inverted")
             if dkey not in self._derived or not getattr(_C, "CACHE_DERIVED", True):
-                self._derived[dkey] = F.convert_transposed_os(entry[3], entry[1])
+                inv = F.convert_transposed_os(entry[3], entry[1])
+                sb = getattr(entry[3], "_sb", None)
+                if sb is not None:
+                    inv._sb = dict(sb, ws=None, counts=None)
+                self._derived[dkey] = inv
             new_entry = list(entry[1:])
             new_entry[2] = self._derived[dkey]
             return new_entry
@@ -102,7 +111,9 @@ class KernelMapCache(object):
         for i, t_stride in enumerate(target_strides):
             self._coordinates_cache[as_tuple(t_stride, size=3)] = voxels[i + 1]
 
-        kmaps = F.build_kmap_streamed(voxels, kernel_sizes, source_strides[:-1], dataflow)
+        # the layers of this package read the pair lists through the engine's own structures, so the list sizes can
+        # stay on the device (no second host synchronisation per scene)
+        kmaps = F.build_kmap_streamed(voxels, kernel_sizes, source_strides[:-1], dataflow, exact_sizes=False)
 
         for i in range(len(kernel_sizes)):
             t_stride = as_tuple(source_strides[i + 1], size=3)
@@ -148,6 +159,9 @@ class SparseConv(Module):
         # optional fused epilogue (set by spira_b200.fuse): per-channel fp32 scale / shift and a ReLU flag that the
         # kernels apply to the fp32 accumulator before the single rounding to fp16
         self._fused = None
+        self._folded = None        # 1x1x1 layer with a BatchNorm folded into it by spira_b200.fuse: (weight, bias)
+        self._call = None          # prepared native call (spira_b200.nn.functional._C.ConvCall)
+        self._trivial = all(x == 1 for x in self.stride) and all(x == 1 for x in self.kernel_size)
 
     def set_fused_epilogue(self, scale: Optional[torch.Tensor], shift: Optional[torch.Tensor], relu: bool):
         """``y = relu?((conv(x) + bias) * scale + shift [+ residual])`` inside the convolution kernel."""
@@ -172,7 +186,7 @@ class SparseConv(Module):
 
     @property
     def is_trivial(self):
-        return all(x == 1 for x in self.stride) and all(x == 1 for x in self.kernel_size)
+        return self._trivial
 
     @contextlib.contextmanager
     def tune_gs(self, free_buffers: bool = True):
@@ -186,8 +200,18 @@ class SparseConv(Module):
             self._tuning_data = None
 
     def forward(self, inputs: SparseTensor, residual: Optional[torch.Tensor] = None):
+        output = self._forward(inputs, residual)
+        rec = _compile._recorder
+        if rec is not None:
+            rec.conv(self, inputs, residual, output)
+        return output
+
+    def _forward(self, inputs: SparseTensor, residual: Optional[torch.Tensor] = None):
         source_features = inputs._features
         if self.is_trivial:
+            if self._folded is not None:
+                return SparseTensor(features=torch.addmm(self._folded[1], source_features, self._folded[0]),
+                                    coordinates=inputs._coordinates, stride=inputs._stride)
             kernel = self.kernel.view(self.in_channels, self.out_channels)
             target_features = torch.mm(source_features, kernel)
             target_coordinates = inputs._coordinates
@@ -208,18 +232,21 @@ class SparseConv(Module):
             # NON-transposed twin; a transposed layer exchanges the roles of sources and targets
             n_src, n_tgt = (m[1], m[0]) if self.transposed else (m[0], m[1])
 
-            if self._fused is not None or residual is not None:
+            sb = getattr(m[2], "_sb", None) if hasattr(_C, "run_conv_os") else None
+            if sb is not None and (map_dataflow == 0 or force_os or sb.get("ws") is not None):
                 # engine-native call: bias / BatchNorm affine / residual / ReLU are applied in the kernel epilogue
-                fz = self._fused or dict(scale=None, shift=None, relu=False)
-                kw = dict(bias=self.bias, scale=fz["scale"], shift=fz["shift"], residual=residual, relu=fz["relu"])
+                call = self._call
+                if call is None or call.stamp != _C.conv_call_stamp(self.kernel, self.bias, self._fused):
+                    call = self._call = _C.ConvCall(self.kernel, self.bias, self._fused)
                 if map_dataflow == 0 or force_os:
-                    target_features = _C.conv_os(n_src, n_tgt, m[2], source_features, self.kernel, **kw)
+                    target_features = _C.run_conv_os(call, n_src, n_tgt, m[2], source_features, residual)
                 else:
-                    lists = (getattr(m[3], "_sb", None) or {}).get("ws")
-                    if lists is None:
-                        raise RuntimeError("[spira_b200] the fused epilogue needs kernel maps built by this engine")
-                    target_features = _C.conv_ws(n_src, n_tgt, source_features, self.kernel, lists, swap=self.transposed, **kw)
+                    if self._tuning_data is not None and map_dataflow % 2 == 0:
+                        self._tuning_data.append(((m[4], m[3]) if self.transposed else (m[3], m[4])) + (m[5],))
+                    target_features = _C.run_conv_ws(call, n_src, n_tgt, sb["ws"], source_features, self.transposed, residual)
                 return SparseTensor(features=target_features, coordinates=target_coordinates, stride=target_stride)
+            if self._fused is not None or residual is not None:
+                raise RuntimeError("[spira_b200] the fused epilogue needs kernel maps built by this engine")
             if map_dataflow == 0 or force_os:
                 target_features = F.sparse_convolution_forward_os(n_src, n_tgt, m[2], source_features, self.kernel)
             elif map_dataflow % 2 == 1:

@@ -28,7 +28,8 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream(device) -> C.c_void_p:
-    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    idx = torch.device(device).index
+    return C.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device() if idx is None else idx))
 
 
 def _require_cuda(*tensors):
@@ -164,7 +165,10 @@ def _dataflow_layout(dataflow: int) -> int:
     return LAYOUT_OS if dataflow == 0 else LAYOUT_WS
 
 
-def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows):
+LAZY_SIZES = True   # cuda_binary_search_streamed(..., exact_sizes=False) keeps the list sizes on the device
+
+
+def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_sizes=True):
     """Shared implementation of the serial and the network-wide builders.
 
     ``voxel_pairs[i] = (sources, targets)``.  One search launch per group of <= 16 maps, one
@@ -232,18 +236,28 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows):
                               _ptr(m["naddrs"]), _ptr(m["qnaddrs"]), _ptr(m["tile_base"]), _ptr(sizes[j]), stream)
             else:
                 m["nbsizes"].zero_(); m["naddrs"].zero_(); m["qnaddrs"].zero_(); sizes[j].zero_()
-        host_sizes = sizes.cpu().tolist()
+        # exact_sizes: one host read of all list sizes (the reference reads them per map) so that nbmaps has its exact
+        # shape [2, nnz].  Otherwise nothing is read back: the lists get their worst-case capacity (rows * T pairs,
+        # allocated but never touched beyond nnz) and the kernels take the sizes from naddrs / qnaddrs on the device.
+        host_sizes = sizes.cpu().tolist() if exact_sizes else None
         for j, m in enumerate(ws_maps):
-            mapsize, qmapsize = host_sizes[j]
             rows = m["rows"]
-            nbmaps = torch.empty((2, mapsize), dtype=torch.int32, device=dev)
-            if mapsize > 0:
+            if exact_sizes:
+                mapsize, qmapsize = host_sizes[j]
+                cap = mapsize
+            else:
+                mapsize = qmapsize = None
+                cap = rows * m["T"]
+            nbmaps = torch.empty((2, cap), dtype=torch.int32, device=dev)
+            if cap > 0 and m["Tal"] > 0:
                 _lib.call("spira_b200_kmap_ws_pairs", _ptr(m["dense"]), rows, m["Tal"], _ptr(m["naddrs"]),
                           _ptr(m["tile_base"]), _ptr(nbmaps[0]), _ptr(nbmaps[1]), stream)
             w = WsLists()
             w.nbmaps, w.in_idx, w.out_idx = nbmaps, nbmaps[0], nbmaps[1]
             w.nbsizes, w.naddrs, w.qnaddrs = m["nbsizes"][:rows], m["naddrs"][:rows + 1], m["qnaddrs"][:rows + 1]
-            w.rows, w.mirror, w.mapsize, w.qmapsize = rows, bool(m["half"]), int(mapsize), int(qmapsize)
+            w.rows, w.mirror = rows, bool(m["half"])
+            w.mapsize = None if mapsize is None else int(mapsize)
+            w.qmapsize = None if qmapsize is None else int(qmapsize)
             m["ws"] = w
 
     results = []
@@ -274,14 +288,14 @@ def cuda_binary_search(sources, targets, kernel_size, source_stride, dataflow: i
     return _build_maps([(sources.contiguous(), targets.contiguous())], [kernel_size], [source_stride], [dataflow])[0]
 
 
-def cuda_binary_search_streamed(voxels, kernel_sizes, source_strides, dataflow):
+def cuda_binary_search_streamed(voxels, kernel_sizes, source_strides, dataflow, exact_sizes=True):
     """All kernel maps of a network in one go; map ``i`` uses ``voxels[i // 2]`` as sources and
     ``voxels[(i + 1) // 2]`` as targets (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:894-1645, :945-946)."""
     if not (len(kernel_sizes) == len(source_strides) == len(dataflow)):
         raise RuntimeError("[spira_b200] kernel_sizes, source_strides and dataflow must have the same length")
     voxels = [v.contiguous() for v in voxels]
     pairs = [(voxels[i // 2], voxels[(i + 1) // 2]) for i in range(len(kernel_sizes))]
-    return _build_maps(pairs, kernel_sizes, source_strides, dataflow)
+    return _build_maps(pairs, kernel_sizes, source_strides, dataflow, exact_sizes)
 
 
 def cuda_binary_search_no_small_z(sources, targets, kernel_size, source_stride):
@@ -376,9 +390,12 @@ def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None
     if out_in_map.dim() != 2 or out_in_map.shape[1] != K or out_in_map.shape[0] < num_targets:
         raise RuntimeError(f"[spira_b200] out_in_map must be [T_al, {K}] with T_al >= {num_targets}, got {tuple(out_in_map.shape)}")
     out = torch.empty((num_targets, cout), dtype=torch.float16, device=sources.device)
+    if out_in_map.shape[0] != _aligned(num_targets):
+        # the kernels read whole 128-row tiles of the map: bring a short map to T_al rows
+        padded = torch.full((_aligned(num_targets), K), -1, dtype=torch.int32, device=out_in_map.device)
+        padded[:num_targets] = out_in_map[:num_targets]
+        out_in_map = padded
     packed = None if force_simt else packed_weights(weights, _lib.load().spira_b200_get_option(b"os_pack_mode"))
-    if packed is not None and out_in_map.shape[0] != _aligned(num_targets):
-        packed = None
     ep, keep = _epilogue(bias, scale, shift, residual, relu)
     _lib.call("spira_b200_conv_os", _ptr(sources), _ptr(weights), _ptr(packed), C.byref(ep) if ep is not None else None,
               _ptr(out_in_map), int(num_sources), int(num_targets), K, cin, cout, _ptr(out), _ptr(status_word(sources.device)),
@@ -401,8 +418,114 @@ def conv_ws(num_sources, num_targets, sources, weights, lists: WsLists, *, swap=
     ep, keep = _epilogue(bias, scale, shift, residual, relu)
     _lib.call("spira_b200_conv_ws", _ptr(sources), _ptr(weights), _ptr(packed), C.byref(ep) if ep is not None else None,
               _ptr(lists.in_idx), _ptr(lists.out_idx), _ptr(lists.naddrs), _ptr(lists.qnaddrs), lists.rows,
-              lists.qmapsize // 128, 1 if mirror else 0, 1 if swap else 0, int(num_sources), int(num_targets), K, cin, cout,
+              -1 if lists.qmapsize is None else lists.qmapsize // 128, 1 if mirror else 0, 1 if swap else 0, int(num_sources), int(num_targets), K, cin, cout,
               _ptr(accum), _ptr(out), _ptr(status_word(sources.device)), _stream(sources.device))
+    return out
+
+
+# ---- prepared per-layer calls: the hot path of a network forward ----------------------------------------------------
+_raw_stream = torch._C._cuda_getCurrentRawStream     # (device index) -> cudaStream_t as int, no Python object churn
+
+
+def _no_call():
+    return None
+
+
+class ConvCall:
+    """Everything about one layer that does not change between forwards: the packed weight images, the epilogue
+    struct, the resolved C functions.  ``SparseConv`` keeps one and the two ``run_*`` functions below add only the
+    per-call pointers, so that a forward costs a few microseconds of Python per layer."""
+    __slots__ = ("stamp", "weights", "K", "cin", "cout", "w_ptr", "packed", "ep", "ep_ref", "keep", "dev_index", "status",
+                 "status_ptr", "fn_os", "fn_ws", "eligible")
+
+    def __init__(self, weights: torch.Tensor, bias, fused):
+        lib = _lib.load()
+        if weights.dtype != torch.float16 or not weights.is_cuda or not weights.is_contiguous():
+            raise RuntimeError("[spira_b200] layer weights must be contiguous float16 CUDA tensors")
+        self.weights = weights
+        self.K, self.cin, self.cout = weights.shape
+        self.w_ptr = weights.data_ptr()
+        self.eligible = bool(lib.spira_b200_tensor_core_eligible(self.K, self.cin, self.cout))
+        self.packed = {}
+        scale = shift = None
+        relu = False
+        if fused is not None:
+            scale, shift, relu = fused["scale"], fused["shift"], fused["relu"]
+        self.ep, self.keep = _epilogue(bias, scale, shift, None, relu)
+        if self.ep is None:
+            self.ep = Epilogue()
+        self.ep_ref = C.byref(self.ep)
+        self.dev_index = weights.device.index
+        self.status = status_word(weights.device)
+        self.status_ptr = self.status.data_ptr()
+        self.fn_os, self.fn_ws = lib.spira_b200_conv_os, lib.spira_b200_conv_ws
+        self.stamp = (weights.data_ptr(), weights._version, None if bias is None else (bias.data_ptr(), bias._version),
+                      None if fused is None else (id(fused["scale"]), id(fused["shift"]), fused["relu"]))
+
+    # a prepared call holds raw pointers: copies and pickles of a layer start without one and rebuild it lazily
+    def __deepcopy__(self, memo):
+        return None
+
+    def __reduce__(self):
+        return (_no_call, ())
+
+    def packed_ptr(self, mode: int):
+        if not self.eligible:
+            return None
+        p = self.packed.get(mode)
+        if p is None:
+            p = packed_weights(self.weights, mode)
+            self.packed[mode] = p
+        return p.data_ptr()
+
+
+def conv_call_stamp(weights, bias, fused):
+    return (weights.data_ptr(), weights._version, None if bias is None else (bias.data_ptr(), bias._version),
+            None if fused is None else (id(fused["scale"]), id(fused["shift"]), fused["relu"]))
+
+
+def run_conv_os(call: ConvCall, num_sources: int, num_targets: int, out_in_map: torch.Tensor, feats: torch.Tensor,
+                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Output-stationary forward of a prepared layer.  ``out_in_map`` is an engine-built ``[T_al, K]`` map."""
+    if not feats.is_contiguous():
+        feats = feats.contiguous()
+    out = torch.empty((num_targets, call.cout), dtype=torch.float16, device=feats.device)
+    call.ep.residual = residual.data_ptr() if residual is not None else None
+    args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(_lib.load().spira_b200_get_option(b"os_pack_mode")),
+            call.ep_ref, out_in_map.data_ptr(), num_sources, num_targets, call.K, call.cin, call.cout, out.data_ptr(),
+            call.status_ptr, _raw_stream(call.dev_index))
+    if _lib.profile_hook is not None:
+        _lib.profile_hook("spira_b200_conv_os", args, lambda: _lib.check(call.fn_os(*args)))
+    else:
+        rc = call.fn_os(*args)
+        if rc != 0:
+            _lib.check(rc)
+    _lib.launch_count += 1
+    return out
+
+
+def run_conv_ws(call: ConvCall, num_sources: int, num_targets: int, lists: WsLists, feats: torch.Tensor, swap: bool,
+                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Weight-stationary forward of a prepared layer over the engine's pair lists."""
+    if not feats.is_contiguous():
+        feats = feats.contiguous()
+    if lists.mirror and swap:
+        raise RuntimeError("[spira_b200] a mirrored (submanifold) list cannot be used transposed")
+    out = torch.empty((num_targets, call.cout), dtype=torch.float16, device=feats.device)
+    accum = torch.empty((num_targets, call.cout), dtype=torch.float32, device=feats.device)
+    call.ep.residual = residual.data_ptr() if residual is not None else None
+    args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(PACK_WS), call.ep_ref, lists.in_idx.data_ptr(),
+            lists.out_idx.data_ptr(), lists.naddrs.data_ptr(), lists.qnaddrs.data_ptr(), lists.rows,
+            -1 if lists.qmapsize is None else lists.qmapsize // 128, 1 if lists.mirror else 0, 1 if swap else 0,
+            num_sources, num_targets, call.K, call.cin, call.cout, accum.data_ptr(), out.data_ptr(), call.status_ptr,
+            _raw_stream(call.dev_index))
+    if _lib.profile_hook is not None:
+        _lib.profile_hook("spira_b200_conv_ws", args, lambda: _lib.check(call.fn_ws(*args)))
+    else:
+        rc = call.fn_ws(*args)
+        if rc != 0:
+            _lib.check(rc)
+    _lib.launch_count += 2
     return out
 
 

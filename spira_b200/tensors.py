@@ -40,7 +40,11 @@ class SparseTensor(object):
         return self
 
     def __add__(self, other):
-        return SparseTensor(coordinates=self._coordinates, features=self._features + other._features, stride=self._stride)
+        from spira_b200 import compile as _compile
+        output = SparseTensor(coordinates=self._coordinates, features=self._features + other._features, stride=self._stride)
+        if _compile._recorder is not None:
+            _compile._recorder.add(self, other, output)
+        return output
 
     def order(self):
         """Packs ``[N,3]`` coordinates into sorted keys and permutes the features accordingly

@@ -8,4 +8,8 @@ __all__ = ["fapply"]
 
 def fapply(input, fn: Callable[..., torch.Tensor], *args, **kwargs):
     from spira_b200.tensors import SparseTensor
-    return SparseTensor(coordinates=input._coordinates, features=fn(input._features, *args, **kwargs), stride=input._stride)
+    from spira_b200 import compile as _compile
+    output = SparseTensor(coordinates=input._coordinates, features=fn(input._features, *args, **kwargs), stride=input._stride)
+    if _compile._recorder is not None:
+        _compile._recorder.apply(fn, args, kwargs, input, output)
+    return output

@@ -59,26 +59,57 @@ class DataflowConfig:
         return {"map_dataflow": self.map_dataflow, "force_os": self.force_os}
 
 
+# Calibration of the selector's cost model, measured on B200 with the kernels of this package (per-layer CUDA-event
+# timings of a MinkUNet18-style network on ~125k-voxel scenes):
+_CHUNK_US = (0.45, 0.0012)     # one pipeline stage of 128 rows x 64 channels (targets-as-M kernel): a + b * c_out us
+_CHUNK256_US = 0.85            # one stage of 256 rows x 64 channels (targets-as-N kernel, c_out <= 96, K <= 32)
+_ATOMIC_BYTES_PER_US = 2.6e6   # fp32 vector reductions into the weight-stationary scratch: ~2.6 TB/s
+_STREAM_BYTES_PER_US = 4.0e6   # zero-fill + final conversion pass of the scratch
+_WS_FIXED_US = 12.0            # memset + conversion launches
+_OS_FIXED_US = 6.0
+_SM_COUNT = 148
+
+
+def estimate_layer_us(c_in: int, c_out: int, kernel_volume: int, num_targets: int, nnz: int,
+                      nonempty_tile_offsets: int = None, submanifold: bool = True):
+    """(output-stationary, weight-stationary) time estimates in microseconds.
+
+    OS runs one CTA per tile of 128 (or, for c_out <= 96, 256) targets -- ``ceil(tiles / 148)`` waves -- and streams
+    one stage per non-empty (tile, offset, 64 input channels); WS streams one stage per 128 compacted pairs and 64
+    input channels over all SMs but pays an fp32 read-modify-write of the output per pair plus a zero-fill and a
+    conversion pass."""
+    import math
+    chunk = _CHUNK_US[0] + _CHUNK_US[1] * c_out
+    tiles = max(1, math.ceil(num_targets / 128))
+    per_in = c_in / 64.0
+    if nonempty_tile_offsets is None:
+        nonempty_tile_offsets = tiles * kernel_volume
+    offsets_per_tile = min(kernel_volume, nonempty_tile_offsets / tiles)
+    if c_out <= 96 and kernel_volume <= 32:
+        tiles256 = max(1, math.ceil(num_targets / 256))
+        os_us = math.ceil(tiles256 / _SM_COUNT) * offsets_per_tile * per_in * _CHUNK256_US + _OS_FIXED_US
+    else:
+        os_us = math.ceil(tiles / _SM_COUNT) * offsets_per_tile * per_in * chunk + _OS_FIXED_US
+    rows = (kernel_volume + 1) // 2 if submanifold and kernel_volume % 2 == 1 else kernel_volume
+    ws_stages = (nnz / 128.0 + rows / 2.0) * math.ceil(per_in)
+    ws_us = (math.ceil(ws_stages / _SM_COUNT) * chunk + nnz * c_out * 4 / _ATOMIC_BYTES_PER_US
+             + num_targets * c_out * 10 / _STREAM_BYTES_PER_US + _WS_FIXED_US)
+    return os_us, ws_us
+
+
 def choose_dataflow(c_in: int, c_out: int, kernel_volume: int, num_targets: int, nnz: int, nonempty_tile_offsets: int,
                     transposed_or_strided: bool = False) -> int:
-    """Cost model of the selector: returns 0 (output-stationary) or 1 (weight-stationary).
+    """Selector: 0 (output-stationary) or 1 (weight-stationary) from layer shape and measured map density.
 
-    Both kernels are gather-bound, so the cost is the number of 128-row operand tiles they
-    move.  OS moves one tile per (128-target tile, offset) that has at least one neighbour
-    (``nonempty_tile_offsets``) and writes each output once.  WS moves ``ceil(nnz_k / 128)`` tiles
-    per offset -- about ``nnz / 128 + K / 2`` -- but pays an fp32 read-modify-write of the
-    output per pair (4 bytes x c_out x 2 against 2 bytes x c_in gathered) and a final conversion
-    pass.  Channel counts the tensor-core kernels cannot tile run output-stationary on the SIMT kernel.
-    """
+    Channel counts the tensor-core kernels cannot tile run output-stationary on the SIMT kernel.  Otherwise the
+    dataflow with the smaller :func:`estimate_layer_us` wins; in practice OS wins on the large, surface-dense levels
+    (no atomics, one pass over the output) and WS on the small deep levels (16-40 tiles cannot fill 148 SMs
+    output-stationary) and on transposed layers (about two neighbours per fine voxel)."""
     if c_in % 8 != 0 or c_out % 16 != 0 or c_out > 256 or num_targets == 0:
         return 0
-    os_tiles = float(max(nonempty_tile_offsets, 1))
-    ws_tiles = nnz / 128.0 + kernel_volume / 2.0
-    gather = 2.0 * c_in
-    scatter = 8.0 * c_out
-    os_cost = os_tiles * gather + (num_targets / 128.0) * 2.0 * c_out
-    ws_cost = ws_tiles * (gather + scatter) + (num_targets / 128.0) * 10.0 * c_out
-    return 1 if ws_cost < 0.8 * os_cost else 0
+    os_us, ws_us = estimate_layer_us(c_in, c_out, kernel_volume, num_targets, nnz, nonempty_tile_offsets,
+                                     submanifold=not transposed_or_strided)
+    return 1 if ws_us < os_us else 0
 
 
 def _map_statistics(cache, conv, inputs_stride):
@@ -165,7 +196,10 @@ def tune(model: Module, data_loader: Iterable, kernel_map_cache=None, map_datafl
         if not module.is_trivial and kernel_map_cache is not None:
             st = _map_statistics(kernel_map_cache, module, stride)
             if st is not None:
-                stats[g].append((module.in_channels, module.out_channels, module.transposed) + st)
+                T, nnz, nonempty = st
+                if module.transposed:       # the map was built for the twin layer: its targets are this layer's sources
+                    T, nonempty = outputs._features.shape[0], None
+                stats[g].append((module.in_channels, module.out_channels, module.transposed, T, nnz, nonempty))
 
     handles = [m.register_forward_hook(functools.partial(hook, name=n)) for n, m in convs.items()]
     for m in convs.values():
@@ -180,16 +214,22 @@ def tune(model: Module, data_loader: Iterable, kernel_map_cache=None, map_datafl
 
     best: Dict[Tuple, DataflowConfig] = {}
     for g, names in group_to_name.items():
-        votes = []
+        # the layers of a group share their kernel maps, hence their dataflow: minimise the summed estimates
+        os_total = ws_total = 0.0
+        kv = g[1][0] * g[1][1] * g[1][2]
         for (cin, cout, transposed, T, nnz, nonempty) in stats.get(g, []):
-            kv = g[1][0] * g[1][1] * g[1][2]
-            votes.append(choose_dataflow(cin, cout, kv, T, nnz, nonempty, transposed or any(v != 1 for v in g[2])))
-        df = 1 if votes and sum(votes) * 2 > len(votes) else 0
+            if choose_dataflow(cin, cout, kv, T, nnz, nonempty) == 0 and (cin % 8 or cout % 16 or cout > 256):
+                ws_total = float("inf")      # a layer the tensor-core kernels cannot tile pins the group to OS
+                continue
+            o, w = estimate_layer_us(cin, cout, kv, T, nnz, nonempty, submanifold=not (transposed or any(v != 1 for v in g[2])))
+            os_total += o
+            ws_total += w
+        df = 1 if ws_total < os_total else 0
         if df not in allowed:
             df = 0 if 0 in allowed else min(allowed)
         best[g] = DataflowConfig(map_dataflow=df, force_os=False)
         if verbose:
-            print(f"group {g}: {len(names)} layer(s) -> map_dataflow={df}")
+            print(f"group {g}: {len(names)} layer(s), estimated OS {os_total:.0f} us / WS {ws_total:.0f} us -> map_dataflow={df}")
     apply(name_to_group, best)
 
     if verify and len(best) > 0:
@@ -204,7 +244,7 @@ def tune(model: Module, data_loader: Iterable, kernel_map_cache=None, map_datafl
             trial[g] = flipped
             apply(name_to_group, trial)
             t = _time_model(model, samples, kernel_map_cache)
-            if t < 0.97 * base:
+            if t < 0.95 * base:
                 best, base = trial, t
                 if verbose:
                     print(f"group {g}: timing overrides the model -> map_dataflow={flipped.map_dataflow} ({t:.3f} ms)")

@@ -116,3 +116,64 @@ def test_fused_epilogues_match_the_module_by_module_result(lib):
         scale = y_ref._features.float().abs().max().item()
         assert (y_ref._features.float() - y_fused._features.float()).abs().max().item() <= 3e-2 * max(scale, 1.0)
     _C.check_status()
+
+
+def test_compiled_replay_matches_eager(lib):
+    """compile_model(): the recorded tape replayed on OTHER scenes gives what the eager modules give."""
+    import spira_b200 as sp
+    from spira_b200 import models, scenes, nn as spnn
+    from spira_b200.nn.functional import _C
+    torch.manual_seed(2)
+    model = sp.fuse(models.minkunet18(4, 19, 3).cuda().half().eval())
+    cache = spnn.KernelMapCache()
+    sp.set_kernel_map_cache(model, cache)
+    sched = models.map_schedule(4, 3, 3)
+    full = scenes.lidar_scene(4)
+
+    def prepare(n, seed, dataflows):
+        x = sp.SparseTensor(torch.from_numpy(full[:n]).cuda(), torch.from_numpy(scenes.features(n, 4, seed)).cuda()).order()
+        cache.reset()
+        cache.add_all_kernel_maps(x._coordinates, *sched, (1, 1, 1), dataflows)
+        return x
+
+    for dataflows in ([0] * 9, [0, 1, 0, 1, 0, 1, 1, 1, 1]):
+        for i, m in enumerate(mod for mod in model.modules() if isinstance(mod, spnn.SparseConv)):
+            pass
+        # per-layer dataflow follows the map of its group
+        def set_flows():
+            for mod in model.modules():
+                if isinstance(mod, spnn.SparseConv):
+                    mod._tunable_config["map_dataflow"] = 0
+        set_flows()
+        if any(dataflows):
+            ks, ss, ts = sched
+            flow_of = {}
+            for i in range(len(ks)):
+                stride_ratio = tuple(b // a for a, b in zip(ss[i], ss[i + 1]))
+                flow_of[(ss[i], ks[i], stride_ratio)] = dataflows[i]
+            hooks = []
+            def hook(mod, inp, out):
+                st = inp[0]._stride
+                eff = tuple(a // b for a, b in zip(st, mod.stride)) if mod.transposed else st
+                mod._tunable_config["map_dataflow"] = flow_of.get((eff, mod.kernel_size, mod.stride), 0)
+            x0 = prepare(30000, 0, [1] * 9)
+            for mod in model.modules():
+                if isinstance(mod, spnn.SparseConv):
+                    mod._tunable_config["map_dataflow"] = 1
+                    hooks.append(mod.register_forward_hook(hook))
+            with torch.no_grad():
+                model(x0)
+            for h in hooks:
+                h.remove()
+        x = prepare(30000, 1, dataflows)
+        compiled = sp.compile_model(model, x, cache)
+        for n, seed in ((30000, 1), (52000, 2), (17000, 3)):
+            x = prepare(n, seed, dataflows)
+            with torch.no_grad():
+                want = model(x)
+            got = compiled(x)
+            assert got._stride == want._stride and got._features.shape == want._features.shape
+            scale = want._features.float().abs().max().item()
+            tol = 0.0 if not any(dataflows) else 2e-2 * max(scale, 1.0)     # OS is deterministic; WS sums with atomics
+            assert (got._features.float() - want._features.float()).abs().max().item() <= tol
+    _C.check_status()
