@@ -294,7 +294,7 @@ def profile_kernels(engine, scene):
         sb = getattr(entry[3], "_sb", None) if entry is not None else None
         meta["nnz"] = int(sb["counts"].sum().item()) if sb is not None else None
     out = {}
-    conv_calls = [(n, args, a.elapsed_time(b)) for n, args, a, b in records if n in ("spira_b200_conv_os", "spira_b200_conv_ws")]
+    conv_calls = [(n, args, a.elapsed_time(b)) for n, args, a, b in records if n in ("spira_b200_conv_os", "spira_b200_conv_os_grouped", "spira_b200_conv_ws")]
     for n, args, a, b in records:
         d = out.setdefault(n, dict(calls=0, ms=0.0))
         d["calls"] += 1
@@ -304,7 +304,7 @@ def profile_kernels(engine, scene):
         if meta["nnz"] is None:
             continue
         flops = 2.0 * meta["nnz"] * meta["cin"] * meta["cout"]
-        map_bytes = meta["K"] * meta["T"] * 4 if n.endswith("conv_os") else meta["nnz"] * 8
+        map_bytes = meta["K"] * meta["T"] * 4 if "conv_os" in n else meta["nnz"] * 8
         byts = meta["S"] * meta["cin"] * 2 + meta["K"] * meta["cin"] * meta["cout"] * 2 + meta["T"] * meta["cout"] * 2 + map_bytes
         layers.append(dict(meta, kernel=n, ms=ms, flops=flops, bytes=byts))
     return out, layers
@@ -614,7 +614,7 @@ def run_layer(args, device, pk, pk_kind):
     if df == 0:
         fn = lambda: _C.conv_os(n, n, m[2], feats, w)
     else:
-        fn = lambda: _C.conv_ws(n, n, feats, w, m[3]._sb["ws"])
+        fn = lambda: _C.conv_ws(n, n, feats, w, m[2]._sb["ws"])
     mean_ms, min_ms = _time_calls(fn, args.steps, args.warmup, l2buf)
     _C.check_status()
     map_ms, _ = _time_calls(lambda: _C.cuda_binary_search(keys, keys, (3, 3, 3), (1, 1, 1), df), args.steps, args.warmup, l2buf)

@@ -44,7 +44,11 @@ const char *spira_b200_last_error(void);
 int spira_b200_reset_error(void);
 
 /* Run-time options of the calling process (not thread safe; set them before launching work):
- *   "gather_tma"        1: the tensor-core kernels fetch feature rows with TMA gather4, 0: with 16-byte cp.async
+ *   "gather_tma"        1: the tensor-core kernels fetch feature rows with TMA gather4, 0 (default): with 16-byte
+ *                       cp.async
+ *   "os_n256"           1 (default): output-stationary layers with c_out <= 128 and K <= 32 whose four-stage pipeline
+ *                       fits in shared memory (c_out <= 96 for K = 27) run the kernel that puts 256 targets on the
+ *                       MMA's N side and the weights on its M side; 0: always 128 targets as M
  * get_option additionally answers "os_pack_mode": the SPIRA_B200_PACK_* image spira_b200_conv_os expects under
  * the current options.  Unknown names: set_option fails, get_option returns -1. */
 int spira_b200_set_option(const char *name, int value);
@@ -174,6 +178,35 @@ int spira_b200_pack_weights(const void *weights, int K, int c_in, int c_out, int
 int spira_b200_conv_os(const void *feats, const void *weights, const void *packed,
                        const spira_b200_epilogue *epilogue, const int32_t *map_os, int64_t num_sources,
                        int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status, void *stream);
+
+/* Grouped output-stationary maps (K <= 32).  No reference counterpart: the reference's output-stationary kernel
+ * (cuda/kernels/output_stat.cuh) walks the map in target order, where almost every (tile of targets, offset) pair
+ * has SOME neighbour although only ~30 % of the rows do, so most of the multiplied rows are zeros.
+ * spira_b200_kmap_group sorts the rows of up to SPIRA_B200_MAX_MAPS [T_al][K] maps by their K-bit presence mask
+ * (fullest first, stable) with ONE radix sort over all of them, and writes per map:
+ *   grouped_map [T_al][K]   row i = map row row_of[i] (rows >= num_targets: -1)
+ *   row_of      [T_al]      target (output row) of grouped row i, -1 for padding rows
+ *   tile_masks  [T_al/128]  bit k = some row of the 128-row tile has a neighbour at offset k
+ *   stats       [2]         number of non-empty (128-row tile, offset) and (256-row tile, offset) pairs
+ * The workspace size depends on the number of rows of all maps of the call together.
+ * spira_b200_conv_os_grouped computes the same result as spira_b200_conv_os on the original map, bit for bit (a
+ * skipped chunk only contributes zeros), and visits only the chunks named by the tile masks. */
+typedef struct spira_b200_group_desc {
+  const int32_t *map_os; /* [T_al][K], T_al = num_targets rounded up to 128 */
+  int64_t num_targets;   /* > 0 */
+  int32_t K;             /* 1..32 */
+  int32_t *grouped_map;
+  int32_t *row_of;
+  uint32_t *tile_masks;
+  int32_t *stats;
+} spira_b200_group_desc;
+int spira_b200_kmap_group_workspace(int64_t total_targets, size_t *bytes);
+int spira_b200_kmap_group(const spira_b200_group_desc *descs, int n_maps, void *workspace, size_t workspace_bytes,
+                          void *stream);
+int spira_b200_conv_os_grouped(const void *feats, const void *packed, const spira_b200_epilogue *epilogue,
+                               const int32_t *grouped_map, const int32_t *row_of, const uint32_t *tile_masks,
+                               int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out, void *out,
+                               int32_t *status, void *stream);
 
 /* Weight-stationary gather-GEMM-scatter over compacted pair lists: for row k and pair p in
  * [naddrs[k], naddrs[k+1]):  accum[out_idx[p]][:] += feats[in_idx[p]][:] @ W[k].  With

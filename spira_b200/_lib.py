@@ -24,6 +24,12 @@ class KmapDesc(C.Structure):
     ]
 
 
+class GroupDesc(C.Structure):
+    """Mirror of ``spira_b200_group_desc`` (include/spira_b200.h)."""
+    _fields_ = [("map_os", c_void_p), ("num_targets", c_int64), ("K", c_int32), ("grouped_map", c_void_p),
+                ("row_of", c_void_p), ("tile_masks", c_void_p), ("stats", c_void_p)]
+
+
 class Epilogue(C.Structure):
     """Mirror of ``spira_b200_epilogue`` (include/spira_b200.h)."""
     _fields_ = [("bias", c_void_p), ("scale", c_void_p), ("shift", c_void_p), ("residual", c_void_p),
@@ -59,6 +65,10 @@ SIGNATURES = {
     "spira_b200_pack_weights": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "spira_b200_conv_os": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_int64, c_int64, c_int, c_int,
                            c_int, c_void_p, c_void_p, c_void_p],
+    "spira_b200_kmap_group_workspace": [c_int64, C.POINTER(c_size_t)],
+    "spira_b200_kmap_group": [C.POINTER(GroupDesc), c_int, c_void_p, c_size_t, c_void_p],
+    "spira_b200_conv_os_grouped": [c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                   c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "spira_b200_conv_ws": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                            c_void_p, c_void_p],
@@ -103,7 +113,8 @@ KERNELS_PER_CALL = {
     "spira_b200_pack": 1, "spira_b200_unpack": 1, "spira_b200_flatten_sort": 1, "spira_b200_permute_rows": 1,
     "spira_b200_downsample": 1, "spira_b200_kmap_search": 1, "spira_b200_kmap_ws_sizes": 2, "spira_b200_kmap_ws_pairs": 1,
     "spira_b200_kmap_masks": 1, "spira_b200_convert_transposed_os": 1, "spira_b200_transpose_map": 1,
-    "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_ws": 2, "spira_b200_conv_ws_static": 2,
+    "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_os_grouped": 1, "spira_b200_kmap_group": 3,
+    "spira_b200_conv_ws": 2, "spira_b200_conv_ws_static": 2,
 }
 launch_count = 0          # kernels launched through `call` since import (or since it was last reset by the caller)
 profile_hook = None       # optional callable(name, args, run) -> None used by the benchmark to time single calls

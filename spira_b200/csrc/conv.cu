@@ -64,7 +64,9 @@ struct ConvParams {
   Epilogue ep;
   int32_t *status;
   // OS
-  const int32_t *map;  // [T_al][K]
+  const int32_t *map;           // [T_al][K]
+  const int32_t *row_of;        // grouped map: output row of map row i (-1: padding), else null
+  const uint32_t *tile_masks;   // grouped map: per 128 rows, bit k = some row has a neighbour at offset k, else null
   // WS
   const int32_t *in_idx, *out_idx, *naddrs, *qnaddrs;
   int rows, mirror, n_tiles_plain, centre_tiles;
@@ -327,15 +329,24 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       uint32_t q_base = 0;
       int q_mod_teams = 0;            // q_base % teams
       int my_stage = team;            // stage of this team's next item (items of a team advance by `teams` stages)
+      int my_slot = 0;                // my_stage / teams
       uint32_t my_phase = 0;
+      // This thread always writes the same 8 (row, piece) places of its team's stages; bit slot * 8 + i remembers that
+      // place i of stage slot * teams + team holds zeros, so the zero-fill for a missing neighbour (most of them are
+      // missing) is skipped when the place is zero already.  stages / teams <= 4 slots.
+      uint32_t zero_rows = 0;
       if (tid == 0 && P.slab_bufs == 2 && static_cast<int>(blockIdx.x) < n_tiles) {
         mbar_arrive_expect_tx(bar_slab0, slab_bytes);
         bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(blockIdx.x) * kRows * P.K, slab_bytes, bar_slab0);
       }
       for (int w = tid; w < 2 * n_words; w += kProducers) cmask[w] = 0;
+      // grouped maps come with the offsets present in each tile; the mask of the next tile is fetched a tile ahead
+      uint32_t tile_mask = (P.tile_masks && static_cast<int>(blockIdx.x) < n_tiles) ? P.tile_masks[blockIdx.x] : 0u;
       // Every thread runs the same sequence of named barriers; a failed wait only takes effect through the
       // OR-reduction of those barriers, so that all producer warps leave the loop in the same iteration.
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
+        const uint32_t this_mask = tile_mask;
+        if (P.tile_masks && tile + static_cast<int>(gridDim.x) < n_tiles) tile_mask = P.tile_masks[tile + gridDim.x];
         const int buf = (P.slab_bufs == 2) ? (tile_i & 1) : 0;
         const int32_t *my_slab = slab + buf * kRows * P.K;
         uint32_t *my_cmask = cmask + (tile_i & 1) * n_words;
@@ -362,11 +373,17 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         for (int j = warp; j < P.n_chunks; j += kProducerWarps) {
           const int k_lo = __float2int_rd((static_cast<float>(j * kChunk) + 0.5f) * inv_c_in);
           const int k_hi = min(__float2int_rd((static_cast<float>(j * kChunk + kChunk - 8) + 0.5f) * inv_c_in), P.K - 1);
-          int v = -1;
-          for (int k = k_lo; k <= k_hi; ++k)
+          bool any;
+          if (P.tile_masks) {
+            any = (this_mask & ((0xffffffffu >> (31 - (k_hi - k_lo))) << k_lo)) != 0;    // K <= 32 for grouped maps
+          } else {
+            int v = -1;
+            for (int k = k_lo; k <= k_hi; ++k)
 #pragma unroll
-            for (int qd = 0; qd < 4; ++qd) v = max(v, my_slab[(lane + 32 * qd) * P.K + k]);
-          if (__ballot_sync(0xffffffffu, v >= 0) && lane == 0) atomicOr(&my_cmask[j >> 5], 1u << (j & 31));
+              for (int qd = 0; qd < 4; ++qd) v = max(v, my_slab[(lane + 32 * qd) * P.K + k]);
+            any = __ballot_sync(0xffffffffu, v >= 0) != 0;
+          }
+          if (any && lane == 0) atomicOr(&my_cmask[j >> 5], 1u << (j & 31));
         }
         if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
         // the mask of the NEXT tile starts from zero (its previous user, tile_i - 1, is finished for all warps)
@@ -378,19 +395,23 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         // Chunk number e (0-based, in increasing j) of the tile is pipeline item q = q_base + e and goes to stage
         // q % stages; this team owns the items with q % teams == team (teams divides stages).  All of it is tracked
         // incrementally: an integer division per chunk would dominate this latency-bound instruction stream.
-        int word = 0, before = 0;                        // position inside the mask for the n-th set bit
+        int word = 0, pos = 0;                           // walks the set bits of the mask: `pos` of them are behind
+        uint32_t bits = force_first ? 1u : my_cmask[0];
         int e = team - q_mod_teams;
         if (e < 0) e += teams;
         for (; active && ok && e < n_chunks_tile; e += teams) {
-          int j = 0;
-          if (!force_first) {
-            while (before + __popc(my_cmask[word]) <= e) { before += __popc(my_cmask[word]); ++word; }
-            j = (word << 5) + __fns(my_cmask[word], 0, e - before + 1);
+          while (true) {                                 // e < number of set bits, so the walk stays inside the mask
+            while (bits == 0) bits = my_cmask[++word];
+            if (pos == e) break;
+            bits &= bits - 1;
+            ++pos;
           }
-          const int stage = my_stage;
+          const int j = (word << 5) + __ffs(bits) - 1;
+          const int stage = my_stage, slot_shift = my_slot * 8;
           if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
           my_stage += teams;
-          if (my_stage >= stages) { my_stage -= stages; my_phase ^= 1; }
+          ++my_slot;
+          if (my_stage >= stages) { my_stage -= stages; my_slot = 0; my_phase ^= 1; }
           if (r == 0) post_weights(stage, j, min(kChunk, P.R - j * kChunk), e == 0, e == n_chunks_tile - 1);
           // this thread's piece belongs to one offset k and starts at channel c of it
           const int rr = j * kChunk + piece * 8;
@@ -399,12 +420,21 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           const bool piece_valid = rr < P.R;
           const uint32_t dst = sbase + stage * kABytes + dst_off;
           const int32_t *col = my_slab + rowbase * P.K + k;
+          const uint32_t was_zero = zero_rows >> slot_shift;
+          uint32_t now_zero = 0;
+          // all map entries first: the copies below are compiler barriers, and a shared-memory load issued between
+          // them would queue behind them in the load/store unit
+          int idx[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) idx[i] = piece_valid ? col[i * 16 * P.K] : -1;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const int idx = piece_valid ? col[i * 16 * P.K] : -1;
-            const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
-            cp_async_16(dst + i * 2048, src, idx >= 0 ? 16u : 0u);
+            const __half *src = P.feats + (idx[i] >= 0 ? (static_cast<int64_t>(idx[i]) * P.c_in + c) : 0);
+            // a missing neighbour needs zeros: nothing to do if the previous fill of this stage left zeros there
+            if (idx[i] >= 0 || !((was_zero >> i) & 1u)) cp_async_16(dst + i * 2048, src, idx[i] >= 0 ? 16u : 0u);
+            now_zero |= (idx[i] >= 0 ? 0u : 1u) << i;
           }
+          zero_rows = (zero_rows & ~(0xffu << slot_shift)) | (now_zero << slot_shift);
           cp_async_mbar_arrive_noinc(bar_full(stage));
         }
         q_base += n_chunks_tile;
@@ -419,17 +449,18 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     if (lane == 0) {
       const uint32_t idesc = idesc_f16_m128(P.c_out);
       int stage = 0, phase = 0;
-      uint32_t acc_phase[2] = {0, 0};
+      uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
       bool ok = true;
       int tile_i = 0;
       for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++tile_i) {
         const int b = tile_i & 1;
-        if (!mbar_wait(bar_acc_empty(b), acc_phase[b] ^ 1, abort_flag)) break;
-        acc_phase[b] ^= 1;
+        if (!mbar_wait(bar_acc_empty(b), ((acc_phase >> b) & 1u) ^ 1u, abort_flag)) break;
+        acc_phase ^= 1u << b;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * P.acc_stride;
         while (true) {
           if (!mbar_wait(bar_full(stage), phase, abort_flag)) { ok = false; break; }
+          fence_proxy_async();     // the rows were written by cp.async (generic proxy), the MMA reads them through the async proxy
           tc_fence_after();
           const int m = meta[stage];
           const int nk = m & 0xff;
@@ -453,12 +484,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     // =========================== epilogue ===========================
     const int q = warp & 3;
     const int row = q * 32 + lane;
-    uint32_t acc_phase[2] = {0, 0};
+    uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
       const int b = tile_i & 1;
-      if (!mbar_wait(bar_acc_full(b), acc_phase[b], abort_flag)) break;
-      acc_phase[b] ^= 1;
+      if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag)) break;
+      acc_phase ^= 1u << b;
       tc_fence_after();
       const uint32_t taddr = tmem_base + b * P.acc_stride + (static_cast<uint32_t>(q * 32) << 16);
       int64_t out_row;
@@ -466,7 +497,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         out_row = slab[kRows + (tile_i & (kScatterRing - 1)) * kRows + row];
       } else {
         const int64_t t = static_cast<int64_t>(tile) * kRows + row;
-        out_row = t < P.T ? t : -1;
+        out_row = t < P.T ? (P.row_of ? P.row_of[t] : t) : -1;
       }
       for (int c0 = 0; c0 < P.c_out; c0 += 32) {
         uint32_t r[32];
@@ -554,7 +585,9 @@ struct ConvN2Params {
   __half *out;
   Epilogue ep;
   int32_t *status;
-  const int32_t *map;  // [T_al][K]
+  const int32_t *map;           // [T_al][K]
+  const int32_t *row_of;        // grouped map: output row of map row i (-1: padding), else null
+  const uint32_t *tile_masks;   // grouped map: per 128 rows, bit k = some row has a neighbour at offset k, else null
   int T, T_al, n_tiles, K, c_in, c_out, R, n_chunks;
   int stages, w_bytes, w_stride;
   int off_feat, off_slab, off_tr, off_cm, off_meta, off_bar;
@@ -614,10 +647,25 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     const float inv_c_in = 1.0f / static_cast<float>(P.c_in);
     const int n_words = (P.n_chunks + 31) >> 5;
     bool ok = true;
-    int tile_i = 0, q_mod_teams = 0, my_stage = team;
+    int tile_i = 0, q_mod_teams = 0, my_stage = team, my_slot = 0;
     uint32_t my_phase = 0;
+    // Most neighbours of an output-stationary tile are missing (~70 % on LiDAR scenes) and their rows must read as
+    // zeros.  This thread always writes the same 16 (row, piece) places of the same stages (stage = slot * 4 + team), so
+    // it remembers which of them hold zeros (bit slot * 16 + i) and skips the zero-fill of a place that is zero already.
+    uint32_t zero_rows = 0;
     for (int w = tid; w < 2 * n_words; w += kProducers) cmask[w] = 0;
+    // grouped maps come with the offsets present in each 128-row tile; the masks of the next tile are fetched a tile ahead
+    const int n_tiles128 = P.T_al >> 7;
+    auto load_tile_mask = [&](int tile) -> uint32_t {
+      if (!P.tile_masks || tile >= P.n_tiles) return 0u;
+      uint32_t m = P.tile_masks[2 * tile];
+      if (2 * tile + 1 < n_tiles128) m |= P.tile_masks[2 * tile + 1];
+      return m;
+    };
+    uint32_t tile_mask = load_tile_mask(blockIdx.x);
     for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+      const uint32_t this_mask = tile_mask;
+      tile_mask = load_tile_mask(tile + gridDim.x);
       uint32_t *my_cmask = cmask + (tile_i & 1) * n_words;
       // every warp has issued its share of the previous tile: the slab may be overwritten
       if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
@@ -635,11 +683,17 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
       for (int j = warp; j < P.n_chunks; j += kProducerWarps) {
         const int k_lo = __float2int_rd((static_cast<float>(j * kChunk) + 0.5f) * inv_c_in);
         const int k_hi = min(__float2int_rd((static_cast<float>(j * kChunk + kChunk - 8) + 0.5f) * inv_c_in), P.K - 1);
-        int v = -1;
-        for (int k = k_lo; k <= k_hi; ++k)
+        bool any;
+        if (P.tile_masks) {
+          any = (this_mask & ((0xffffffffu >> (31 - (k_hi - k_lo))) << k_lo)) != 0;      // K <= 32 for grouped maps
+        } else {
+          int v = -1;
+          for (int k = k_lo; k <= k_hi; ++k)
 #pragma unroll
-          for (int qd = 0; qd < 8; ++qd) v = max(v, slab[(lane + 32 * qd) * P.K + k]);
-        if (__ballot_sync(0xffffffffu, v >= 0) && lane == 0) atomicOr(&my_cmask[j >> 5], 1u << (j & 31));
+            for (int qd = 0; qd < 8; ++qd) v = max(v, slab[(lane + 32 * qd) * P.K + k]);
+          any = __ballot_sync(0xffffffffu, v >= 0) != 0;
+        }
+        if (any && lane == 0) atomicOr(&my_cmask[j >> 5], 1u << (j & 31));
       }
       if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
       for (int w = tid; w < n_words; w += kProducers) cmask[((tile_i + 1) & 1) * n_words + w] = 0;
@@ -647,19 +701,23 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
       for (int w = 0; w < n_words; ++w) n_chunks_tile += __popc(my_cmask[w]);
       const bool force_first = (n_chunks_tile == 0);
       if (force_first) n_chunks_tile = 1;
-      int word = 0, before = 0;
+      int word = 0, pos = 0;                             // walks the set bits of the mask: `pos` of them are behind
+      uint32_t bits = force_first ? 1u : my_cmask[0];
       int e = team - q_mod_teams;
       if (e < 0) e += kTeams;
       for (; ok && e < n_chunks_tile; e += kTeams) {
-        int j = 0;
-        if (!force_first) {
-          while (before + __popc(my_cmask[word]) <= e) { before += __popc(my_cmask[word]); ++word; }
-          j = (word << 5) + __fns(my_cmask[word], 0, e - before + 1);
+        while (true) {                                   // e < number of set bits, so the walk stays inside the mask
+          while (bits == 0) bits = my_cmask[++word];
+          if (pos == e) break;
+          bits &= bits - 1;
+          ++pos;
         }
-        const int stage = my_stage;
+        const int j = (word << 5) + __ffs(bits) - 1;
+        const int stage = my_stage, slot_shift = my_slot * 16;
         if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
         my_stage += kTeams;
-        if (my_stage >= stages) { my_stage -= stages; my_phase ^= 1; }
+        ++my_slot;
+        if (my_stage >= stages) { my_stage -= stages; my_slot = 0; my_phase ^= 1; }
         if (r == 0) {
           const int valid = min(kChunk, P.R - j * kChunk);
           meta[stage] = ((valid + 15) >> 4) | ((e == 0) << 8) | ((e == n_chunks_tile - 1) << 9);
@@ -673,12 +731,21 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
         const bool piece_valid = rr < P.R;
         const uint32_t dst = sbase + P.off_feat + stage * kN2FeatBytes + dst_off;
         const int32_t *col = slab + rowbase * P.K + k;
+        const uint32_t was_zero = zero_rows >> slot_shift;
+        uint32_t now_zero = 0;
+        // all map entries first: the copies below are compiler barriers, and a shared-memory load issued between them
+        // would queue behind them in the load/store unit
+        int idx[kN2Rows / 16];
+#pragma unroll
+        for (int i = 0; i < kN2Rows / 16; ++i) idx[i] = piece_valid ? col[i * 16 * P.K] : -1;
 #pragma unroll
         for (int i = 0; i < kN2Rows / 16; ++i) {
-          const int idx = piece_valid ? col[i * 16 * P.K] : -1;
-          const __half *src = P.feats + (idx >= 0 ? (static_cast<int64_t>(idx) * P.c_in + c) : 0);
-          cp_async_16(dst + i * 2048, src, idx >= 0 ? 16u : 0u);
+          const __half *src = P.feats + (idx[i] >= 0 ? (static_cast<int64_t>(idx[i]) * P.c_in + c) : 0);
+          // a missing neighbour needs zeros: nothing to do if the previous fill of this stage left zeros there
+          if (idx[i] >= 0 || !((was_zero >> i) & 1u)) cp_async_16(dst + i * 2048, src, idx[i] >= 0 ? 16u : 0u);
+          now_zero |= (idx[i] >= 0 ? 0u : 1u) << i;
         }
+        zero_rows = (zero_rows & ~(0xffffu << slot_shift)) | (now_zero << slot_shift);
         cp_async_mbar_arrive_noinc(bar_full(stage));
       }
       q_mod_teams += n_chunks_tile % kTeams;
@@ -691,17 +758,18 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
       // fp16 x fp16 -> fp32, both K-major, M = 128 (channels), N = 256 (targets)
       const uint32_t idesc = (1u << 4) | ((static_cast<uint32_t>(kN2Rows) >> 3) << 17) | ((128u >> 4) << 24);
       int stage = 0, phase = 0;
-      uint32_t acc_phase[2] = {0, 0};
+      uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
       bool ok = true;
       int tile_i = 0;
       for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
         const int b = tile_i & 1;
-        if (!mbar_wait(bar_acc_empty(b), acc_phase[b] ^ 1, abort_flag)) break;
-        acc_phase[b] ^= 1;
+        if (!mbar_wait(bar_acc_empty(b), ((acc_phase >> b) & 1u) ^ 1u, abort_flag)) break;
+        acc_phase ^= 1u << b;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * kN2Rows;
         while (true) {
           if (!mbar_wait(bar_full(stage), phase, abort_flag)) { ok = false; break; }
+          fence_proxy_async();     // the rows were written by cp.async (generic proxy), the MMA reads them through the async proxy
           tc_fence_after();
           const int m = meta[stage];
           const int nk = m & 0xff;
@@ -734,12 +802,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     const float scale = (has_channel && P.ep.scale) ? P.ep.scale[c] : 1.f;
     const float shift = (has_channel && P.ep.shift) ? P.ep.shift[c] : 0.f;
     uint32_t *tr = reinterpret_cast<uint32_t *>(smem + P.off_tr) + q * (32 * 17);
-    uint32_t acc_phase[2] = {0, 0};
+    uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
     for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
       const int b = tile_i & 1;
-      if (!mbar_wait(bar_acc_full(b), acc_phase[b], abort_flag)) break;
-      acc_phase[b] ^= 1;
+      if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag)) break;
+      acc_phase ^= 1u << b;
       tc_fence_after();
       if (n_valid > 0) {
         const uint32_t taddr = tmem_base + b * kN2Rows + (static_cast<uint32_t>(q * 32) << 16);
@@ -769,8 +837,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
           }
           __syncwarp();
           if (t < P.T) {
-            __half *dst = P.out + t * P.c_out + q * 32;
-            const __half *res = P.ep.residual ? P.ep.residual + t * P.c_out + q * 32 : nullptr;
+            const int64_t orow = P.row_of ? P.row_of[t] : t;
+            __half *dst = P.out + orow * P.c_out + q * 32;
+            const __half *res = P.ep.residual ? P.ep.residual + orow * P.c_out + q * 32 : nullptr;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               if (g * 8 < n_valid) {
@@ -1127,10 +1196,9 @@ extern "C" int spira_b200_pack_weights(const void *weights, int K, int c_in, int
   return SPIRA_B200_OK;
 }
 
-extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const void *packed,
-                                  const spira_b200_epilogue *epilogue, const int32_t *map_os, int64_t num_sources,
-                                  int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status,
-                                  void *stream) {
+static int conv_os_impl(const void *feats, const void *weights, const void *packed, const spira_b200_epilogue *epilogue,
+                        const int32_t *map_os, const int32_t *row_of, const uint32_t *tile_masks, int64_t num_sources,
+                        int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status, void *stream) {
   SB_CHECK_ARG(num_sources >= 0 && num_targets >= 0 && num_targets < (int64_t(1) << 31) - 128 &&
                    num_sources < (int64_t(1) << 31),
                "conv_os: sizes out of range");
@@ -1141,6 +1209,7 @@ extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const 
   SB_CHECK_ARG((ep.scale == nullptr) == (ep.shift == nullptr), "conv_os: scale and shift must be given together");
   if (packed == nullptr) {
     SB_CHECK_ARG(weights != nullptr, "conv_os: neither weights nor a packed image given");
+    SB_CHECK_ARG(row_of == nullptr, "conv_os: a grouped map needs the packed weight image (tensor-core eligible layer)");
     const size_t stem_smem = static_cast<size_t>(K) * c_in * c_out * 4 + static_cast<size_t>(128) * K * 4;
     const bool aligned16 = reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(map_os) % 16 == 0 &&
                            (ep.residual == nullptr || reinterpret_cast<uintptr_t>(ep.residual) % 16 == 0);
@@ -1176,6 +1245,8 @@ extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const 
     Q.ep = ep;
     Q.status = status;
     Q.map = map_os;
+    Q.row_of = row_of;
+    Q.tile_masks = tile_masks;
     Q.T = static_cast<int>(num_targets);
     Q.T_al = static_cast<int>(align128(num_targets));
     Q.n_tiles = static_cast<int>(div_up(num_targets, kN2Rows));
@@ -1198,6 +1269,8 @@ extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const 
   P.ep = ep;
   P.status = status;
   P.map = map_os;
+  P.row_of = row_of;
+  P.tile_masks = tile_masks;
   P.T = static_cast<int>(num_targets);
   P.n_tiles = static_cast<int>(align128(num_targets) / kRows);
   P.K = K; P.c_in = c_in; P.c_out = c_out;
@@ -1208,6 +1281,25 @@ extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const 
   size_t smem = plan_smem(P, false);
   if (smem == 0) return fail(SPIRA_B200_ERR_UNSUPPORTED, "conv_os: K=%d c_out=%d does not fit the shared-memory plan", K, c_out);
   return launch_conv_tc<false>(P, tma, smem, num_sources, as_stream(stream));
+}
+
+extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const void *packed,
+                                  const spira_b200_epilogue *epilogue, const int32_t *map_os, int64_t num_sources,
+                                  int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status,
+                                  void *stream) {
+  return conv_os_impl(feats, weights, packed, epilogue, map_os, nullptr, nullptr, num_sources, num_targets, K, c_in, c_out,
+                      out, status, stream);
+}
+
+extern "C" int spira_b200_conv_os_grouped(const void *feats, const void *packed, const spira_b200_epilogue *epilogue,
+                                          const int32_t *grouped_map, const int32_t *row_of, const uint32_t *tile_masks,
+                                          int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out,
+                                          void *out, int32_t *status, void *stream) {
+  SB_CHECK_ARG(num_targets == 0 || (row_of && tile_masks && packed), "conv_os_grouped: null pointer");
+  SB_CHECK_ARG(K <= 32, "conv_os_grouped: K=%d, grouped maps have at most 32 offsets", K);
+  SB_CHECK_ARG(!g_gather_tma, "conv_os_grouped: not available with the TMA gather producer");
+  return conv_os_impl(feats, nullptr, packed, epilogue, grouped_map, row_of, tile_masks, num_sources, num_targets, K, c_in,
+                      c_out, out, status, stream);
 }
 
 extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const void *packed,

@@ -1,0 +1,171 @@
+// Grouping the targets of an output-stationary kernel map by neighbour pattern.
+//
+// The output-stationary convolution processes a tile of consecutive map rows per (weight offset, 64 input channels)
+// chunk and skips a chunk only if NO row of the tile has a neighbour at that offset.  In spatial order nearly every
+// (tile, offset) pair has some neighbour (97 % on LiDAR-like scenes) although only ~30 % of the individual rows do,
+// so ~3.3x more rows are multiplied than there are pairs.  Rows with the same set of present offsets need exactly the
+// same chunks: sorting the rows by their K-bit presence mask (fullest first) makes tiles homogeneous and the ratio of
+// processed rows to pairs drops to ~1.2.  The convolution then runs over the re-ordered map and writes output row
+// `row_of[i]` for grouped row i; per-tile presence masks tell it which chunks to visit without scanning the tile.
+//
+// The reference has no counterpart: its output-stationary kernel walks the map in target order.
+#include <cub/cub.cuh>
+
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int kGroupTile = 128;
+
+struct GroupBatch {
+  const int32_t *map_os[SPIRA_B200_MAX_MAPS];
+  int32_t *grouped_map[SPIRA_B200_MAX_MAPS];
+  int32_t *row_of[SPIRA_B200_MAX_MAPS];
+  uint32_t *tile_masks[SPIRA_B200_MAX_MAPS];
+  int32_t *stats[SPIRA_B200_MAX_MAPS];
+  int32_t T[SPIRA_B200_MAX_MAPS], K[SPIRA_B200_MAX_MAPS];
+  int32_t row_base[SPIRA_B200_MAX_MAPS + 1];    // first row of map m among the concatenated rows of all maps
+  int32_t tile_base[SPIRA_B200_MAX_MAPS + 1];   // first 128-row tile of map m among all tiles
+  int32_t n_maps;
+};
+
+// Sort key of row t of map m: map index on top (the maps stay apart), then K - popcount when it fits beside the mask
+// (fullest rows first, rows with equal masks adjacent), then the mask; without room for the count, the complemented mask.
+__global__ void __launch_bounds__(256) group_keys_kernel(const __grid_constant__ GroupBatch B, uint64_t *__restrict__ keys,
+                                                          int32_t *__restrict__ iota) {
+  const int64_t g = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  if (g >= B.row_base[B.n_maps]) return;
+  int m = 0;
+  while (m + 1 < B.n_maps && g >= B.row_base[m + 1]) ++m;
+  const int64_t t = g - B.row_base[m];
+  const int K = B.K[m];
+  const int32_t *row = B.map_os[m] + t * K;
+  uint32_t mask = 0;
+  for (int k = 0; k < K; ++k) mask |= (row[k] >= 0 ? 1u : 0u) << k;
+  const uint32_t low = (K <= 27) ? ((static_cast<uint32_t>(K - __popc(mask)) << 27) | mask) : ~mask;
+  keys[g] = (static_cast<uint64_t>(m) << 32) | low;
+  iota[g] = static_cast<int32_t>(g);
+  if (t == 0) { B.stats[m][0] = 0; B.stats[m][1] = 0; }      // counted by the kernels that follow on the stream
+}
+
+// One CTA per 128 grouped rows: gathers the rows of the map in the new order (through shared memory, so that the
+// grouped map is written with coalesced stores) and ORs their presence masks.
+__global__ void __launch_bounds__(kGroupTile) group_rows_kernel(const __grid_constant__ GroupBatch B,
+                                                                 const int32_t *__restrict__ order) {
+  extern __shared__ int32_t s_rows[];   // [128][K]
+  __shared__ uint32_t s_mask;
+  const int tid = threadIdx.x;
+  int m = 0;
+  while (m + 1 < B.n_maps && static_cast<int>(blockIdx.x) >= B.tile_base[m + 1]) ++m;
+  const int tile = blockIdx.x - B.tile_base[m];
+  const int K = B.K[m], T = B.T[m];
+  const int64_t g = static_cast<int64_t>(tile) * kGroupTile + tid;
+  if (tid == 0) s_mask = 0;
+  __syncthreads();
+  // the sorted values are global row numbers; the rows of map m occupy [row_base[m], row_base[m] + T) of the order
+  const int32_t src = g < T ? order[B.row_base[m] + g] - B.row_base[m] : -1;
+  B.row_of[m][g] = src;
+  const int32_t *map_os = B.map_os[m];
+  uint32_t mask = 0;
+  for (int k = 0; k < K; ++k) {
+    const int32_t v = src >= 0 ? map_os[static_cast<int64_t>(src) * K + k] : -1;
+    s_rows[tid * K + k] = v;
+    mask |= (v >= 0 ? 1u : 0u) << k;
+  }
+  mask = __reduce_or_sync(0xffffffffu, mask);
+  if ((tid & 31) == 0 && mask != 0) atomicOr(&s_mask, mask);
+  __syncthreads();
+  int32_t *dst = B.grouped_map[m] + static_cast<int64_t>(tile) * kGroupTile * K;
+  for (int i = tid; i < kGroupTile * K; i += kGroupTile) dst[i] = s_rows[i];
+  if (tid == 0) {
+    B.tile_masks[m][tile] = s_mask;
+    atomicAdd(&B.stats[m][0], __popc(s_mask));
+  }
+}
+
+// stats[1]: non-empty (256-row tile, offset) pairs; one thread per pair of 128-row tiles
+__global__ void __launch_bounds__(256) group_stats_kernel(const __grid_constant__ GroupBatch B) {
+  const int64_t p = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;      // over all 128-row tiles; even ones work
+  if (p >= B.tile_base[B.n_maps]) return;
+  int m = 0;
+  while (m + 1 < B.n_maps && p >= B.tile_base[m + 1]) ++m;
+  const int tile = static_cast<int>(p) - B.tile_base[m];
+  if (tile & 1) return;
+  const int n_tiles = B.tile_base[m + 1] - B.tile_base[m];
+  uint32_t mk = B.tile_masks[m][tile];
+  if (tile + 1 < n_tiles) mk |= B.tile_masks[m][tile + 1];
+  if (mk != 0) atomicAdd(&B.stats[m][1], __popc(mk));
+}
+
+static size_t sort_temp_bytes(int64_t n) {
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, bytes, static_cast<const uint64_t *>(nullptr), static_cast<uint64_t *>(nullptr),
+                                  static_cast<const int32_t *>(nullptr), static_cast<int32_t *>(nullptr),
+                                  static_cast<int>(n));
+  return bytes;
+}
+
+static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int spira_b200_kmap_group_workspace(int64_t total_targets, size_t *bytes) {
+  SB_CHECK_ARG(bytes != nullptr, "kmap_group_workspace: null output");
+  SB_CHECK_ARG(total_targets >= 0 && total_targets < (int64_t(1) << 31) - 128, "kmap_group: total_targets out of range");
+  *bytes = 2 * round256(total_targets * 8) + 2 * round256(total_targets * 4) + round256(sort_temp_bytes(total_targets)) + 256;
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_kmap_group(const spira_b200_group_desc *descs, int n_maps, void *workspace,
+                                     size_t workspace_bytes, void *stream) {
+  SB_CHECK_ARG(n_maps >= 0 && n_maps <= SPIRA_B200_MAX_MAPS, "kmap_group: n_maps=%d (at most %d per call)", n_maps,
+               SPIRA_B200_MAX_MAPS);
+  if (n_maps == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(descs != nullptr, "kmap_group: null descriptor array");
+  GroupBatch B{};
+  int64_t rows = 0, tiles = 0;
+  int max_K = 1;
+  for (int m = 0; m < n_maps; ++m) {
+    const spira_b200_group_desc &d = descs[m];
+    SB_CHECK_ARG(d.num_targets > 0 && d.num_targets < (int64_t(1) << 31) - 128, "kmap_group: map %d: num_targets out of range", m);
+    SB_CHECK_ARG(d.K >= 1 && d.K <= 32, "kmap_group: map %d: K=%d, the presence mask of a row must fit 32 bits", m, d.K);
+    SB_CHECK_ARG(d.map_os && d.grouped_map && d.row_of && d.tile_masks && d.stats, "kmap_group: map %d: null pointer", m);
+    B.map_os[m] = d.map_os; B.grouped_map[m] = d.grouped_map; B.row_of[m] = d.row_of; B.tile_masks[m] = d.tile_masks;
+    B.stats[m] = d.stats;
+    B.T[m] = static_cast<int32_t>(d.num_targets); B.K[m] = d.K;
+    B.row_base[m] = static_cast<int32_t>(rows); B.tile_base[m] = static_cast<int32_t>(tiles);
+    rows += d.num_targets;
+    tiles += div_up(d.num_targets, kGroupTile);
+    max_K = d.K > max_K ? d.K : max_K;
+  }
+  SB_CHECK_ARG(rows < (int64_t(1) << 31) - 128, "kmap_group: %lld rows in one call", (long long)rows);
+  B.row_base[n_maps] = static_cast<int32_t>(rows);
+  B.tile_base[n_maps] = static_cast<int32_t>(tiles);
+  B.n_maps = n_maps;
+  size_t need = 0;
+  spira_b200_kmap_group_workspace(rows, &need);
+  SB_CHECK_ARG(workspace != nullptr && workspace_bytes >= need, "kmap_group: workspace of %zu bytes, %zu needed", workspace_bytes, need);
+  cudaStream_t st = as_stream(stream);
+  unsigned char *w = static_cast<unsigned char *>(workspace);
+  w += (256 - reinterpret_cast<uintptr_t>(w) % 256) % 256;
+  const size_t col8 = round256(rows * 8), col4 = round256(rows * 4);
+  uint64_t *keys = reinterpret_cast<uint64_t *>(w);
+  uint64_t *keys_sorted = reinterpret_cast<uint64_t *>(w + col8);
+  int32_t *iota = reinterpret_cast<int32_t *>(w + 2 * col8);
+  int32_t *order = reinterpret_cast<int32_t *>(w + 2 * col8 + col4);
+  void *temp = w + 2 * col8 + 2 * col4;
+  size_t temp_bytes = sort_temp_bytes(rows);
+  group_keys_kernel<<<static_cast<unsigned>(div_up(rows, 256)), 256, 0, st>>>(B, keys, iota);
+  SB_CHECK_LAUNCH();
+  int map_bits = 0;
+  while ((1 << map_bits) < n_maps) ++map_bits;
+  SB_CHECK_CUDA(cub::DeviceRadixSort::SortPairs(temp, temp_bytes, keys, keys_sorted, iota, order, static_cast<int>(rows), 0,
+                                                32 + map_bits, st));
+  group_rows_kernel<<<static_cast<unsigned>(tiles), kGroupTile, kGroupTile * max_K * sizeof(int32_t), st>>>(B, order);
+  SB_CHECK_LAUNCH();
+  group_stats_kernel<<<static_cast<unsigned>(div_up(tiles, 256)), 256, 0, st>>>(B);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}

@@ -79,7 +79,7 @@ class KernelMapCache(object):
             if sb is None or sb.get("layout") == _C.LAYOUT_WS:
                 flipped = _C.transpose_map(entry[3])
                 if sb is not None:
-                    flipped._sb = dict(sb, layout=_C.LAYOUT_OS)
+                    flipped._sb = dict(sb, layout=_C.LAYOUT_OS, grouped=_C.group_os_map(flipped, entry[2]))
                 entry[3] = flipped
             entry[0] = True
 
@@ -91,7 +91,7 @@ class KernelMapCache(object):
                 inv = F.convert_transposed_os(entry[3], entry[1])
                 sb = getattr(entry[3], "_sb", None)
                 if sb is not None:
-                    inv._sb = dict(sb, ws=None, counts=None)
+                    inv._sb = dict(sb, ws=None, counts=None, grouped=_C.group_os_map(inv, entry[1]))
                 self._derived[dkey] = inv
             new_entry = list(entry[1:])
             new_entry[2] = self._derived[dkey]

@@ -20,7 +20,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from spira_b200 import _lib
-from spira_b200._lib import KmapDesc, Epilogue, LAYOUT_OS, LAYOUT_WS, PACK_OS, PACK_WS, MAX_MAPS, MAX_LEVELS
+from spira_b200._lib import KmapDesc, GroupDesc, Epilogue, LAYOUT_OS, LAYOUT_WS, PACK_OS, PACK_WS, MAX_MAPS, MAX_LEVELS
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -166,6 +166,58 @@ def _dataflow_layout(dataflow: int) -> int:
 
 
 LAZY_SIZES = True   # cuda_binary_search_streamed(..., exact_sizes=False) keeps the list sizes on the device
+GROUP_OS = True     # output-stationary maps also get their rows grouped by neighbour pattern (spira_b200_kmap_group)
+GROUP_MIN_TARGETS = 1024
+
+
+class GroupedMap:
+    """An output-stationary map with its rows sorted by presence mask: ``map [T_al, K]``, ``row_of [T_al]`` (the
+    target of each grouped row), ``tile_masks [T_al / 128]`` and ``stats [2]`` (non-empty (tile, offset) pairs for
+    128- and 256-row tiles, on the device)."""
+    __slots__ = ("map", "row_of", "tile_masks", "stats", "map_ptr", "row_of_ptr", "tile_masks_ptr")
+
+
+_group_ws_bytes = {}
+
+
+def group_os_maps(maps) -> list:
+    """Groups the rows of engine-built ``[T_al, K]`` maps, ``maps = [(map, num_targets), ...]``, with one sort per
+    <= 16 maps.  Returns one :class:`GroupedMap` (or None where grouping is off or does not apply) per input."""
+    out = [None] * len(maps)
+    todo = [i for i, (mp, T) in enumerate(maps) if GROUP_OS and mp.shape[1] <= 32 and T >= GROUP_MIN_TARGETS]
+    for first in range(0, len(todo), MAX_MAPS):
+        part = todo[first:first + MAX_MAPS]
+        dev = maps[part[0]][0].device
+        descs = (GroupDesc * len(part))()
+        total = 0
+        for d, i in zip(descs, part):
+            mp, T = maps[i]
+            Tal, K = mp.shape
+            g = GroupedMap()
+            g.map = torch.empty((Tal, K), dtype=torch.int32, device=dev)
+            g.row_of = torch.empty(Tal, dtype=torch.int32, device=dev)
+            g.tile_masks = torch.empty(Tal // 128, dtype=torch.int32, device=dev)
+            g.stats = torch.empty(2, dtype=torch.int32, device=dev)
+            g.map_ptr, g.row_of_ptr, g.tile_masks_ptr = g.map.data_ptr(), g.row_of.data_ptr(), g.tile_masks.data_ptr()
+            d.map_os, d.num_targets, d.K = mp.data_ptr(), int(T), K
+            d.grouped_map, d.row_of, d.tile_masks, d.stats = g.map_ptr, g.row_of_ptr, g.tile_masks_ptr, g.stats.data_ptr()
+            out[i] = g
+            total += int(T)
+        need = _group_ws_bytes.get(total)
+        if need is None:
+            n = C.c_size_t()
+            _lib.call("spira_b200_kmap_group_workspace", total, C.byref(n))
+            if len(_group_ws_bytes) > 4096:
+                _group_ws_bytes.clear()
+            need = _group_ws_bytes[total] = n.value
+        work = torch.empty(need, dtype=torch.uint8, device=dev)
+        _lib.call("spira_b200_kmap_group", descs, len(part), _ptr(work), need, _stream(dev))
+    return out
+
+
+def group_os_map(map_os: torch.Tensor, num_targets: int) -> Optional[GroupedMap]:
+    """Single-map form of :func:`group_os_maps`."""
+    return group_os_maps([(map_os, int(num_targets))])[0]
 
 
 def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_sizes=True):
@@ -260,15 +312,18 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
             w.qmapsize = None if qmapsize is None else int(qmapsize)
             m["ws"] = w
 
+    os_maps = [m for m in info if m["layout"] == LAYOUT_OS]
+    for m, g in zip(os_maps, group_os_maps([(m["dense"], m["T"]) for m in os_maps])):
+        m["grouped"] = g
+
     results = []
     for m in info:
         df, dense = m["df"], m["dense"]
-        dense._sb = dict(counts=m["counts"], ws=m.get("ws"), kernel_size=m["ks"], layout=m["layout"])
+        dense._sb = dict(counts=m["counts"], ws=m.get("ws"), kernel_size=m["ks"], layout=m["layout"], grouped=m.get("grouped"))
         if df == 0:
             results.append((m["S"], m["T"], dense, None, None, None, None, None, None))
         elif df in (1, 3, 5, 7):
-            w = m["ws"]
-            w.nbmaps._sb = dense._sb
+            w = m["ws"]      # reachable from the dense map only: nothing in the lists points back (no reference cycle)
             results.append((m["S"], m["T"], dense, w.nbmaps, w.nbsizes, w.naddrs, w.qnaddrs, w.mapsize, w.qmapsize))
         else:
             w = m["ws"]
@@ -382,8 +437,9 @@ def _check_feats(sources, weights):
 
 
 def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None, scale=None, shift=None, residual=None,
-            relu=False, force_simt=False) -> torch.Tensor:
-    """Output-stationary forward with the optional fused epilogue."""
+            relu=False, force_simt=False, grouped=True) -> torch.Tensor:
+    """Output-stationary forward with the optional fused epilogue.  An engine-built map that carries a grouped twin
+    (rows sorted by neighbour pattern) runs over the twin unless ``grouped=False``; the result is the same."""
     _check_feats(sources, weights)
     sources, weights, out_in_map = sources.contiguous(), weights.contiguous(), out_in_map.contiguous()
     K, cin, cout = weights.shape
@@ -397,6 +453,13 @@ def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None
         out_in_map = padded
     packed = None if force_simt else packed_weights(weights, _lib.load().spira_b200_get_option(b"os_pack_mode"))
     ep, keep = _epilogue(bias, scale, shift, residual, relu)
+    sb = getattr(out_in_map, "_sb", None)
+    g = sb.get("grouped") if (sb is not None and grouped and GROUP_OS) else None
+    if g is not None and packed is not None and get_option("gather_tma") == 0:
+        _lib.call("spira_b200_conv_os_grouped", _ptr(sources), _ptr(packed), C.byref(ep) if ep is not None else None, g.map_ptr,
+                  g.row_of_ptr, g.tile_masks_ptr, int(num_sources), int(num_targets), K, cin, cout, _ptr(out),
+                  _ptr(status_word(sources.device)), _stream(sources.device))
+        return out
     _lib.call("spira_b200_conv_os", _ptr(sources), _ptr(weights), _ptr(packed), C.byref(ep) if ep is not None else None,
               _ptr(out_in_map), int(num_sources), int(num_targets), K, cin, cout, _ptr(out), _ptr(status_word(sources.device)),
               _stream(sources.device))
@@ -436,7 +499,7 @@ class ConvCall:
     struct, the resolved C functions.  ``SparseConv`` keeps one and the two ``run_*`` functions below add only the
     per-call pointers, so that a forward costs a few microseconds of Python per layer."""
     __slots__ = ("stamp", "weights", "K", "cin", "cout", "w_ptr", "packed", "ep", "ep_ref", "keep", "dev_index", "status",
-                 "status_ptr", "fn_os", "fn_ws", "eligible")
+                 "status_ptr", "fn_os", "fn_ws", "fn_os_grouped", "eligible")
 
     def __init__(self, weights: torch.Tensor, bias, fused):
         lib = _lib.load()
@@ -458,7 +521,7 @@ class ConvCall:
         self.dev_index = weights.device.index
         self.status = status_word(weights.device)
         self.status_ptr = self.status.data_ptr()
-        self.fn_os, self.fn_ws = lib.spira_b200_conv_os, lib.spira_b200_conv_ws
+        self.fn_os, self.fn_ws, self.fn_os_grouped = lib.spira_b200_conv_os, lib.spira_b200_conv_ws, lib.spira_b200_conv_os_grouped
         self.stamp = (weights.data_ptr(), weights._version, None if bias is None else (bias.data_ptr(), bias._version),
                       None if fused is None else (id(fused["scale"]), id(fused["shift"]), fused["relu"]))
 
@@ -491,13 +554,22 @@ def run_conv_os(call: ConvCall, num_sources: int, num_targets: int, out_in_map: 
         feats = feats.contiguous()
     out = torch.empty((num_targets, call.cout), dtype=torch.float16, device=feats.device)
     call.ep.residual = residual.data_ptr() if residual is not None else None
-    args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(_lib.load().spira_b200_get_option(b"os_pack_mode")),
-            call.ep_ref, out_in_map.data_ptr(), num_sources, num_targets, call.K, call.cin, call.cout, out.data_ptr(),
-            call.status_ptr, _raw_stream(call.dev_index))
-    if _lib.profile_hook is not None:
-        _lib.profile_hook("spira_b200_conv_os", args, lambda: _lib.check(call.fn_os(*args)))
+    sb = getattr(out_in_map, "_sb", None)
+    g = sb.get("grouped") if sb is not None else None
+    mode = _lib.load().spira_b200_get_option(b"os_pack_mode")
+    if g is not None and call.eligible and GROUP_OS and mode == PACK_OS:
+        name, fn = "spira_b200_conv_os_grouped", call.fn_os_grouped
+        args = (feats.data_ptr(), call.packed_ptr(PACK_OS), call.ep_ref, g.map_ptr, g.row_of_ptr, g.tile_masks_ptr,
+                num_sources, num_targets, call.K, call.cin, call.cout, out.data_ptr(), call.status_ptr,
+                _raw_stream(call.dev_index))
     else:
-        rc = call.fn_os(*args)
+        name, fn = "spira_b200_conv_os", call.fn_os
+        args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(mode), call.ep_ref, out_in_map.data_ptr(), num_sources,
+                num_targets, call.K, call.cin, call.cout, out.data_ptr(), call.status_ptr, _raw_stream(call.dev_index))
+    if _lib.profile_hook is not None:
+        _lib.profile_hook(name, args, lambda: _lib.check(fn(*args)))
+    else:
+        rc = fn(*args)
         if rc != 0:
             _lib.check(rc)
     _lib.launch_count += 1

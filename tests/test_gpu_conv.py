@@ -161,7 +161,7 @@ def test_fused_epilogue(C, scene, mode):
         acc = O.conv_from_pairs(f.float(), w.float(), *_pairs_os(m[2].cpu().numpy(), n), n)
     else:
         m = C.cuda_binary_search(tk, tk, (3, 3, 3), (1, 1, 1), 1)
-        got = C.conv_ws(n, n, f.cuda(), w.cuda(), m[3]._sb["ws"], **kw)
+        got = C.conv_ws(n, n, f.cuda(), w.cuda(), m[2]._sb["ws"], **kw)
         d = m[2].cpu().numpy()
         k, t = np.nonzero(d[:, :n] >= 0)
         acc = O.conv_from_pairs(f.float(), w.float(), d[k, t], t, k, n)
@@ -197,3 +197,66 @@ def test_module_level_dataflows_agree(C, scene):
     for k, v in outs.items():
         assert_features_close(v, base)
     C.check_status()
+
+
+# ---- grouped output-stationary maps (rows sorted by neighbour pattern) ------------------------------------------------
+def test_grouping_reorders_the_map_without_changing_it(C, scene):
+    keys, down = scene
+    for src, tgt, stride in ((keys, keys, (1, 1, 1)), (keys, down, (1, 1, 1))):
+        m = C.cuda_binary_search(keys_to_torch(src), keys_to_torch(tgt), (3, 3, 3), stride, 0)
+        T = len(tgt)
+        g = m[2]._sb["grouped"]
+        assert g is not None
+        dense = m[2].cpu().numpy()
+        gm, row_of = g.map.cpu().numpy(), g.row_of.cpu().numpy()
+        Tal = dense.shape[0]
+        assert gm.shape == dense.shape and row_of.shape == (Tal,)
+        assert np.array_equal(np.sort(row_of[:T]), np.arange(T)) and (row_of[T:] == -1).all()
+        assert np.array_equal(gm[:T], dense[row_of[:T]]) and (gm[T:] == -1).all()
+        present = gm >= 0
+        bits = (present.astype(np.uint64) << np.arange(27, dtype=np.uint64)).sum(1)
+        key = ((27 - present.sum(1)).astype(np.uint64) << np.uint64(27)) | bits
+        assert (np.diff(key[:T].astype(np.int64)) >= 0).all()                      # fullest rows first, equal masks adjacent
+        same = key[:T][1:] == key[:T][:-1]
+        assert (np.diff(row_of[:T])[same] > 0).all()                               # stable: spatial order inside a group
+        tm = present.reshape(-1, 128, 27).any(1)
+        want_masks = (tm.astype(np.uint64) << np.arange(27, dtype=np.uint64)).sum(1).astype(np.uint32)
+        assert np.array_equal(g.tile_masks.cpu().numpy().view(np.uint32), want_masks)
+        pairs = tm.reshape(-1, 27) if tm.shape[0] % 2 == 0 else np.concatenate([tm, np.zeros((1, 27), bool)])
+        n256 = pairs.reshape(-1, 2, 27).any(1).sum()
+        assert g.stats.cpu().tolist() == [int(tm.sum()), int(n256)]
+        # grouping pays: far fewer (tile, offset) pairs have to be visited than in target order
+        assert tm.sum() < 0.8 * (dense[:Tal].reshape(-1, 128, 27) >= 0).any(1).sum()
+
+
+@pytest.mark.parametrize("cin,cout", [(32, 32), (64, 64), (96, 96), (128, 96), (128, 128), (256, 256), (64, 48), (24, 16)])
+def test_grouped_convolution_is_bit_identical(C, scene, cin, cout):
+    keys, down = scene
+    rng = np.random.default_rng(cin + cout)
+    for src, tgt in ((keys, keys), (keys, down)):
+        S, T = len(src), len(tgt)
+        m = C.cuda_binary_search(keys_to_torch(src), keys_to_torch(tgt), (3, 3, 3), (1, 1, 1), 0)
+        assert m[2]._sb["grouped"] is not None
+        f, w = tensors(S, cin, cout, 27, cin * 7 + cout)
+        res = torch.from_numpy(rng.normal(size=(T, cout)).astype(np.float16)).cuda()
+        scale = torch.from_numpy(rng.uniform(0.5, 1.5, cout).astype(np.float32)).cuda()
+        shift = torch.from_numpy(rng.normal(size=cout).astype(np.float32)).cuda()
+        for kw in ({}, dict(scale=scale, shift=shift, residual=res, relu=True)):
+            a = C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=True, **kw)
+            b = C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=False, **kw)
+            assert torch.equal(a, b)
+        assert_features_close(C.conv_os(S, T, m[2], f.cuda(), w.cuda()), O.conv_os(f, w, m[2].cpu().numpy(), T))
+    C.check_status()
+
+
+def test_grouping_rejects_wide_kernels(C, lib):
+    import ctypes
+    from spira_b200._lib import GroupDesc
+    n = ctypes.c_size_t()
+    assert lib.spira_b200_kmap_group_workspace(1000, ctypes.byref(n)) == 0 and n.value > 0
+    buf = torch.zeros(1 << 20, dtype=torch.int32, device="cuda")
+    d = (GroupDesc * 1)()
+    d[0].map_os = d[0].grouped_map = d[0].row_of = d[0].tile_masks = d[0].stats = buf.data_ptr()
+    d[0].num_targets, d[0].K = 1000, 125
+    rc = lib.spira_b200_kmap_group(d, 1, buf.data_ptr(), n.value, None)
+    assert rc != 0 and b"32" in lib.spira_b200_last_error()

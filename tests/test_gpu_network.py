@@ -177,3 +177,32 @@ def test_compiled_replay_matches_eager(lib):
             tol = 0.0 if not any(dataflows) else 2e-2 * max(scale, 1.0)     # OS is deterministic; WS sums with atomics
             assert (got._features.float() - want._features.float()).abs().max().item() <= tol
     _C.check_status()
+
+
+@pytest.mark.parametrize("dataflow", [0, 1, 2])
+def test_rebuilding_maps_every_scene_releases_the_previous_ones(lib, dataflow):
+    """A serving loop resets the cache and rebuilds all maps per scene: device memory must return to the same level
+    (the map structures hold no reference cycle that would keep a scene's lists alive)."""
+    import gc
+    import spira_b200 as sp
+    from spira_b200 import models, scenes, nn as spnn
+    c = scenes.lidar_scene(5)[:30000]
+    coords = torch.from_numpy(c).cuda()
+    feats = torch.from_numpy(scenes.features(len(c), 4, 5)).cuda()
+    model = models.minkunet18(4, 19, 3).cuda().half().eval()
+    cache = spnn.KernelMapCache()
+    sp.set_kernel_map_cache(model, cache)
+    sched = models.map_schedule(4, 3, 3)
+    gc.collect()
+    gc.disable()
+    try:
+        levels = []
+        for _ in range(6):
+            y, _x = run(model, cache, coords, feats, sched, dataflow)
+            del y, _x
+            cache.reset()
+            torch.cuda.synchronize()
+            levels.append(torch.cuda.memory_allocated())
+    finally:
+        gc.enable()
+    assert levels[-1] == levels[1], levels

@@ -29,7 +29,7 @@ def test_static_scratch_matches_caller_scratch(lib):
     n = len(keys)
     tk = keys_to_torch(keys)
     m = _C.cuda_binary_search(tk, tk, (3, 3, 3), (1, 1, 1), 1)
-    lists = m[3]._sb["ws"]
+    lists = m[2]._sb["ws"]
     rng = np.random.default_rng(41)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     status = _C.status_word("cuda")
