@@ -88,6 +88,18 @@ int spira_b200_downsample(const void *keys, int64_t n, int key_bytes, int n_leve
                           void *const *host_out_keys, int32_t *counts, void *workspace, size_t workspace_bytes,
                           void *stream);
 
+/* The same result for keys that are ALREADY SORTED ascending (what spira_b200_flatten_sort returns) and strides
+ * that, per axis, equal or double the stride of the level before (level 0 relative to stride 1), without any sort:
+ * flooring to a coarser stride disturbs the order only inside a coarse cell, so the final position of every coarse
+ * key is a sum of lengths of contiguous ranges of the sorted input, found by binary searches; level l+1 is computed
+ * from the output of level l, whose size stays on the device.  The reference sorts every level from scratch
+ * (csrc/spira/torch/cuda_arg_sort_coordinates.cu:107-200).  Other stride sequences: SPIRA_B200_ERR_UNSUPPORTED (use
+ * spira_b200_downsample).  `status` (device int32, may be NULL) is set to 2 if the input turns out not to be sorted. */
+int spira_b200_downsample_sorted_workspace(int64_t n, int key_bytes, size_t *bytes);
+int spira_b200_downsample_sorted(const void *sorted_keys, int64_t n, int key_bytes, int n_levels,
+                                 const int32_t *host_strides, void *const *host_out_keys, int32_t *counts,
+                                 void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
 /* ---- kernel-map search -------------------------------------------------------------------- */
 
 typedef struct spira_b200_kmap_desc {

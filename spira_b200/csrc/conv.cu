@@ -56,6 +56,13 @@ struct Epilogue {
   int relu;
 };
 
+// Tile number of a persistent CTA's i-th turn.  Rounds alternate direction: grouped maps are sorted from the heaviest
+// tile (most offsets present) to the lightest, so CTA 0 would otherwise receive the heaviest tile of every round.
+__device__ __forceinline__ int snake_tile(int i) {
+  const int G = gridDim.x, b = blockIdx.x;
+  return i * G + ((i & 1) ? G - 1 - b : b);
+}
+
 struct ConvParams {
   const __half *feats;
   const unsigned char *packed;
@@ -136,6 +143,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // i-th tile of this CTA: the output-stationary cp.async path alternates the direction of the rounds
+  auto tile_at = [&](int i) -> int {
+    if constexpr (!kWS && !kTma) return snake_tile(i);
+    return static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x);
+  };
 
   if (kTma && warp < kProducerWarps) {
     // =========================== producer (TMA gather4): warp 0 only ===========================
@@ -335,18 +347,19 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       // place i of stage slot * teams + team holds zeros, so the zero-fill for a missing neighbour (most of them are
       // missing) is skipped when the place is zero already.  stages / teams <= 4 slots.
       uint32_t zero_rows = 0;
-      if (tid == 0 && P.slab_bufs == 2 && static_cast<int>(blockIdx.x) < n_tiles) {
+      if (tid == 0 && P.slab_bufs == 2 && tile_at(0) < n_tiles) {
         mbar_arrive_expect_tx(bar_slab0, slab_bytes);
-        bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(blockIdx.x) * kRows * P.K, slab_bytes, bar_slab0);
+        bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(tile_at(0)) * kRows * P.K, slab_bytes, bar_slab0);
       }
       for (int w = tid; w < 2 * n_words; w += kProducers) cmask[w] = 0;
       // grouped maps come with the offsets present in each tile; the mask of the next tile is fetched a tile ahead
-      uint32_t tile_mask = (P.tile_masks && static_cast<int>(blockIdx.x) < n_tiles) ? P.tile_masks[blockIdx.x] : 0u;
+      uint32_t tile_mask = (P.tile_masks && tile_at(0) < n_tiles) ? P.tile_masks[tile_at(0)] : 0u;
       // Every thread runs the same sequence of named barriers; a failed wait only takes effect through the
       // OR-reduction of those barriers, so that all producer warps leave the loop in the same iteration.
-      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
+      for (int tile = tile_at(0); tile < n_tiles; tile = tile_at(++tile_i)) {
+        const int next = tile_at(tile_i + 1);
         const uint32_t this_mask = tile_mask;
-        if (P.tile_masks && tile + static_cast<int>(gridDim.x) < n_tiles) tile_mask = P.tile_masks[tile + gridDim.x];
+        if (P.tile_masks && next < n_tiles) tile_mask = P.tile_masks[next];
         const int buf = (P.slab_bufs == 2) ? (tile_i & 1) : 0;
         const int32_t *my_slab = slab + buf * kRows * P.K;
         uint32_t *my_cmask = cmask + (tile_i & 1) * n_words;
@@ -354,7 +367,6 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           if (!mbar_wait(bar_slab0 + 8u * buf, (tile_i >> 1) & 1, abort_flag)) ok = false;
           // all warps have issued their share of the previous tile: the other slab and chunk mask are free
           if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
-          const int next = tile + gridDim.x;
           if (tid == 0 && next < n_tiles) {
             mbar_arrive_expect_tx(bar_slab0 + 8u * (buf ^ 1), slab_bytes);
             bulk_g2s(sbase + P.off_slab + (buf ^ 1) * slab_bytes, P.map + static_cast<int64_t>(next) * kRows * P.K, slab_bytes,
@@ -452,7 +464,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
       bool ok = true;
       int tile_i = 0;
-      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++tile_i) {
+      for (int tile = tile_at(0); ok && tile < n_tiles; tile = tile_at(++tile_i)) {
         const int b = tile_i & 1;
         if (!mbar_wait(bar_acc_empty(b), ((acc_phase >> b) & 1u) ^ 1u, abort_flag)) break;
         acc_phase ^= 1u << b;
@@ -486,7 +498,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     const int row = q * 32 + lane;
     uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
+    for (int tile = tile_at(0); tile < n_tiles; tile = tile_at(++tile_i)) {
       const int b = tile_i & 1;
       if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag)) break;
       acc_phase ^= 1u << b;
@@ -662,10 +674,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
       if (2 * tile + 1 < n_tiles128) m |= P.tile_masks[2 * tile + 1];
       return m;
     };
-    uint32_t tile_mask = load_tile_mask(blockIdx.x);
-    for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+    uint32_t tile_mask = load_tile_mask(snake_tile(0));
+    for (int tile = snake_tile(0); tile < P.n_tiles; tile = snake_tile(++tile_i)) {
       const uint32_t this_mask = tile_mask;
-      tile_mask = load_tile_mask(tile + gridDim.x);
+      tile_mask = load_tile_mask(snake_tile(tile_i + 1));
       uint32_t *my_cmask = cmask + (tile_i & 1) * n_words;
       // every warp has issued its share of the previous tile: the slab may be overwritten
       if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
@@ -761,7 +773,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
       uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
       bool ok = true;
       int tile_i = 0;
-      for (int tile = blockIdx.x; ok && tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+      for (int tile = snake_tile(0); ok && tile < P.n_tiles; tile = snake_tile(++tile_i)) {
         const int b = tile_i & 1;
         if (!mbar_wait(bar_acc_empty(b), ((acc_phase >> b) & 1u) ^ 1u, abort_flag)) break;
         acc_phase ^= 1u << b;
@@ -804,7 +816,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     uint32_t *tr = reinterpret_cast<uint32_t *>(smem + P.off_tr) + q * (32 * 17);
     uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
-    for (int tile = blockIdx.x; tile < P.n_tiles; tile += gridDim.x, ++tile_i) {
+    for (int tile = snake_tile(0); tile < P.n_tiles; tile = snake_tile(++tile_i)) {
       const int b = tile_i & 1;
       if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag)) break;
       acc_phase ^= 1u << b;

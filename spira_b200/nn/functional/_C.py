@@ -134,17 +134,43 @@ def cuda_streamed_output_generate(coordinates: torch.Tensor, target_strides: Seq
         group = strides[first:first + MAX_LEVELS]
         L = len(group)
         bufs = torch.empty((L, n), dtype=coordinates.dtype, device=dev)
-        counts = torch.empty(L, dtype=torch.int32, device=dev)
-        need = C.c_size_t()
-        _lib.call("spira_b200_downsample_workspace", n, kb, L, C.byref(need))
-        ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
         host_strides = (C.c_int32 * (3 * L))(*[v for s in group for v in s])
         host_out = (C.c_void_p * L)(*[bufs[l].data_ptr() for l in range(L)])
-        _lib.call("spira_b200_downsample", _ptr(coordinates), n, kb, L, host_strides, host_out, _ptr(counts), _ptr(ws),
-                  need.value, _stream(dev))
-        host_counts = counts.cpu().tolist()
+        host_counts = None
+        if first == 0 and SORT_FREE_DOWNSAMPLE and _strides_double(group):
+            # sorted input (the usual case: the keys come from flatten_sort) needs no sort; the kernel reports an
+            # unsorted input in the word behind the counts, which arrives with the same host read
+            counts = torch.zeros(L + 1, dtype=torch.int32, device=dev)
+            need = C.c_size_t()
+            _lib.call("spira_b200_downsample_sorted_workspace", n, kb, C.byref(need))
+            ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
+            _lib.call("spira_b200_downsample_sorted", _ptr(coordinates), n, kb, L, host_strides, host_out, _ptr(counts),
+                      _ptr(ws), need.value, _ptr(counts[L:]), _stream(dev))
+            host_counts = counts.cpu().tolist()
+            if host_counts[L] != 0:
+                host_counts = None
+        if host_counts is None:
+            counts = torch.empty(L, dtype=torch.int32, device=dev)
+            need = C.c_size_t()
+            _lib.call("spira_b200_downsample_workspace", n, kb, L, C.byref(need))
+            ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
+            _lib.call("spira_b200_downsample", _ptr(coordinates), n, kb, L, host_strides, host_out, _ptr(counts), _ptr(ws),
+                      need.value, _stream(dev))
+            host_counts = counts.cpu().tolist()
         outputs += [bufs[l, :host_counts[l]] for l in range(L)]
     return outputs
+
+
+SORT_FREE_DOWNSAMPLE = True
+
+
+def _strides_double(strides) -> bool:
+    prev = (1, 1, 1)
+    for s in strides:
+        if any(v != p and v != 2 * p for v, p in zip(s, prev)):
+            return False
+        prev = s
+    return True
 
 
 def cuda_downsample(coordinates: torch.Tensor, stride_x: int, stride_y: int, stride_z: int) -> torch.Tensor:

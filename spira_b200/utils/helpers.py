@@ -62,34 +62,47 @@ class DataflowConfig:
 # Calibration of the selector's cost model, measured on B200 with the kernels of this package (per-layer CUDA-event
 # timings of a MinkUNet18-style network on ~125k-voxel scenes):
 _CHUNK_US = (0.45, 0.0012)     # one pipeline stage of 128 rows x 64 channels (targets-as-M kernel): a + b * c_out us
-_CHUNK256_US = 0.85            # one stage of 256 rows x 64 channels (targets-as-N kernel, c_out <= 96, K <= 32)
+_CHUNK256_US = 0.72            # one stage of 256 rows x 64 channels (targets-as-N kernel, c_out <= 96, K <= 32)
+_GROUPED_REDUNDANCY = (1.2, 1.3)   # rows visited per real pair once the map rows are grouped (128- / 256-row tiles)
+_IMBALANCE = (1.7, 1.4)        # heaviest CTA over the mean (128- / 256-row tiles)
+_TILE_OVERHEAD_CHUNKS = 8.0    # per-tile prologue and epilogue, in units of one stage
 _ATOMIC_BYTES_PER_US = 2.6e6   # fp32 vector reductions into the weight-stationary scratch: ~2.6 TB/s
 _STREAM_BYTES_PER_US = 4.0e6   # zero-fill + final conversion pass of the scratch
-_WS_FIXED_US = 12.0            # memset + conversion launches
-_OS_FIXED_US = 6.0
+_WS_FIXED_US = 22.0            # memset + conversion launches and the latency floor of three dependent kernels
+_OS_FIXED_US = 14.0
+_INVERT_US = (40.0, 3.0e6)     # output-stationary map of a transposed layer: fixed cost + map bytes per us (inverse + grouping)
 _SM_COUNT = 148
 
 
 def estimate_layer_us(c_in: int, c_out: int, kernel_volume: int, num_targets: int, nnz: int,
-                      nonempty_tile_offsets: int = None, submanifold: bool = True):
+                      nonempty_tile_offsets: int = None, submanifold: bool = True, transposed: bool = False):
     """(output-stationary, weight-stationary) time estimates in microseconds.
 
-    OS runs one CTA per tile of 128 (or, for c_out <= 96, 256) targets -- ``ceil(tiles / 148)`` waves -- and streams
-    one stage per non-empty (tile, offset, 64 input channels); WS streams one stage per 128 compacted pairs and 64
+    OS runs one persistent CTA per SM over tiles of 128 (or, for c_out <= 96, 256) map rows and streams one stage per
+    (tile, 64 reduction elements) with a neighbour.  Maps with K <= 32 have their rows grouped by neighbour pattern,
+    which leaves ~1.2-1.3 visited rows per real pair; other maps visit every non-empty (tile, offset) pair
+    (``nonempty_tile_offsets``, from the search's hit counters).  WS streams one stage per 128 compacted pairs and 64
     input channels over all SMs but pays an fp32 read-modify-write of the output per pair plus a zero-fill and a
-    conversion pass."""
+    conversion pass.  A transposed OS layer also pays for inverting (and grouping) the map of its twin."""
     import math
     chunk = _CHUNK_US[0] + _CHUNK_US[1] * c_out
-    tiles = max(1, math.ceil(num_targets / 128))
     per_in = c_in / 64.0
-    if nonempty_tile_offsets is None:
-        nonempty_tile_offsets = tiles * kernel_volume
-    offsets_per_tile = min(kernel_volume, nonempty_tile_offsets / tiles)
-    if c_out <= 96 and kernel_volume <= 32:
-        tiles256 = max(1, math.ceil(num_targets / 256))
-        os_us = math.ceil(tiles256 / _SM_COUNT) * offsets_per_tile * per_in * _CHUNK256_US + _OS_FIXED_US
+    wide = not (c_out <= 96 and kernel_volume <= 32)
+    rows_per_tile = 128 if wide else 256
+    tiles = max(1, math.ceil(num_targets / rows_per_tile))
+    ctas = min(_SM_COUNT, tiles)
+    stage_us = chunk if wide else _CHUNK256_US
+    if kernel_volume <= 32:
+        stages = _GROUPED_REDUNDANCY[0 if wide else 1] * nnz / rows_per_tile * per_in
     else:
-        os_us = math.ceil(tiles / _SM_COUNT) * offsets_per_tile * per_in * chunk + _OS_FIXED_US
+        tiles128 = max(1, math.ceil(num_targets / 128))
+        if nonempty_tile_offsets is None:
+            nonempty_tile_offsets = tiles128 * kernel_volume
+        stages = nonempty_tile_offsets * per_in
+    os_us = _OS_FIXED_US + stage_us * (_IMBALANCE[0 if wide else 1] * stages / ctas
+                                       + _TILE_OVERHEAD_CHUNKS * math.ceil(tiles / ctas))
+    if transposed:
+        os_us += _INVERT_US[0] + num_targets * kernel_volume * 8 / _INVERT_US[1]
     rows = (kernel_volume + 1) // 2 if submanifold and kernel_volume % 2 == 1 else kernel_volume
     ws_stages = (nnz / 128.0 + rows / 2.0) * math.ceil(per_in)
     ws_us = (math.ceil(ws_stages / _SM_COUNT) * chunk + nnz * c_out * 4 / _ATOMIC_BYTES_PER_US
@@ -221,7 +234,8 @@ def tune(model: Module, data_loader: Iterable, kernel_map_cache=None, map_datafl
             if choose_dataflow(cin, cout, kv, T, nnz, nonempty) == 0 and (cin % 8 or cout % 16 or cout > 256):
                 ws_total = float("inf")      # a layer the tensor-core kernels cannot tile pins the group to OS
                 continue
-            o, w = estimate_layer_us(cin, cout, kv, T, nnz, nonempty, submanifold=not (transposed or any(v != 1 for v in g[2])))
+            o, w = estimate_layer_us(cin, cout, kv, T, nnz, nonempty, submanifold=not (transposed or any(v != 1 for v in g[2])),
+                                     transposed=transposed)
             os_total += o
             ws_total += w
         df = 1 if ws_total < os_total else 0

@@ -69,3 +69,40 @@ def test_bad_arguments_raise(C):
         C.cuda_downsample(torch.zeros(4, dtype=torch.int32, device="cuda"), 3, 2, 2)     # not a power of two
     with pytest.raises(NotImplementedError):
         C.cuda_unflatten(torch.zeros(4, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("double", [False, True])
+@pytest.mark.parametrize("strides", [[(2, 2, 2), (4, 4, 4), (8, 8, 8), (16, 16, 16)], [(2, 2, 1), (2, 4, 2), (4, 4, 2), (4, 8, 4)],
+                                     [(1, 1, 2)], [(1, 1, 1), (2, 2, 2)]])
+def test_sort_free_downsampling_of_sorted_keys(C, double, strides):
+    """Strides that double level by level take the path without a sort; it must agree with the oracle, with the
+    sorting path, and fall back to the sorting path when the input is not sorted."""
+    c = cloud(7, 40000, 32, 200, zhi=120)
+    keys, _ = O.flat_sort(c, double)
+    assert C._strides_double(strides)
+    want = O.streamed_output_generate(keys, strides)
+    got = C.cuda_streamed_output_generate(keys_to_torch(keys), strides)
+    for g, w in zip(got, want):
+        np.testing.assert_array_equal(keys_from_torch(g), w)
+    C.SORT_FREE_DOWNSAMPLE = False
+    try:
+        ref = C.cuda_streamed_output_generate(keys_to_torch(keys), strides)
+    finally:
+        C.SORT_FREE_DOWNSAMPLE = True
+    for g, r in zip(got, ref):
+        assert torch.equal(g, r)
+    shuffled = keys[np.random.default_rng(1).permutation(len(keys))]
+    again = C.cuda_streamed_output_generate(keys_to_torch(shuffled), strides)
+    for g, w in zip(again, want):
+        np.testing.assert_array_equal(keys_from_torch(g), w)
+
+
+def test_sort_free_downsampling_rejects_other_strides(C, lib):
+    import ctypes
+    n = ctypes.c_size_t()
+    assert lib.spira_b200_downsample_sorted_workspace(100, 4, ctypes.byref(n)) == 0
+    buf = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    strides = (ctypes.c_int32 * 3)(4, 4, 4)
+    outs = (ctypes.c_void_p * 1)(buf.data_ptr())
+    rc = lib.spira_b200_downsample_sorted(buf.data_ptr(), 100, 4, 1, strides, outs, buf.data_ptr(), buf.data_ptr(), n.value, None, None)
+    assert rc != 0
