@@ -135,6 +135,25 @@ int spira_b200_kmap_ws_sizes(const int32_t *tile_counts, int rows, int64_t n_til
 int spira_b200_kmap_ws_pairs(const int32_t *map_ws, int rows, int64_t aligned_targets, const int32_t *naddrs,
                              const int32_t *tile_base, int32_t *in_idx, int32_t *out_idx, void *stream);
 
+/* spira_b200_kmap_ws_sizes + spira_b200_kmap_ws_pairs for up to SPIRA_B200_MAX_MAPS maps with three launches in
+ * total and no host read in between: the pair lists get a capacity the caller can bound without knowing nnz
+ * (rows * num_targets entries each); sizes[0..1] = (nnz, nnz rounded per row to 128) stay on the device. */
+typedef struct spira_b200_ws_desc {
+  const int32_t *map_ws;      /* [K][aligned_targets] */
+  const int32_t *tile_counts; /* [K][aligned_targets / 128] from spira_b200_kmap_search */
+  int64_t aligned_targets;
+  int32_t K;                  /* rows of the map: tile_base and nbsizes are produced for all of them */
+  int32_t rows;               /* rows listed and covered by naddrs / qnaddrs: K, or (K + 1) / 2 for mirrored lists */
+  int32_t *nbsizes;           /* [K] */
+  int32_t *naddrs;            /* [rows + 1] */
+  int32_t *qnaddrs;           /* [rows + 1] */
+  int32_t *tile_base;         /* [K][aligned_targets / 128] */
+  int32_t *sizes;             /* [2] */
+  int32_t *in_idx;            /* capacity >= rows * num_targets */
+  int32_t *out_idx;
+} spira_b200_ws_desc;
+int spira_b200_kmap_ws_lists(const spira_b200_ws_desc *descs, int n_maps, void *stream);
+
 /* source_masks[K][S], target_masks[K][T] (rank of each pair inside its row, -1 elsewhere) from a
  * LAYOUT_WS map; both outputs are fully written.  Replaces GenerateMasksFromKernelMap
  * (csrc/spira/cuda/kernels/generate_masks_from_kernel_map.cuh:9-62). */

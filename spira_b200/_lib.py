@@ -30,6 +30,13 @@ class GroupDesc(C.Structure):
                 ("row_of", c_void_p), ("tile_masks", c_void_p), ("stats", c_void_p)]
 
 
+class WsDesc(C.Structure):
+    """Mirror of ``spira_b200_ws_desc`` (include/spira_b200.h)."""
+    _fields_ = [("map_ws", c_void_p), ("tile_counts", c_void_p), ("aligned_targets", c_int64), ("K", c_int32), ("rows", c_int32),
+                ("nbsizes", c_void_p), ("naddrs", c_void_p), ("qnaddrs", c_void_p), ("tile_base", c_void_p), ("sizes", c_void_p),
+                ("in_idx", c_void_p), ("out_idx", c_void_p)]
+
+
 class Epilogue(C.Structure):
     """Mirror of ``spira_b200_epilogue`` (include/spira_b200.h)."""
     _fields_ = [("bias", c_void_p), ("scale", c_void_p), ("shift", c_void_p), ("residual", c_void_p),
@@ -60,6 +67,7 @@ SIGNATURES = {
     "spira_b200_kmap_search": [C.POINTER(KmapDesc), c_int, c_int, c_void_p],
     "spira_b200_kmap_ws_sizes": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "spira_b200_kmap_ws_pairs": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "spira_b200_kmap_ws_lists": [C.POINTER(WsDesc), c_int, c_void_p],
     "spira_b200_kmap_masks": [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
     "spira_b200_convert_transposed_os": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p],
     "spira_b200_transpose_map": [c_void_p, c_int64, c_int64, c_void_p, c_void_p],
@@ -114,7 +122,7 @@ def check(code: int) -> None:
 # kernels of this library launched per successful call (library kernels such as the radix sort are not counted)
 KERNELS_PER_CALL = {
     "spira_b200_pack": 1, "spira_b200_unpack": 1, "spira_b200_flatten_sort": 1, "spira_b200_permute_rows": 1,
-    "spira_b200_downsample": 1, "spira_b200_downsample_sorted": 4, "spira_b200_kmap_search": 1, "spira_b200_kmap_ws_sizes": 2, "spira_b200_kmap_ws_pairs": 1,
+    "spira_b200_downsample": 1, "spira_b200_downsample_sorted": 4, "spira_b200_kmap_search": 1, "spira_b200_kmap_ws_sizes": 2, "spira_b200_kmap_ws_pairs": 1, "spira_b200_kmap_ws_lists": 3,
     "spira_b200_kmap_masks": 1, "spira_b200_convert_transposed_os": 1, "spira_b200_transpose_map": 1,
     "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_os_grouped": 1, "spira_b200_kmap_group": 3,
     "spira_b200_conv_ws": 2, "spira_b200_conv_ws_static": 2,

@@ -66,14 +66,16 @@ __global__ void __launch_bounds__(kGroupTile) group_rows_kernel(const __grid_con
   const int32_t src = g < T ? order[B.row_base[m] + g] - B.row_base[m] : -1;
   B.row_of[m][g] = src;
   const int32_t *map_os = B.map_os[m];
+  // a warp copies its 32 rows one after the other: lane k reads entry k, so that a row costs one request
+  const int lane = tid & 31, row0 = tid & ~31;
   uint32_t mask = 0;
-  for (int k = 0; k < K; ++k) {
-    const int32_t v = src >= 0 ? map_os[static_cast<int64_t>(src) * K + k] : -1;
-    s_rows[tid * K + k] = v;
-    mask |= (v >= 0 ? 1u : 0u) << k;
+  for (int r = 0; r < 32; ++r) {
+    const int32_t s_r = __shfl_sync(0xffffffffu, src, r);
+    const int32_t v = (s_r >= 0 && lane < K) ? map_os[static_cast<int64_t>(s_r) * K + lane] : -1;
+    if (lane < K) s_rows[(row0 + r) * K + lane] = v;
+    mask |= __ballot_sync(0xffffffffu, v >= 0);
   }
-  mask = __reduce_or_sync(0xffffffffu, mask);
-  if ((tid & 31) == 0 && mask != 0) atomicOr(&s_mask, mask);
+  if (lane == 0 && mask != 0) atomicOr(&s_mask, mask);
   __syncthreads();
   int32_t *dst = B.grouped_map[m] + static_cast<int64_t>(tile) * kGroupTile * K;
   for (int i = tid; i < kGroupTile * K; i += kGroupTile) dst[i] = s_rows[i];

@@ -207,12 +207,11 @@ __global__ void __launch_bounds__(kTile) kmap_search_kernel(const __grid_constan
 // ---- weight-stationary post-processing ------------------------------------------------------
 
 // One CTA per map row: exclusive scan of the row's per-tile counts.
-__global__ void __launch_bounds__(256) ws_row_scan_kernel(const int32_t *__restrict__ tile_counts, int64_t n_tiles,
-                                                           int32_t *__restrict__ tile_base,
-                                                           int32_t *__restrict__ nbsizes) {
+__device__ __forceinline__ void ws_row_scan_body(const int32_t *__restrict__ tile_counts, int64_t n_tiles,
+                                                 int32_t *__restrict__ tile_base, int32_t *__restrict__ nbsizes, int k) {
   __shared__ int s_warp[8];
   __shared__ int s_carry;
-  const int k = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) s_carry = 0;
   __syncthreads();
   for (int64_t b = 0; b < n_tiles; b += 256) {
@@ -237,9 +236,14 @@ __global__ void __launch_bounds__(256) ws_row_scan_kernel(const int32_t *__restr
   if (tid == 0) nbsizes[k] = s_carry;
 }
 
-__global__ void ws_addr_kernel(const int32_t *__restrict__ nbsizes, int rows, int32_t *__restrict__ naddrs,
-                               int32_t *__restrict__ qnaddrs, int32_t *__restrict__ sizes) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+__global__ void __launch_bounds__(256) ws_row_scan_kernel(const int32_t *__restrict__ tile_counts, int64_t n_tiles,
+                                                           int32_t *__restrict__ tile_base,
+                                                           int32_t *__restrict__ nbsizes) {
+  ws_row_scan_body(tile_counts, n_tiles, tile_base, nbsizes, blockIdx.x);
+}
+
+__device__ __forceinline__ void ws_addr_body(const int32_t *__restrict__ nbsizes, int rows, int32_t *__restrict__ naddrs,
+                                             int32_t *__restrict__ qnaddrs, int32_t *__restrict__ sizes) {
   int acc = 0, qacc = 0;
   for (int k = 0; k < rows; ++k) {
     naddrs[k] = acc;
@@ -254,13 +258,18 @@ __global__ void ws_addr_kernel(const int32_t *__restrict__ nbsizes, int rows, in
   sizes[1] = qacc;
 }
 
-// grid (n_tiles, rows): compaction of one 128-target tile of one row, order preserved.
-__global__ void __launch_bounds__(kTile) ws_pairs_kernel(const int32_t *__restrict__ map_ws, int64_t T_al,
-                                                          int64_t n_tiles, const int32_t *__restrict__ naddrs,
-                                                          const int32_t *__restrict__ tile_base,
-                                                          int32_t *__restrict__ in_idx, int32_t *__restrict__ out_idx) {
+__global__ void ws_addr_kernel(const int32_t *__restrict__ nbsizes, int rows, int32_t *__restrict__ naddrs,
+                               int32_t *__restrict__ qnaddrs, int32_t *__restrict__ sizes) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  ws_addr_body(nbsizes, rows, naddrs, qnaddrs, sizes);
+}
+
+// compaction of one 128-target tile of one row, order preserved.
+__device__ __forceinline__ void ws_pairs_body(const int32_t *__restrict__ map_ws, int64_t T_al, int64_t n_tiles,
+                                              const int32_t *__restrict__ naddrs, const int32_t *__restrict__ tile_base,
+                                              int32_t *__restrict__ in_idx, int32_t *__restrict__ out_idx, int tile, int k) {
   __shared__ int s_warp[kTile / 32];
-  const int tile = blockIdx.x, k = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t t = static_cast<int64_t>(tile) * kTile + tid;
   const int v = map_ws[k * T_al + t];
   const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
@@ -272,6 +281,47 @@ __global__ void __launch_bounds__(kTile) ws_pairs_kernel(const int32_t *__restri
   const int64_t pos = static_cast<int64_t>(naddrs[k]) + tile_base[k * n_tiles + tile] + rank;
   in_idx[pos] = v;
   out_idx[pos] = static_cast<int32_t>(t);
+}
+
+// grid (n_tiles, rows)
+__global__ void __launch_bounds__(kTile) ws_pairs_kernel(const int32_t *__restrict__ map_ws, int64_t T_al,
+                                                          int64_t n_tiles, const int32_t *__restrict__ naddrs,
+                                                          const int32_t *__restrict__ tile_base,
+                                                          int32_t *__restrict__ in_idx, int32_t *__restrict__ out_idx) {
+  ws_pairs_body(map_ws, T_al, n_tiles, naddrs, tile_base, in_idx, out_idx, blockIdx.x, blockIdx.y);
+}
+
+// ---- the same three steps for up to SPIRA_B200_MAX_MAPS maps per launch ---------------------------------------------
+struct WsBatch {
+  const int32_t *map_ws[SPIRA_B200_MAX_MAPS];
+  const int32_t *tile_counts[SPIRA_B200_MAX_MAPS];
+  int32_t *nbsizes[SPIRA_B200_MAX_MAPS], *naddrs[SPIRA_B200_MAX_MAPS], *qnaddrs[SPIRA_B200_MAX_MAPS];
+  int32_t *tile_base[SPIRA_B200_MAX_MAPS], *sizes[SPIRA_B200_MAX_MAPS];
+  int32_t *in_idx[SPIRA_B200_MAX_MAPS], *out_idx[SPIRA_B200_MAX_MAPS];
+  int32_t T_al[SPIRA_B200_MAX_MAPS], K[SPIRA_B200_MAX_MAPS], rows[SPIRA_B200_MAX_MAPS];
+  int32_t scan_base[SPIRA_B200_MAX_MAPS + 1];    // first CTA of map m in the row-scan launch (one CTA per map row)
+  int32_t pairs_base[SPIRA_B200_MAX_MAPS + 1];   // first CTA of map m in the compaction launch (tiles x listed rows)
+  int32_t n_maps;
+};
+
+__global__ void __launch_bounds__(256) ws_row_scan_batched_kernel(const __grid_constant__ WsBatch B) {
+  int m = 0;
+  while (m + 1 < B.n_maps && static_cast<int>(blockIdx.x) >= B.scan_base[m + 1]) ++m;
+  ws_row_scan_body(B.tile_counts[m], B.T_al[m] / kTile, B.tile_base[m], B.nbsizes[m], blockIdx.x - B.scan_base[m]);
+}
+
+__global__ void ws_addr_batched_kernel(const __grid_constant__ WsBatch B) {
+  const int m = blockIdx.x;
+  if (threadIdx.x == 0) ws_addr_body(B.nbsizes[m], B.rows[m], B.naddrs[m], B.qnaddrs[m], B.sizes[m]);
+}
+
+__global__ void __launch_bounds__(kTile) ws_pairs_batched_kernel(const __grid_constant__ WsBatch B) {
+  int m = 0;
+  while (m + 1 < B.n_maps && static_cast<int>(blockIdx.x) >= B.pairs_base[m + 1]) ++m;
+  const int local = blockIdx.x - B.pairs_base[m];
+  const int n_tiles = B.T_al[m] / kTile;
+  ws_pairs_body(B.map_ws[m], B.T_al[m], n_tiles, B.naddrs[m], B.tile_base[m], B.in_idx[m], B.out_idx[m], local % n_tiles,
+                local / n_tiles);
 }
 
 __global__ void __launch_bounds__(kTile) masks_kernel(const int32_t *__restrict__ map_ws, int64_t S, int64_t T,
@@ -407,6 +457,40 @@ extern "C" int spira_b200_kmap_ws_pairs(const int32_t *map_ws, int rows, int64_t
   dim3 grid(static_cast<unsigned>(n_tiles), static_cast<unsigned>(rows));
   ws_pairs_kernel<<<grid, kTile, 0, as_stream(stream)>>>(map_ws, aligned_targets, n_tiles, naddrs, tile_base, in_idx,
                                                          out_idx);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_kmap_ws_lists(const spira_b200_ws_desc *descs, int n_maps, void *stream) {
+  SB_CHECK_ARG(n_maps >= 0 && n_maps <= SPIRA_B200_MAX_MAPS, "kmap_ws_lists: n_maps=%d (at most %d per call)", n_maps,
+               SPIRA_B200_MAX_MAPS);
+  if (n_maps == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(descs != nullptr, "kmap_ws_lists: null descriptor array");
+  WsBatch B{};
+  int64_t scan = 0, pairs = 0;
+  for (int m = 0; m < n_maps; ++m) {
+    const spira_b200_ws_desc &d = descs[m];
+    SB_CHECK_ARG(d.K >= 1 && d.K <= kMaxK && d.rows >= 1 && d.rows <= d.K, "kmap_ws_lists: map %d: K=%d rows=%d", m, d.K, d.rows);
+    SB_CHECK_ARG(d.aligned_targets > 0 && d.aligned_targets % 128 == 0 && d.aligned_targets < (int64_t(1) << 31),
+                 "kmap_ws_lists: map %d: aligned_targets=%lld", m, (long long)d.aligned_targets);
+    SB_CHECK_ARG(d.map_ws && d.tile_counts && d.nbsizes && d.naddrs && d.qnaddrs && d.tile_base && d.sizes && d.in_idx && d.out_idx,
+                 "kmap_ws_lists: map %d: null pointer", m);
+    B.map_ws[m] = d.map_ws; B.tile_counts[m] = d.tile_counts; B.nbsizes[m] = d.nbsizes; B.naddrs[m] = d.naddrs;
+    B.qnaddrs[m] = d.qnaddrs; B.tile_base[m] = d.tile_base; B.sizes[m] = d.sizes; B.in_idx[m] = d.in_idx; B.out_idx[m] = d.out_idx;
+    B.T_al[m] = static_cast<int32_t>(d.aligned_targets); B.K[m] = d.K; B.rows[m] = d.rows;
+    B.scan_base[m] = static_cast<int32_t>(scan); B.pairs_base[m] = static_cast<int32_t>(pairs);
+    scan += d.K;
+    pairs += (d.aligned_targets / kTile) * d.rows;
+  }
+  SB_CHECK_ARG(pairs < (int64_t(1) << 31), "kmap_ws_lists: too many tiles in one call");
+  B.scan_base[n_maps] = static_cast<int32_t>(scan); B.pairs_base[n_maps] = static_cast<int32_t>(pairs);
+  B.n_maps = n_maps;
+  cudaStream_t st = as_stream(stream);
+  ws_row_scan_batched_kernel<<<static_cast<unsigned>(scan), 256, 0, st>>>(B);
+  SB_CHECK_LAUNCH();
+  ws_addr_batched_kernel<<<n_maps, 32, 0, st>>>(B);
+  SB_CHECK_LAUNCH();
+  ws_pairs_batched_kernel<<<static_cast<unsigned>(pairs), kTile, 0, st>>>(B);
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
 }

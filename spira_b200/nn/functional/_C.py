@@ -20,7 +20,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from spira_b200 import _lib
-from spira_b200._lib import KmapDesc, GroupDesc, Epilogue, LAYOUT_OS, LAYOUT_WS, PACK_OS, PACK_WS, MAX_MAPS, MAX_LEVELS
+from spira_b200._lib import KmapDesc, GroupDesc, WsDesc, Epilogue, LAYOUT_OS, LAYOUT_WS, PACK_OS, PACK_WS, MAX_MAPS, MAX_LEVELS
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -288,17 +288,44 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
             d.map, d.tile_counts = m["dense"].data_ptr(), m["counts"].data_ptr()
         _lib.call("spira_b200_kmap_search", descs, len(group), kb, stream)
 
-    # weight-stationary post-processing: sizes for every such map, one host read, then the pairs
+    # weight-stationary post-processing
     ws_maps = [m for m in info if m["layout"] == LAYOUT_WS]
-    if ws_maps:
+    for m in ws_maps:
+        # submanifold map with an odd kernel volume: only the first (K+1)/2 rows are listed, the rest is applied by
+        # symmetry (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:269)
+        m["half"] = (m["S"] == m["T"]) and (m["K"] % 2 == 1)
+        m["rows"] = (m["K"] + 1) // 2 if m["half"] else m["K"]
+    if ws_maps and not exact_sizes and all(m["Tal"] > 0 and m["T"] > 0 for m in ws_maps):
+        # Nothing is read back: the lists get their worst-case capacity (rows * T pairs, allocated but never touched
+        # beyond nnz), the kernels take the sizes from naddrs / qnaddrs on the device, and all maps share three launches.
+        for first in range(0, len(ws_maps), MAX_MAPS):
+            group = ws_maps[first:first + MAX_MAPS]
+            descs = (WsDesc * len(group))()
+            for d, m in zip(descs, group):
+                K, rows, nt = m["K"], m["rows"], m["Tal"] // 128
+                small = torch.empty(K + 2 * (rows + 1) + 2, dtype=torch.int32, device=dev)
+                m["nbsizes"], m["naddrs"] = small[:K], small[K:K + rows + 1]
+                m["qnaddrs"], sizes = small[K + rows + 1:K + 2 * rows + 2], small[K + 2 * rows + 2:]
+                m["tile_base"] = torch.empty((K, nt), dtype=torch.int32, device=dev)
+                nbmaps = torch.empty((2, rows * m["T"]), dtype=torch.int32, device=dev)
+                base = small.data_ptr()
+                d.map_ws, d.tile_counts, d.aligned_targets = m["dense"].data_ptr(), m["counts"].data_ptr(), m["Tal"]
+                d.K, d.rows = K, rows
+                d.nbsizes, d.naddrs, d.qnaddrs, d.sizes = base, base + 4 * K, base + 4 * (K + rows + 1), base + 4 * (K + 2 * rows + 2)
+                d.tile_base = m["tile_base"].data_ptr()
+                d.in_idx, d.out_idx = nbmaps.data_ptr(), nbmaps.data_ptr() + 4 * rows * m["T"]
+                w = WsLists()
+                w.nbmaps, w.in_idx, w.out_idx = nbmaps, nbmaps[0], nbmaps[1]
+                w.nbsizes, w.naddrs, w.qnaddrs = m["nbsizes"][:rows], m["naddrs"], m["qnaddrs"]
+                w.rows, w.mirror, w.mapsize, w.qmapsize = rows, bool(m["half"]), None, None
+                m["ws"] = w
+            _lib.call("spira_b200_kmap_ws_lists", descs, len(group), stream)
+    elif ws_maps:
+        # sizes for every map, ONE host read of all list sizes (the reference reads them per map), then the pairs with
+        # their exact shape [2, nnz]
         sizes = torch.empty((len(ws_maps), 2), dtype=torch.int32, device=dev)
         for j, m in enumerate(ws_maps):
-            K, nt = m["K"], m["Tal"] // 128
-            # submanifold map with an odd kernel volume: only the first (K+1)/2 rows are listed, the rest is
-            # applied by symmetry (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:269)
-            half = (m["S"] == m["T"]) and (K % 2 == 1)
-            rows = (K + 1) // 2 if half else K
-            m["rows"], m["half"] = rows, half
+            K, nt, rows = m["K"], m["Tal"] // 128, m["rows"]
             m["nbsizes"] = torch.empty(K, dtype=torch.int32, device=dev)
             m["naddrs"] = torch.empty(K + 1, dtype=torch.int32, device=dev)
             m["qnaddrs"] = torch.empty(K + 1, dtype=torch.int32, device=dev)
@@ -314,9 +341,6 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
                               _ptr(m["naddrs"]), _ptr(m["qnaddrs"]), _ptr(m["tile_base"]), _ptr(sizes[j]), stream)
             else:
                 m["nbsizes"].zero_(); m["naddrs"].zero_(); m["qnaddrs"].zero_(); sizes[j].zero_()
-        # exact_sizes: one host read of all list sizes (the reference reads them per map) so that nbmaps has its exact
-        # shape [2, nnz].  Otherwise nothing is read back: the lists get their worst-case capacity (rows * T pairs,
-        # allocated but never touched beyond nnz) and the kernels take the sizes from naddrs / qnaddrs on the device.
         host_sizes = sizes.cpu().tolist() if exact_sizes else None
         for j, m in enumerate(ws_maps):
             rows = m["rows"]

@@ -70,7 +70,7 @@ _ATOMIC_BYTES_PER_US = 2.6e6   # fp32 vector reductions into the weight-stationa
 _STREAM_BYTES_PER_US = 4.0e6   # zero-fill + final conversion pass of the scratch
 _WS_FIXED_US = 22.0            # memset + conversion launches and the latency floor of three dependent kernels
 _OS_FIXED_US = 14.0
-_INVERT_US = (40.0, 3.0e6)     # output-stationary map of a transposed layer: fixed cost + map bytes per us (inverse + grouping)
+_INVERT_US = (90.0, 3.0e6)     # output-stationary map of a transposed layer: inverse + its own grouping (a sort), fixed + bytes per us
 _SM_COUNT = 148
 
 
