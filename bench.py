@@ -321,13 +321,13 @@ def roofline_from_layers(layers, pk, pk_kind):
     if ideal_hbm_ms >= ideal_tensor_ms:
         ach = byts / (t_ms * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(ach / pk["hbm_gbs"], 4),
-                "traffic": None, "kernel": "conv_tc_kernel / conv_*_simt_kernel (all sparse-convolution layers of one scene)",
+                "traffic": None, "kernel": "conv_os_n256_kernel / conv_tc_kernel / conv_os_stem_kernel (all sparse-convolution layers of one scene)",
                 "peak_source": f"of {pk_kind}", "launches": len(layers), "kernel_ms_per_step": round(t_ms, 4),
                 "algorithmic_bytes_per_step": int(byts), "tflops": round(flops / (t_ms * 1e-3) / 1e12, 2)}
     ach = flops / (t_ms * 1e-3) / 1e12
     return {"bound": "tensor", "achieved": round(ach, 2), "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
             "frac": round(ach / pk["bf16_tflops_sustained"], 4), "traffic": None,
-            "kernel": "conv_tc_kernel / conv_*_simt_kernel (all sparse-convolution layers of one scene)", "peak_source": f"of {pk_kind}",
+            "kernel": "conv_os_n256_kernel / conv_tc_kernel / conv_os_stem_kernel (all sparse-convolution layers of one scene)", "peak_source": f"of {pk_kind}",
             "launches": len(layers), "kernel_ms_per_step": round(t_ms, 4), "algorithmic_flops_per_step": int(flops),
             "gbs": round(byts / (t_ms * 1e-3) / 1e9, 1)}
 
@@ -515,6 +515,12 @@ def main():
         d2h_bytes[0] = y.numel() * y.element_size()
         return y
 
+    # set-up, both arms alike: every scene of the rank runs once through both entry points, so that the caching
+    # allocator has seen every tensor size before the W warm-up steps (a first-time size costs a cudaMalloc)
+    for i in range(len(dev)):
+        step_resident(i)
+        step_e2e(i)
+    torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -537,7 +543,9 @@ def main():
         "dtype": "f16 (fp32 accumulate); u32 packed keys", "data": "synthetic",
         "config": {"workload": wl["label"], "voxels_per_scene": n_vox, "scenes_per_rank": len(dev),
                    "timed_region": "order() + add_all_kernel_maps() + model forward, per scene",
-                   "l2": "256 MiB buffer rewritten between timed steps", "dataflows": chosen_note, "sharding": "independent scenes per GPU, no collective",
+                   "l2": "256 MiB buffer rewritten between timed steps",
+                   "setup": "tune / compile, then every scene once untimed (allocator priming), then the W warm-up steps",
+                   "dataflows": chosen_note, "sharding": "independent scenes per GPU, no collective",
                    "fused_epilogue": bool(args.impl == "ours" and not args.no_fuse),
                    "recorded_tape": bool(args.impl == "ours" and not args.no_compile)},
         "e2e": {"value": round(e2e_value, 3), "unit": "scenes/s", "ms_per_step": round(e2e_ms / args.steps, 4),
