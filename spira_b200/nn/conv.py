@@ -103,7 +103,24 @@ class KernelMapCache(object):
                             init_stride: Union[int, Tuple[int, ...]], dataflow: List[int]):
         """Network-wide precompute: all down-sampled coordinate sets, then all kernel maps in one batched
         search (reference: conv.py:116-151)."""
-        output = F.streamed_output_generate(source_coordinates, target_strides) if len(target_strides) else []
+        t_strides = [as_tuple(s, size=3, name="target_stride") for s in target_strides]
+        k_sizes = [as_tuple(k, size=3, name="kernel_size") for k in kernel_sizes]
+        k_strides = [as_tuple(s, size=3, name="kernel_stride") for s in source_strides[:-1]]
+        if not (len(k_sizes) == len(k_strides) == len(dataflow)):
+            raise ValueError("All argument lists must have the same length in add_all_kernel_maps")
+        source_coordinates = source_coordinates.contiguous()
+        pending = _C.streamed_output_generate_begin(source_coordinates, t_strides) if len(t_strides) and len(k_sizes) \
+            and hasattr(_C, "streamed_output_generate_begin") else None
+        # The layers of this package read the pair lists through the engine's own structures, so the list sizes stay on
+        # the device: the level sizes are the only host read of a scene.  Map 0 has the level-0 keys on both sides and
+        # does not need them: its search (and grouping or list building) is enqueued while the sizes travel to the host.
+        first = None
+        if pending is not None:
+            first = _C.cuda_binary_search_pairs([(source_coordinates, source_coordinates)], k_sizes[:1], k_strides[:1],
+                                                dataflow[:1], exact_sizes=False)
+            output = _C.streamed_output_generate_end(pending)
+        else:
+            output = F.streamed_output_generate(source_coordinates, t_strides) if len(t_strides) else []
         voxels: List[torch.Tensor] = [source_coordinates] + output
 
         s_stride = as_tuple(init_stride, size=3)
@@ -111,9 +128,12 @@ class KernelMapCache(object):
         for i, t_stride in enumerate(target_strides):
             self._coordinates_cache[as_tuple(t_stride, size=3)] = voxels[i + 1]
 
-        # the layers of this package read the pair lists through the engine's own structures, so the list sizes can
-        # stay on the device (no second host synchronisation per scene)
-        kmaps = F.build_kmap_streamed(voxels, kernel_sizes, source_strides[:-1], dataflow, exact_sizes=False)
+        if first is not None:
+            pairs = [(voxels[i // 2], voxels[(i + 1) // 2]) for i in range(1, len(k_sizes))]
+            kmaps = first + (_C.cuda_binary_search_pairs(pairs, k_sizes[1:], k_strides[1:], dataflow[1:], exact_sizes=False)
+                             if pairs else [])
+        else:
+            kmaps = F.build_kmap_streamed(voxels, kernel_sizes, source_strides[:-1], dataflow, exact_sizes=False)
 
         for i in range(len(kernel_sizes)):
             t_stride = as_tuple(source_strides[i + 1], size=3)

@@ -173,6 +173,69 @@ def _strides_double(strides) -> bool:
     return True
 
 
+class PendingLevels:
+    """Down-sampling whose kernels are enqueued and whose level sizes are on their way to the host."""
+    __slots__ = ("coordinates", "strides", "bufs", "counts", "host", "done", "levels")
+
+
+_side_channel = {}      # device index -> (side stream, pinned int32 buffer for the level sizes)
+
+
+def streamed_output_generate_begin(coordinates: torch.Tensor, target_strides) -> Optional[PendingLevels]:
+    """First half of :func:`cuda_streamed_output_generate` for sorted keys and doubling strides: launches the kernels and
+    starts the copy of the level sizes on a side stream, so that the caller can enqueue work that does not depend on
+    the sizes (the level-0 kernel map) before it waits in :func:`streamed_output_generate_end`.  Returns None when this
+    path does not apply (then call the blocking function)."""
+    strides = [tuple(int(v) for v in s) for s in target_strides]
+    L = len(strides)
+    if not (SORT_FREE_DOWNSAMPLE and coordinates.is_cuda and coordinates.dim() == 1 and 1 <= L <= MAX_LEVELS
+            and _strides_double(strides) and coordinates.shape[0] > 0):
+        return None
+    coordinates = coordinates.contiguous()
+    n, kb, dev = coordinates.shape[0], _key_bytes(coordinates), coordinates.device
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    chan = _side_channel.get(idx)
+    if chan is None:
+        chan = _side_channel[idx] = (torch.cuda.Stream(device=dev), torch.empty(MAX_LEVELS + 1, dtype=torch.int32).pin_memory())
+    side, host = chan
+    p = PendingLevels()
+    p.coordinates, p.strides, p.levels = coordinates, strides, L
+    p.bufs = torch.empty((L, n), dtype=coordinates.dtype, device=dev)
+    p.counts = torch.zeros(L + 1, dtype=torch.int32, device=dev)
+    need = C.c_size_t()
+    _lib.call("spira_b200_downsample_sorted_workspace", n, kb, C.byref(need))
+    ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
+    host_strides = (C.c_int32 * (3 * L))(*[v for s in strides for v in s])
+    host_out = (C.c_void_p * L)(*[p.bufs[l].data_ptr() for l in range(L)])
+    _lib.call("spira_b200_downsample_sorted", _ptr(coordinates), n, kb, L, host_strides, host_out, _ptr(p.counts), _ptr(ws),
+              need.value, _ptr(p.counts[L:]), _stream(dev))
+    main = torch.cuda.current_stream(dev)
+    ready = torch.cuda.Event()
+    ready.record(main)
+    side.wait_event(ready)
+    with torch.cuda.stream(side):
+        host[:L + 1].copy_(p.counts, non_blocking=True)
+        p.done = torch.cuda.Event()
+        p.done.record(side)
+    p.host = host
+    return p
+
+
+def streamed_output_generate_end(p: PendingLevels) -> List[torch.Tensor]:
+    """Waits for the level sizes only (not for work enqueued since) and returns the level key sets."""
+    p.done.synchronize()
+    L = p.levels
+    host_counts = p.host[:L + 1].tolist()
+    if host_counts[L] != 0:      # the keys were not sorted: take the sorting path
+        global SORT_FREE_DOWNSAMPLE
+        SORT_FREE_DOWNSAMPLE, keep = False, SORT_FREE_DOWNSAMPLE
+        try:
+            return cuda_streamed_output_generate(p.coordinates, p.strides)
+        finally:
+            SORT_FREE_DOWNSAMPLE = keep
+    return [p.bufs[l, :host_counts[l]] for l in range(L)]
+
+
 def cuda_downsample(coordinates: torch.Tensor, stride_x: int, stride_y: int, stride_z: int) -> torch.Tensor:
     """``unique(sort(keys & mask))`` (csrc/spira/torch/cuda_arg_sort_coordinates.cu:68-105)."""
     return cuda_streamed_output_generate(coordinates, [(stride_x, stride_y, stride_z)])[0]
@@ -401,6 +464,14 @@ def cuda_binary_search_streamed(voxels, kernel_sizes, source_strides, dataflow, 
     voxels = [v.contiguous() for v in voxels]
     pairs = [(voxels[i // 2], voxels[(i + 1) // 2]) for i in range(len(kernel_sizes))]
     return _build_maps(pairs, kernel_sizes, source_strides, dataflow, exact_sizes)
+
+
+def cuda_binary_search_pairs(voxel_pairs, kernel_sizes, source_strides, dataflow, exact_sizes=True):
+    """Like :func:`cuda_binary_search_streamed` with the (sources, targets) pair of every map given explicitly."""
+    if not (len(voxel_pairs) == len(kernel_sizes) == len(source_strides) == len(dataflow)):
+        raise RuntimeError("[spira_b200] voxel_pairs, kernel_sizes, source_strides and dataflow must have the same length")
+    return _build_maps([(a.contiguous(), b.contiguous()) for a, b in voxel_pairs], kernel_sizes, source_strides, dataflow,
+                       exact_sizes)
 
 
 def cuda_binary_search_no_small_z(sources, targets, kernel_size, source_stride):
