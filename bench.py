@@ -380,6 +380,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap"])
+    ap.add_argument("--no-n256", action="store_true", help="output-stationary layers always use the targets-as-M kernel")
+    ap.add_argument("--team-threads", type=int, default=0, choices=[0, 128, 256, 512],
+                    help="producer threads per pipeline stage of the exchanged-operand kernel (0 = library default)")
     ap.add_argument("--gather", default="default", choices=["default", "tma", "cpasync"], help="row-gather engine of the tensor-core kernels")
     ap.add_argument("--cin", type=int, default=64)
     ap.add_argument("--cout", type=int, default=64)
@@ -404,6 +407,12 @@ def main():
     n_gpus = world
 
     pk, pk_kind = peaks()
+    if args.impl == "ours" and args.no_n256:
+        from spira_b200.nn.functional import _C as native_
+        native_.set_option("os_n256", 0)
+    if args.impl == "ours" and args.team_threads:
+        from spira_b200.nn.functional import _C as native_
+        native_.set_option("os_team_threads", args.team_threads)
     if args.impl == "ours" and args.gather != "default":
         from spira_b200 import build
         build.build()

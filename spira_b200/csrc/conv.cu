@@ -589,7 +589,6 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
 // =====================================================================================================================
 constexpr int kN2Rows = 256;                 // targets per tile (MMA N)
 constexpr int kN2FeatBytes = kN2Rows * 128;  // one feature stage
-constexpr int kN2TeamThreads = 128;          // a team: 8 lanes per row, 16 rows per thread
 
 struct ConvN2Params {
   const __half *feats;
@@ -605,7 +604,14 @@ struct ConvN2Params {
   int off_feat, off_slab, off_tr, off_cm, off_meta, off_bar;
 };
 
+// kTeamThreads: producer threads that fill one stage together (128, 256 or 512: 4, 2 or 1 teams; 8 lanes per row, so a
+// thread owns one 16-byte piece of 16, 8 or 4 rows).  Stage s is filled by team s % teams.
+template <int kTeamThreads>
 __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __grid_constant__ ConvN2Params P) {
+  constexpr int kN2TeamThreads = kTeamThreads;
+  constexpr int kRowsPerThread = kN2Rows * 8 / kTeamThreads;     // 16, 8, 4
+  constexpr int kRowStep = kTeamThreads / 8;                     // rows between two places of a thread
+  constexpr uint32_t kSlotMask = (1u << kRowsPerThread) - 1u;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char *smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
@@ -624,7 +630,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int stages = P.stages;
-  constexpr int kTeams = kProducers / kN2TeamThreads;   // 4
+  constexpr int kTeams = kProducers / kN2TeamThreads;   // 4, 2, 1
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -649,21 +655,22 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < kProducerWarps) {
-    // =========================== producers: 4 teams of 128 threads, stage s is filled by team s % 4 ===========
-    // Thread r of a team owns ONE 16-byte piece (r & 7) of 16 rows (r >> 3, +16, ...): the eight lanes that share a row
-    // read 128 contiguous bytes, so a warp-level copy touches 4 rows instead of 32 different cache lines (the L1
-    // processes one line per cycle: a thread-per-row mapping is bound by that, not by bandwidth).
-    const int team = warp >> 2, r = tid & 127;
+    // =========================== producers: teams of kTeamThreads threads, stage s is filled by team s % kTeams ======
+    // Thread r of a team owns ONE 16-byte piece (r & 7) of kRowsPerThread rows (r >> 3, + kRowStep, ...): the eight lanes
+    // that share a row read 128 contiguous bytes, so a warp-level copy touches 4 rows instead of 32 different cache lines
+    // (the L1 processes one line per cycle: a thread-per-row mapping is bound by that, not by bandwidth).
+    const int team = tid / kN2TeamThreads, r = tid % kN2TeamThreads;
     const int piece = r & 7, rowbase = r >> 3;
-    const uint32_t dst_off = rowbase * 128 + ((piece ^ (rowbase & 7)) << 4);   // (row & 7) == (rowbase & 7) for all 16 rows
+    const uint32_t dst_off = rowbase * 128 + ((piece ^ (rowbase & 7)) << 4);   // (row & 7) == (rowbase & 7) for all rows
     const float inv_c_in = 1.0f / static_cast<float>(P.c_in);
     const int n_words = (P.n_chunks + 31) >> 5;
     bool ok = true;
     int tile_i = 0, q_mod_teams = 0, my_stage = team, my_slot = 0;
     uint32_t my_phase = 0;
     // Most neighbours of an output-stationary tile are missing (~70 % on LiDAR scenes) and their rows must read as
-    // zeros.  This thread always writes the same 16 (row, piece) places of the same stages (stage = slot * 4 + team), so
-    // it remembers which of them hold zeros (bit slot * 16 + i) and skips the zero-fill of a place that is zero already.
+    // zeros.  This thread always writes the same (row, piece) places of the same stages (stage = slot * kTeams + team),
+    // so it remembers which of them hold zeros (bit slot * kRowsPerThread + i) and skips the zero-fill of a place that is
+    // zero already.
     uint32_t zero_rows = 0;
     for (int w = tid; w < 2 * n_words; w += kProducers) cmask[w] = 0;
     // grouped maps come with the offsets present in each 128-row tile; the masks of the next tile are fetched a tile ahead
@@ -725,7 +732,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
           ++pos;
         }
         const int j = (word << 5) + __ffs(bits) - 1;
-        const int stage = my_stage, slot_shift = my_slot * 16;
+        const int stage = my_stage, slot_shift = my_slot * kRowsPerThread;
         if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
         my_stage += kTeams;
         ++my_slot;
@@ -747,17 +754,17 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
         uint32_t now_zero = 0;
         // all map entries first: the copies below are compiler barriers, and a shared-memory load issued between them
         // would queue behind them in the load/store unit
-        int idx[kN2Rows / 16];
+        int idx[kRowsPerThread];
 #pragma unroll
-        for (int i = 0; i < kN2Rows / 16; ++i) idx[i] = piece_valid ? col[i * 16 * P.K] : -1;
+        for (int i = 0; i < kRowsPerThread; ++i) idx[i] = piece_valid ? col[i * kRowStep * P.K] : -1;
 #pragma unroll
-        for (int i = 0; i < kN2Rows / 16; ++i) {
+        for (int i = 0; i < kRowsPerThread; ++i) {
           const __half *src = P.feats + (idx[i] >= 0 ? (static_cast<int64_t>(idx[i]) * P.c_in + c) : 0);
           // a missing neighbour needs zeros: nothing to do if the previous fill of this stage left zeros there
-          if (idx[i] >= 0 || !((was_zero >> i) & 1u)) cp_async_16(dst + i * 2048, src, idx[i] >= 0 ? 16u : 0u);
+          if (idx[i] >= 0 || !((was_zero >> i) & 1u)) cp_async_16(dst + i * (kRowStep * 128), src, idx[i] >= 0 ? 16u : 0u);
           now_zero |= (idx[i] >= 0 ? 0u : 1u) << i;
         }
-        zero_rows = (zero_rows & ~(0xffffu << slot_shift)) | (now_zero << slot_shift);
+        zero_rows = (zero_rows & ~(kSlotMask << slot_shift)) | (now_zero << slot_shift);
         cp_async_mbar_arrive_noinc(bar_full(stage));
       }
       q_mod_teams += n_chunks_tile % kTeams;
@@ -1152,7 +1159,7 @@ static size_t plan_smem(ConvParams &P, bool ws) {
 }
 
 // Shared-memory plan of conv_os_n256_kernel; returns the dynamic shared memory size or 0 if it does not fit.
-static size_t plan_smem_n256(ConvN2Params &P) {
+static size_t plan_smem_n256(ConvN2Params &P, int teams) {
   P.w_bytes = P.c_out * 128;
   P.w_stride = (P.w_bytes + 1023) / 1024 * 1024;
   const int slab_bytes = kN2Rows * P.K * 4;
@@ -1162,7 +1169,7 @@ static size_t plan_smem_n256(ConvN2Params &P) {
   const int per_stage = P.w_stride + kN2FeatBytes;
   int stages = (kSmemBudget - fixed) / per_stage;
   if (stages > kMaxStages) stages = kMaxStages;
-  stages &= ~3;                       // four producer teams: stage s is filled by team s % 4
+  stages -= stages % teams;           // stage s is filled by team s % teams
   if (stages < 4) return 0;
   P.stages = stages;
   P.off_feat = stages * P.w_stride;   // the weight stages come first: an M=128 descriptor may read past a short one
@@ -1175,6 +1182,7 @@ static size_t plan_smem_n256(ConvN2Params &P) {
 }
 
 static int g_os_n256 = 1;          // 1: layers with c_out <= 128 use the exchanged-operand kernel
+static int g_os_team_threads = 128;   // producer threads per stage of that kernel: 128, 256 or 512
 
 }  // namespace sb
 
@@ -1265,13 +1273,18 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
     Q.K = K; Q.c_in = c_in; Q.c_out = c_out;
     Q.R = K * c_in;
     Q.n_chunks = static_cast<int>(div_up(Q.R, kChunk));
-    size_t smem2 = plan_smem_n256(Q);
+    size_t smem2 = plan_smem_n256(Q, kProducers / g_os_team_threads);
     if (smem2 != 0) {
-      SB_CHECK_CUDA(cudaFuncSetAttribute(conv_os_n256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
-      int grid = Q.n_tiles < sm_count() ? Q.n_tiles : sm_count();
-      conv_os_n256_kernel<<<grid, kConvThreads, smem2, as_stream(stream)>>>(Q);
-      SB_CHECK_LAUNCH();
-      return SPIRA_B200_OK;
+      const int grid = Q.n_tiles < sm_count() ? Q.n_tiles : sm_count();
+      auto launch = [&](auto kernel) -> int {
+        SB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
+        kernel<<<grid, kConvThreads, smem2, as_stream(stream)>>>(Q);
+        SB_CHECK_LAUNCH();
+        return SPIRA_B200_OK;
+      };
+      if (g_os_team_threads == 512) return launch(conv_os_n256_kernel<512>);
+      if (g_os_team_threads == 256) return launch(conv_os_n256_kernel<256>);
+      return launch(conv_os_n256_kernel<128>);
     }
   }
   ConvParams P{};
@@ -1309,7 +1322,6 @@ extern "C" int spira_b200_conv_os_grouped(const void *feats, const void *packed,
                                           void *out, int32_t *status, void *stream) {
   SB_CHECK_ARG(num_targets == 0 || (row_of && tile_masks && packed), "conv_os_grouped: null pointer");
   SB_CHECK_ARG(K <= 32, "conv_os_grouped: K=%d, grouped maps have at most 32 offsets", K);
-  SB_CHECK_ARG(!g_gather_tma, "conv_os_grouped: not available with the TMA gather producer");
   return conv_os_impl(feats, nullptr, packed, epilogue, grouped_map, row_of, tile_masks, num_sources, num_targets, K, c_in,
                       c_out, out, status, stream);
 }
@@ -1383,6 +1395,11 @@ extern "C" int spira_b200_set_option(const char *name, int value) {
   SB_CHECK_ARG(name != nullptr, "set_option: null name");
   if (std::strcmp(name, "gather_tma") == 0) { g_gather_tma = value ? 1 : 0; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_n256") == 0) { g_os_n256 = value ? 1 : 0; return SPIRA_B200_OK; }
+  if (std::strcmp(name, "os_team_threads") == 0) {
+    SB_CHECK_ARG(value == 128 || value == 256 || value == 512, "set_option: os_team_threads must be 128, 256 or 512");
+    g_os_team_threads = value;
+    return SPIRA_B200_OK;
+  }
   return fail(SPIRA_B200_ERR_ARGUMENT, "set_option: unknown option '%s'", name);
 }
 
@@ -1390,6 +1407,7 @@ extern "C" int spira_b200_get_option(const char *name) {
   if (name == nullptr) return -1;
   if (std::strcmp(name, "gather_tma") == 0) return g_gather_tma;
   if (std::strcmp(name, "os_n256") == 0) return g_os_n256;
+  if (std::strcmp(name, "os_team_threads") == 0) return g_os_team_threads;
   if (std::strcmp(name, "os_pack_mode") == 0) return g_gather_tma ? SPIRA_B200_PACK_WS : SPIRA_B200_PACK_OS;
   return -1;
 }

@@ -576,7 +576,7 @@ def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None
     ep, keep = _epilogue(bias, scale, shift, residual, relu)
     sb = getattr(out_in_map, "_sb", None)
     g = sb.get("grouped") if (sb is not None and grouped and GROUP_OS) else None
-    if g is not None and packed is not None and get_option("gather_tma") == 0:
+    if g is not None and packed is not None:
         _lib.call("spira_b200_conv_os_grouped", _ptr(sources), _ptr(packed), C.byref(ep) if ep is not None else None, g.map_ptr,
                   g.row_of_ptr, g.tile_masks_ptr, int(num_sources), int(num_targets), K, cin, cout, _ptr(out),
                   _ptr(status_word(sources.device)), _stream(sources.device))
@@ -678,9 +678,9 @@ def run_conv_os(call: ConvCall, num_sources: int, num_targets: int, out_in_map: 
     sb = getattr(out_in_map, "_sb", None)
     g = sb.get("grouped") if sb is not None else None
     mode = _lib.load().spira_b200_get_option(b"os_pack_mode")
-    if g is not None and call.eligible and GROUP_OS and mode == PACK_OS:
+    if g is not None and call.eligible and GROUP_OS:
         name, fn = "spira_b200_conv_os_grouped", call.fn_os_grouped
-        args = (feats.data_ptr(), call.packed_ptr(PACK_OS), call.ep_ref, g.map_ptr, g.row_of_ptr, g.tile_masks_ptr,
+        args = (feats.data_ptr(), call.packed_ptr(mode), call.ep_ref, g.map_ptr, g.row_of_ptr, g.tile_masks_ptr,
                 num_sources, num_targets, call.K, call.cin, call.cout, out.data_ptr(), call.status_ptr,
                 _raw_stream(call.dev_index))
     else:
