@@ -46,9 +46,9 @@ int spira_b200_reset_error(void);
 /* Run-time options of the calling process (not thread safe; set them before launching work):
  *   "gather_tma"        1: the tensor-core kernels fetch feature rows with TMA gather4, 0 (default): with 16-byte
  *                       cp.async
- *   "os_n256"           1 (default): output-stationary layers with c_out <= 128 and K <= 32 whose four-stage pipeline
- *                       fits in shared memory (c_out <= 96 for K = 27) run the kernel that puts 256 targets on the
- *                       MMA's N side and the weights on its M side; 0: always 128 targets as M
+ *   "os_n256"           1 (default): output-stationary layers with 64 < c_out <= 128 and K <= 32 whose four-stage
+ *                       pipeline fits in shared memory (c_out <= 96 for K = 27) run the kernel that puts 256 targets
+ *                       on the MMA's N side and the weights on its M side; 0: always 128 targets as M
  *   "os_team_threads"   128 (default), 256 or 512: producer threads that fill one pipeline stage of that kernel
  *                       together (4, 2 or 1 teams); measured equal within noise for 128 and 256, slower for 512
  * get_option additionally answers "os_pack_mode": the SPIRA_B200_PACK_* image spira_b200_conv_os expects under

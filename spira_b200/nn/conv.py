@@ -32,6 +32,9 @@ class KernelMapCache(object):
         self._kernel_maps_cache = dict()
         self._coordinates_cache = dict()
         self._derived = dict()   # maps derived from cached ones (transposed / inverted), built once
+        # keys of the maps a transposed output-stationary layer asked the inverse of; kept across reset(): the next
+        # network-wide build makes those inverses right away, grouped by the same sort as all other maps
+        self._inverse_keys = set()
 
     def reset(self):
         self._coordinates_cache.clear()
@@ -92,6 +95,7 @@ class KernelMapCache(object):
                 sb = getattr(entry[3], "_sb", None)
                 if sb is not None:
                     inv._sb = dict(sb, ws=None, counts=None, grouped=_C.group_os_map(inv, entry[1]))
+                    self._inverse_keys.add(key)
                 self._derived[dkey] = inv
             new_entry = list(entry[1:])
             new_entry[2] = self._derived[dkey]
@@ -128,18 +132,39 @@ class KernelMapCache(object):
         for i, t_stride in enumerate(target_strides):
             self._coordinates_cache[as_tuple(t_stride, size=3)] = voxels[i + 1]
 
-        if first is not None:
+        deferred = first is not None
+        if deferred:
+            # the remaining maps are grouped below, together with the inverses the transposed layers will ask for
             pairs = [(voxels[i // 2], voxels[(i + 1) // 2]) for i in range(1, len(k_sizes))]
-            kmaps = first + (_C.cuda_binary_search_pairs(pairs, k_sizes[1:], k_strides[1:], dataflow[1:], exact_sizes=False)
-                             if pairs else [])
+            kmaps = first + (_C.cuda_binary_search_pairs(pairs, k_sizes[1:], k_strides[1:], dataflow[1:], exact_sizes=False,
+                                                         group=False) if pairs else [])
         else:
             kmaps = F.build_kmap_streamed(voxels, kernel_sizes, source_strides[:-1], dataflow, exact_sizes=False)
 
+        keys = []
         for i in range(len(kernel_sizes)):
             t_stride = as_tuple(source_strides[i + 1], size=3)
             key = (s_stride, t_stride, as_tuple(kernel_sizes[i], size=3))
             self._kernel_maps_cache[key] = [False, *kmaps[i]]
+            keys.append(key)
             s_stride = t_stride
+
+        if deferred:
+            todo = []       # (tensor that carries the grouped twin, number of rows)
+            for i, key in enumerate(keys):
+                entry = self._kernel_maps_cache[key]
+                sb = getattr(entry[3], "_sb", None)
+                if sb is None or sb.get("layout") != _C.LAYOUT_OS:
+                    continue
+                if i > 0:
+                    todo.append((entry[3], entry[2]))
+                if key in self._inverse_keys:
+                    inv = F.convert_transposed_os(entry[3], entry[1])
+                    inv._sb = dict(sb, ws=None, counts=None, grouped=None)
+                    self._derived[(key, "inverted")] = inv
+                    todo.append((inv, entry[1]))
+            for (mp, _), g in zip(todo, _C.group_os_maps(todo)):
+                mp._sb["grouped"] = g
         return self
 
 

@@ -309,7 +309,7 @@ def group_os_map(map_os: torch.Tensor, num_targets: int) -> Optional[GroupedMap]
     return group_os_maps([(map_os, int(num_targets))])[0]
 
 
-def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_sizes=True):
+def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_sizes=True, group=True):
     """Shared implementation of the serial and the network-wide builders.
 
     ``voxel_pairs[i] = (sources, targets)``.  One search launch per group of <= 16 maps, one
@@ -425,9 +425,10 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
             w.qmapsize = None if qmapsize is None else int(qmapsize)
             m["ws"] = w
 
-    os_maps = [m for m in info if m["layout"] == LAYOUT_OS]
-    for m, g in zip(os_maps, group_os_maps([(m["dense"], m["T"]) for m in os_maps])):
-        m["grouped"] = g
+    if group:       # else the caller groups these maps together with others of its own
+        os_maps = [m for m in info if m["layout"] == LAYOUT_OS]
+        for m, g in zip(os_maps, group_os_maps([(m["dense"], m["T"]) for m in os_maps])):
+            m["grouped"] = g
 
     results = []
     for m in info:
@@ -466,12 +467,13 @@ def cuda_binary_search_streamed(voxels, kernel_sizes, source_strides, dataflow, 
     return _build_maps(pairs, kernel_sizes, source_strides, dataflow, exact_sizes)
 
 
-def cuda_binary_search_pairs(voxel_pairs, kernel_sizes, source_strides, dataflow, exact_sizes=True):
-    """Like :func:`cuda_binary_search_streamed` with the (sources, targets) pair of every map given explicitly."""
+def cuda_binary_search_pairs(voxel_pairs, kernel_sizes, source_strides, dataflow, exact_sizes=True, group=True):
+    """Like :func:`cuda_binary_search_streamed` with the (sources, targets) pair of every map given explicitly.
+    ``group=False`` leaves the output-stationary maps without their grouped twin (:func:`group_os_maps` adds it)."""
     if not (len(voxel_pairs) == len(kernel_sizes) == len(source_strides) == len(dataflow)):
         raise RuntimeError("[spira_b200] voxel_pairs, kernel_sizes, source_strides and dataflow must have the same length")
     return _build_maps([(a.contiguous(), b.contiguous()) for a, b in voxel_pairs], kernel_sizes, source_strides, dataflow,
-                       exact_sizes)
+                       exact_sizes, group)
 
 
 def cuda_binary_search_no_small_z(sources, targets, kernel_size, source_stride):

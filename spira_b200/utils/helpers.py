@@ -62,15 +62,16 @@ class DataflowConfig:
 # Calibration of the selector's cost model, measured on B200 with the kernels of this package (per-layer CUDA-event
 # timings of a MinkUNet18-style network on ~125k-voxel scenes):
 _CHUNK_US = (0.45, 0.0012)     # one pipeline stage of 128 rows x 64 channels (targets-as-M kernel): a + b * c_out us
-_CHUNK256_US = 0.72            # one stage of 256 rows x 64 channels (targets-as-N kernel, c_out <= 96, K <= 32)
+_CHUNK256_US = 0.72            # one stage of 256 rows x 64 channels (targets-as-N kernel, 64 < c_out <= 96, K <= 32)
 _GROUPED_REDUNDANCY = (1.2, 1.3)   # rows visited per real pair once the map rows are grouped (128- / 256-row tiles)
-_IMBALANCE = (1.7, 1.4)        # heaviest CTA over the mean (128- / 256-row tiles)
-_TILE_OVERHEAD_CHUNKS = 8.0    # per-tile prologue and epilogue, in units of one stage
+_IMBALANCE = (1.3, 1.3)        # heaviest CTA over the mean (128- / 256-row tiles)
+_TILE_OVERHEAD_CHUNKS = (3.0, 6.0)   # per-tile prologue and epilogue, in units of one stage (128- / 256-row tiles)
+_HEAVIEST_TILE = 0.75          # share of all offsets present in the fullest tile of a grouped map
 _ATOMIC_BYTES_PER_US = 2.6e6   # fp32 vector reductions into the weight-stationary scratch: ~2.6 TB/s
 _STREAM_BYTES_PER_US = 4.0e6   # zero-fill + final conversion pass of the scratch
 _WS_FIXED_US = 22.0            # memset + conversion launches and the latency floor of three dependent kernels
 _OS_FIXED_US = 14.0
-_INVERT_US = (90.0, 3.0e6)     # output-stationary map of a transposed layer: inverse + its own grouping (a sort), fixed + bytes per us
+_INVERT_US = (15.0, 3.0e6)     # output-stationary map of a transposed layer: inverse + its share of the grouping, fixed + bytes per us
 _SM_COUNT = 148
 
 
@@ -78,7 +79,7 @@ def estimate_layer_us(c_in: int, c_out: int, kernel_volume: int, num_targets: in
                       nonempty_tile_offsets: int = None, submanifold: bool = True, transposed: bool = False):
     """(output-stationary, weight-stationary) time estimates in microseconds.
 
-    OS runs one persistent CTA per SM over tiles of 128 (or, for c_out <= 96, 256) map rows and streams one stage per
+    OS runs one persistent CTA per SM over tiles of 128 (or, for 64 < c_out <= 96, 256) map rows and streams one stage per
     (tile, 64 reduction elements) with a neighbour.  Maps with K <= 32 have their rows grouped by neighbour pattern,
     which leaves ~1.2-1.3 visited rows per real pair; other maps visit every non-empty (tile, offset) pair
     (``nonempty_tile_offsets``, from the search's hit counters).  WS streams one stage per 128 compacted pairs and 64
@@ -87,7 +88,7 @@ def estimate_layer_us(c_in: int, c_out: int, kernel_volume: int, num_targets: in
     import math
     chunk = _CHUNK_US[0] + _CHUNK_US[1] * c_out
     per_in = c_in / 64.0
-    wide = not (c_out <= 96 and kernel_volume <= 32)
+    wide = not (64 < c_out <= 96 and kernel_volume <= 32)     # 128-row tiles (targets as M) unless the 256-target kernel applies
     rows_per_tile = 128 if wide else 256
     tiles = max(1, math.ceil(num_targets / rows_per_tile))
     ctas = min(_SM_COUNT, tiles)
@@ -99,8 +100,11 @@ def estimate_layer_us(c_in: int, c_out: int, kernel_volume: int, num_targets: in
         if nonempty_tile_offsets is None:
             nonempty_tile_offsets = tiles128 * kernel_volume
         stages = nonempty_tile_offsets * per_in
-    os_us = _OS_FIXED_US + stage_us * (_IMBALANCE[0 if wide else 1] * stages / ctas
-                                       + _TILE_OVERHEAD_CHUNKS * math.ceil(tiles / ctas))
+    which = 0 if wide else 1
+    per_cta = _IMBALANCE[which] * stages / ctas + _TILE_OVERHEAD_CHUNKS[which] * math.ceil(tiles / ctas)
+    if kernel_volume <= 32:     # no CTA finishes before the fullest tile of the grouped map
+        per_cta = max(per_cta, _HEAVIEST_TILE * kernel_volume * per_in + _TILE_OVERHEAD_CHUNKS[which])
+    os_us = _OS_FIXED_US + stage_us * per_cta
     if transposed:
         os_us += _INVERT_US[0] + num_targets * kernel_volume * 8 / _INVERT_US[1]
     rows = (kernel_volume + 1) // 2 if submanifold and kernel_volume % 2 == 1 else kernel_volume

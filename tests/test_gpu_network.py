@@ -206,3 +206,27 @@ def test_rebuilding_maps_every_scene_releases_the_previous_ones(lib, dataflow):
     finally:
         gc.enable()
     assert levels[-1] == levels[1], levels
+
+
+def test_inverse_maps_of_transposed_layers_are_prebuilt_from_the_second_scene_on(lib):
+    import spira_b200 as sp
+    from spira_b200 import models, scenes, nn as spnn
+    torch.manual_seed(1)
+    c = scenes.lidar_scene(6)[:40000]
+    coords = torch.from_numpy(c).cuda()
+    feats = torch.from_numpy(scenes.features(len(c), 4, 6)).cuda()
+    model = models.minkunet18(4, 19, 3).cuda().half().eval()
+    cache = spnn.KernelMapCache()
+    sp.set_kernel_map_cache(model, cache)
+    sched = models.map_schedule(4, 3, 3)
+    y0, _ = run(model, cache, coords, feats, sched, 0)          # inverses built on demand, their keys remembered
+    assert len(cache._inverse_keys) == 4
+    x = sp.SparseTensor(coords.clone(), feats.clone()).order()
+    ks, ss, ts = sched
+    cache.reset()
+    cache.add_all_kernel_maps(x._coordinates, ks, ss, ts, (1, 1, 1), [0] * len(ks))
+    inv = [v for k, v in cache._derived.items() if k[1] == "inverted"]
+    assert len(inv) == 4 and all(v._sb["grouped"] is not None for v in inv if v.shape[0] >= 1024)
+    with torch.no_grad():
+        y1 = model(x)
+    assert torch.equal(y0._features, y1._features)
