@@ -71,7 +71,8 @@ _ATOMIC_BYTES_PER_US = 2.6e6   # fp32 vector reductions into the weight-stationa
 _STREAM_BYTES_PER_US = 4.0e6   # zero-fill + final conversion pass of the scratch
 _WS_FIXED_US = 22.0            # memset + conversion launches and the latency floor of three dependent kernels
 _OS_FIXED_US = 14.0
-_INVERT_US = (15.0, 3.0e6)     # output-stationary map of a transposed layer: inverse + its share of the grouping, fixed + bytes per us
+_INVERT_US = (150.0, 3.0e6)    # output-stationary map of a transposed layer: inverse, its rows in the grouping sort, its own
+                               # grouped copy (measured end to end: the step gets slower unless the layer saves more than that)
 _SM_COUNT = 148
 
 
