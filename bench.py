@@ -226,9 +226,14 @@ def flush_l2(buf):
 
 
 def timed_loop(step_fn, n_steps, warmup, l2buf, dist_ctx):
+    import gc
     for i in range(warmup):
         step_fn(i)
     torch.cuda.synchronize()
+    # serving hygiene, both arms alike: the long-lived objects (model, tapes, scenes) leave the collector's view, so that
+    # a full collection cannot land in the middle of a timed step (it costs tens of milliseconds with torch loaded)
+    gc.collect()
+    gc.freeze()
     if dist_ctx:
         torch.distributed.barrier()
     evs = []
@@ -248,8 +253,10 @@ def timed_loop(step_fn, n_steps, warmup, l2buf, dist_ctx):
     if dist_ctx:
         torch.distributed.barrier()
     from spira_b200 import sharding
-    total_ms = sharding.max_over_ranks(sum(a.elapsed_time(b) for a, b in evs), torch.device("cuda"))
-    return total_ms, wall
+    gc.unfreeze()
+    per_step = [a.elapsed_time(b) for a, b in evs]
+    total_ms = sharding.max_over_ranks(sum(per_step), torch.device("cuda"))
+    return total_ms, wall + (per_step,)
 
 
 def profile_kernels(engine, scene):
@@ -380,6 +387,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap"])
+    ap.add_argument("--no-defer", action="store_true", help="add_all_kernel_maps completes all maps before it returns")
     ap.add_argument("--no-n256", action="store_true", help="output-stationary layers always use the targets-as-M kernel")
     ap.add_argument("--team-threads", type=int, default=0, choices=[0, 128, 256, 512],
                     help="producer threads per pipeline stage of the exchanged-operand kernel (0 = library default)")
@@ -407,6 +415,9 @@ def main():
     n_gpus = world
 
     pk, pk_kind = peaks()
+    if args.impl == "ours" and args.no_defer:
+        from spira_b200.nn.functional import _C as native_
+        native_.DEFER_MAPS = False
     if args.impl == "ours" and args.no_n256:
         from spira_b200.nn.functional import _C as native_
         native_.set_option("os_n256", 0)
@@ -561,6 +572,7 @@ def main():
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches if args.impl == "ours" else 0,
         "host_enqueue_ms_per_step": round(wall[1] * 1e3 / args.steps, 4),
+        "step_ms_min_median_max": [round(min(wall[2]), 4), round(statistics.median(wall[2]), 4), round(max(wall[2]), 4)],
         "clocks": clocks,
     }
     if args.impl == "reference":

@@ -107,8 +107,10 @@ class CompiledModel:
         cache = self.cache
         slots: List[Optional[torch.Tensor]] = [None] * self.n_slots
         slots[0] = inputs._features
-        if inputs._stride not in cache._coordinates_cache:
-            cache._coordinates_cache[inputs._stride] = inputs._coordinates
+        if inputs._stride not in cache._coords:           # (not the property: that would complete a pending map build)
+            cache.finish()
+            if inputs._stride not in cache._coords:
+                cache._coords[inputs._stride] = inputs._coordinates
         for op in self.ops:
             kind = op[0]
             if kind == 0:

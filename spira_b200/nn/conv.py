@@ -26,34 +26,67 @@ from spira_b200.utils.typing import ScalarOrTuple
 
 
 class KernelMapCache(object):
-    """Coordinates per stride and kernel maps per ``(source_stride, target_stride, kernel_size)``."""
+    """Coordinates per stride and kernel maps per ``(source_stride, target_stride, kernel_size)``.
+
+    ``add_all_kernel_maps`` enqueues the down-sampling and the level-0 map and returns; everything that needs the level
+    sizes on the host is completed on the first request that needs it (``finish()``).  The level-0 layers of a
+    network are then enqueued first and keep the GPU busy while the remaining maps are being prepared."""
 
     def __init__(self):
-        self._kernel_maps_cache = dict()
-        self._coordinates_cache = dict()
-        self._derived = dict()   # maps derived from cached ones (transposed / inverted), built once
+        self._maps = dict()
+        self._coords = dict()
+        self._derived_maps = dict()   # maps derived from cached ones (transposed / inverted), built once
+        self._pending = None          # arguments of a network-wide build that has not been completed yet
         # keys of the maps a transposed output-stationary layer asked the inverse of; kept across reset(): the next
         # network-wide build makes those inverses right away, grouped by the same sort as all other maps
         self._inverse_keys = set()
 
+    # the three dictionaries under their historical names: reading them completes a pending build first
+    @property
+    def _kernel_maps_cache(self):
+        self.finish()
+        return self._maps
+
+    @property
+    def _coordinates_cache(self):
+        self.finish()
+        return self._coords
+
+    @property
+    def _derived(self):
+        self.finish()
+        return self._derived_maps
+
     def reset(self):
-        self._coordinates_cache.clear()
-        self._kernel_maps_cache.clear()
-        self._derived.clear()
+        self._pending = None
+        self._coords.clear()
+        self._maps.clear()
+        self._derived_maps.clear()
+
+    def finish(self):
+        """Completes a pending ``add_all_kernel_maps`` (no-op otherwise)."""
+        if self._pending is not None:
+            pending, self._pending = self._pending, None
+            self._complete(*pending)
+        return self
 
     def get_target_coordinates(self, source_coordinates: torch.Tensor, source_stride: ScalarOrTuple[int],
                                target_stride: ScalarOrTuple[int], transposed: bool = False):
         if type(source_stride) is not tuple:
             source_stride = as_tuple(source_stride, size=3, name="source_stride")
-        if source_stride not in self._coordinates_cache:
-            self._coordinates_cache[source_stride] = source_coordinates
-        if target_stride in self._coordinates_cache:
-            return self._coordinates_cache[target_stride]
+        if source_stride not in self._coords:
+            self.finish()
+            if source_stride not in self._coords:
+                self._coords[source_stride] = source_coordinates
+        if target_stride not in self._coords:
+            self.finish()
+        if target_stride in self._coords:
+            return self._coords[target_stride]
         if transposed:
             raise RuntimeError("Layer must transpose=True must have its corresponding "
                                "non-transposed layer before its execution")
         target_coordinates = F.downsample(source_coordinates, target_stride)
-        self._coordinates_cache[target_stride] = target_coordinates
+        self._coords[target_stride] = target_coordinates
         return target_coordinates
 
     def get_kernel_map(self, source_coordinates: torch.Tensor, source_stride: ScalarOrTuple[int],
@@ -68,13 +101,15 @@ class KernelMapCache(object):
             kernel_size = as_tuple(kernel_size, size=3, name="kernel_size")
         key = (target_stride, source_stride, kernel_size) if transposed else (source_stride, target_stride, kernel_size)
 
-        if key not in self._kernel_maps_cache:
+        if key not in self._maps:
+            self.finish()
+        if key not in self._maps:
             if transposed:
                 raise RuntimeError("Layer must transpose=True must have its corresponding "
                                    "non-transposed layer before its execution")
             kernel_map = F.build_kmap(source_coordinates, target_coordinates, kernel_size, source_stride, map_dataflow)
-            self._kernel_maps_cache[key] = [False, *kernel_map]
-        entry = self._kernel_maps_cache[key]  # [flipped_flag, *tuple9]
+            self._maps[key] = [False, *kernel_map]
+        entry = self._maps[key]  # [flipped_flag, *tuple9]
 
         if force_os and not entry[0]:
             # a [K, T_al] map used output-stationary: transpose it once (reference: conv.py:80-83)
@@ -90,15 +125,17 @@ class KernelMapCache(object):
             # output-stationary map of the transposed layer = inverse of the cached one.  The reference
             # rebuilds it on every forward (conv.py:85-89); it depends only on the cached map, so it is kept.
             dkey = (key, "inverted")
-            if dkey not in self._derived or not getattr(_C, "CACHE_DERIVED", True):
+            if self._pending is not None and dkey not in self._derived_maps:
+                self.finish()
+            if dkey not in self._derived_maps or not getattr(_C, "CACHE_DERIVED", True):
                 inv = F.convert_transposed_os(entry[3], entry[1])
                 sb = getattr(entry[3], "_sb", None)
                 if sb is not None:
                     inv._sb = dict(sb, ws=None, counts=None, grouped=_C.group_os_map(inv, entry[1]))
                     self._inverse_keys.add(key)
-                self._derived[dkey] = inv
+                self._derived_maps[dkey] = inv
             new_entry = list(entry[1:])
-            new_entry[2] = self._derived[dkey]
+            new_entry[2] = self._derived_maps[dkey]
             return new_entry
         return entry[1:]
 
@@ -107,65 +144,75 @@ class KernelMapCache(object):
                             init_stride: Union[int, Tuple[int, ...]], dataflow: List[int]):
         """Network-wide precompute: all down-sampled coordinate sets, then all kernel maps in one batched
         search (reference: conv.py:116-151)."""
+        self.finish()
         t_strides = [as_tuple(s, size=3, name="target_stride") for s in target_strides]
         k_sizes = [as_tuple(k, size=3, name="kernel_size") for k in kernel_sizes]
-        k_strides = [as_tuple(s, size=3, name="kernel_stride") for s in source_strides[:-1]]
-        if not (len(k_sizes) == len(k_strides) == len(dataflow)):
+        s_strides = [as_tuple(s, size=3, name="kernel_stride") for s in source_strides]
+        dataflow = list(dataflow)
+        if not (len(k_sizes) == len(s_strides) - 1 == len(dataflow)):
             raise ValueError("All argument lists must have the same length in add_all_kernel_maps")
         source_coordinates = source_coordinates.contiguous()
-        pending = _C.streamed_output_generate_begin(source_coordinates, t_strides) if len(t_strides) and len(k_sizes) \
+        s0 = as_tuple(init_stride, size=3)
+        self._coords[s0] = source_coordinates
+        levels = _C.streamed_output_generate_begin(source_coordinates, t_strides) if len(t_strides) and len(k_sizes) \
             and hasattr(_C, "streamed_output_generate_begin") else None
         # The layers of this package read the pair lists through the engine's own structures, so the list sizes stay on
         # the device: the level sizes are the only host read of a scene.  Map 0 has the level-0 keys on both sides and
-        # does not need them: its search (and grouping or list building) is enqueued while the sizes travel to the host.
+        # does not need them: it is built now, and the rest waits until somebody asks for it (finish()).
         first = None
-        if pending is not None:
-            first = _C.cuda_binary_search_pairs([(source_coordinates, source_coordinates)], k_sizes[:1], k_strides[:1],
+        if levels is not None:
+            first = _C.cuda_binary_search_pairs([(source_coordinates, source_coordinates)], k_sizes[:1], s_strides[:1],
                                                 dataflow[:1], exact_sizes=False)
-            output = _C.streamed_output_generate_end(pending)
+            self._maps[(s0, s_strides[1], k_sizes[0])] = [False, *first[0]]
+        self._pending = (source_coordinates, k_sizes, s_strides, t_strides, s0, dataflow, levels, first)
+        if levels is None or not getattr(_C, "DEFER_MAPS", True):
+            self.finish()
+        return self
+
+    def _complete(self, source_coordinates, k_sizes, s_strides, t_strides, s0, dataflow, levels, first):
+        if levels is not None:
+            output = _C.streamed_output_generate_end(levels)
         else:
             output = F.streamed_output_generate(source_coordinates, t_strides) if len(t_strides) else []
         voxels: List[torch.Tensor] = [source_coordinates] + output
-
-        s_stride = as_tuple(init_stride, size=3)
-        self._coordinates_cache[s_stride] = voxels[0]
-        for i, t_stride in enumerate(target_strides):
-            self._coordinates_cache[as_tuple(t_stride, size=3)] = voxels[i + 1]
+        for i, t_stride in enumerate(t_strides):
+            self._coords[t_stride] = voxels[i + 1]
 
         deferred = first is not None
         if deferred:
             # the remaining maps are grouped below, together with the inverses the transposed layers will ask for
             pairs = [(voxels[i // 2], voxels[(i + 1) // 2]) for i in range(1, len(k_sizes))]
-            kmaps = first + (_C.cuda_binary_search_pairs(pairs, k_sizes[1:], k_strides[1:], dataflow[1:], exact_sizes=False,
+            kmaps = first + (_C.cuda_binary_search_pairs(pairs, k_sizes[1:], s_strides[1:-1], dataflow[1:], exact_sizes=False,
                                                          group=False) if pairs else [])
         else:
-            kmaps = F.build_kmap_streamed(voxels, kernel_sizes, source_strides[:-1], dataflow, exact_sizes=False)
+            kmaps = F.build_kmap_streamed(voxels, k_sizes, s_strides[:-1], dataflow, exact_sizes=False)
 
         keys = []
-        for i in range(len(kernel_sizes)):
-            t_stride = as_tuple(source_strides[i + 1], size=3)
-            key = (s_stride, t_stride, as_tuple(kernel_sizes[i], size=3))
-            self._kernel_maps_cache[key] = [False, *kmaps[i]]
+        s_stride = s0
+        for i in range(len(k_sizes)):
+            t_stride = s_strides[i + 1]
+            key = (s_stride, t_stride, k_sizes[i])
+            if not (deferred and i == 0):
+                self._maps[key] = [False, *kmaps[i]]
             keys.append(key)
             s_stride = t_stride
 
         if deferred:
             todo = []       # (tensor that carries the grouped twin, number of rows)
             for i, key in enumerate(keys):
-                entry = self._kernel_maps_cache[key]
+                entry = self._maps[key]
                 sb = getattr(entry[3], "_sb", None)
                 if sb is None or sb.get("layout") != _C.LAYOUT_OS:
                     continue
                 if i > 0:
                     todo.append((entry[3], entry[2]))
-                if key in self._inverse_keys:
+                if key in self._inverse_keys and (key, "inverted") not in self._derived_maps:
                     inv = F.convert_transposed_os(entry[3], entry[1])
                     inv._sb = dict(sb, ws=None, counts=None, grouped=None)
-                    self._derived[(key, "inverted")] = inv
+                    self._derived_maps[(key, "inverted")] = inv
                     todo.append((inv, entry[1]))
             for (mp, _), g in zip(todo, _C.group_os_maps(todo)):
                 mp._sb["grouped"] = g
-        return self
 
 
 class SparseConv(Module):

@@ -255,6 +255,7 @@ def _dataflow_layout(dataflow: int) -> int:
 
 
 LAZY_SIZES = True   # cuda_binary_search_streamed(..., exact_sizes=False) keeps the list sizes on the device
+DEFER_MAPS = True   # KernelMapCache.add_all_kernel_maps returns after the level-0 map; the rest is completed on first use
 GROUP_OS = True     # output-stationary maps also get their rows grouped by neighbour pattern (spira_b200_kmap_group)
 GROUP_MIN_TARGETS = 1024
 
