@@ -301,7 +301,7 @@ def profile_kernels(engine, scene):
         sb = getattr(entry[3], "_sb", None) if entry is not None else None
         meta["nnz"] = int(sb["counts"].sum().item()) if sb is not None else None
     out = {}
-    conv_calls = [(n, args, a.elapsed_time(b)) for n, args, a, b in records if n in ("spira_b200_conv_os", "spira_b200_conv_os_grouped", "spira_b200_conv_ws")]
+    conv_calls = [(n, args, a.elapsed_time(b)) for n, args, a, b in records if n in ("spira_b200_conv_os", "spira_b200_conv_os_grouped", "spira_b200_conv_ws", "spira_b200_conv_ws_fused")]
     for n, args, a, b in records:
         d = out.setdefault(n, dict(calls=0, ms=0.0))
         d["calls"] += 1

@@ -258,6 +258,17 @@ int spira_b200_conv_ws(const void *feats, const void *weights, const void *packe
                        int swap, int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out, float *accum,
                        void *out, int32_t *status, void *stream);
 
+/* spira_b200_conv_ws with the zero-fill and the final conversion inside the convolution kernel (one launch instead of
+ * three; tensor-core eligible layers only, `packed` required).  No reference counterpart.  The kernel is launched
+ * cooperatively: after their last tile the CTAs meet at a grid barrier (bounded wait, reported through `status`), then
+ * every CTA converts its slice of the scratch to fp16 with the epilogue applied and writes zeros back.  Contract:
+ *   zeroed_accum[0 .. num_targets * c_out) holds zeros on entry and holds zeros again when the call has completed;
+ *   calls on one device must be ordered on one stream (they share the arrival counter of the grid barrier). */
+int spira_b200_conv_ws_fused(const void *feats, const void *packed, const spira_b200_epilogue *epilogue,
+                             const int32_t *in_idx, const int32_t *out_idx, const int32_t *naddrs, const int32_t *qnaddrs,
+                             int rows, int64_t num_tiles128, int mirror, int swap, int64_t num_sources, int64_t num_targets,
+                             int K, int c_in, int c_out, float *zeroed_accum, void *out, int32_t *status, void *stream);
+
 /* Capacity, in floats, of the scratch array built into the library for spira_b200_conv_ws_static (16 MiB per GPU). */
 #define SPIRA_B200_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)
 

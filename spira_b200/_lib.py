@@ -83,6 +83,8 @@ SIGNATURES = {
     "spira_b200_conv_ws": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                            c_void_p, c_void_p],
+    "spira_b200_conv_ws_fused": [c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
+                                 c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "spira_b200_conv_ws_static": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_void_p],
@@ -125,7 +127,7 @@ KERNELS_PER_CALL = {
     "spira_b200_downsample": 1, "spira_b200_downsample_sorted": 4, "spira_b200_kmap_search": 1, "spira_b200_kmap_ws_sizes": 2, "spira_b200_kmap_ws_pairs": 1, "spira_b200_kmap_ws_lists": 3,
     "spira_b200_kmap_masks": 1, "spira_b200_convert_transposed_os": 1, "spira_b200_transpose_map": 1,
     "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_os_grouped": 1, "spira_b200_kmap_group": 3,
-    "spira_b200_conv_ws": 2, "spira_b200_conv_ws_static": 2,
+    "spira_b200_conv_ws": 2, "spira_b200_conv_ws_fused": 1, "spira_b200_conv_ws_static": 2,
 }
 launch_count = 0          # kernels launched through `call` since import (or since it was last reset by the caller)
 profile_hook = None       # optional callable(name, args, run) -> None used by the benchmark to time single calls

@@ -77,6 +77,8 @@ struct ConvParams {
   // WS
   const int32_t *in_idx, *out_idx, *naddrs, *qnaddrs;
   int rows, mirror, n_tiles_plain, centre_tiles;
+  int fused;                 // WS: the CTAs meet at a grid barrier and convert the scratch themselves (cooperative launch)
+  unsigned barrier_target;   // value of the device-wide arrival counter once every CTA of this launch has arrived
   // common
   int T, n_tiles, K, c_in, c_out, R, n_chunks;  // n_chunks: OS = ceil(R/64); WS = ceil(c_in/64) per offset
   int stages, teams, slab_bufs, b_bytes, acc_stride, tmem_cols;
@@ -88,6 +90,10 @@ __device__ __forceinline__ float epilogue_apply(float v, int c, const Epilogue &
   if (ep.scale) v = v * ep.scale[c] + ep.shift[c];
   return v;
 }
+
+// Arrival counter of the grid barrier of fused weight-stationary launches.  It only ever grows: launch number n of a
+// device (in stream order) waits for the value the host computed as the sum of the grid sizes up to and including n.
+__device__ unsigned g_grid_arrivals = 0;
 
 // kTma: the producers are ONE warp whose lanes each issue a TMA gather4 (4 feature rows x 128 bytes, zero fill for
 // row index -1) per pipeline stage; otherwise 128 threads gather with 16-byte cp.async.
@@ -561,6 +567,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       tc_fence_before();
       mbar_arrive(bar_acc_empty(b));
     }
+    if constexpr (kWS) {
+      if (P.fused) __threadfence();      // this thread's reductions are performed before the CTA arrives at the grid barrier
+    }
   }
 
   // =========================== teardown ===========================
@@ -572,6 +581,58 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     const unsigned long long t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) { }
     __syncthreads();
+  }
+  if constexpr (kWS) {
+    if (P.fused) {
+      // ---- grid barrier (all CTAs are resident: cooperative launch), then every CTA converts its slice of the scratch:
+      // fp32 sums -> epilogue -> fp16 output, and the slice is zeroed again for the next layer that uses the scratch.
+      // Every CTA arrives exactly once, also after a failed wait, so the counter stays in step with the host.
+      __shared__ int s_go;
+      if (tid == 0) {
+        __threadfence();
+        atomicAdd(&g_grid_arrivals, 1u);
+        bool arrived = false;
+        if (*abort_flag == 0) {
+          const unsigned long long t0 = global_timer_ns();
+          while (true) {
+            const unsigned seen = *reinterpret_cast<volatile unsigned *>(&g_grid_arrivals);
+            if (static_cast<int>(seen - P.barrier_target) >= 0) { arrived = true; break; }
+            if (global_timer_ns() - t0 > kWaitLimitNs) break;
+          }
+          if (!arrived && P.status) atomicExch(P.status, 1);
+        }
+        __threadfence();
+        s_go = arrived ? 1 : 0;
+      }
+      __syncthreads();
+      if (s_go) {
+        const int64_t n4 = static_cast<int64_t>(P.T) * P.c_out / 4;      // c_out % 16 == 0: a float4 stays in one row
+        const int64_t per = (n4 + gridDim.x - 1) / gridDim.x;
+        const int64_t lo = per * blockIdx.x, hi = min(n4, lo + per);
+        float4 *acc4 = reinterpret_cast<float4 *>(P.accum);
+        for (int64_t i = lo + tid; i < hi; i += kConvThreads) {
+          const float4 a = __ldcg(acc4 + i);
+          const int c = static_cast<int>((i * 4) % P.c_out);
+          float v[4] = {epilogue_apply(a.x, c, P.ep), epilogue_apply(a.y, c + 1, P.ep), epilogue_apply(a.z, c + 2, P.ep),
+                        epilogue_apply(a.w, c + 3, P.ep)};
+          if (P.ep.residual) {
+            const uint2 rv = *reinterpret_cast<const uint2 *>(P.ep.residual + i * 4);
+            const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+            v[0] += __low2float(rh[0]); v[1] += __high2float(rh[0]); v[2] += __low2float(rh[1]); v[3] += __high2float(rh[1]);
+          }
+          if (P.ep.relu) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = fmaxf(v[e], 0.f);
+          }
+          const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+          uint2 o;
+          o.x = *reinterpret_cast<const uint32_t *>(&h0);
+          o.y = *reinterpret_cast<const uint32_t *>(&h1);
+          *reinterpret_cast<uint2 *>(P.out + i * 4) = o;
+          __stcg(acc4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+      }
+    }
   }
   if (warp == kMmaWarp) {
     tc_fence_after();
@@ -1109,11 +1170,31 @@ static int make_feats_tensor_map(CUtensorMap *map, const void *feats, int64_t nu
   return SPIRA_B200_OK;
 }
 
+static unsigned g_arrivals_host[64] = {0};   // per device: sum of the grid sizes of all fused launches so far
+
 template <bool kWS>
 static int launch_conv_tc(ConvParams &P, bool tma, size_t smem, int64_t num_sources, cudaStream_t st) {
   alignas(64) CUtensorMap tmap;
   std::memset(&tmap, 0, sizeof(tmap));
   int grid = (P.n_tiles >= 0 && P.n_tiles < sm_count()) ? P.n_tiles : sm_count();
+  if (kWS && P.fused) {
+    // the CTAs wait for one another: cooperative launch (all of them resident), at least one CTA to convert the scratch
+    if (grid <= 0) grid = 1;
+    int dev = 0;
+    SB_CHECK_CUDA(cudaGetDevice(&dev));
+    SB_CHECK_ARG(dev >= 0 && dev < 64, "conv_ws_fused: device %d out of range", dev);
+    SB_CHECK_CUDA(cudaFuncSetAttribute(conv_tc_kernel<kWS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    g_arrivals_host[dev] += static_cast<unsigned>(grid);
+    P.barrier_target = g_arrivals_host[dev];
+    void *args[] = {&P, &tmap};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(&conv_tc_kernel<kWS, false>), dim3(grid),
+                                                dim3(kConvThreads), args, smem, st);
+    if (e != cudaSuccess) {
+      g_arrivals_host[dev] -= static_cast<unsigned>(grid);      // nothing was launched: nobody will arrive
+      return fail(SPIRA_B200_ERR_CUDA, "conv_ws_fused: cooperative launch failed: %s", cudaGetErrorString(e));
+    }
+    return SPIRA_B200_OK;
+  }
   if (grid <= 0) return SPIRA_B200_OK;
   if (tma) {
     int rc = make_feats_tensor_map(&tmap, P.feats, num_sources, P.c_in);
@@ -1328,11 +1409,10 @@ extern "C" int spira_b200_conv_os_grouped(const void *feats, const void *packed,
                       c_out, out, status, stream);
 }
 
-extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const void *packed,
-                                  const spira_b200_epilogue *epilogue, const int32_t *in_idx, const int32_t *out_idx,
-                                  const int32_t *naddrs, const int32_t *qnaddrs, int rows, int64_t num_tiles128,
-                                  int mirror, int swap, int64_t num_sources, int64_t num_targets, int K, int c_in,
-                                  int c_out, float *accum, void *out, int32_t *status, void *stream) {
+static int conv_ws_impl(const void *feats, const void *weights, const void *packed, const spira_b200_epilogue *epilogue,
+                        const int32_t *in_idx, const int32_t *out_idx, const int32_t *naddrs, const int32_t *qnaddrs, int rows,
+                        int64_t num_tiles128, int mirror, int swap, int64_t num_sources, int64_t num_targets, int K, int c_in,
+                        int c_out, float *accum, void *out, int32_t *status, void *stream, bool fused) {
   SB_CHECK_ARG(num_sources >= 0 && num_targets >= 0 && num_targets < (int64_t(1) << 31) && num_sources < (int64_t(1) << 31),
                "conv_ws: sizes out of range");
   SB_CHECK_ARG(K >= 1 && c_in >= 1 && c_out >= 1 && rows >= 1 && rows <= K, "conv_ws: K=%d c_in=%d c_out=%d rows=%d", K, c_in,
@@ -1345,11 +1425,17 @@ extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const 
   SB_CHECK_ARG((ep.scale == nullptr) == (ep.shift == nullptr), "conv_ws: scale and shift must be given together");
   cudaStream_t st = as_stream(stream);
   const int64_t n_out = num_targets * c_out;
-  SB_CHECK_CUDA(cudaMemsetAsync(accum, 0, sizeof(float) * n_out, st));
+  if (!fused) SB_CHECK_CUDA(cudaMemsetAsync(accum, 0, sizeof(float) * n_out, st));
   const int32_t *gi = swap ? out_idx : in_idx;
   const int32_t *go = swap ? in_idx : out_idx;
-  if (num_tiles128 != 0) {
-    SB_CHECK_ARG(gi && go && feats, "conv_ws: null pointer");
+  if (fused) {
+    SB_CHECK_ARG(packed != nullptr && tc_eligible(K, c_in, c_out) && !g_gather_tma,
+                 "conv_ws_fused: needs a tensor-core eligible layer with its packed weights and the cp.async producers");
+    SB_CHECK_ARG(reinterpret_cast<uintptr_t>(out) % 16 == 0 && (!epilogue || reinterpret_cast<uintptr_t>(epilogue->residual) % 8 == 0),
+                 "conv_ws_fused: out must be 16-byte and residual 8-byte aligned");
+  }
+  if (num_tiles128 != 0 || fused) {
+    SB_CHECK_ARG((num_tiles128 == 0 || (gi && go)) && (feats || num_sources == 0), "conv_ws: null pointer");
     if (packed == nullptr) {
       SB_CHECK_ARG(weights != nullptr, "conv_ws: neither weights nor a packed image given");
       dim3 grid(static_cast<unsigned>(sm_count() * 2), static_cast<unsigned>(mirror ? 2 * rows - 1 : rows));
@@ -1366,6 +1452,9 @@ extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const 
       P.feats = static_cast<const __half *>(feats);
       P.packed = static_cast<const unsigned char *>(packed);
       P.accum = accum;
+      P.out = static_cast<__half *>(out);
+      P.ep = ep;
+      P.fused = fused ? 1 : 0;
       P.status = status;
       P.in_idx = gi; P.out_idx = go; P.naddrs = naddrs; P.qnaddrs = qnaddrs;
       P.rows = rows; P.mirror = mirror;
@@ -1374,6 +1463,9 @@ extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const 
       if (num_tiles128 < 0) {
         P.n_tiles_plain = -1;      // the kernel reads qnaddrs[rows] itself
         P.n_tiles = -1;
+      } else if (num_tiles128 == 0) {
+        P.n_tiles_plain = 0;       // no pair at all (fused call: the scratch is still converted)
+        P.n_tiles = 0;
       } else {
         P.n_tiles_plain = static_cast<int>(num_tiles128);
         P.n_tiles = static_cast<int>(mirror ? 2 * num_tiles128 - P.centre_tiles : num_tiles128);
@@ -1388,9 +1480,28 @@ extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const 
       if (rc != SPIRA_B200_OK) return rc;
     }
   }
+  if (fused) return SPIRA_B200_OK;
   finalize_kernel<<<static_cast<unsigned>(div_up(n_out, 256)), 256, 0, st>>>(accum, ep, n_out, c_out, static_cast<__half *>(out));
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_conv_ws(const void *feats, const void *weights, const void *packed,
+                                  const spira_b200_epilogue *epilogue, const int32_t *in_idx, const int32_t *out_idx,
+                                  const int32_t *naddrs, const int32_t *qnaddrs, int rows, int64_t num_tiles128,
+                                  int mirror, int swap, int64_t num_sources, int64_t num_targets, int K, int c_in,
+                                  int c_out, float *accum, void *out, int32_t *status, void *stream) {
+  return conv_ws_impl(feats, weights, packed, epilogue, in_idx, out_idx, naddrs, qnaddrs, rows, num_tiles128, mirror, swap,
+                      num_sources, num_targets, K, c_in, c_out, accum, out, status, stream, false);
+}
+
+extern "C" int spira_b200_conv_ws_fused(const void *feats, const void *packed, const spira_b200_epilogue *epilogue,
+                                        const int32_t *in_idx, const int32_t *out_idx, const int32_t *naddrs,
+                                        const int32_t *qnaddrs, int rows, int64_t num_tiles128, int mirror, int swap,
+                                        int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out,
+                                        float *zeroed_accum, void *out, int32_t *status, void *stream) {
+  return conv_ws_impl(feats, nullptr, packed, epilogue, in_idx, out_idx, naddrs, qnaddrs, rows, num_tiles128, mirror, swap,
+                      num_sources, num_targets, K, c_in, c_out, zeroed_accum, out, status, stream, true);
 }
 
 extern "C" int spira_b200_set_option(const char *name, int value) {

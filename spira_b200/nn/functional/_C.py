@@ -255,6 +255,7 @@ def _dataflow_layout(dataflow: int) -> int:
 
 
 LAZY_SIZES = True   # cuda_binary_search_streamed(..., exact_sizes=False) keeps the list sizes on the device
+WS_FUSED = True     # weight-stationary layers run as ONE cooperative launch over a persistent, always-zero scratch
 DEFER_MAPS = True   # KernelMapCache.add_all_kernel_maps returns after the level-0 map; the rest is completed on first use
 GROUP_OS = True     # output-stationary maps also get their rows grouped by neighbour pattern (spira_b200_kmap_group)
 GROUP_MIN_TARGETS = 1024
@@ -591,21 +592,34 @@ def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None
 
 
 def conv_ws(num_sources, num_targets, sources, weights, lists: WsLists, *, swap=False, bias=None, scale=None, shift=None,
-            residual=None, relu=False, force_simt=False) -> torch.Tensor:
-    """Weight-stationary forward over compacted pair lists with the optional fused epilogue."""
+            residual=None, relu=False, force_simt=False, fused=None) -> torch.Tensor:
+    """Weight-stationary forward over compacted pair lists with the optional fused epilogue.  ``fused`` (default:
+    ``WS_FUSED`` where it applies) selects the single cooperative launch over the persistent zero scratch; the sums are
+    the same (the order of the fp32 reductions varies from run to run on either path)."""
     _check_feats(sources, weights)
     sources, weights = sources.contiguous(), weights.contiguous()
     K, cin, cout = weights.shape
     out = torch.empty((num_targets, cout), dtype=torch.float16, device=sources.device)
-    accum = torch.empty((num_targets, cout), dtype=torch.float32, device=sources.device)
     packed = None if force_simt else packed_weights(weights, PACK_WS)
     mirror = bool(lists.mirror)
     if mirror and swap:
         raise RuntimeError("[spira_b200] a mirrored (submanifold) list cannot be used transposed")
     ep, keep = _epilogue(bias, scale, shift, residual, relu)
+    n_tiles = -1 if lists.qmapsize is None else lists.qmapsize // 128
+    can_fuse = packed is not None and num_targets > 0 and get_option("gather_tma") == 0
+    if fused is None:
+        fused = WS_FUSED
+    if fused and can_fuse:
+        accum = zero_scratch(sources.device, num_targets * cout)
+        _lib.call("spira_b200_conv_ws_fused", _ptr(sources), _ptr(packed), C.byref(ep) if ep is not None else None,
+                  _ptr(lists.in_idx), _ptr(lists.out_idx), _ptr(lists.naddrs), _ptr(lists.qnaddrs), lists.rows, n_tiles,
+                  1 if mirror else 0, 1 if swap else 0, int(num_sources), int(num_targets), K, cin, cout, _ptr(accum), _ptr(out),
+                  _ptr(status_word(sources.device)), _stream(sources.device))
+        return out
+    accum = torch.empty((num_targets, cout), dtype=torch.float32, device=sources.device)
     _lib.call("spira_b200_conv_ws", _ptr(sources), _ptr(weights), _ptr(packed), C.byref(ep) if ep is not None else None,
-              _ptr(lists.in_idx), _ptr(lists.out_idx), _ptr(lists.naddrs), _ptr(lists.qnaddrs), lists.rows,
-              -1 if lists.qmapsize is None else lists.qmapsize // 128, 1 if mirror else 0, 1 if swap else 0, int(num_sources), int(num_targets), K, cin, cout,
+              _ptr(lists.in_idx), _ptr(lists.out_idx), _ptr(lists.naddrs), _ptr(lists.qnaddrs), lists.rows, n_tiles,
+              1 if mirror else 0, 1 if swap else 0, int(num_sources), int(num_targets), K, cin, cout,
               _ptr(accum), _ptr(out), _ptr(status_word(sources.device)), _stream(sources.device))
     return out
 
@@ -623,7 +637,7 @@ class ConvCall:
     struct, the resolved C functions.  ``SparseConv`` keeps one and the two ``run_*`` functions below add only the
     per-call pointers, so that a forward costs a few microseconds of Python per layer."""
     __slots__ = ("stamp", "weights", "K", "cin", "cout", "w_ptr", "packed", "ep", "ep_ref", "keep", "dev_index", "status",
-                 "status_ptr", "fn_os", "fn_ws", "fn_os_grouped", "eligible")
+                 "status_ptr", "fn_os", "fn_ws", "fn_os_grouped", "fn_ws_fused", "eligible")
 
     def __init__(self, weights: torch.Tensor, bias, fused):
         lib = _lib.load()
@@ -646,6 +660,7 @@ class ConvCall:
         self.status = status_word(weights.device)
         self.status_ptr = self.status.data_ptr()
         self.fn_os, self.fn_ws, self.fn_os_grouped = lib.spira_b200_conv_os, lib.spira_b200_conv_ws, lib.spira_b200_conv_os_grouped
+        self.fn_ws_fused = lib.spira_b200_conv_ws_fused
         self.stamp = (weights.data_ptr(), weights._version, None if bias is None else (bias.data_ptr(), bias._version),
                       None if fused is None else (id(fused["scale"]), id(fused["shift"]), fused["relu"]))
 
@@ -700,6 +715,19 @@ def run_conv_os(call: ConvCall, num_sources: int, num_targets: int, out_in_map: 
     return out
 
 
+_zero_scratch = {}      # device index -> fp32 tensor that holds zeros whenever no weight-stationary call is in flight
+
+
+def zero_scratch(device, floats: int) -> torch.Tensor:
+    """Persistent scratch of the fused weight-stationary call: zero on entry, zero again on completion.  It grows
+    (a new zero-filled tensor) when a layer needs more; calls on one device are stream-ordered."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _zero_scratch.get(idx)
+    if t is None or t.numel() < floats:
+        t = _zero_scratch[idx] = torch.zeros(max(floats + floats // 2, 1 << 20), dtype=torch.float32, device=device)
+    return t
+
+
 def run_conv_ws(call: ConvCall, num_sources: int, num_targets: int, lists: WsLists, feats: torch.Tensor, swap: bool,
                 residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Weight-stationary forward of a prepared layer over the engine's pair lists."""
@@ -708,20 +736,29 @@ def run_conv_ws(call: ConvCall, num_sources: int, num_targets: int, lists: WsLis
     if lists.mirror and swap:
         raise RuntimeError("[spira_b200] a mirrored (submanifold) list cannot be used transposed")
     out = torch.empty((num_targets, call.cout), dtype=torch.float16, device=feats.device)
-    accum = torch.empty((num_targets, call.cout), dtype=torch.float32, device=feats.device)
     call.ep.residual = residual.data_ptr() if residual is not None else None
-    args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(PACK_WS), call.ep_ref, lists.in_idx.data_ptr(),
-            lists.out_idx.data_ptr(), lists.naddrs.data_ptr(), lists.qnaddrs.data_ptr(), lists.rows,
-            -1 if lists.qmapsize is None else lists.qmapsize // 128, 1 if lists.mirror else 0, 1 if swap else 0,
-            num_sources, num_targets, call.K, call.cin, call.cout, accum.data_ptr(), out.data_ptr(), call.status_ptr,
-            _raw_stream(call.dev_index))
-    if _lib.profile_hook is not None:
-        _lib.profile_hook("spira_b200_conv_ws", args, lambda: _lib.check(call.fn_ws(*args)))
+    n_tiles = -1 if lists.qmapsize is None else lists.qmapsize // 128
+    if WS_FUSED and call.eligible and num_targets > 0 and _lib.load().spira_b200_get_option(b"gather_tma") == 0:
+        accum = zero_scratch(feats.device, num_targets * call.cout)
+        name, fn, launches = "spira_b200_conv_ws_fused", call.fn_ws_fused, 1
+        args = (feats.data_ptr(), call.packed_ptr(PACK_WS), call.ep_ref, lists.in_idx.data_ptr(), lists.out_idx.data_ptr(),
+                lists.naddrs.data_ptr(), lists.qnaddrs.data_ptr(), lists.rows, n_tiles, 1 if lists.mirror else 0,
+                1 if swap else 0, num_sources, num_targets, call.K, call.cin, call.cout, accum.data_ptr(), out.data_ptr(),
+                call.status_ptr, _raw_stream(call.dev_index))
     else:
-        rc = call.fn_ws(*args)
+        accum = torch.empty((num_targets, call.cout), dtype=torch.float32, device=feats.device)
+        name, fn, launches = "spira_b200_conv_ws", call.fn_ws, 2
+        args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(PACK_WS), call.ep_ref, lists.in_idx.data_ptr(),
+                lists.out_idx.data_ptr(), lists.naddrs.data_ptr(), lists.qnaddrs.data_ptr(), lists.rows, n_tiles,
+                1 if lists.mirror else 0, 1 if swap else 0, num_sources, num_targets, call.K, call.cin, call.cout,
+                accum.data_ptr(), out.data_ptr(), call.status_ptr, _raw_stream(call.dev_index))
+    if _lib.profile_hook is not None:
+        _lib.profile_hook(name, args, lambda: _lib.check(fn(*args)))
+    else:
+        rc = fn(*args)
         if rc != 0:
             _lib.check(rc)
-    _lib.launch_count += 2
+    _lib.launch_count += launches
     return out
 
 

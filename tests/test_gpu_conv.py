@@ -260,3 +260,42 @@ def test_grouping_rejects_wide_kernels(C, lib):
     d[0].num_targets, d[0].K = 1000, 125
     rc = lib.spira_b200_kmap_group(d, 1, buf.data_ptr(), n.value, None)
     assert rc != 0 and b"32" in lib.spira_b200_last_error()
+
+
+# ---- weight-stationary convolution as one cooperative launch over the persistent zero scratch --------------------------
+@pytest.mark.parametrize("cin,cout", [(32, 32), (64, 64), (96, 96), (128, 128), (256, 256), (64, 48)])
+def test_fused_weight_stationary_call_agrees_and_leaves_zeros(C, scene, cin, cout):
+    """Same sums as the three-launch call; the order of the fp32 reductions differs from run to run in both, so the
+    comparison allows the last bits of fp16."""
+    keys, down = scene
+    rng = np.random.default_rng(cin * 3 + cout)
+    for src, tgt, swap in ((keys, keys, False), (keys, down, False), (keys, down, True)):
+        m = C.cuda_binary_search(keys_to_torch(src), keys_to_torch(tgt), (3, 3, 3), (1, 1, 1), 1)
+        lists = m[2]._sb["ws"]
+        S, T = (len(tgt), len(src)) if swap else (len(src), len(tgt))       # a transposed layer exchanges the roles
+        f, w = tensors(S, cin, cout, 27, cin * 11 + cout)
+        res = torch.from_numpy(rng.normal(size=(T, cout)).astype(np.float16)).cuda()
+        scale = torch.from_numpy(rng.uniform(0.5, 1.5, cout).astype(np.float32)).cuda()
+        shift = torch.from_numpy(rng.normal(size=cout).astype(np.float32)).cuda()
+        for kw in ({}, dict(scale=scale, shift=shift, residual=res, relu=True)):
+            for _ in range(2):                   # twice: the second call finds the scratch as the first one left it
+                a = C.conv_ws(S, T, f.cuda(), w.cuda(), lists, swap=swap, fused=True, **kw)
+            b = C.conv_ws(S, T, f.cuda(), w.cuda(), lists, swap=swap, fused=False, **kw)
+            assert torch.allclose(a.float(), b.float(), rtol=4e-3, atol=4e-3)
+        scratch = C.zero_scratch(torch.device("cuda", torch.cuda.current_device()), 1)
+        assert int(torch.count_nonzero(scratch)) == 0
+    C.check_status()
+
+
+def test_fused_weight_stationary_call_without_pairs(C):
+    """A map with no pair at all still converts the (zero) scratch: the output is the epilogue of zero."""
+    a = np.array([[40, 40, 40], [80, 80, 80]], dtype=np.int32)
+    ka, _ = O.flat_sort(a)
+    b = np.array([[200, 200, 100]], dtype=np.int32)
+    kb, _ = O.flat_sort(b)
+    m = C.cuda_binary_search(keys_to_torch(ka), keys_to_torch(kb), (3, 3, 3), (1, 1, 1), 1)
+    f, w = tensors(2, 32, 32, 27, 1)
+    bias = torch.full((32,), 0.5, dtype=torch.float16).cuda()
+    got = C.conv_ws(2, 1, f.cuda(), w.cuda(), m[2]._sb["ws"], bias=bias, fused=True)
+    assert torch.equal(got, torch.full((1, 32), 0.5, dtype=torch.float16).cuda())
+    C.check_status()
