@@ -299,7 +299,9 @@ def profile_kernels(engine, scene):
         key = (t, s, meta["ksize"]) if meta["transposed"] else (s, t, meta["ksize"])
         entry = engine.cache._kernel_maps_cache.get(key)
         sb = getattr(entry[3], "_sb", None) if entry is not None else None
-        meta["nnz"] = int(sb["counts"].sum().item()) if sb is not None else None
+        from spira_b200.nn.functional import _C as _native
+        counts = _native.map_counts(entry[3]) if (sb is not None and hasattr(_native, "map_counts")) else (sb or {}).get("counts")
+        meta["nnz"] = int(counts.sum().item()) if counts is not None else None
     out = {}
     conv_calls = [(n, args, a.elapsed_time(b)) for n, args, a, b in records if n in ("spira_b200_conv_os", "spira_b200_conv_os_grouped", "spira_b200_conv_ws", "spira_b200_conv_ws_fused")]
     for n, args, a, b in records:

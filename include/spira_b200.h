@@ -43,6 +43,14 @@ const char *spira_b200_last_error(void);
  * cuda_reset_error (csrc/spira/torch/cuda_memory_buffer.cu:15-16). */
 int spira_b200_reset_error(void);
 
+/* Reads `bytes` from device memory into PINNED host memory without waiting for work that is enqueued on `stream`
+ * after this call: `copy_stream` (a different stream) waits for the current end of `stream`, copies, and records
+ * `done_event` (a cudaEvent_t of the caller); cudaEventSynchronize(done_event) then tells when the bytes are there.
+ * Used for the one host read of a scene (the sizes of the down-sampled levels), so that the level-0 kernel map can be
+ * enqueued behind it at once.  No reference counterpart (the reference synchronises the device here). */
+int spira_b200_read_back(const void *device_src, void *pinned_dst, size_t bytes, void *stream, void *copy_stream,
+                         void *done_event);
+
 /* Run-time options of the calling process (not thread safe; set them before launching work):
  *   "gather_tma"        1: the tensor-core kernels fetch feature rows with TMA gather4, 0 (default): with 16-byte
  *                       cp.async
@@ -96,7 +104,7 @@ int spira_b200_downsample(const void *keys, int64_t n, int key_bytes, int n_leve
  * key is a sum of lengths of contiguous ranges of the sorted input, found by binary searches; level l+1 is computed
  * from the output of level l, whose size stays on the device.  The reference sorts every level from scratch
  * (csrc/spira/torch/cuda_arg_sort_coordinates.cu:107-200).  Other stride sequences: SPIRA_B200_ERR_UNSUPPORTED (use
- * spira_b200_downsample).  `status` (device int32, may be NULL) is set to 2 if the input turns out not to be sorted. */
+ * spira_b200_downsample).  `status` (device int32, may be NULL) is cleared by the call and set to 2 if the input turns out not to be sorted. */
 int spira_b200_downsample_sorted_workspace(int64_t n, int key_bytes, size_t *bytes);
 int spira_b200_downsample_sorted(const void *sorted_keys, int64_t n, int key_bytes, int n_levels,
                                  const int32_t *host_strides, void *const *host_out_keys, int32_t *counts,

@@ -51,6 +51,7 @@ MAX_MAPS, MAX_LEVELS = 16, 8
 SIGNATURES = {
     "spira_b200_version": [],
     "spira_b200_reset_error": [],
+    "spira_b200_read_back": [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p],
     "spira_b200_set_option": [C.c_char_p, c_int],
     "spira_b200_get_option": [C.c_char_p],
     "spira_b200_pack": [c_void_p, c_int64, c_int, c_void_p, c_void_p],

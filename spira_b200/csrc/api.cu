@@ -39,3 +39,22 @@ extern "C" int spira_b200_reset_error(void) {
   sb::error_buffer()[0] = 0;
   return SPIRA_B200_OK;
 }
+
+// Stream-ordered read-back that does not wait for work enqueued later on `stream`: an event marks the current end
+// of `stream`, `copy_stream` waits for it and copies, `done_event` (recorded on `copy_stream`) tells the host when
+// the bytes have arrived.  One library-owned event per device serves as the marker.
+extern "C" int spira_b200_read_back(const void *device_src, void *pinned_dst, size_t bytes, void *stream, void *copy_stream,
+                                    void *done_event) {
+  SB_CHECK_ARG(device_src && pinned_dst && copy_stream && done_event, "read_back: null pointer");
+  SB_CHECK_ARG(copy_stream != stream, "read_back: copy_stream must differ from stream");
+  static cudaEvent_t marker[64] = {nullptr};
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  SB_CHECK_ARG(dev >= 0 && dev < 64, "read_back: device %d out of range", dev);
+  if (marker[dev] == nullptr) SB_CHECK_CUDA(cudaEventCreateWithFlags(&marker[dev], cudaEventDisableTiming));
+  SB_CHECK_CUDA(cudaEventRecord(marker[dev], sb::as_stream(stream)));
+  SB_CHECK_CUDA(cudaStreamWaitEvent(sb::as_stream(copy_stream), marker[dev], 0));
+  SB_CHECK_CUDA(cudaMemcpyAsync(pinned_dst, device_src, bytes, cudaMemcpyDeviceToHost, sb::as_stream(copy_stream)));
+  SB_CHECK_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(done_event), sb::as_stream(copy_stream)));
+  return SPIRA_B200_OK;
+}

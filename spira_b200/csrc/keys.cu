@@ -254,6 +254,7 @@ int downsample_sorted_impl(const KeyT *keys, int64_t n, int n_levels, const int3
   int prev[3] = {1, 1, 1};
   const KeyT *in = keys;
   const int32_t *n_dev = nullptr;
+  if (status) SB_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
   for (int l = 0; l < n_levels; ++l) {
     const int32_t *s = strides + 3 * l;
     SB_CHECK_CUDA(cudaMemsetAsync(flags, 0, n, stream));

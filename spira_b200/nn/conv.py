@@ -131,7 +131,7 @@ class KernelMapCache(object):
                 inv = F.convert_transposed_os(entry[3], entry[1])
                 sb = getattr(entry[3], "_sb", None)
                 if sb is not None:
-                    inv._sb = dict(sb, ws=None, counts=None, grouped=_C.group_os_map(inv, entry[1]))
+                    inv._sb = dict(sb, ws=None, counts=None, _counts=None, grouped=_C.group_os_map(inv, entry[1]))
                     self._inverse_keys.add(key)
                 self._derived_maps[dkey] = inv
             new_entry = list(entry[1:])
@@ -163,11 +163,21 @@ class KernelMapCache(object):
         if levels is not None:
             first = _C.cuda_binary_search_pairs([(source_coordinates, source_coordinates)], k_sizes[:1], s_strides[:1],
                                                 dataflow[:1], exact_sizes=False)
-            self._maps[(s0, s_strides[1], k_sizes[0])] = [False, *first[0]]
+            self._maps[(s0, s_strides[1], k_sizes[0])] = self._entry(first[0])
         self._pending = (source_coordinates, k_sizes, s_strides, t_strides, s0, dataflow, levels, first)
         if levels is None or not getattr(_C, "DEFER_MAPS", True):
             self.finish()
         return self
+
+    @staticmethod
+    def _entry(kmap):
+        """Cache entry ``[flipped_flag, *tuple9]``.  The network-wide build keeps the weight-stationary lists on the device
+        (``map._sb["ws"]``, no list size is read back, slots 7 and 8 are None), so the reference-shaped list slots 3-6 of
+        such an entry stay None as well instead of being materialised as tensor views for every map of every scene; the
+        single-map path (``F.build_kmap``) fills all slots."""
+        if type(kmap).__name__ == "_WsTuple":
+            return [False, kmap[0], kmap[1], kmap[2], None, None, None, None, None, None]
+        return [False, *kmap]
 
     def _complete(self, source_coordinates, k_sizes, s_strides, t_strides, s0, dataflow, levels, first):
         if levels is not None:
@@ -193,7 +203,7 @@ class KernelMapCache(object):
             t_stride = s_strides[i + 1]
             key = (s_stride, t_stride, k_sizes[i])
             if not (deferred and i == 0):
-                self._maps[key] = [False, *kmaps[i]]
+                self._maps[key] = self._entry(kmaps[i])
             keys.append(key)
             s_stride = t_stride
 
@@ -208,7 +218,7 @@ class KernelMapCache(object):
                     todo.append((entry[3], entry[2]))
                 if key in self._inverse_keys and (key, "inverted") not in self._derived_maps:
                     inv = F.convert_transposed_os(entry[3], entry[1])
-                    inv._sb = dict(sb, ws=None, counts=None, grouped=None)
+                    inv._sb = dict(sb, ws=None, counts=None, _counts=None, grouped=None)
                     self._derived_maps[(key, "inverted")] = inv
                     todo.append((inv, entry[1]))
             for (mp, _), g in zip(todo, _C.group_os_maps(todo)):

@@ -178,7 +178,9 @@ class PendingLevels:
     __slots__ = ("coordinates", "strides", "bufs", "counts", "host", "done", "levels")
 
 
-_side_channel = {}      # device index -> (side stream, pinned int32 buffer for the level sizes)
+_side_channel = {}      # device index -> (side stream, pinned int32 buffer, its address, "sizes arrived" event, event handle)
+_ds_ws_bytes = {}       # (n, key bytes) -> workspace bytes of the sort-free down-sampling
+_ds_strides = {}        # strides tuple -> ctypes int32 array
 
 
 def streamed_output_generate_begin(coordinates: torch.Tensor, target_strides) -> Optional[PendingLevels]:
@@ -186,38 +188,48 @@ def streamed_output_generate_begin(coordinates: torch.Tensor, target_strides) ->
     starts the copy of the level sizes on a side stream, so that the caller can enqueue work that does not depend on
     the sizes (the level-0 kernel map) before it waits in :func:`streamed_output_generate_end`.  Returns None when this
     path does not apply (then call the blocking function)."""
-    strides = [tuple(int(v) for v in s) for s in target_strides]
+    strides = tuple(tuple(int(v) for v in s) for s in target_strides)
     L = len(strides)
     if not (SORT_FREE_DOWNSAMPLE and coordinates.is_cuda and coordinates.dim() == 1 and 1 <= L <= MAX_LEVELS
-            and _strides_double(strides) and coordinates.shape[0] > 0):
+            and coordinates.shape[0] > 0):
         return None
+    host_strides = _ds_strides.get(strides)
+    if host_strides is None:
+        if not _strides_double(strides):
+            return None
+        if len(_ds_strides) > 256:
+            _ds_strides.clear()
+        host_strides = _ds_strides[strides] = (C.c_int32 * (3 * L))(*[v for s in strides for v in s])
     coordinates = coordinates.contiguous()
     n, kb, dev = coordinates.shape[0], _key_bytes(coordinates), coordinates.device
     idx = dev.index if dev.index is not None else torch.cuda.current_device()
     chan = _side_channel.get(idx)
     if chan is None:
-        chan = _side_channel[idx] = (torch.cuda.Stream(device=dev), torch.empty(MAX_LEVELS + 1, dtype=torch.int32).pin_memory())
-    side, host = chan
+        side = torch.cuda.Stream(device=dev)
+        host = torch.zeros(MAX_LEVELS + 1, dtype=torch.int32).pin_memory()
+        done = torch.cuda.Event()
+        done.record(side)                       # creates the underlying event, whose handle the library records later
+        chan = _side_channel[idx] = (side, host, host.data_ptr(), done, done.cuda_event)
+    side, host, host_ptr, done, done_handle = chan
+    need = _ds_ws_bytes.get((n, kb))
+    if need is None:
+        size = C.c_size_t()
+        _lib.call("spira_b200_downsample_sorted_workspace", n, kb, C.byref(size))
+        if len(_ds_ws_bytes) > 4096:
+            _ds_ws_bytes.clear()
+        need = _ds_ws_bytes[(n, kb)] = size.value
     p = PendingLevels()
     p.coordinates, p.strides, p.levels = coordinates, strides, L
     p.bufs = torch.empty((L, n), dtype=coordinates.dtype, device=dev)
-    p.counts = torch.zeros(L + 1, dtype=torch.int32, device=dev)
-    need = C.c_size_t()
-    _lib.call("spira_b200_downsample_sorted_workspace", n, kb, C.byref(need))
-    ws = torch.empty(need.value, dtype=torch.uint8, device=dev)
-    host_strides = (C.c_int32 * (3 * L))(*[v for s in strides for v in s])
-    host_out = (C.c_void_p * L)(*[p.bufs[l].data_ptr() for l in range(L)])
-    _lib.call("spira_b200_downsample_sorted", _ptr(coordinates), n, kb, L, host_strides, host_out, _ptr(p.counts), _ptr(ws),
-              need.value, _ptr(p.counts[L:]), _stream(dev))
-    main = torch.cuda.current_stream(dev)
-    ready = torch.cuda.Event()
-    ready.record(main)
-    side.wait_event(ready)
-    with torch.cuda.stream(side):
-        host[:L + 1].copy_(p.counts, non_blocking=True)
-        p.done = torch.cuda.Event()
-        p.done.record(side)
-    p.host = host
+    p.counts = torch.empty(L + 1, dtype=torch.int32, device=dev)      # [L] = "the input was not sorted"
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    base, counts_ptr = p.bufs.data_ptr(), p.counts.data_ptr()
+    host_out = (C.c_void_p * L)(*[base + l * n * kb for l in range(L)])
+    main = _raw_stream(idx)
+    _lib.call("spira_b200_downsample_sorted", coordinates.data_ptr(), n, kb, L, host_strides, host_out, counts_ptr, ws.data_ptr(),
+              need, counts_ptr + 4 * L, main)
+    _lib.call("spira_b200_read_back", counts_ptr, host_ptr, 4 * (L + 1), main, side.cuda_stream, done_handle)
+    p.host, p.done = host, done
     return p
 
 
@@ -246,8 +258,29 @@ def cuda_downsample(coordinates: torch.Tensor, stride_x: int, stride_y: int, str
 # ------------------------------------------------------------------------------------------------
 class WsLists:
     """Compacted pair lists of a weight-stationary map (engine-native form of the reference's
-    ``nbmaps / nbsizes / naddrs / qnaddrs`` slots)."""
-    __slots__ = ("in_idx", "out_idx", "nbsizes", "naddrs", "qnaddrs", "rows", "mirror", "mapsize", "qmapsize", "nbmaps")
+    ``nbmaps / nbsizes / naddrs / qnaddrs`` slots).
+
+    The kernels only need four device addresses (``in_ptr, out_ptr, naddrs_ptr, qnaddrs_ptr``).  The tensor views
+    ``nbmaps [2, cap]``, ``in_idx``, ``out_idx``, ``nbsizes``, ``naddrs``, ``qnaddrs`` are either set directly or, for
+    lists carved out of one arena by the network-wide builder, made on first access (``_lazy``: name -> (offset, shape)
+    in int32 units of ``_arena``)."""
+
+    def __getattr__(self, name):
+        lazy = self.__dict__.get("_lazy")
+        if lazy is not None and name in lazy:
+            off, shape = lazy[name]
+            n = 1
+            for v in shape:
+                n *= v
+            t = self._arena[off:off + n].view(shape)
+            setattr(self, name, t)
+            return t
+        raise AttributeError(name)
+
+    def set_pointers(self):
+        self.in_ptr, self.out_ptr = self.in_idx.data_ptr(), self.out_idx.data_ptr()
+        self.naddrs_ptr, self.qnaddrs_ptr = self.naddrs.data_ptr(), self.qnaddrs.data_ptr()
+        return self
 
 
 def _dataflow_layout(dataflow: int) -> int:
@@ -264,8 +297,20 @@ GROUP_MIN_TARGETS = 1024
 class GroupedMap:
     """An output-stationary map with its rows sorted by presence mask: ``map [T_al, K]``, ``row_of [T_al]`` (the
     target of each grouped row), ``tile_masks [T_al / 128]`` and ``stats [2]`` (non-empty (tile, offset) pairs for
-    128- and 256-row tiles, on the device)."""
-    __slots__ = ("map", "row_of", "tile_masks", "stats", "map_ptr", "row_of_ptr", "tile_masks_ptr")
+    128- and 256-row tiles, on the device).  The kernels take the three addresses; the tensors are views of one
+    allocation shared by all maps of a call and are made on first access."""
+
+    def __getattr__(self, name):
+        lazy = self.__dict__.get("_lazy")
+        if lazy is not None and name in lazy:
+            off, shape = lazy[name]
+            n = 1
+            for v in shape:
+                n *= v
+            t = self._arena[off:off + n].view(shape)
+            setattr(self, name, t)
+            return t
+        raise AttributeError(name)
 
 
 _group_ws_bytes = {}
@@ -279,30 +324,43 @@ def group_os_maps(maps) -> list:
     for first in range(0, len(todo), MAX_MAPS):
         part = todo[first:first + MAX_MAPS]
         dev = maps[part[0]][0].device
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        total_rows, ints, offs = 0, 0, []
+        for i in part:
+            mp, T = maps[i]
+            Tal, K = mp.shape
+            o_map = ints
+            ints += Tal * K
+            o_row = ints
+            ints += Tal
+            o_mask = ints
+            ints += (Tal // 128 + 63) & ~63
+            o_stats = ints
+            ints += 64
+            offs.append((o_map, o_row, o_mask, o_stats))
+            total_rows += int(T)
+        need = _group_ws_bytes.get(total_rows)
+        if need is None:
+            size = C.c_size_t()
+            _lib.call("spira_b200_kmap_group_workspace", total_rows, C.byref(size))
+            if len(_group_ws_bytes) > 4096:
+                _group_ws_bytes.clear()
+            need = _group_ws_bytes[total_rows] = size.value
+        arena = torch.empty(ints, dtype=torch.int32, device=dev)
+        work = torch.empty(need, dtype=torch.uint8, device=dev)
+        base = arena.data_ptr()
         descs = (GroupDesc * len(part))()
-        total = 0
-        for d, i in zip(descs, part):
+        for d, i, (o_map, o_row, o_mask, o_stats) in zip(descs, part, offs):
             mp, T = maps[i]
             Tal, K = mp.shape
             g = GroupedMap()
-            g.map = torch.empty((Tal, K), dtype=torch.int32, device=dev)
-            g.row_of = torch.empty(Tal, dtype=torch.int32, device=dev)
-            g.tile_masks = torch.empty(Tal // 128, dtype=torch.int32, device=dev)
-            g.stats = torch.empty(2, dtype=torch.int32, device=dev)
-            g.map_ptr, g.row_of_ptr, g.tile_masks_ptr = g.map.data_ptr(), g.row_of.data_ptr(), g.tile_masks.data_ptr()
+            g._arena = arena
+            g._lazy = dict(map=(o_map, (Tal, K)), row_of=(o_row, (Tal,)), tile_masks=(o_mask, (Tal // 128,)), stats=(o_stats, (2,)))
+            g.map_ptr, g.row_of_ptr, g.tile_masks_ptr = base + 4 * o_map, base + 4 * o_row, base + 4 * o_mask
             d.map_os, d.num_targets, d.K = mp.data_ptr(), int(T), K
-            d.grouped_map, d.row_of, d.tile_masks, d.stats = g.map_ptr, g.row_of_ptr, g.tile_masks_ptr, g.stats.data_ptr()
+            d.grouped_map, d.row_of, d.tile_masks, d.stats = g.map_ptr, g.row_of_ptr, g.tile_masks_ptr, base + 4 * o_stats
             out[i] = g
-            total += int(T)
-        need = _group_ws_bytes.get(total)
-        if need is None:
-            n = C.c_size_t()
-            _lib.call("spira_b200_kmap_group_workspace", total, C.byref(n))
-            if len(_group_ws_bytes) > 4096:
-                _group_ws_bytes.clear()
-            need = _group_ws_bytes[total] = n.value
-        work = torch.empty(need, dtype=torch.uint8, device=dev)
-        _lib.call("spira_b200_kmap_group", descs, len(part), _ptr(work), need, _stream(dev))
+        _lib.call("spira_b200_kmap_group", descs, len(part), work.data_ptr(), need, _raw_stream(idx))
     return out
 
 
@@ -342,16 +400,16 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
         info.append(dict(src=src, tgt=tgt, S=S, T=T, K=K, Tal=Tal, ks=ks, st=st, df=df, layout=layout, dense=dense,
                          counts=counts))
     for first in range(0, n, MAX_MAPS):
-        group = info[first:first + MAX_MAPS]
-        descs = (KmapDesc * len(group))()
-        for d, m in zip(descs, group):
+        batch = info[first:first + MAX_MAPS]
+        descs = (KmapDesc * len(batch))()
+        for d, m in zip(descs, batch):
             d.sources, d.targets = m["src"].data_ptr(), m["tgt"].data_ptr()
             d.num_sources, d.num_targets = m["S"], m["T"]
             d.kernel_size[:] = m["ks"]
             d.source_stride[:] = m["st"]
             d.layout = m["layout"]
             d.map, d.tile_counts = m["dense"].data_ptr(), m["counts"].data_ptr()
-        _lib.call("spira_b200_kmap_search", descs, len(group), kb, stream)
+        _lib.call("spira_b200_kmap_search", descs, len(batch), kb, stream)
 
     # weight-stationary post-processing
     ws_maps = [m for m in info if m["layout"] == LAYOUT_WS]
@@ -364,9 +422,9 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
         # Nothing is read back: the lists get their worst-case capacity (rows * T pairs, allocated but never touched
         # beyond nnz), the kernels take the sizes from naddrs / qnaddrs on the device, and all maps share three launches.
         for first in range(0, len(ws_maps), MAX_MAPS):
-            group = ws_maps[first:first + MAX_MAPS]
-            descs = (WsDesc * len(group))()
-            for d, m in zip(descs, group):
+            batch = ws_maps[first:first + MAX_MAPS]
+            descs = (WsDesc * len(batch))()
+            for d, m in zip(descs, batch):
                 K, rows, nt = m["K"], m["rows"], m["Tal"] // 128
                 small = torch.empty(K + 2 * (rows + 1) + 2, dtype=torch.int32, device=dev)
                 m["nbsizes"], m["naddrs"] = small[:K], small[K:K + rows + 1]
@@ -383,8 +441,8 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
                 w.nbmaps, w.in_idx, w.out_idx = nbmaps, nbmaps[0], nbmaps[1]
                 w.nbsizes, w.naddrs, w.qnaddrs = m["nbsizes"][:rows], m["naddrs"], m["qnaddrs"]
                 w.rows, w.mirror, w.mapsize, w.qmapsize = rows, bool(m["half"]), None, None
-                m["ws"] = w
-            _lib.call("spira_b200_kmap_ws_lists", descs, len(group), stream)
+                m["ws"] = w.set_pointers()
+            _lib.call("spira_b200_kmap_ws_lists", descs, len(batch), stream)
     elif ws_maps:
         # sizes for every map, ONE host read of all list sizes (the reference reads them per map), then the pairs with
         # their exact shape [2, nnz]
@@ -425,7 +483,7 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
             w.rows, w.mirror = rows, bool(m["half"])
             w.mapsize = None if mapsize is None else int(mapsize)
             w.qmapsize = None if qmapsize is None else int(qmapsize)
-            m["ws"] = w
+            m["ws"] = w.set_pointers()
 
     if group:       # else the caller groups these maps together with others of its own
         os_maps = [m for m in info if m["layout"] == LAYOUT_OS]
@@ -454,6 +512,123 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
     return results
 
 
+def _build_maps_arena(voxel_pairs, kernel_sizes, source_strides, dataflows, group=True):
+    """The network-wide builder's hot path (dataflows 0 and 1, nothing read back): every buffer of every map of the
+    call lives in ONE int32 allocation; the kernels get addresses, tensor views are made only where a caller needs
+    one (the dense map of every tuple; the list slots of a weight-stationary tuple on first access)."""
+    n = len(voxel_pairs)
+    dev = voxel_pairs[0][0].device
+    kb = _key_bytes(voxel_pairs[0][0])
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    stream = _raw_stream(idx)
+    metas, total = [], 0
+
+    def take(ints):                       # offsets stay multiples of 64 ints (256 bytes)
+        nonlocal total
+        off = total
+        total += (ints + 63) & ~63
+        return off
+
+    for i in range(n):
+        src, tgt = voxel_pairs[i]
+        ks, st, df = kernel_sizes[i], source_strides[i], dataflows[i]
+        S, T = src.shape[0], tgt.shape[0]
+        K = ks[0] * ks[1] * ks[2]
+        Tal = (T + 127) & ~127
+        nt = Tal >> 7
+        m = [src, tgt, S, T, K, Tal, nt, ks, st, df, take(Tal * K), take(K * nt)]
+        if df == 1:
+            half = S == T and K % 2 == 1
+            rows = (K + 1) // 2 if half else K
+            # nbsizes [K], naddrs [rows + 1], qnaddrs [rows + 1], sizes [2]; tile_base [K][nt]; nbmaps [2][rows * T]
+            m += [half, rows, take(K + 2 * (rows + 1) + 2), take(K * nt), take(2 * rows * T)]
+        metas.append(m)
+    arena = torch.empty(total, dtype=torch.int32, device=dev)
+    base = arena.data_ptr()
+
+    for first in range(0, n, MAX_MAPS):
+        batch = metas[first:first + MAX_MAPS]
+        descs = (KmapDesc * len(batch))()
+        for d, m in zip(descs, batch):
+            d.sources, d.targets, d.num_sources, d.num_targets = m[0].data_ptr(), m[1].data_ptr(), m[2], m[3]
+            d.kernel_size[:] = m[7]
+            d.source_stride[:] = m[8]
+            d.layout = LAYOUT_OS if m[9] == 0 else LAYOUT_WS
+            d.map, d.tile_counts = base + 4 * m[10], base + 4 * m[11]
+        _lib.call("spira_b200_kmap_search", descs, len(batch), kb, stream)
+
+    ws = [m for m in metas if m[9] == 1]
+    for first in range(0, len(ws), MAX_MAPS):
+        batch = ws[first:first + MAX_MAPS]
+        descs = (WsDesc * len(batch))()
+        for d, m in zip(descs, batch):
+            K, T, rows, small = m[4], m[3], m[13], base + 4 * m[14]
+            d.map_ws, d.tile_counts, d.aligned_targets, d.K, d.rows = base + 4 * m[10], base + 4 * m[11], m[5], K, rows
+            d.nbsizes, d.naddrs, d.qnaddrs, d.sizes = small, small + 4 * K, small + 4 * (K + rows + 1), small + 4 * (K + 2 * rows + 2)
+            d.tile_base = base + 4 * m[15]
+            d.in_idx, d.out_idx = base + 4 * m[16], base + 4 * (m[16] + rows * T)
+        _lib.call("spira_b200_kmap_ws_lists", descs, len(batch), stream)
+
+    results, os_maps = [], []
+    for m in metas:
+        src, tgt, S, T, K, Tal, nt, ks, st, df, dense_off, counts_off = m[:12]
+        if df == 0:
+            dense = arena[dense_off:dense_off + Tal * K].view(Tal, K)
+            dense._sb = dict(ws=None, kernel_size=ks, layout=LAYOUT_OS, grouped=None, _arena=arena, _counts=(counts_off, (K, nt)))
+            os_maps.append((dense, T))
+            results.append((S, T, dense, None, None, None, None, None, None))
+        else:
+            half, rows, small, tb_off, nb_off = m[12:]
+            dense = arena[dense_off:dense_off + Tal * K].view(K, Tal)
+            w = WsLists()
+            w._arena = arena
+            w._lazy = dict(nbmaps=(nb_off, (2, rows * T)), in_idx=(nb_off, (rows * T,)), out_idx=(nb_off + rows * T, (rows * T,)),
+                           nbsizes=(small, (rows,)), naddrs=(small + K, (rows + 1,)), qnaddrs=(small + K + rows + 1, (rows + 1,)))
+            w.in_ptr, w.out_ptr = base + 4 * nb_off, base + 4 * (nb_off + rows * T)
+            w.naddrs_ptr, w.qnaddrs_ptr = base + 4 * (small + K), base + 4 * (small + K + rows + 1)
+            w.rows, w.mirror, w.mapsize, w.qmapsize = rows, bool(half), None, None
+            dense._sb = dict(ws=w, kernel_size=ks, layout=LAYOUT_WS, grouped=None, _arena=arena, _counts=(counts_off, (K, nt)))
+            results.append(_WsTuple((S, T, dense, w)))
+    if group and os_maps:
+        for (dense, _), g in zip(os_maps, group_os_maps(os_maps)):
+            dense._sb["grouped"] = g
+    return results
+
+
+class _WsTuple(tuple):
+    """The 9-slot result of a weight-stationary map whose list slots (3: nbmaps, 4: nbsizes, 5: naddrs, 6: qnaddrs) are
+    views made when somebody reads them; slots 7 and 8 (the list sizes on the host) are None: nothing was read back."""
+
+    def __new__(cls, head):
+        return super().__new__(cls, (head[0], head[1], head[2], None, None, None, None, None, None))
+
+    def __init__(self, head):
+        self._lists = head[3]
+
+    def __getitem__(self, i):
+        if isinstance(i, int) and 3 <= (i if i >= 0 else i + 9) <= 6:
+            w = self._lists
+            return (w.nbmaps, w.nbsizes, w.naddrs, w.qnaddrs)[(i if i >= 0 else i + 9) - 3]
+        if isinstance(i, slice):
+            return tuple(self[j] for j in range(*i.indices(9)))
+        return super().__getitem__(i)
+
+    def __iter__(self):
+        return (self[j] for j in range(9))
+
+
+def map_counts(map_tensor: torch.Tensor) -> Optional[torch.Tensor]:
+    """Hit counters ``[K, T_al / 128]`` of an engine-built map (``None`` for foreign maps)."""
+    sb = getattr(map_tensor, "_sb", None)
+    if sb is None:
+        return None
+    c = sb.get("counts")
+    if c is None and sb.get("_counts") is not None:
+        off, shape = sb["_counts"]
+        c = sb["counts"] = sb["_arena"][off:off + shape[0] * shape[1]].view(shape)
+    return c
+
+
 def cuda_binary_search(sources, targets, kernel_size, source_stride, dataflow: int = 0):
     """One kernel map.  Reference: ``BinarySearch`` (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:211-892)."""
     return _build_maps([(sources.contiguous(), targets.contiguous())], [kernel_size], [source_stride], [dataflow])[0]
@@ -474,8 +649,22 @@ def cuda_binary_search_pairs(voxel_pairs, kernel_sizes, source_strides, dataflow
     ``group=False`` leaves the output-stationary maps without their grouped twin (:func:`group_os_maps` adds it)."""
     if not (len(voxel_pairs) == len(kernel_sizes) == len(source_strides) == len(dataflow)):
         raise RuntimeError("[spira_b200] voxel_pairs, kernel_sizes, source_strides and dataflow must have the same length")
-    return _build_maps([(a.contiguous(), b.contiguous()) for a, b in voxel_pairs], kernel_sizes, source_strides, dataflow,
-                       exact_sizes, group)
+    pairs = [(a.contiguous(), b.contiguous()) for a, b in voxel_pairs]
+    if not exact_sizes and _arena_path_applies(pairs, kernel_sizes, source_strides, dataflow):
+        return _build_maps_arena(pairs, [tuple(int(v) for v in k) for k in kernel_sizes],
+                                 [tuple(int(v) for v in t) for t in source_strides], [int(d) for d in dataflow], group)
+    return _build_maps(pairs, kernel_sizes, source_strides, dataflow, exact_sizes, group)
+
+
+def _arena_path_applies(pairs, kernel_sizes, source_strides, dataflow) -> bool:
+    if not LAZY_SIZES or not pairs:
+        return False
+    dtype = pairs[0][0].dtype
+    for (a, b), d in zip(pairs, dataflow):
+        if d not in (0, 1) or not a.is_cuda or not b.is_cuda or a.dtype != dtype or b.dtype != dtype or a.dim() != 1 \
+                or b.dim() != 1 or a.shape[0] == 0 or b.shape[0] == 0:
+            return False
+    return True
 
 
 def cuda_binary_search_no_small_z(sources, targets, kernel_size, source_stride):
@@ -612,13 +801,13 @@ def conv_ws(num_sources, num_targets, sources, weights, lists: WsLists, *, swap=
     if fused and can_fuse:
         accum = zero_scratch(sources.device, num_targets * cout)
         _lib.call("spira_b200_conv_ws_fused", _ptr(sources), _ptr(packed), C.byref(ep) if ep is not None else None,
-                  _ptr(lists.in_idx), _ptr(lists.out_idx), _ptr(lists.naddrs), _ptr(lists.qnaddrs), lists.rows, n_tiles,
+                  lists.in_ptr, lists.out_ptr, lists.naddrs_ptr, lists.qnaddrs_ptr, lists.rows, n_tiles,
                   1 if mirror else 0, 1 if swap else 0, int(num_sources), int(num_targets), K, cin, cout, _ptr(accum), _ptr(out),
                   _ptr(status_word(sources.device)), _stream(sources.device))
         return out
     accum = torch.empty((num_targets, cout), dtype=torch.float32, device=sources.device)
     _lib.call("spira_b200_conv_ws", _ptr(sources), _ptr(weights), _ptr(packed), C.byref(ep) if ep is not None else None,
-              _ptr(lists.in_idx), _ptr(lists.out_idx), _ptr(lists.naddrs), _ptr(lists.qnaddrs), lists.rows, n_tiles,
+              lists.in_ptr, lists.out_ptr, lists.naddrs_ptr, lists.qnaddrs_ptr, lists.rows, n_tiles,
               1 if mirror else 0, 1 if swap else 0, int(num_sources), int(num_targets), K, cin, cout,
               _ptr(accum), _ptr(out), _ptr(status_word(sources.device)), _stream(sources.device))
     return out
@@ -741,15 +930,15 @@ def run_conv_ws(call: ConvCall, num_sources: int, num_targets: int, lists: WsLis
     if WS_FUSED and call.eligible and num_targets > 0 and _lib.load().spira_b200_get_option(b"gather_tma") == 0:
         accum = zero_scratch(feats.device, num_targets * call.cout)
         name, fn, launches = "spira_b200_conv_ws_fused", call.fn_ws_fused, 1
-        args = (feats.data_ptr(), call.packed_ptr(PACK_WS), call.ep_ref, lists.in_idx.data_ptr(), lists.out_idx.data_ptr(),
-                lists.naddrs.data_ptr(), lists.qnaddrs.data_ptr(), lists.rows, n_tiles, 1 if lists.mirror else 0,
+        args = (feats.data_ptr(), call.packed_ptr(PACK_WS), call.ep_ref, lists.in_ptr, lists.out_ptr,
+                lists.naddrs_ptr, lists.qnaddrs_ptr, lists.rows, n_tiles, 1 if lists.mirror else 0,
                 1 if swap else 0, num_sources, num_targets, call.K, call.cin, call.cout, accum.data_ptr(), out.data_ptr(),
                 call.status_ptr, _raw_stream(call.dev_index))
     else:
         accum = torch.empty((num_targets, call.cout), dtype=torch.float32, device=feats.device)
         name, fn, launches = "spira_b200_conv_ws", call.fn_ws, 2
-        args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(PACK_WS), call.ep_ref, lists.in_idx.data_ptr(),
-                lists.out_idx.data_ptr(), lists.naddrs.data_ptr(), lists.qnaddrs.data_ptr(), lists.rows, n_tiles,
+        args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(PACK_WS), call.ep_ref, lists.in_ptr,
+                lists.out_ptr, lists.naddrs_ptr, lists.qnaddrs_ptr, lists.rows, n_tiles,
                 1 if lists.mirror else 0, 1 if swap else 0, num_sources, num_targets, call.K, call.cin, call.cout,
                 accum.data_ptr(), out.data_ptr(), call.status_ptr, _raw_stream(call.dev_index))
     if _lib.profile_hook is not None:
@@ -776,7 +965,7 @@ def _lists_from_reference_slots(naddrs, qnaddrs, nbmaps, mapsize, qmapsize, num_
     w.nbsizes = None
     w.mirror = (w.rows == (K + 1) // 2) and K % 2 == 1 and num_sources == num_targets and w.rows != K
     w.mapsize, w.qmapsize = int(mapsize), int(qmapsize)
-    return w
+    return w.set_pointers()
 
 
 def cuda_sparse_convolution_forward_ws_merged(num_sources, num_targets, sources, weights, naddrs, qnaddrs, nbmaps, mapsize,

@@ -144,7 +144,10 @@ def _map_statistics(cache, conv, inputs_stride):
     sb = getattr(entry[3], "_sb", None)
     if sb is None:
         return None
-    counts = sb["counts"]
+    from spira_b200.nn.functional import _C
+    counts = _C.map_counts(entry[3])
+    if counts is None:
+        return None
     nnz = int(counts.sum().item())
     nonempty = int((counts > 0).sum().item())
     return int(entry[2]), nnz, nonempty
