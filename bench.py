@@ -18,6 +18,7 @@ Prints ONE JSON line (rank 0).
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -225,7 +226,7 @@ def flush_l2(buf):
     buf.add_(1)     # read + write of a buffer twice the size of L2
 
 
-def timed_loop(step_fn, n_steps, warmup, l2buf, dist_ctx):
+def timed_loop(step_fn, n_steps, warmup, l2buf, dist_ctx, drain_fn=None):
     import gc
     for i in range(warmup):
         step_fn(i)
@@ -245,6 +246,8 @@ def timed_loop(step_fn, n_steps, warmup, l2buf, dist_ctx):
         a.record()
         c0 = time.perf_counter()
         step_fn(warmup + i)
+        if drain_fn is not None and i == n_steps - 1:
+            drain_fn()          # work a step left on another stream ends inside the timed region of the last step
         enqueue += time.perf_counter() - c0
         b.record()
         evs.append((a, b))
@@ -526,16 +529,58 @@ def main():
     out_host = {}
     d2h_bytes = [0]
 
+    # End to end, both arms alike: the inputs of a step come from pinned host memory (H2D on the compute stream, inside
+    # the step) and its logits go back to pinned host memory.  The D2H copy runs on a copy stream behind an event, so that
+    # the next step's kernels do not queue behind it; the timed region ends after the last copy has landed (the loop's
+    # final synchronize).  Every copy is accounted for: a step's end marker waits for the copy of the step before it, and
+    # the last step's marker waits for its own.
+    copy_stream = torch.cuda.Stream(device=device)
+    pending_out = {}
+
+    h2d = {}        # step number -> event: its inputs have been copied to the staging buffers (issued one step ahead)
+
+    def upload(i, stream_ctx):
+        j = i % len(dev)
+        with stream_ctx:
+            stage_c[j].copy_(host[j][0], non_blocking=True)
+            stage_f[j].copy_(host[j][1], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        h2d[i] = ev
+
     def step_e2e(i):
         j = i % len(dev)
-        stage_c[j].copy_(host[j][0], non_blocking=True)
-        stage_f[j].copy_(host[j][1], non_blocking=True)
+        main = torch.cuda.current_stream()
+        if i not in h2d:                     # first step of a loop: nothing was uploaded ahead
+            upload(i, contextlib.nullcontext())
+        main.wait_event(h2d.pop(i))
+        # the next step's inputs travel while this step computes (its staging buffers belong to another scene)
+        if len(dev) > 1:
+            h2d.clear()
+            mark = torch.cuda.Event()
+            mark.record(main)                # everything enqueued so far (the steps that last read those buffers) comes first
+            copy_stream.wait_event(mark)
+            upload(i + 1, torch.cuda.stream(copy_stream))
         y = engine.step(stage_c[j], stage_f[j])
         if j not in out_host:
             out_host[j] = torch.empty(y.shape, dtype=y.dtype).pin_memory()
-        out_host[j].copy_(y, non_blocking=True)
+        main = torch.cuda.current_stream()
+        if "done" in pending_out:
+            main.wait_event(pending_out["done"])     # the previous step's copy ends inside this step's timed region
+        ready = torch.cuda.Event()
+        ready.record()
+        copy_stream.wait_event(ready)
+        with torch.cuda.stream(copy_stream):
+            out_host[j].copy_(y, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+        y.record_stream(copy_stream)
+        pending_out["done"] = done
         d2h_bytes[0] = y.numel() * y.element_size()
         return y
+
+    def drain_e2e():
+        torch.cuda.current_stream().wait_stream(copy_stream)
 
     # set-up, both arms alike: every scene of the rank runs once through both entry points, so that the caching
     # allocator has seen every tensor size before the W warm-up steps (a first-time size costs a cudaMalloc)
@@ -549,7 +594,7 @@ def main():
     launches0 = _lib.launch_count
     total_ms, wall = timed_loop(step_resident, args.steps, args.warmup, l2buf, dist_ctx)
     launches = _lib.launch_count - launches0
-    e2e_ms, _ = timed_loop(step_e2e, args.steps, args.warmup, l2buf, dist_ctx)
+    e2e_ms, _ = timed_loop(step_e2e, args.steps, args.warmup, l2buf, dist_ctx, drain_e2e)
     clocks = sampler.stop() if rank == 0 else None
 
     ms_per_step = total_ms / args.steps
