@@ -393,6 +393,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap"])
     ap.add_argument("--no-defer", action="store_true", help="add_all_kernel_maps completes all maps before it returns")
+    ap.add_argument("--n256-min-targets", type=int, default=-1, help="layers with fewer targets use 128-target tiles (-1 = library default)")
     ap.add_argument("--no-n256", action="store_true", help="output-stationary layers always use the targets-as-M kernel")
     ap.add_argument("--team-threads", type=int, default=0, choices=[0, 128, 256, 512],
                     help="producer threads per pipeline stage of the exchanged-operand kernel (0 = library default)")
@@ -423,6 +424,9 @@ def main():
     if args.impl == "ours" and args.no_defer:
         from spira_b200.nn.functional import _C as native_
         native_.DEFER_MAPS = False
+    if args.impl == "ours" and args.n256_min_targets >= 0:
+        from spira_b200.nn.functional import _C as native_
+        native_.set_option("os_n256_min_targets", args.n256_min_targets)
     if args.impl == "ours" and args.no_n256:
         from spira_b200.nn.functional import _C as native_
         native_.set_option("os_n256", 0)

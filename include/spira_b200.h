@@ -57,6 +57,8 @@ int spira_b200_read_back(const void *device_src, void *pinned_dst, size_t bytes,
  *   "os_n256"           1 (default): output-stationary layers with 64 < c_out <= 128 and K <= 32 whose four-stage
  *                       pipeline fits in shared memory (c_out <= 96 for K = 27) run the kernel that puts 256 targets
  *                       on the MMA's N side and the weights on its M side; 0: always 128 targets as M
+ *   "os_n256_min_targets" layers with fewer targets than this use the 128-target tiles even where the 256-target kernel
+ *                       applies: with few tiles per SM the heaviest tile sets the time and smaller tiles balance better
  *   "os_team_threads"   128 (default), 256 or 512: producer threads that fill one pipeline stage of that kernel
  *                       together (4, 2 or 1 teams); measured equal within noise for 128 and 256, slower for 512
  * get_option additionally answers "os_pack_mode": the SPIRA_B200_PACK_* image spira_b200_conv_os expects under

@@ -120,7 +120,15 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
   const int stages = P.stages;
   // tile counts: given by the host, or (weight-stationary lists whose sizes never left the device) read here
   int n_tiles = P.n_tiles, n_tiles_plain = P.n_tiles_plain;
+  // weight-stationary: list offsets of all rows, staged once (finding the row of a tile is a walk over them, and a walk
+  // over global memory costs one L2 round trip per step); visible to all roles after the set-up barrier below
+  int32_t *s_naddrs = reinterpret_cast<int32_t *>(smem + P.off_flags);
+  int32_t *s_qnaddrs = s_naddrs + ((P.rows + 1 + 3) & ~3);
   if constexpr (kWS) {
+    for (int i = tid; i <= P.rows; i += kConvThreads) {
+      s_naddrs[i] = P.naddrs[i];
+      s_qnaddrs[i] = P.qnaddrs[i];
+    }
     if (P.n_tiles < 0) {
       n_tiles_plain = P.qnaddrs[P.rows] >> 7;
       n_tiles = P.mirror ? 2 * n_tiles_plain - P.centre_tiles : n_tiles_plain;
@@ -182,9 +190,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           if (mirrored) tt -= n_tiles_plain;
           const int q0 = tt * kRows;
           int k = 0;
-          while (k + 1 < P.rows && P.qnaddrs[k + 1] <= q0) ++k;
-          const int p0 = P.naddrs[k] + (q0 - P.qnaddrs[k]);
-          const int n = min(kRows, P.naddrs[k + 1] - p0);
+          while (k + 1 < P.rows && s_qnaddrs[k + 1] <= q0) ++k;
+          const int p0 = s_naddrs[k] + (q0 - s_qnaddrs[k]);
+          const int n = min(kRows, s_naddrs[k + 1] - p0);
           w_row = mirrored ? (P.K - 1 - k) : k;
           const int32_t *g = mirrored ? P.out_idx : P.in_idx;
           const int32_t *sc = mirrored ? P.in_idx : P.out_idx;
@@ -307,11 +315,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           if (mirrored) tt -= n_tiles_plain;
           const int q0 = tt * kRows;
           int k = (mirrored == hint_mirrored) ? k_hint : 0;     // tiles arrive in increasing order
-          while (k + 1 < P.rows && P.qnaddrs[k + 1] <= q0) ++k;
+          while (k + 1 < P.rows && s_qnaddrs[k + 1] <= q0) ++k;
           k_hint = k;
           hint_mirrored = mirrored;
-          const int p0 = P.naddrs[k] + (q0 - P.qnaddrs[k]);
-          const int n = min(kRows, P.naddrs[k + 1] - p0);
+          const int p0 = s_naddrs[k] + (q0 - s_qnaddrs[k]);
+          const int n = min(kRows, s_naddrs[k + 1] - p0);
           w_row = mirrored ? (P.K - 1 - k) : k;
           const int32_t *g = mirrored ? P.out_idx : P.in_idx;
 #pragma unroll
@@ -1220,7 +1228,9 @@ static size_t plan_smem(ConvParams &P, bool ws) {
   P.slab_bufs = (!ws && 2 * slab_one <= 32 * 1024) ? 2 : 1;
   int slab_bytes = ws ? slab_one : P.slab_bufs * slab_one;
   int n_words = ws ? 1 : (P.n_chunks + 31) / 32;
-  int fixed = slab_bytes + round16(P.K * 4) + round16(2 * n_words * 4) + round16(kMaxStages * 4) + 8 * (2 * kMaxStages + 8) + 16;
+  // weight-stationary: the list offsets of all rows (naddrs, qnaddrs: rows + 1 entries each) are staged in shared memory
+  const int rowtab_bytes = ws ? 2 * round16((P.rows + 1) * 4) : round16(P.K * 4);
+  int fixed = slab_bytes + rowtab_bytes + round16(2 * n_words * 4) + round16(kMaxStages * 4) + 8 * (2 * kMaxStages + 8) + 16;
   int per_stage = kABytes + P.b_bytes;
   int stages = (kSmemBudget - fixed) / per_stage;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -1233,7 +1243,7 @@ static size_t plan_smem(ConvParams &P, bool ws) {
   P.off_b = stages * kABytes;
   P.off_slab = P.off_b + stages * P.b_bytes;
   P.off_flags = P.off_slab + slab_bytes;
-  P.off_cm = P.off_flags + round16(P.K * 4);
+  P.off_cm = P.off_flags + rowtab_bytes;
   P.off_meta = P.off_cm + round16(2 * n_words * 4);
   P.off_bar = P.off_meta + round16(kMaxStages * 4);
   return static_cast<size_t>(P.off_bar) + 8 * (2 * kMaxStages + 8) + 16 + 1024;
@@ -1264,6 +1274,7 @@ static size_t plan_smem_n256(ConvN2Params &P, int teams) {
 
 static int g_os_n256 = 1;          // 1: layers with 64 < c_out <= 128 use the exchanged-operand kernel
 static int g_os_team_threads = 128;   // producer threads per stage of that kernel: 128, 256 or 512
+static int g_os_n256_min_targets = 0; // layers with fewer targets use the 128-target tiles (finer load balance)
 
 }  // namespace sb
 
@@ -1340,7 +1351,7 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
                "conv_os: feats, packed, out, map and residual must be 16-byte aligned");
   // On grouped maps both kernels run at the speed of the row gathers; the 256-target tiles then only pay off for the
   // wider layers (measured: 32 channels 20 % slower, 64 equal, 96 5 % faster than 128-target tiles).
-  if (g_os_n256 && !g_gather_tma && c_out > 64 && c_out <= 128 && K <= 32) {
+  if (g_os_n256 && !g_gather_tma && c_out > 64 && c_out <= 128 && K <= 32 && num_targets >= g_os_n256_min_targets) {
     ConvN2Params Q{};
     Q.feats = static_cast<const __half *>(feats);
     Q.packed = static_cast<const unsigned char *>(packed);
@@ -1508,6 +1519,7 @@ extern "C" int spira_b200_set_option(const char *name, int value) {
   SB_CHECK_ARG(name != nullptr, "set_option: null name");
   if (std::strcmp(name, "gather_tma") == 0) { g_gather_tma = value ? 1 : 0; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_n256") == 0) { g_os_n256 = value ? 1 : 0; return SPIRA_B200_OK; }
+  if (std::strcmp(name, "os_n256_min_targets") == 0) { g_os_n256_min_targets = value < 0 ? 0 : value; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_team_threads") == 0) {
     SB_CHECK_ARG(value == 128 || value == 256 || value == 512, "set_option: os_team_threads must be 128, 256 or 512");
     g_os_team_threads = value;
@@ -1521,6 +1533,7 @@ extern "C" int spira_b200_get_option(const char *name) {
   if (std::strcmp(name, "gather_tma") == 0) return g_gather_tma;
   if (std::strcmp(name, "os_n256") == 0) return g_os_n256;
   if (std::strcmp(name, "os_team_threads") == 0) return g_os_team_threads;
+  if (std::strcmp(name, "os_n256_min_targets") == 0) return g_os_n256_min_targets;
   if (std::strcmp(name, "os_pack_mode") == 0) return g_gather_tma ? SPIRA_B200_PACK_WS : SPIRA_B200_PACK_OS;
   return -1;
 }

@@ -51,3 +51,23 @@ def test_argument_errors_without_a_gpu(lib):
     assert lib.spira_b200_packed_weight_bytes(27, 32, 64, 1, ctypes.byref(n)) == 0 and n.value == 27 * 64 * 128
     with pytest.raises(RuntimeError, match="spira_b200"):
         _lib.call("spira_b200_kmap_search", None, 99, 4, None)
+
+
+def test_new_struct_layouts_match_the_header():
+    from spira_b200 import _lib
+    assert ctypes.sizeof(_lib.GroupDesc) == 8 + 8 + 8 + 4 * 8           # ptr, i64, i32 (+pad), 4 ptr
+    assert ctypes.sizeof(_lib.WsDesc) == 2 * 8 + 8 + 2 * 4 + 7 * 8      # 2 ptr, i64, 2 i32, 7 ptr
+
+
+def test_more_argument_errors_without_a_gpu(lib):
+    from spira_b200 import _lib
+    n = ctypes.c_size_t()
+    assert lib.spira_b200_kmap_group_workspace(-1, ctypes.byref(n)) != 0
+    assert lib.spira_b200_kmap_group(None, 99, None, 0, None) != 0 and b"n_maps" in lib.spira_b200_last_error()
+    assert lib.spira_b200_kmap_ws_lists(None, 17, None) != 0 and b"n_maps" in lib.spira_b200_last_error()
+    assert lib.spira_b200_kmap_group(None, 0, None, 0, None) == 0       # nothing to do
+    assert lib.spira_b200_downsample_sorted_workspace(10, 3, ctypes.byref(n)) != 0
+    assert lib.spira_b200_set_option(b"os_team_threads", 100) != 0
+    assert lib.spira_b200_set_option(b"no_such_option", 1) != 0 and lib.spira_b200_get_option(b"no_such_option") == -1
+    assert lib.spira_b200_get_option(b"os_team_threads") == 128 and lib.spira_b200_get_option(b"os_n256") == 1
+    assert lib.spira_b200_read_back(None, None, 4, None, None, None) != 0

@@ -1,0 +1,60 @@
+"""CPU: host-side logic that needs no GPU -- stride rules of the sort-free down-sampling, the selector's cost model,
+the lazily materialised result tuples."""
+import pytest
+
+
+def test_strides_that_double_level_by_level():
+    from spira_b200.nn.functional import _C
+    assert _C._strides_double([(2, 2, 2), (4, 4, 4), (8, 8, 8)])
+    assert _C._strides_double([(1, 1, 2), (2, 1, 2), (2, 2, 4)])
+    assert not _C._strides_double([(4, 4, 4)])                       # 1 -> 4 skips a level
+    assert not _C._strides_double([(2, 2, 2), (8, 8, 8)])
+    assert not _C._strides_double([(2, 2, 2), (1, 2, 2)])            # strides never shrink
+    assert not _C._strides_double([(3, 3, 3)])
+
+
+def test_selector_model_orders_the_obvious_cases():
+    from spira_b200.utils.helpers import estimate_layer_us, choose_dataflow
+    # big surface-dense level, narrow layer: output-stationary (no atomics); tiny deep level, wide layer: weight-stationary
+    os_us, ws_us = estimate_layer_us(96, 96, 27, 127363, 1042915)
+    assert os_us < ws_us
+    os_us, ws_us = estimate_layer_us(256, 256, 27, 1961, 13223)
+    assert ws_us < os_us
+    assert choose_dataflow(96, 96, 27, 127363, 1042915, None) == 0
+    assert choose_dataflow(256, 256, 27, 1961, 13223, None) == 1
+    assert choose_dataflow(4, 32, 27, 127363, 1042915, None) == 0     # the tensor-core kernels cannot tile a 4-channel stem
+    # a transposed output-stationary layer also pays for its inverse map
+    a, _ = estimate_layer_us(96, 96, 27, 127363, 271937, submanifold=False, transposed=False)
+    b, _ = estimate_layer_us(96, 96, 27, 127363, 271937, submanifold=False, transposed=True)
+    assert b > a
+    # more pairs never make a layer cheaper
+    for df in (0, 1):
+        small = estimate_layer_us(64, 64, 27, 14014, 50000)[df]
+        large = estimate_layer_us(64, 64, 27, 14014, 150000)[df]
+        assert large >= small
+
+
+def test_weight_stationary_result_tuple_fills_its_list_slots_on_demand():
+    from spira_b200.nn.functional import _C
+
+    class Lists:
+        nbmaps, nbsizes, naddrs, qnaddrs = "nbmaps", "nbsizes", "naddrs", "qnaddrs"
+    t = _C._WsTuple((10, 7, "map", Lists()))
+    assert len(t) == 9 and t[0] == 10 and t[1] == 7 and t[2] == "map"
+    assert t[3] == "nbmaps" and t[4] == "nbsizes" and t[5] == "naddrs" and t[6] == "qnaddrs" and t[-3] == "qnaddrs"
+    assert t[7] is None and t[8] is None
+    assert list(t) == [10, 7, "map", "nbmaps", "nbsizes", "naddrs", "qnaddrs", None, None]
+    assert t[2:5] == ("map", "nbmaps", "nbsizes")
+    s, tt, m, *rest = t
+    assert (s, tt, m) == (10, 7, "map") and rest[0] == "nbmaps"
+
+
+def test_cache_entries_of_the_network_wide_build_keep_list_slots_empty():
+    from spira_b200.nn import KernelMapCache
+    from spira_b200.nn.functional import _C
+
+    class Lists:
+        nbmaps = nbsizes = naddrs = qnaddrs = "x"
+    e = KernelMapCache._entry(_C._WsTuple((3, 2, "map", Lists())))
+    assert e == [False, 3, 2, "map", None, None, None, None, None, None]
+    assert KernelMapCache._entry((3, 2, "map", 1, 2, 3, 4, 5, 6)) == [False, 3, 2, "map", 1, 2, 3, 4, 5, 6]
