@@ -6,7 +6,7 @@
 One step = one whole scene through the reference's timed region (scripts/end_to_end_experiment.py:191-207):
 ``SparseTensor.order()`` + network-wide kernel-map build (``KernelMapCache.add_all_kernel_maps``) + the network's
 forward pass.  Default workload: MinkUNet18-style network, fp16, random init, one ~125k-voxel scene per step
-(BASELINE.json configs[2]).  With N > 1 (launched by torch.distributed.run) every rank owns one GPU and its own
+(the headline workload).  With N > 1 (launched by torch.distributed.run) every rank owns one GPU and its own
 scenes; nothing is exchanged on the data path, so scaling is weak and ``value`` = scenes of all ranks / slowest rank.
 
 ``--impl reference`` drives the reference's own native module (built from its unmodified sources into
@@ -24,6 +24,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 from pathlib import Path
@@ -492,7 +493,7 @@ def main():
         def loader():
             for c, f in dev:
                 yield sp.SparseTensor(c, f).order()
-        _, chosen = sp.tune(engine.model, loader(), engine.cache, n_samples=2, save_dir=str(ROOT / "gpurun_out" / ".tune"),
+        _, chosen = sp.tune(engine.model, loader(), engine.cache, n_samples=2, save_dir=os.path.join(tempfile.gettempdir(), "spira_b200_tune"),
                             tune_tag=f"{args.workload}_r{rank}", force_retune=True, return_dataflows=True, verify=False)
         engine.apply_groups(chosen)
         chosen_note = {str(k): v for k, v in chosen.items()}
@@ -675,7 +676,7 @@ def _time_calls(fn, steps, warmup, l2buf):
 
 
 def run_layer(args, device, pk, pk_kind):
-    """BASELINE.json configs[0]: one submanifold 3^3 layer, c_in -> c_out, 50,000 voxels in a 512^3 grid (64-bit keys)."""
+    """Single-layer workload: one submanifold 3^3 layer, c_in -> c_out, 50,000 voxels in a 512^3 grid (64-bit keys)."""
     from spira_b200 import scenes as sc
     from spira_b200.nn.functional import _C
     if args.scene == "c0":
@@ -721,7 +722,7 @@ def run_layer(args, device, pk, pk_kind):
 
 
 def run_kmap(args, device, pk, pk_kind):
-    """BASELINE.json configs[1]: kernel maps only, 4 LiDAR-like scenes: 3^3, 5^3, stride-2 down-sampling + transposed reuse."""
+    """Kernel-map workload: kernel maps only, 4 LiDAR-like scenes: 3^3, 5^3, stride-2 down-sampling + transposed reuse."""
     from spira_b200 import scenes as sc
     from spira_b200.nn.functional import _C
     scenes_k = []
