@@ -291,3 +291,46 @@ def conv_ws_transposed(feats, weights, dense_ws: np.ndarray, num_sources_of_map:
     keep ``widx`` for the non-mirrored half)."""
     k, t = np.nonzero(dense_ws >= 0)
     return conv_from_pairs(feats, weights, t, dense_ws[k, t], k, num_sources_of_map)
+
+
+# ----------------------------------------------------------------------------------------------
+# engine-native structures without a counterpart in the reference: specified here, checked on the GPU
+# ----------------------------------------------------------------------------------------------
+def group_os_map(out_in_map: np.ndarray, num_targets: int):
+    """Rows of an output-stationary map ``[T_al, K]`` (K <= 32) sorted by presence mask.
+
+    Key of row t: ``(K - popcount(mask)) << 27 | mask`` for K <= 27 (fullest rows first, rows with equal masks adjacent),
+    else ``~mask``; the sort is stable, so rows with the same key keep their spatial order.  Returns
+    ``(grouped_map [T_al, K], row_of [T_al], tile_masks [T_al / 128] uint32, stats (n128, n256))`` where padding rows
+    are -1, ``tile_masks[i]`` has bit k set if some row of tile i has a neighbour at offset k, and the stats count the
+    non-empty (tile, offset) pairs for 128- and 256-row tiles.  The convolution over the grouped map writes output row
+    ``row_of[i]`` for grouped row i and equals the convolution over the original map.
+    """
+    Tal, K = out_in_map.shape
+    assert K <= 32 and Tal % 128 == 0 and num_targets <= Tal
+    present = out_in_map[:num_targets] >= 0
+    mask = (present.astype(np.uint64) << np.arange(K, dtype=np.uint64)).sum(1)
+    if K <= 27:
+        key = ((K - present.sum(1)).astype(np.uint64) << np.uint64(27)) | mask
+    else:
+        key = (~mask) & np.uint64(0xFFFFFFFF)
+    order = np.argsort(key, kind="stable").astype(np.int32)
+    row_of = np.full(Tal, -1, dtype=np.int32)
+    row_of[:num_targets] = order
+    grouped = np.full((Tal, K), -1, dtype=np.int32)
+    grouped[:num_targets] = out_in_map[order]
+    tiles = (grouped >= 0).reshape(Tal // 128, 128, K).any(1)
+    tile_masks = (tiles.astype(np.uint64) << np.arange(K, dtype=np.uint64)).sum(1).astype(np.uint32)
+    pairs = tiles if tiles.shape[0] % 2 == 0 else np.concatenate([tiles, np.zeros((1, K), bool)])
+    n256 = int(pairs.reshape(-1, 2, K).any(1).sum())
+    return grouped, row_of, tile_masks, (int(tiles.sum()), n256)
+
+
+def conv_os_grouped(feats, weights, grouped_map: np.ndarray, row_of: np.ndarray, num_targets: int):
+    """Convolution over a grouped map: row i of the result of :func:`conv_os` on ``grouped_map`` lands in output row
+    ``row_of[i]``."""
+    import torch
+    rows = conv_os(feats, weights, grouped_map, num_targets)
+    out = torch.empty_like(rows)
+    out[torch.from_numpy(row_of[:num_targets].astype(np.int64))] = rows
+    return out

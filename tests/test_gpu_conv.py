@@ -208,23 +208,13 @@ def test_grouping_reorders_the_map_without_changing_it(C, scene):
         g = m[2]._sb["grouped"]
         assert g is not None
         dense = m[2].cpu().numpy()
-        gm, row_of = g.map.cpu().numpy(), g.row_of.cpu().numpy()
-        Tal = dense.shape[0]
-        assert gm.shape == dense.shape and row_of.shape == (Tal,)
-        assert np.array_equal(np.sort(row_of[:T]), np.arange(T)) and (row_of[T:] == -1).all()
-        assert np.array_equal(gm[:T], dense[row_of[:T]]) and (gm[T:] == -1).all()
-        present = gm >= 0
-        bits = (present.astype(np.uint64) << np.arange(27, dtype=np.uint64)).sum(1)
-        key = ((27 - present.sum(1)).astype(np.uint64) << np.uint64(27)) | bits
-        assert (np.diff(key[:T].astype(np.int64)) >= 0).all()                      # fullest rows first, equal masks adjacent
-        same = key[:T][1:] == key[:T][:-1]
-        assert (np.diff(row_of[:T])[same] > 0).all()                               # stable: spatial order inside a group
-        tm = present.reshape(-1, 128, 27).any(1)
-        want_masks = (tm.astype(np.uint64) << np.arange(27, dtype=np.uint64)).sum(1).astype(np.uint32)
+        want_map, want_rows, want_masks, want_stats = O.group_os_map(dense, T)
+        assert np.array_equal(g.map.cpu().numpy(), want_map)
+        assert np.array_equal(g.row_of.cpu().numpy(), want_rows)
         assert np.array_equal(g.tile_masks.cpu().numpy().view(np.uint32), want_masks)
-        pairs = tm.reshape(-1, 27) if tm.shape[0] % 2 == 0 else np.concatenate([tm, np.zeros((1, 27), bool)])
-        n256 = pairs.reshape(-1, 2, 27).any(1).sum()
-        assert g.stats.cpu().tolist() == [int(tm.sum()), int(n256)]
+        assert tuple(g.stats.cpu().tolist()) == want_stats
+        Tal = dense.shape[0]
+        tm = (want_map >= 0).reshape(-1, 128, 27).any(1)
         # grouping pays: far fewer (tile, offset) pairs have to be visited than in target order
         assert tm.sum() < 0.8 * (dense[:Tal].reshape(-1, 128, 27) >= 0).any(1).sum()
 

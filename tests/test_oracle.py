@@ -194,3 +194,23 @@ def test_transposed_conv_oracle_is_adjoint():
     bwd = O.conv_ws_transposed(y, w.transpose(1, 2).contiguous(), ws, len(keys))
     # <conv(x), y> == <x, conv_T(y)> when the transposed layer uses the transposed weight matrices
     np.testing.assert_allclose((fwd * y).sum().item(), (x * bwd).sum().item(), rtol=1e-3)
+
+
+def test_grouped_map_is_a_row_permutation_and_convolves_to_the_same_result():
+    import torch
+    from helpers import surface
+    c = surface(31, 3000)
+    keys, _ = O.flat_sort(c)
+    dense = O.kernel_map(keys, keys, (3, 3, 3), (1, 1, 1), "os")
+    T = len(keys)
+    g, row_of, masks, (n128, n256) = O.group_os_map(dense, T)
+    assert sorted(row_of[:T].tolist()) == list(range(T)) and (row_of[T:] == -1).all()
+    assert np.array_equal(g[:T], dense[row_of[:T]]) and (g[T:] == -1).all()
+    pop = (g[:T] >= 0).sum(1)
+    assert (np.diff(pop) <= 0).all()                                  # fullest rows first
+    before = (dense.reshape(-1, 128, 27) >= 0).any(1).sum()
+    assert n128 == sum(bin(int(m)).count("1") for m in masks) and n128 < before and n256 <= n128
+    rng = np.random.default_rng(0)
+    f = torch.from_numpy(rng.normal(size=(T, 16)).astype(np.float16))
+    w = torch.from_numpy((rng.normal(size=(27, 16, 16)) / 20).astype(np.float16))
+    assert torch.equal(O.conv_os(f, w, dense, T), O.conv_os_grouped(f, w, g, row_of, T))
