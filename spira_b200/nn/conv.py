@@ -160,7 +160,7 @@ class KernelMapCache(object):
         # the device: the level sizes are the only host read of a scene.  Map 0 has the level-0 keys on both sides and
         # does not need them: it is built now, and the rest waits until somebody asks for it (finish()).
         first = None
-        if levels is not None:
+        if levels is not None and getattr(_C, "DEFER_MAPS", True):
             first = _C.cuda_binary_search_pairs([(source_coordinates, source_coordinates)], k_sizes[:1], s_strides[:1],
                                                 dataflow[:1], exact_sizes=False)
             self._maps[(s0, s_strides[1], k_sizes[0])] = self._entry(first[0])
@@ -194,6 +194,11 @@ class KernelMapCache(object):
             pairs = [(voxels[i // 2], voxels[(i + 1) // 2]) for i in range(1, len(k_sizes))]
             kmaps = first + (_C.cuda_binary_search_pairs(pairs, k_sizes[1:], s_strides[1:-1], dataflow[1:], exact_sizes=False,
                                                          group=False) if pairs else [])
+        elif hasattr(_C, "cuda_binary_search_pairs"):
+            # everything at once: one search launch, one grouping sort (inverses included)
+            pairs = [(voxels[i // 2], voxels[(i + 1) // 2]) for i in range(len(k_sizes))]
+            kmaps = _C.cuda_binary_search_pairs(pairs, k_sizes, s_strides[:-1], dataflow, exact_sizes=False, group=False)
+            deferred = True
         else:
             kmaps = F.build_kmap_streamed(voxels, k_sizes, s_strides[:-1], dataflow, exact_sizes=False)
 
@@ -202,7 +207,7 @@ class KernelMapCache(object):
         for i in range(len(k_sizes)):
             t_stride = s_strides[i + 1]
             key = (s_stride, t_stride, k_sizes[i])
-            if not (deferred and i == 0):
+            if not (first is not None and i == 0):
                 self._maps[key] = self._entry(kmaps[i])
             keys.append(key)
             s_stride = t_stride
@@ -214,7 +219,7 @@ class KernelMapCache(object):
                 sb = getattr(entry[3], "_sb", None)
                 if sb is None or sb.get("layout") != _C.LAYOUT_OS:
                     continue
-                if i > 0:
+                if i > 0 or first is None:
                     todo.append((entry[3], entry[2]))
                 if key in self._inverse_keys and (key, "inverted") not in self._derived_maps:
                     inv = F.convert_transposed_os(entry[3], entry[1])
