@@ -405,6 +405,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap"])
+    ap.add_argument("--no-group", action="store_true", help="output-stationary maps keep their target order (no grouping by neighbour pattern)")
     ap.add_argument("--no-defer", action="store_true", help="add_all_kernel_maps completes all maps before it returns")
     ap.add_argument("--n256-min-targets", type=int, default=-1, help="layers with fewer targets use 128-target tiles (-1 = library default)")
     ap.add_argument("--no-n256", action="store_true", help="output-stationary layers always use the targets-as-M kernel")
@@ -434,6 +435,9 @@ def main():
     n_gpus = world
 
     pk, pk_kind = peaks()
+    if args.impl == "ours" and args.no_group:
+        from spira_b200.nn.functional import _C as native_
+        native_.GROUP_OS = False
     if args.impl == "ours" and args.no_defer:
         from spira_b200.nn.functional import _C as native_
         native_.DEFER_MAPS = False

@@ -40,6 +40,16 @@ class KernelMapCache(object):
         # keys of the maps a transposed output-stationary layer asked the inverse of; kept across reset(): the next
         # network-wide build makes those inverses right away, grouped by the same sort as all other maps
         self._inverse_keys = set()
+        # map key -> False: the rows of this output-stationary map keep their target order (set by spira.tune where the
+        # layers that use the map save less than the grouping costs); maps not named here are grouped
+        self._group_policy = dict()
+
+    def set_group_policy(self, policy: Dict[tuple, bool]):
+        self._group_policy = dict(policy)
+        return self
+
+    def _groups(self, key) -> bool:
+        return self._group_policy.get(key, True)
 
     # the three dictionaries under their historical names: reading them completes a pending build first
     @property
@@ -131,7 +141,8 @@ class KernelMapCache(object):
                 inv = F.convert_transposed_os(entry[3], entry[1])
                 sb = getattr(entry[3], "_sb", None)
                 if sb is not None:
-                    inv._sb = dict(sb, ws=None, counts=None, _counts=None, grouped=_C.group_os_map(inv, entry[1]))
+                    inv._sb = dict(sb, ws=None, counts=None, _counts=None,
+                                   grouped=_C.group_os_map(inv, entry[1]) if self._groups(key) else None)
                     self._inverse_keys.add(key)
                 self._derived_maps[dkey] = inv
             new_entry = list(entry[1:])
@@ -162,7 +173,7 @@ class KernelMapCache(object):
         first = None
         if levels is not None and getattr(_C, "DEFER_MAPS", True):
             first = _C.cuda_binary_search_pairs([(source_coordinates, source_coordinates)], k_sizes[:1], s_strides[:1],
-                                                dataflow[:1], exact_sizes=False)
+                                                dataflow[:1], exact_sizes=False, group=self._groups((s0, s_strides[1], k_sizes[0])))
             self._maps[(s0, s_strides[1], k_sizes[0])] = self._entry(first[0])
         self._pending = (source_coordinates, k_sizes, s_strides, t_strides, s0, dataflow, levels, first)
         if levels is None or not getattr(_C, "DEFER_MAPS", True):
@@ -217,7 +228,7 @@ class KernelMapCache(object):
             for i, key in enumerate(keys):
                 entry = self._maps[key]
                 sb = getattr(entry[3], "_sb", None)
-                if sb is None or sb.get("layout") != _C.LAYOUT_OS:
+                if sb is None or sb.get("layout") != _C.LAYOUT_OS or not self._groups(key):
                     continue
                 if i > 0 or first is None:
                     todo.append((entry[3], entry[2]))

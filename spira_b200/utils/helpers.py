@@ -76,8 +76,17 @@ _INVERT_US = (150.0, 3.0e6)    # output-stationary map of a transposed layer: in
 _SM_COUNT = 148
 
 
+_GROUP_COST_US = (12.0, 4.0e-4)    # grouping the rows of one map: fixed + per row (its share of the sort, the re-ordered copy)
+
+
+def grouping_cost_us(num_targets: int) -> float:
+    """Time the network-wide build spends on grouping one output-stationary map of ``num_targets`` rows."""
+    return _GROUP_COST_US[0] + _GROUP_COST_US[1] * num_targets
+
+
 def estimate_layer_us(c_in: int, c_out: int, kernel_volume: int, num_targets: int, nnz: int,
-                      nonempty_tile_offsets: int = None, submanifold: bool = True, transposed: bool = False):
+                      nonempty_tile_offsets: int = None, submanifold: bool = True, transposed: bool = False,
+                      grouped: bool = True):
     """(output-stationary, weight-stationary) time estimates in microseconds.
 
     OS runs one persistent CTA per SM over tiles of 128 (or, for 64 < c_out <= 96, 256) map rows and streams one stage per
@@ -85,7 +94,8 @@ def estimate_layer_us(c_in: int, c_out: int, kernel_volume: int, num_targets: in
     which leaves ~1.2-1.3 visited rows per real pair; other maps visit every non-empty (tile, offset) pair
     (``nonempty_tile_offsets``, from the search's hit counters).  WS streams one stage per 128 compacted pairs and 64
     input channels over all SMs but pays an fp32 read-modify-write of the output per pair plus a zero-fill and a
-    conversion pass.  A transposed OS layer also pays for inverting (and grouping) the map of its twin."""
+    conversion pass.  A transposed OS layer also pays for inverting (and grouping) the map of its twin.
+    ``grouped=False`` gives the OS estimate for a map that keeps its target order."""
     import math
     chunk = _CHUNK_US[0] + _CHUNK_US[1] * c_out
     per_in = c_in / 64.0
@@ -94,16 +104,17 @@ def estimate_layer_us(c_in: int, c_out: int, kernel_volume: int, num_targets: in
     tiles = max(1, math.ceil(num_targets / rows_per_tile))
     ctas = min(_SM_COUNT, tiles)
     stage_us = chunk if wide else _CHUNK256_US
-    if kernel_volume <= 32:
+    grouped = grouped and kernel_volume <= 32
+    if grouped:
         stages = _GROUPED_REDUNDANCY[0 if wide else 1] * nnz / rows_per_tile * per_in
     else:
         tiles128 = max(1, math.ceil(num_targets / 128))
         if nonempty_tile_offsets is None:
             nonempty_tile_offsets = tiles128 * kernel_volume
-        stages = nonempty_tile_offsets * per_in
+        stages = nonempty_tile_offsets * per_in * (128.0 / rows_per_tile)       # counted per 128-row tile
     which = 0 if wide else 1
     per_cta = _IMBALANCE[which] * stages / ctas + _TILE_OVERHEAD_CHUNKS[which] * math.ceil(tiles / ctas)
-    if kernel_volume <= 32:     # no CTA finishes before the fullest tile of the grouped map
+    if grouped:                 # no CTA finishes before the fullest tile of the grouped map
         per_cta = max(per_cta, _HEAVIEST_TILE * kernel_volume * per_in + _TILE_OVERHEAD_CHUNKS[which])
     os_us = _OS_FIXED_US + stage_us * per_cta
     if transposed:
@@ -193,11 +204,21 @@ def tune(model: Module, data_loader: Iterable, kernel_map_cache=None, map_datafl
                 m._tunable_config['map_dataflow'] = best[g].map_dataflow
                 m._tunable_config['force_os'] = best[g].force_os
 
+    def apply_grouping(flags):
+        # the cache groups the rows of every output-stationary map unless told otherwise: map key = (source stride,
+        # target stride, kernel size) of the group's non-transposed layer
+        if kernel_map_cache is not None and hasattr(kernel_map_cache, "set_group_policy"):
+            policy = {}
+            for (eff, ksize, stride), flag in flags.items():
+                policy[(tuple(eff), tuple(a * b for a, b in zip(eff, stride)), tuple(ksize))] = bool(flag)
+            kernel_map_cache.set_group_policy(policy)
+
     if os.path.exists(save_path) and not force_retune:
         try:
             blob = torch.load(save_path, weights_only=False)
             best = {g: DataflowConfig(**c) for g, c in blob["best_configs"].items()}
             apply(blob["name_to_group"], best)
+            apply_grouping(blob.get("group_rows", {}))
             out = {g: c.map_dataflow for g, c in best.items()}
             return (model, out) if return_dataflows else model
         except Exception as e:  # unreadable cache -> tune again
@@ -234,6 +255,7 @@ def tune(model: Module, data_loader: Iterable, kernel_map_cache=None, map_datafl
         h.remove()
 
     best: Dict[Tuple, DataflowConfig] = {}
+    group_rows: Dict[Tuple, bool] = {}       # output-stationary groups: group the rows of their map by neighbour pattern?
     for g, names in group_to_name.items():
         # the layers of a group share their kernel maps, hence their dataflow: minimise the summed estimates
         os_total = ws_total = 0.0
@@ -250,8 +272,19 @@ def tune(model: Module, data_loader: Iterable, kernel_map_cache=None, map_datafl
         if df not in allowed:
             df = 0 if 0 in allowed else min(allowed)
         best[g] = DataflowConfig(map_dataflow=df, force_os=False)
+        # Is grouping the rows of this map worth its sort?  Compare what the layers of the group save with the cost.
+        layers_of_g = [st for st in stats.get(g, []) if not (st[0] % 8 or st[1] % 16 or st[1] > 256)]
+        if df == 0 and kv <= 32 and layers_of_g:
+            saved = 0.0
+            for (cin, cout, transposed, T, nnz, nonempty) in layers_of_g:
+                sub = not (transposed or any(v != 1 for v in g[2]))
+                saved += (estimate_layer_us(cin, cout, kv, T, nnz, nonempty, submanifold=sub, grouped=False)[0]
+                          - estimate_layer_us(cin, cout, kv, T, nnz, nonempty, submanifold=sub, grouped=True)[0])
+            rows = max(st[3] for st in layers_of_g)
+            group_rows[g] = saved > grouping_cost_us(rows)
         if verbose:
-            print(f"group {g}: {len(names)} layer(s), estimated OS {os_total:.0f} us / WS {ws_total:.0f} us -> map_dataflow={df}")
+            print(f"group {g}: {len(names)} layer(s), estimated OS {os_total:.0f} us / WS {ws_total:.0f} us -> map_dataflow={df}"
+                  + (f", rows grouped: {group_rows[g]}" if g in group_rows else ""))
     apply(name_to_group, best)
 
     if verify and len(best) > 0:
@@ -272,9 +305,11 @@ def tune(model: Module, data_loader: Iterable, kernel_map_cache=None, map_datafl
                     print(f"group {g}: timing overrides the model -> map_dataflow={flipped.map_dataflow} ({t:.3f} ms)")
             apply(name_to_group, best)
 
+    apply_grouping(group_rows)
     os.makedirs(save_dir, exist_ok=True)
     torch.save({"name_to_group": name_to_group,
                 "best_configs": {g: c.to_dict() for g, c in best.items()},
+                "group_rows": dict(group_rows),
                 "layer_configs": {n: dict(m._tunable_config) for n, m in convs.items()}}, save_path)
     if kernel_map_cache is not None:
         kernel_map_cache.reset()

@@ -230,3 +230,23 @@ def test_inverse_maps_of_transposed_layers_are_prebuilt_from_the_second_scene_on
     with torch.no_grad():
         y1 = model(x)
     assert torch.equal(y0._features, y1._features)
+
+
+def test_group_policy_switches_the_grouping_off_per_map(lib):
+    import spira_b200 as sp
+    from spira_b200 import models, scenes, nn as spnn
+    torch.manual_seed(2)
+    c = scenes.lidar_scene(7)[:30000]
+    coords = torch.from_numpy(c).cuda()
+    feats = torch.from_numpy(scenes.features(len(c), 4, 7)).cuda()
+    model = models.minkunet18(4, 19, 3).cuda().half().eval()
+    cache = spnn.KernelMapCache()
+    sp.set_kernel_map_cache(model, cache)
+    sched = models.map_schedule(4, 3, 3)
+    y0, _ = run(model, cache, coords, feats, sched, 0)
+    key0 = ((1, 1, 1), (1, 1, 1), (3, 3, 3))
+    assert cache._kernel_maps_cache[key0][3]._sb["grouped"] is not None
+    cache.set_group_policy({k: False for k in cache._kernel_maps_cache})
+    y1, _ = run(model, cache, coords, feats, sched, 0)
+    assert all(e[3]._sb["grouped"] is None for e in cache._kernel_maps_cache.values())
+    assert torch.equal(y0._features, y1._features)        # grouping never changes a result

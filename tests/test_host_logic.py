@@ -58,3 +58,17 @@ def test_cache_entries_of_the_network_wide_build_keep_list_slots_empty():
     e = KernelMapCache._entry(_C._WsTuple((3, 2, "map", Lists())))
     assert e == [False, 3, 2, "map", None, None, None, None, None, None]
     assert KernelMapCache._entry((3, 2, "map", 1, 2, 3, 4, 5, 6)) == [False, 3, 2, "map", 1, 2, 3, 4, 5, 6]
+
+
+def test_grouping_is_weighed_against_its_cost():
+    from spira_b200.utils.helpers import estimate_layer_us, grouping_cost_us
+    # five wide layers on one 127 k-voxel map save far more than the sort costs; two 16-channel layers on 300 k do not
+    saved = 5 * (estimate_layer_us(96, 96, 27, 127363, 1042915, 25985, grouped=False)[0]
+                 - estimate_layer_us(96, 96, 27, 127363, 1042915, 25985, grouped=True)[0])
+    assert saved > grouping_cost_us(127363)
+    saved = 2 * (estimate_layer_us(16, 16, 27, 300000, 2400000, 2343 * 27, grouped=False)[0]
+                 - estimate_layer_us(16, 16, 27, 300000, 2400000, 2343 * 27, grouped=True)[0])
+    assert saved < grouping_cost_us(300000)
+    assert estimate_layer_us(96, 96, 27, 127363, 1042915, 25985, grouped=False)[0] > estimate_layer_us(96, 96, 27, 127363, 1042915, 25985)[0]
+    # kernels wider than 32 offsets are never grouped: the flag changes nothing
+    assert estimate_layer_us(64, 64, 125, 50000, 900000, 40000, grouped=True) == estimate_layer_us(64, 64, 125, 50000, 900000, 40000, grouped=False)
