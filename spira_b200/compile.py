@@ -89,7 +89,11 @@ class CompiledModel:
                 _, module, i, r, o, in_stride, out_stride = op
                 cfg = module._tunable_config
                 os_flow = cfg["map_dataflow"] == 0 or cfg["force_os"]
-                self.ops.append((0, module, i, r, o, in_stride, out_stride, os_flow, cfg["map_dataflow"], cfg["force_os"]))
+                # cache key of the layer's map (the non-transposed twin's for a transposed layer); the replay reads the
+                # cache's dictionaries directly where the generic lookup would only confirm what the tape already knows
+                key = (out_stride, in_stride, module.kernel_size) if module.transposed else (in_stride, out_stride, module.kernel_size)
+                fast = not cfg["force_os"] and not module._trivial
+                self.ops.append((0, module, i, r, o, in_stride, out_stride, os_flow, cfg["map_dataflow"], cfg["force_os"], key, fast))
             elif op[0] == "apply":
                 self.ops.append((1,) + op[1:])
             elif op[0] == "cat":
@@ -114,7 +118,7 @@ class CompiledModel:
         for op in self.ops:
             kind = op[0]
             if kind == 0:
-                _, module, i, r, o, in_stride, out_stride, os_flow, dataflow, force_os = op
+                _, module, i, r, o, in_stride, out_stride, os_flow, dataflow, force_os, key, fast = op
                 x = slots[i]
                 if module._trivial:
                     folded = module._folded
@@ -124,7 +128,18 @@ class CompiledModel:
                         y = torch.mm(x, module.kernel.view(module.in_channels, module.out_channels))
                         slots[o] = y if module.bias is None else y + module.bias
                     continue
-                m = cache.get_kernel_map(None, in_stride, None, out_stride, module.kernel_size, dataflow, force_os, module.transposed)
+                m = None
+                if fast:
+                    e = cache._maps.get(key)
+                    if e is not None and not e[0]:
+                        if not (os_flow and module.transposed):
+                            m = (e[1], e[2], e[3])
+                        else:
+                            inv = cache._derived_maps.get((key, "inverted"))
+                            if inv is not None:
+                                m = (e[1], e[2], inv)
+                if m is None:
+                    m = cache.get_kernel_map(None, in_stride, None, out_stride, module.kernel_size, dataflow, force_os, module.transposed)
                 n_src, n_tgt = (m[1], m[0]) if module.transposed else (m[0], m[1])
                 call = module._call
                 if call is None or call.stamp != _C.conv_call_stamp(module.kernel, module.bias, module._fused):

@@ -875,6 +875,9 @@ def conv_call_stamp(weights, bias, fused):
             None if fused is None else (id(fused["scale"]), id(fused["shift"]), fused["relu"]))
 
 
+_pack_mode = [-1]       # SPIRA_B200_PACK_* image the output-stationary entry point expects (-1: ask the library)
+
+
 def run_conv_os(call: ConvCall, num_sources: int, num_targets: int, out_in_map: torch.Tensor, feats: torch.Tensor,
                 residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Output-stationary forward of a prepared layer.  ``out_in_map`` is an engine-built ``[T_al, K]`` map."""
@@ -884,7 +887,9 @@ def run_conv_os(call: ConvCall, num_sources: int, num_targets: int, out_in_map: 
     call.ep.residual = residual.data_ptr() if residual is not None else None
     sb = getattr(out_in_map, "_sb", None)
     g = sb.get("grouped") if sb is not None else None
-    mode = _lib.load().spira_b200_get_option(b"os_pack_mode")
+    mode = _pack_mode[0]
+    if mode < 0:
+        mode = _pack_mode[0] = _lib.load().spira_b200_get_option(b"os_pack_mode")
     if g is not None and call.eligible and GROUP_OS:
         name, fn = "spira_b200_conv_os_grouped", call.fn_os_grouped
         args = (feats.data_ptr(), call.packed_ptr(mode), call.ep_ref, g.map_ptr, g.row_of_ptr, g.tile_masks_ptr,
@@ -927,7 +932,10 @@ def run_conv_ws(call: ConvCall, num_sources: int, num_targets: int, lists: WsLis
     out = torch.empty((num_targets, call.cout), dtype=torch.float16, device=feats.device)
     call.ep.residual = residual.data_ptr() if residual is not None else None
     n_tiles = -1 if lists.qmapsize is None else lists.qmapsize // 128
-    if WS_FUSED and call.eligible and num_targets > 0 and _lib.load().spira_b200_get_option(b"gather_tma") == 0:
+    mode = _pack_mode[0]
+    if mode < 0:
+        mode = _pack_mode[0] = _lib.load().spira_b200_get_option(b"os_pack_mode")
+    if WS_FUSED and call.eligible and num_targets > 0 and mode == PACK_OS:      # (PACK_OS: the cp.async producers are in use)
         accum = zero_scratch(feats.device, num_targets * call.cout)
         name, fn, launches = "spira_b200_conv_ws_fused", call.fn_ws_fused, 1
         args = (feats.data_ptr(), call.packed_ptr(PACK_WS), call.ep_ref, lists.in_ptr, lists.out_ptr,
@@ -1035,9 +1043,15 @@ def cuda_time_scatter(tile_size, threshold, is_hybrid, weights, source_masks, ta
     return _time_ws(weights, source_masks, target_masks)
 
 
+_option_epoch = [0]      # bumped by set_option: prepared calls re-read the options they depend on
+
+
 def set_option(name: str, value: int) -> None:
-    """Process-wide kernel options, e.g. ``set_option("gather_tma", 1)`` (see include/spira_b200.h)."""
+    """Process-wide kernel options, e.g. ``set_option("gather_tma", 1)`` (see include/spira_b200.h).  Set options
+    through this function: the prepared per-layer calls cache the weight image mode that follows from them."""
     _lib.call("spira_b200_set_option", name.encode(), int(value))
+    _option_epoch[0] += 1
+    _pack_mode[0] = -1
 
 
 def get_option(name: str) -> int:
