@@ -70,6 +70,7 @@ def check_status(device=None) -> None:
             continue
         if int(t.item()) != 0:
             t.zero_()
+            _zero_scratch.pop(idx, None)     # a kernel that gave up may have left sums behind: start from a fresh zero scratch
             raise RuntimeError("[spira_b200] a tensor-core kernel gave up on an internal wait (status word set)")
 
 
