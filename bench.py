@@ -404,7 +404,7 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap"])
+    ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap", "gather"])
     ap.add_argument("--no-group", action="store_true", help="output-stationary maps keep their target order (no grouping by neighbour pattern)")
     ap.add_argument("--no-defer", action="store_true", help="add_all_kernel_maps completes all maps before it returns")
     ap.add_argument("--n256-min-targets", type=int, default=-1, help="layers with fewer targets use 128-target tiles (-1 = library default)")
@@ -455,11 +455,11 @@ def main():
         build.build()
         from spira_b200.nn.functional import _C as native
         native.set_option("gather_tma", 1 if args.gather == "tma" else 0)
-    if args.workload in ("layer", "kmap"):
+    if args.workload in ("layer", "kmap", "gather"):
         from spira_b200 import build, _lib
         build.build()
         _lib.load()
-        line = run_layer(args, device, pk, pk_kind) if args.workload == "layer" else run_kmap(args, device, pk, pk_kind)
+        line = {"layer": run_layer, "kmap": run_kmap, "gather": run_gather}[args.workload](args, device, pk, pk_kind)
         line["n_gpus"] = n_gpus
         if rank == 0:
             print(json.dumps(line))
@@ -697,6 +697,51 @@ def _time_calls(fn, steps, warmup, l2buf):
     torch.cuda.synchronize()
     t = [a.elapsed_time(b) for a, b in evs]
     return sum(t) / len(t), min(t)
+
+
+def run_gather(args, device, pk, pk_kind):
+    """Ceiling of the row-gather pattern of the output-stationary kernels: the neighbour rows of one 3^3 layer of a
+    LiDAR-like scene (``--cin`` channels, 64 of them = 128 bytes taken per row, like one pipeline stage) are read through
+    the library's probe kernel in four orders and folded away, nothing is written."""
+    from spira_b200 import scenes as sc, _lib
+    from spira_b200.nn.functional import _C
+    c = sc.lidar_scene(1)
+    n = len(c)
+    keys, _ = _C.cuda_flatten_sort(torch.from_numpy(c).to(device), False)
+    feats = torch.from_numpy(sc.features(n, args.cin, 0)).to(device)
+    m = _C.cuda_binary_search(keys, keys, (3, 3, 3), (1, 1, 1), 0)
+    dense, grouped = m[2][:n], m[2]._sb["grouped"].map[:n]
+    def pairs_in_tile_order(mp):           # present entries, tile by tile (256 rows), offset by offset, row by row
+        pad = (-mp.shape[0]) % 256
+        t = torch.cat([mp, mp.new_full((pad, mp.shape[1]), -1)]).view(-1, 256, mp.shape[1]).permute(0, 2, 1).reshape(-1)
+        return t[t >= 0].contiguous()
+    orders = {
+        "order of the output-stationary kernel, targets in spatial order": pairs_in_tile_order(dense),
+        "order of the output-stationary kernel, grouped map": pairs_in_tile_order(grouped),
+    }
+    nnz = int((dense >= 0).sum().item())
+    g = torch.Generator(device=device).manual_seed(0)
+    orders["random rows"] = torch.randint(0, n, (nnz,), device=device, generator=g, dtype=torch.int32)
+    orders["consecutive rows"] = (torch.arange(nnz, device=device, dtype=torch.int32) % n).contiguous()
+    taken = min(128, args.cin * 2)
+    sink = torch.zeros(16 * 1024, dtype=torch.int32, device=device)
+    l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+    stream = torch.cuda.current_stream().cuda_stream
+    results = {}
+    for name, idx in orders.items():
+        idx = idx.contiguous()
+        rows = int((idx >= 0).sum().item())
+        fn = lambda: _lib.call("spira_b200_gather_probe", feats.data_ptr(), idx.data_ptr(), idx.numel(), args.cin * 2, taken,
+                               sink.data_ptr(), stream)
+        mean_ms, min_ms = _time_calls(fn, args.steps, args.warmup, l2buf)
+        results[name] = {"rows": rows, "ms": round(mean_ms, 5), "gathered_gbs": round(rows * taken / (min_ms * 1e-3) / 1e9, 1)}
+    best = max(v["gathered_gbs"] for v in results.values())
+    return {"metric": "row gather bandwidth (bytes gathered / time, nothing written)", "value": best, "unit": "GB/s", "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": min(v["ms"] for v in results.values()), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 rows", "data": "synthetic",
+            "config": {"workload": f"gather probe: {n} voxels, rows of {args.cin * 2} bytes, {taken} bytes taken per row, {nnz} pairs of a 3^3 map",
+                       "l2": "256 MiB buffer rewritten between timed steps"},
+            "orders": results, "gpu_launches": args.steps * len(orders)}
 
 
 def run_layer(args, device, pk, pk_kind):

@@ -88,6 +88,12 @@ int spira_b200_flatten_sort(const int32_t *coords, int64_t n, int key_bytes, voi
 int spira_b200_permute_rows(const void *rows_in, const int32_t *perm, int64_t n, int64_t row_bytes, void *rows_out,
                             void *stream);
 
+/* Measurement aid (no reference counterpart): gathers bytes_taken bytes of each of n rows rows[idx[i]] (idx < 0 skipped),
+ * 16 bytes per thread on 8 x SM-count blocks of 256 threads, and folds them away (`sink`: at least 8 x SM-count words,
+ * practically never written).  Timing it gives the ceiling of the row-gather pattern of the convolution kernels. */
+int spira_b200_gather_probe(const void *rows, const int32_t *idx, int64_t n, int64_t row_bytes, int64_t bytes_taken,
+                            uint32_t *sink, void *stream);
+
 /* Scratch bytes for spira_b200_downsample with n input keys and n_levels levels. */
 int spira_b200_downsample_workspace(int64_t n, int key_bytes, int n_levels, size_t *bytes);
 
