@@ -746,7 +746,7 @@ def run_gather(args, device, pk, pk_kind):
 
 def run_layer(args, device, pk, pk_kind):
     """Single-layer workload: one submanifold 3^3 layer, c_in -> c_out, 50,000 voxels in a 512^3 grid (64-bit keys)."""
-    from spira_b200 import scenes as sc
+    from spira_b200 import scenes as sc, _lib
     from spira_b200.nn.functional import _C
     if args.scene == "c0":
         c, double = sc.planes_and_spheres(0), True
@@ -777,7 +777,25 @@ def run_layer(args, device, pk, pk_kind):
     else:
         ach = flops / (mean_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": round(ach, 2), "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": round(ach / pk["bf16_tflops"], 4), "traffic": None}
-    kernel = "conv_tc_kernel<WS>" if df else ("conv_os_n256_kernel" if args.cout <= 96 else "conv_tc_kernel<OS>")
+    kernel = "conv_tc_kernel<WS>" if df else ("conv_os_n256_kernel" if 64 < args.cout <= 96 else "conv_tc_kernel<OS>")
+    if df == 0 and m[2]._sb.get("grouped") is not None and args.cin % 8 == 0:
+        # What actually bounds the output-stationary kernels: bytes that cross from L2 into the SMs (gathered rows + one
+        # weight chunk per visited (tile, 64-wide reduction chunk) + the map), against the rate a dedicated gather probe
+        # reaches for the same access pattern, measured here.
+        stats = m[2]._sb["grouped"].stats.cpu().tolist()
+        tile_rows = 256 if kernel == "conv_os_n256_kernel" else 128
+        visited = stats[1] if tile_rows == 256 else stats[0]              # non-empty (tile, offset) pairs of the grouped map
+        xbar = nnz * args.cin * 2 + visited * (args.cin / 64.0) * args.cout * 128 + m[2].numel() * 4
+        taken = min(128, args.cin * 2)
+        idx = torch.randint(0, n, (nnz,), device=device, dtype=torch.int32)
+        sink = torch.zeros(16 * 1024, dtype=torch.int32, device=device)
+        st = torch.cuda.current_stream().cuda_stream
+        _, probe_ms = _time_calls(lambda: _lib.call("spira_b200_gather_probe", feats.data_ptr(), idx.data_ptr(), nnz, args.cin * 2, taken,
+                                                    sink.data_ptr(), st), args.steps, args.warmup, l2buf)
+        probe_gbs = nnz * taken / (probe_ms * 1e-3) / 1e9
+        roof["l2_to_sm"] = {"bytes_per_launch": int(xbar), "achieved_gbs": round(xbar / (min_ms * 1e-3) / 1e9, 1),
+                            "probe_gbs": round(probe_gbs, 1), "frac_of_probe": round(xbar / (min_ms * 1e-3) / 1e9 / probe_gbs, 3),
+                            "note": "gathered rows + weight chunks + map, over the fastest launch; probe = row gather at full occupancy"}
     # DRAM bytes per launch from an ncu capture of exactly this case (dram__bytes_read.sum + dram__bytes_write.sum)
     if args.scene == "lidar" and (args.cin, args.cout, df) == (96, 96, 0):
         roof["traffic"] = 39_471_000
