@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import argparse
 import contextlib
+import functools
 import json
 import os
 import statistics
@@ -179,6 +180,72 @@ class Engine:
         self.cache.reset()
         self.cache.add_all_kernel_maps(x._coordinates, self.ks, self.ss, self.ts, (1, 1, 1), self.dataflows)
         self.compiled = self.sp.compile_model(self.model, x, self.cache)
+
+
+def tune_reference_groups(engine, dev, start_df):
+    """Greedy per-group dataflow choice for the reference arm, by measurement (two whole-model steps per trial)."""
+    from spira_b200.nn import SparseConv
+    convs = {n: m for n, m in engine.model.named_modules() if isinstance(m, SparseConv) and not m.is_trivial}
+    seen = {}
+
+    def hook(module, inputs, output, name):
+        s = inputs[0]._stride
+        eff = tuple(a // b for a, b in zip(s, module.stride)) if module.transposed else tuple(s)
+        seen[name] = (eff, module.kernel_size, module.stride)
+
+    handles = [m.register_forward_hook(functools.partial(hook, name=n)) for n, m in convs.items()]
+    engine.step(*dev[0])
+    for h in handles:
+        h.remove()
+    groups = sorted(set(seen.values()))
+    if not groups:
+        return None
+    current = {g: start_df for g in groups}
+
+    def apply(cfg):
+        for n, m in convs.items():
+            m._tunable_config["map_dataflow"] = cfg[seen[n]]
+            m._tunable_config["force_os"] = False
+        engine.apply_groups(cfg)
+        engine.dataflows = [cfg.get((engine.ss[i], engine.ks[i], engine.layer_strides[i]), start_df) for i in range(len(engine.ks))]
+
+    def timed():
+        engine.step(*dev[0])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(2):
+            engine.step(*dev[i % len(dev)])
+        b.record()
+        b.synchronize()
+        return a.elapsed_time(b)
+
+    apply(current)
+    base = timed()
+    for g in groups:
+        for alt in (0, 1, 2):
+            if alt == current[g]:
+                continue
+            trial = dict(current)
+            trial[g] = alt
+            try:
+                apply(trial)
+                t = timed()
+            except RuntimeError:
+                ref_mod_reset()
+                continue
+            if t < 0.98 * base:
+                current, base = trial, t
+    apply(current)
+    return current
+
+
+def ref_mod_reset():
+    import spira_b200.nn.functional as F
+    try:
+        F._C.cuda_reset_error()
+    except Exception:
+        pass
 
 
 # ------------------------------------------------------------------------------------------------
@@ -535,6 +602,15 @@ def main():
                 best = (df, t)
         engine.set_uniform_dataflow(best[0])
         chosen_note = {"uniform_map_dataflow": best[0]}
+        # then, like the reference's own tuner (spira/utils/helpers.py:388-618), per layer group: every group tries the
+        # other dataflows on whole-model runs and keeps what is faster
+        try:
+            tuned = tune_reference_groups(engine, dev, best[0])
+            if tuned is not None:
+                chosen_note = {"per_group": {str(k): v for k, v in tuned.items()}, "start": best[0]}
+        except RuntimeError:
+            ref_mod.cuda_reset_error()
+            engine.set_uniform_dataflow(best[0])
 
     if args.impl == "ours" and not args.no_compile:
         engine.compile(*dev[0])
