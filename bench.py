@@ -237,6 +237,25 @@ def tune_reference_groups(engine, dev, start_df):
             if t < 0.98 * base:
                 current, base = trial, t
     apply(current)
+    # the mask-format kernels (even dataflows) also have a padding threshold per group (reference: helpers.py:468-560
+    # sweeps 52 values); a coarse sweep here
+    for g in groups:
+        if current[g] % 2 != 0 or current[g] == 0:
+            continue
+        members = [m for n, m in convs.items() if seen[n] == g]
+        best_thr = members[0]._tunable_config["threshold"]
+        for thr in (0.0, 0.5, 1.0, 2.0, None):
+            for m in members:
+                m._tunable_config["threshold"] = thr
+            try:
+                t = timed()
+            except RuntimeError:
+                ref_mod_reset()
+                continue
+            if t < 0.98 * base:
+                base, best_thr = t, thr
+        for m in members:
+            m._tunable_config["threshold"] = best_thr
     return current
 
 
