@@ -39,7 +39,7 @@ using namespace sb::ptx;
 constexpr int kRows = 128;              // MMA M / rows per tile
 constexpr int kChunk = 64;              // fp16 elements of the reduction per pipeline stage (128 bytes)
 constexpr int kABytes = kRows * 128;    // one A stage
-constexpr int kProducers = 512;          // cp.async producers: up to 4 teams of 128 threads (thread <-> tile row)
+constexpr int kProducers = 512;          // cp.async producers: teams of 128 (or 256 / 512) threads, 8 lanes per tile row
 constexpr int kProducerWarps = kProducers / 32;
 constexpr int kMmaWarp = kProducerWarps + 4;         // warps kProducerWarps .. +3 are the epilogue (warp % 4 = TMEM lane quarter)
 static_assert(kProducerWarps % 4 == 0, "epilogue warps must start at a multiple of 4");
