@@ -250,3 +250,38 @@ def test_group_policy_switches_the_grouping_off_per_map(lib):
     y1, _ = run(model, cache, coords, feats, sched, 0)
     assert all(e[3]._sb["grouped"] is None for e in cache._kernel_maps_cache.values())
     assert torch.equal(y0._features, y1._features)        # grouping never changes a result
+
+
+@pytest.mark.parametrize("dataflow", [0, 1])
+def test_network_on_64_bit_keys_matches_32_bit_keys(lib, dataflow):
+    """The key width changes how coordinates are packed, not which voxels neighbour which: the same scene ordered with
+    64-bit keys yields the same voxel order, the same maps and therefore the same features."""
+    import spira_b200 as sp
+    from spira_b200 import models, scenes, nn as spnn
+    from spira_b200.nn.functional import _C
+    torch.manual_seed(1)
+    c = scenes.lidar_scene(5)[:40000]
+    coords = torch.from_numpy(c).cuda()
+    feats = torch.from_numpy(scenes.features(len(c), 4, 5)).cuda()
+    model = models.minkunet18(4, 19, 2).cuda().half().eval()
+    cache = spnn.KernelMapCache()
+    sp.set_kernel_map_cache(model, cache)
+    ks, ss, ts = models.map_schedule(4, 3, 2)
+    for m in model.modules():
+        if hasattr(m, "_tunable_config"):
+            m._tunable_config["map_dataflow"] = dataflow
+    outs = []
+    for double in (False, True):
+        x = sp.SparseTensor(coords.clone(), feats.clone(), double=double).order()
+        assert x._coordinates.dtype == (torch.int64 if double else torch.int32)
+        cache.reset()
+        cache.add_all_kernel_maps(x._coordinates, ks, ss, ts, (1, 1, 1), [dataflow] * len(ks))
+        with torch.no_grad():
+            outs.append((model(x)._features.clone(), x._features.clone()))
+    (y32, x32), (y64, x64) = outs
+    assert torch.equal(x32, x64)                                             # same voxel order
+    if dataflow == 0:
+        assert torch.equal(y32, y64)                                         # deterministic path: bit-identical
+    else:
+        assert_features_close(y64, y32, rtol=1e-2, atol=4e-3)
+    _C.check_status()
