@@ -94,6 +94,14 @@ int spira_b200_permute_rows(const void *rows_in, const int32_t *perm, int64_t n,
 int spira_b200_gather_probe(const void *rows, const int32_t *idx, int64_t n, int64_t row_bytes, int64_t bytes_taken,
                             uint32_t *sink, void *stream);
 
+/* 1x1x1 layer with few output channels (a classification head): out[n][c_out] = feats[n][c_in] . weights[c_in][c_out]
+ * (+ bias[c_out], may be null), fp16 in and out, fp32 accumulation, one rounding.  The reference sends every 1x1x1
+ * layer to torch.mm and adds the bias in a second pass (spira/nn/conv.py:312-316); a head whose c_out is not a
+ * multiple of 8 misses the library's aligned kernels there.  c_in a multiple of 8, c_out <= 32 and
+ * c_in * roundup(c_out, 8) * 4 + 512 * c_out + 128 <= 48 KB, else SPIRA_B200_ERR_UNSUPPORTED (use the library GEMM). */
+int spira_b200_pointwise(const void *feats, const void *weights, const void *bias, int64_t n, int c_in, int c_out,
+                         void *out, void *stream);
+
 /* Scratch bytes for spira_b200_downsample with n input keys and n_levels levels. */
 int spira_b200_downsample_workspace(int64_t n, int key_bytes, int n_levels, size_t *bytes);
 
@@ -232,7 +240,8 @@ int spira_b200_conv_os(const void *feats, const void *weights, const void *packe
  * (cuda/kernels/output_stat.cuh) walks the map in target order, where almost every (tile of targets, offset) pair
  * has SOME neighbour although only ~30 % of the rows do, so most of the multiplied rows are zeros.
  * spira_b200_kmap_group sorts the rows of up to SPIRA_B200_MAX_MAPS [T_al][K] maps by their K-bit presence mask
- * (fullest first, stable) with ONE radix sort over all of them, and writes per map:
+ * (fullest first, stable; key for K <= 27: (K - popcount) << 19 | mask >> max(0, K - 19), else ~mask) with ONE radix
+ * sort over all of them, and writes per map:
  *   grouped_map [T_al][K]   row i = map row row_of[i] (rows >= num_targets: -1)
  *   row_of      [T_al]      target (output row) of grouped row i, -1 for padding rows
  *   tile_masks  [T_al/128]  bit k = some row of the 128-row tile has a neighbour at offset k

@@ -299,8 +299,9 @@ def conv_ws_transposed(feats, weights, dense_ws: np.ndarray, num_sources_of_map:
 def group_os_map(out_in_map: np.ndarray, num_targets: int):
     """Rows of an output-stationary map ``[T_al, K]`` (K <= 32) sorted by presence mask.
 
-    Key of row t: ``(K - popcount(mask)) << 27 | mask`` for K <= 27 (fullest rows first, rows with equal masks adjacent),
-    else ``~mask``; the sort is stable, so rows with the same key keep their spatial order.  Returns
+    Key of row t: ``(K - popcount(mask)) << 19 | (mask >> max(0, K - 19))`` for K <= 27 (fullest rows first, rows whose
+    masks agree in the 19 highest offsets adjacent), else ``~mask``; the sort is stable, so rows with the same key keep
+    their spatial order.  Returns
     ``(grouped_map [T_al, K], row_of [T_al], tile_masks [T_al / 128] uint32, stats (n128, n256))`` where padding rows
     are -1, ``tile_masks[i]`` has bit k set if some row of tile i has a neighbour at offset k, and the stats count the
     non-empty (tile, offset) pairs for 128- and 256-row tiles.  The convolution over the grouped map writes output row
@@ -311,7 +312,7 @@ def group_os_map(out_in_map: np.ndarray, num_targets: int):
     present = out_in_map[:num_targets] >= 0
     mask = (present.astype(np.uint64) << np.arange(K, dtype=np.uint64)).sum(1)
     if K <= 27:
-        key = ((K - present.sum(1)).astype(np.uint64) << np.uint64(27)) | mask
+        key = ((K - present.sum(1)).astype(np.uint64) << np.uint64(19)) | (mask >> np.uint64(max(0, K - 19)))
     else:
         key = (~mask) & np.uint64(0xFFFFFFFF)
     order = np.argsort(key, kind="stable").astype(np.int32)

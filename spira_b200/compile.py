@@ -122,6 +122,12 @@ class CompiledModel:
                 x = slots[i]
                 if module._trivial:
                     folded = module._folded
+                    if module.out_channels <= 32:
+                        y = _C.pointwise(x, *(folded if folded is not None else
+                                              (module.kernel.view(module.in_channels, module.out_channels), module.bias)))
+                        if y is not None:
+                            slots[o] = y
+                            continue
                     if folded is not None:
                         slots[o] = torch.addmm(folded[1], x, folded[0])
                     else:

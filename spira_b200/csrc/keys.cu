@@ -268,9 +268,9 @@ inline bool strides_double(int n_levels, const int32_t *strides) {
 template <typename KeyT>
 int downsample_sorted_impl(const KeyT *keys, int64_t n, int n_levels, const int32_t *strides, void *const *out_keys,
                            int32_t *counts, void *ws, size_t ws_bytes, int32_t *status, cudaStream_t stream) {
-  // workspace: [vals n][flags n][cub temp]
+  // workspace: [vals n][flags n, one array per level so that ONE memset clears them all][cub temp]
   const size_t temp = select_flagged_temp<KeyT>(n);
-  const size_t need = round256(n * sizeof(KeyT)) + round256(n) + temp;
+  const size_t need = round256(n * sizeof(KeyT)) + SPIRA_B200_MAX_LEVELS * round256(n) + temp;
   if (ws_bytes < need) return fail(SPIRA_B200_ERR_WORKSPACE, "downsample_sorted: workspace %zu < %zu bytes", ws_bytes, need);
   if (n == 0) {
     SB_CHECK_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_levels, stream));
@@ -278,15 +278,16 @@ int downsample_sorted_impl(const KeyT *keys, int64_t n, int n_levels, const int3
   }
   char *base = static_cast<char *>(ws);
   KeyT *vals = reinterpret_cast<KeyT *>(base);
-  unsigned char *flags = reinterpret_cast<unsigned char *>(base + round256(n * sizeof(KeyT)));
-  void *temp_ptr = base + round256(n * sizeof(KeyT)) + round256(n);
+  unsigned char *all_flags = reinterpret_cast<unsigned char *>(base + round256(n * sizeof(KeyT)));
+  void *temp_ptr = base + round256(n * sizeof(KeyT)) + SPIRA_B200_MAX_LEVELS * round256(n);
   int prev[3] = {1, 1, 1};
   const KeyT *in = keys;
   const int32_t *n_dev = nullptr;
   if (status) SB_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+  SB_CHECK_CUDA(cudaMemsetAsync(all_flags, 0, n_levels * round256(n), stream));
   for (int l = 0; l < n_levels; ++l) {
     const int32_t *s = strides + 3 * l;
-    SB_CHECK_CUDA(cudaMemsetAsync(flags, 0, n, stream));
+    unsigned char *flags = all_flags + l * round256(n);
     // level sizes beyond the first are only known on the device: launch for the upper bound n
     coarsen_rank_kernel<KeyT><<<static_cast<int>(div_up(n, 256)), 256, 0, stream>>>(
         in, n_dev, static_cast<int>(n), prev[0], prev[1], prev[2], s[0] / prev[0], s[1] / prev[1], s[2] / prev[2], vals, flags,
@@ -414,7 +415,9 @@ extern "C" int spira_b200_downsample(const void *keys, int64_t n, int key_bytes,
 extern "C" int spira_b200_downsample_sorted_workspace(int64_t n, int key_bytes, size_t *bytes) {
   SB_CHECK_ARG(bytes != nullptr, "downsample_sorted_workspace: null output");
   SB_CHECK_ARG(n >= 0 && n < (int64_t(1) << 31), "downsample_sorted: n=%lld out of range", (long long)n);
-  SB_KEY_DISPATCH(key_bytes, { *bytes = round256(n * sizeof(KeyT)) + round256(n) + select_flagged_temp<KeyT>(n) + 256; })
+  SB_KEY_DISPATCH(key_bytes, {
+    *bytes = round256(n * sizeof(KeyT)) + SPIRA_B200_MAX_LEVELS * round256(n) + select_flagged_temp<KeyT>(n) + 256;
+  })
   return SPIRA_B200_OK;
 }
 

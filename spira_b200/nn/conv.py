@@ -327,6 +327,13 @@ class SparseConv(Module):
     def _forward(self, inputs: SparseTensor, residual: Optional[torch.Tensor] = None):
         source_features = inputs._features
         if self.is_trivial:
+            pointwise = getattr(_C, "pointwise", None)       # (absent when a reference-built binding is installed)
+            if pointwise is not None and self.out_channels <= 32 and not torch.is_grad_enabled():
+                # a head with few output channels runs the engine's own kernel (bias included)
+                w, b = self._folded if self._folded is not None else (self.kernel.view(self.in_channels, self.out_channels), self.bias)
+                y = pointwise(source_features, w, b)
+                if y is not None:
+                    return SparseTensor(features=y, coordinates=inputs._coordinates, stride=inputs._stride)
             if self._folded is not None:
                 return SparseTensor(features=torch.addmm(self._folded[1], source_features, self._folded[0]),
                                     coordinates=inputs._coordinates, stride=inputs._stride)

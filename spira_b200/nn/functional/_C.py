@@ -910,6 +910,38 @@ def run_conv_os(call: ConvCall, num_sources: int, num_targets: int, out_in_map: 
     return out
 
 
+POINTWISE_HEAD = True   # 1x1x1 layers with at most 32 output channels run the engine's own kernel
+
+
+def pointwise(feats: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """``feats @ weight (+ bias)`` for a 1x1x1 layer with few output channels (``weight`` ``[c_in, c_out]``), or ``None``
+    when the layer is outside what ``spira_b200_pointwise`` takes (the caller then uses the library GEMM, like the
+    reference: spira/nn/conv.py:312-316)."""
+    c_in, c_out = weight.shape
+    if not POINTWISE_HEAD or c_out > 32 or c_in % 8 != 0 or c_in < 8 or not feats.is_cuda or feats.dtype != torch.float16 \
+            or weight.dtype != torch.float16 or (bias is not None and bias.dtype != torch.float16) \
+            or c_in * ((c_out + 7) // 8 * 8) * 4 + 512 * c_out + 128 > 48 * 1024:
+        return None
+    if not feats.is_contiguous():
+        feats = feats.contiguous()
+    if not weight.is_contiguous():
+        weight = weight.contiguous()
+    n = feats.shape[0]
+    out = torch.empty((n, c_out), dtype=torch.float16, device=feats.device)
+    idx = feats.device.index if feats.device.index is not None else torch.cuda.current_device()
+    args = (feats.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, n, c_in, c_out,
+            out.data_ptr(), _raw_stream(idx))
+    fn = _lib.load().spira_b200_pointwise
+    if _lib.profile_hook is not None:
+        _lib.profile_hook("spira_b200_pointwise", args, lambda: _lib.check(fn(*args)))
+    else:
+        rc = fn(*args)
+        if rc != 0:
+            _lib.check(rc)
+    _lib.launch_count += 1
+    return out
+
+
 _zero_scratch = {}      # device index -> fp32 tensor that holds zeros whenever no weight-stationary call is in flight
 
 
