@@ -497,6 +497,8 @@ def main():
     ap.add_argument("--no-n256", action="store_true", help="output-stationary layers always use the targets-as-M kernel")
     ap.add_argument("--team-threads", type=int, default=0, choices=[0, 128, 256, 512],
                     help="producer threads per pipeline stage of the exchanged-operand kernel (0 = library default)")
+    ap.add_argument("--stem-variant", type=int, default=-1, choices=[-1, 0, 1, 2],
+                    help="narrow-input (stem) kernel: 0 offset by offset (library default), 1 row loads in batches, 2 two targets per thread")
     ap.add_argument("--gather", default="default", choices=["default", "tma", "cpasync"], help="row-gather engine of the tensor-core kernels")
     ap.add_argument("--cin", type=int, default=64)
     ap.add_argument("--cout", type=int, default=64)
@@ -536,6 +538,9 @@ def main():
     if args.impl == "ours" and args.team_threads:
         from spira_b200.nn.functional import _C as native_
         native_.set_option("os_team_threads", args.team_threads)
+    if args.impl == "ours" and args.stem_variant >= 0:
+        from spira_b200.nn.functional import _C as native_
+        native_.set_option("stem_variant", args.stem_variant)
     if args.impl == "ours" and args.gather != "default":
         from spira_b200 import build
         build.build()

@@ -61,6 +61,9 @@ int spira_b200_read_back(const void *device_src, void *pinned_dst, size_t bytes,
  *                       applies: with few tiles per SM the heaviest tile sets the time and smaller tiles balance better
  *   "os_team_threads"   128 (default), 256 or 512: producer threads that fill one pipeline stage of that kernel
  *                       together (4, 2 or 1 teams); measured equal within noise for 128 and 256, slower for 512
+ *   "stem_variant"      narrow-input layers (c_in <= 8) on the one-thread-per-target kernel: 0 (default) offset by
+ *                       offset, 1 the row loads of nine offsets issued together, 2 two targets per thread (measured
+ *                       28.7 / 30.8 / 33.4 us on a 4 -> 32 stem over 127 k voxels)
  * get_option additionally answers "os_pack_mode": the SPIRA_B200_PACK_* image spira_b200_conv_os expects under
  * the current options.  Unknown names: set_option fails, get_option returns -1. */
 int spira_b200_set_option(const char *name, int value);
@@ -248,7 +251,10 @@ int spira_b200_conv_os(const void *feats, const void *weights, const void *packe
  *   stats       [2]         number of non-empty (128-row tile, offset) and (256-row tile, offset) pairs
  * The workspace size depends on the number of rows of all maps of the call together.
  * spira_b200_conv_os_grouped computes the same result as spira_b200_conv_os on the original map, bit for bit (a
- * skipped chunk only contributes zeros), and visits only the chunks named by the tile masks. */
+ * skipped chunk only contributes zeros), and visits only the chunks named by the tile masks.  `weights` and `packed`
+ * as for spira_b200_conv_os; without a packed image (a layer outside the tensor-core kernels) only the narrow-input
+ * case c_in <= 8, c_out in {16, 32, 64} is covered (one thread per row: grouped rows let the lanes of a warp skip the
+ * same offsets), anything else is SPIRA_B200_ERR_ARGUMENT. */
 typedef struct spira_b200_group_desc {
   const int32_t *map_os; /* [T_al][K], T_al = num_targets rounded up to 128 */
   int64_t num_targets;   /* > 0 */
@@ -261,10 +267,10 @@ typedef struct spira_b200_group_desc {
 int spira_b200_kmap_group_workspace(int64_t total_targets, size_t *bytes);
 int spira_b200_kmap_group(const spira_b200_group_desc *descs, int n_maps, void *workspace, size_t workspace_bytes,
                           void *stream);
-int spira_b200_conv_os_grouped(const void *feats, const void *packed, const spira_b200_epilogue *epilogue,
-                               const int32_t *grouped_map, const int32_t *row_of, const uint32_t *tile_masks,
-                               int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out, void *out,
-                               int32_t *status, void *stream);
+int spira_b200_conv_os_grouped(const void *feats, const void *weights, const void *packed,
+                               const spira_b200_epilogue *epilogue, const int32_t *grouped_map, const int32_t *row_of,
+                               const uint32_t *tile_masks, int64_t num_sources, int64_t num_targets, int K, int c_in,
+                               int c_out, void *out, int32_t *status, void *stream);
 
 /* Weight-stationary gather-GEMM-scatter over compacted pair lists: for row k and pair p in
  * [naddrs[k], naddrs[k+1]):  accum[out_idx[p]][:] += feats[in_idx[p]][:] @ W[k].  With

@@ -81,8 +81,8 @@ SIGNATURES = {
                            c_int, c_void_p, c_void_p, c_void_p],
     "spira_b200_kmap_group_workspace": [c_int64, C.POINTER(c_size_t)],
     "spira_b200_kmap_group": [C.POINTER(GroupDesc), c_int, c_void_p, c_size_t, c_void_p],
-    "spira_b200_conv_os_grouped": [c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_int64, c_int64,
-                                   c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "spira_b200_conv_os_grouped": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_int64,
+                                   c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "spira_b200_conv_ws": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                            c_void_p, c_void_p],

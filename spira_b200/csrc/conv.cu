@@ -1029,62 +1029,134 @@ __global__ void __launch_bounds__(128) conv_os_simt_kernel(const __half *__restr
 
 
 // Output-stationary kernel for the network stems (3-8 input channels, 16/32/64 output channels): far too little
-// arithmetic for the tensor cores and rows too short for 16-byte gathers.  One thread per target keeps all COUT
-// accumulators in registers; the weights sit in shared memory as fp32 and are read as broadcast float4; the tile's map
-// slab is staged with coalesced 16-byte loads.
-template <int COUT>
+// arithmetic for the tensor cores and rows too short for 16-byte gathers.  One thread keeps all COUT accumulators of
+// ROWS targets (rows tid, tid + 128, ... of the block's tile) in registers; the weights sit in shared memory as fp32
+// and are read as broadcast float4; the tile's map slab is staged with coalesced 16-byte loads; the row loads of
+// BATCH offsets are issued together.  On a grouped map (rows sorted by neighbour pattern) the lanes of a warp skip
+// the same offsets: 36 -> 26 us on the 4 -> 32 stem of a 127 k-voxel scene.  ROWS = BATCH = 1 is the default: more
+// rows per thread or more loads in flight cost registers and shared memory, and the resident warps they displace
+// were worth more (see the launch code).
+template <int COUT, int ROWS, int BATCH>
 __global__ void __launch_bounds__(128) conv_os_stem_kernel(const __half *__restrict__ feats, const __half *__restrict__ w,
-                                                            Epilogue ep, const int32_t *__restrict__ map, int64_t T, int K,
+                                                            Epilogue ep, const int32_t *__restrict__ map,
+                                                            const int32_t *__restrict__ row_of, int64_t T, int K,
                                                             int c_in, __half *__restrict__ out) {
   extern __shared__ __align__(16) unsigned char stem_smem[];
   float *ws = reinterpret_cast<float *>(stem_smem);                              // [K][c_in][COUT]
-  int32_t *slab = reinterpret_cast<int32_t *>(stem_smem + static_cast<size_t>(K) * c_in * COUT * 4);   // [128][K]
+  int32_t *slab = reinterpret_cast<int32_t *>(stem_smem + static_cast<size_t>(K) * c_in * COUT * 4);   // [128 * ROWS][K]
   const int tid = threadIdx.x;
-  for (int i = tid; i < K * c_in * COUT; i += 128) ws[i] = __half2float(w[i]);
-  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * 128;
-  const int4 *s4 = reinterpret_cast<const int4 *>(map + t0 * K);                 // the map has T_al rows: always in range
-  for (int i = tid; i < 32 * K; i += 128) reinterpret_cast<int4 *>(slab)[i] = s4[i];
+  if (reinterpret_cast<uintptr_t>(w) % 16 == 0) {                               // (COUT is a multiple of 16: whole 8-value groups)
+    for (int i = tid; i < K * c_in * COUT / 8; i += 128) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(w) + i);
+      const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f2 = __half22float2(h[e]);
+        ws[8 * i + 2 * e] = f2.x;
+        ws[8 * i + 2 * e + 1] = f2.y;
+      }
+    }
+  } else {
+    for (int i = tid; i < K * c_in * COUT; i += 128) ws[i] = __half2float(w[i]);
+  }
+  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * (128 * ROWS);
+  // the map has T_al rows (T rounded up to 128): the last tile may hold fewer than 128 * ROWS of them
+  const int64_t T_al = (T + 127) / 128 * 128;
+  const int rows_here = static_cast<int>(T_al - t0 < 128 * ROWS ? T_al - t0 : 128 * ROWS);
+  const int4 *s4 = reinterpret_cast<const int4 *>(map + t0 * K);
+  const int valid4 = rows_here * K / 4;                                         // (rows_here is a multiple of 128)
+  for (int i = tid; i < 32 * ROWS * K; i += 128)
+    reinterpret_cast<int4 *>(slab)[i] = i < valid4 ? s4[i] : make_int4(-1, -1, -1, -1);
   __syncthreads();
-  const int64_t t = t0 + tid;
-  float acc[COUT];
+  float acc[ROWS][COUT];
 #pragma unroll
-  for (int co = 0; co < COUT; ++co) acc[co] = 0.f;
-  for (int k = 0; k < K; ++k) {
-    const int idx = slab[tid * K + k];
-    if (idx < 0) continue;
-    const __half *f = feats + static_cast<int64_t>(idx) * c_in;
-    const float4 *wk = reinterpret_cast<const float4 *>(ws + static_cast<size_t>(k) * c_in * COUT);
-    for (int ci = 0; ci < c_in; ++ci) {
-      const float x = __half2float(f[ci]);
+  for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-      for (int c4 = 0; c4 < COUT / 4; ++c4) {
-        const float4 wv = wk[ci * (COUT / 4) + c4];
-        acc[4 * c4 + 0] = fmaf(x, wv.x, acc[4 * c4 + 0]);
-        acc[4 * c4 + 1] = fmaf(x, wv.y, acc[4 * c4 + 1]);
-        acc[4 * c4 + 2] = fmaf(x, wv.z, acc[4 * c4 + 2]);
-        acc[4 * c4 + 3] = fmaf(x, wv.w, acc[4 * c4 + 3]);
+    for (int co = 0; co < COUT; ++co) acc[r][co] = 0.f;
+  // Offsets in batches of BATCH: first all row loads of the batch (independent of one another, so that a target with
+  // many neighbours waits for K / BATCH round trips to L2 instead of K), then the arithmetic in offset order.
+  for (int k0 = 0; k0 < K; k0 += BATCH) {
+    int idx[BATCH][ROWS];
+    uint4 raw[BATCH][ROWS];
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j)
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) idx[j][r] = (k0 + j < K) ? slab[(tid + 128 * r) * K + k0 + j] : -1;
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j) {
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        raw[j][r] = make_uint4(0, 0, 0, 0);
+        if (idx[j][r] < 0) continue;
+        const __half *f = feats + static_cast<int64_t>(idx[j][r]) * c_in;
+        // the row in one load where its size allows it (4 channels: 8 bytes, 8 channels: 16 bytes)
+        if (c_in == 4) {
+          const uint2 v = __ldg(reinterpret_cast<const uint2 *>(f));
+          raw[j][r].x = v.x; raw[j][r].y = v.y;
+        } else if (c_in == 8) {
+          raw[j][r] = __ldg(reinterpret_cast<const uint4 *>(f));
+        } else {
+          __half *xs = reinterpret_cast<__half *>(&raw[j][r]);
+#pragma unroll
+          for (int ci = 0; ci < 8; ++ci)
+            if (ci < c_in) xs[ci] = f[ci];
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j) {
+      bool any = false;
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) any = any || idx[j][r] >= 0;
+      if (!any) continue;
+      const float4 *wk = reinterpret_cast<const float4 *>(ws + static_cast<size_t>(k0 + j) * c_in * COUT);
+#pragma unroll
+      for (int ci = 0; ci < 8; ++ci) {
+        if (ci >= c_in) break;
+        float x[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) x[r] = __half2float(reinterpret_cast<const __half *>(&raw[j][r])[ci]);
+#pragma unroll
+        for (int c4 = 0; c4 < COUT / 4; ++c4) {
+          const float4 wv = wk[ci * (COUT / 4) + c4];
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) {
+            if (idx[j][r] < 0) continue;
+            acc[r][4 * c4 + 0] = fmaf(x[r], wv.x, acc[r][4 * c4 + 0]);
+            acc[r][4 * c4 + 1] = fmaf(x[r], wv.y, acc[r][4 * c4 + 1]);
+            acc[r][4 * c4 + 2] = fmaf(x[r], wv.z, acc[r][4 * c4 + 2]);
+            acc[r][4 * c4 + 3] = fmaf(x[r], wv.w, acc[r][4 * c4 + 3]);
+          }
+        }
       }
     }
   }
-  if (t >= T) return;
-  __half *dst = out + t * COUT;
-  const __half *res = ep.residual ? ep.residual + t * COUT : nullptr;
 #pragma unroll
-  for (int c8 = 0; c8 < COUT / 8; ++c8) {
-    uint4 pack, rv = make_uint4(0, 0, 0, 0);
-    if (res) rv = *reinterpret_cast<const uint4 *>(res + 8 * c8);
-    const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
-    uint32_t *pw = reinterpret_cast<uint32_t *>(&pack);
+  for (int r = 0; r < ROWS; ++r) {
+    const int64_t t = t0 + tid + 128 * r;
+    // a grouped map names the output row of each of its rows; its padding rows carry -1
+    int64_t out_row = -1;
+    if (t < T_al) out_row = row_of != nullptr ? static_cast<int64_t>(row_of[t]) : (t < T ? t : -1);
+    if (out_row < 0) continue;
+    __half *dst = out + out_row * COUT;
+    const __half *res = ep.residual ? ep.residual + out_row * COUT : nullptr;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int co = 8 * c8 + 2 * e;
-      float v0 = epilogue_apply(acc[co], co, ep), v1 = epilogue_apply(acc[co + 1], co + 1, ep);
-      if (res) { v0 += __low2float(rh[e]); v1 += __high2float(rh[e]); }
-      if (ep.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
-      const __half2 hv = __floats2half2_rn(v0, v1);
-      pw[e] = *reinterpret_cast<const uint32_t *>(&hv);
+    for (int c8 = 0; c8 < COUT / 8; ++c8) {
+      uint4 pack, rv = make_uint4(0, 0, 0, 0);
+      if (res) rv = *reinterpret_cast<const uint4 *>(res + 8 * c8);
+      const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+      uint32_t *pw = reinterpret_cast<uint32_t *>(&pack);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int co = 8 * c8 + 2 * e;
+        float v0 = epilogue_apply(acc[r][co], co, ep), v1 = epilogue_apply(acc[r][co + 1], co + 1, ep);
+        if (res) { v0 += __low2float(rh[e]); v1 += __high2float(rh[e]); }
+        if (ep.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
+        const __half2 hv = __floats2half2_rn(v0, v1);
+        pw[e] = *reinterpret_cast<const uint32_t *>(&hv);
+      }
+      *reinterpret_cast<uint4 *>(dst + 8 * c8) = pack;
     }
-    *reinterpret_cast<uint4 *>(dst + 8 * c8) = pack;
   }
 }
 
@@ -1274,6 +1346,7 @@ static size_t plan_smem_n256(ConvN2Params &P, int teams) {
 
 static int g_os_n256 = 1;          // 1: layers with 64 < c_out <= 128 use the exchanged-operand kernel
 static int g_os_team_threads = 128;   // producer threads per stage of that kernel: 128, 256 or 512
+static int g_stem_variant = 0;        // stem kernel: 0 offset by offset, 1 row loads in batches, 2 two targets per thread
 static int g_os_n256_min_targets = 0; // layers with fewer targets use the 128-target tiles (finer load balance)
 
 }  // namespace sb
@@ -1321,23 +1394,34 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
   SB_CHECK_ARG((ep.scale == nullptr) == (ep.shift == nullptr), "conv_os: scale and shift must be given together");
   if (packed == nullptr) {
     SB_CHECK_ARG(weights != nullptr, "conv_os: neither weights nor a packed image given");
-    SB_CHECK_ARG(row_of == nullptr, "conv_os: a grouped map needs the packed weight image (tensor-core eligible layer)");
-    const size_t stem_smem = static_cast<size_t>(K) * c_in * c_out * 4 + static_cast<size_t>(128) * K * 4;
+    // g_stem_variant (option "stem_variant", a measurement aid): 0 (default) one target per thread and offset by offset,
+    // 1 one target per thread with the row loads in batches of 9, 2 two targets per thread offset by offset.  Measured
+    // on the 4 -> 32 stem of a 127 k-voxel scene: 28.7 / 30.8 / 33.4 us -- the variant with the most resident warps wins.
+    const int variant = (c_out <= 32) ? g_stem_variant : (g_stem_variant == 2 ? 1 : g_stem_variant);
+    const int stem_rows = variant == 2 ? 2 : 1;
+    const size_t stem_smem = static_cast<size_t>(K) * c_in * c_out * 4 + static_cast<size_t>(128) * stem_rows * K * 4;
     const bool aligned16 = reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(map_os) % 16 == 0 &&
                            (ep.residual == nullptr || reinterpret_cast<uintptr_t>(ep.residual) % 16 == 0);
     if (c_in <= 8 && (c_out == 16 || c_out == 32 || c_out == 64) && stem_smem <= 96 * 1024 && aligned16) {
-      const unsigned grid = static_cast<unsigned>(div_up(num_targets, 128));
+      const unsigned grid = static_cast<unsigned>(div_up(num_targets, 128 * stem_rows));
       auto launch = [&](auto kernel) -> int {
         SB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(stem_smem)));
         kernel<<<grid, 128, stem_smem, as_stream(stream)>>>(static_cast<const __half *>(feats), static_cast<const __half *>(weights),
-                                                            ep, map_os, num_targets, K, c_in, static_cast<__half *>(out));
+                                                            ep, map_os, row_of, num_targets, K, c_in, static_cast<__half *>(out));
         SB_CHECK_LAUNCH();
         return SPIRA_B200_OK;
       };
-      if (c_out == 16) return launch(conv_os_stem_kernel<16>);
-      if (c_out == 32) return launch(conv_os_stem_kernel<32>);
-      return launch(conv_os_stem_kernel<64>);
+      if (variant == 2) return c_out == 16 ? launch(conv_os_stem_kernel<16, 2, 1>) : launch(conv_os_stem_kernel<32, 2, 1>);
+      if (variant == 0) {
+        if (c_out == 16) return launch(conv_os_stem_kernel<16, 1, 1>);
+        if (c_out == 32) return launch(conv_os_stem_kernel<32, 1, 1>);
+        return launch(conv_os_stem_kernel<64, 1, 1>);
+      }
+      if (c_out == 16) return launch(conv_os_stem_kernel<16, 1, 9>);
+      if (c_out == 32) return launch(conv_os_stem_kernel<32, 1, 9>);
+      return launch(conv_os_stem_kernel<64, 1, 9>);
     }
+    SB_CHECK_ARG(row_of == nullptr, "conv_os_grouped: without a packed weight image only c_in <= 8 with c_out 16, 32 or 64 is covered");
     conv_os_simt_kernel<<<static_cast<unsigned>(div_up(num_targets, 4)), 128, 0, as_stream(stream)>>>(
         static_cast<const __half *>(feats), static_cast<const __half *>(weights), ep, map_os, num_targets, K, c_in, c_out,
         static_cast<__half *>(out));
@@ -1410,13 +1494,14 @@ extern "C" int spira_b200_conv_os(const void *feats, const void *weights, const 
                       out, status, stream);
 }
 
-extern "C" int spira_b200_conv_os_grouped(const void *feats, const void *packed, const spira_b200_epilogue *epilogue,
-                                          const int32_t *grouped_map, const int32_t *row_of, const uint32_t *tile_masks,
-                                          int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out,
-                                          void *out, int32_t *status, void *stream) {
-  SB_CHECK_ARG(num_targets == 0 || (row_of && tile_masks && packed), "conv_os_grouped: null pointer");
+extern "C" int spira_b200_conv_os_grouped(const void *feats, const void *weights, const void *packed,
+                                          const spira_b200_epilogue *epilogue, const int32_t *grouped_map,
+                                          const int32_t *row_of, const uint32_t *tile_masks, int64_t num_sources,
+                                          int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status,
+                                          void *stream) {
+  SB_CHECK_ARG(num_targets == 0 || (row_of && tile_masks && (packed || weights)), "conv_os_grouped: null pointer");
   SB_CHECK_ARG(K <= 32, "conv_os_grouped: K=%d, grouped maps have at most 32 offsets", K);
-  return conv_os_impl(feats, nullptr, packed, epilogue, grouped_map, row_of, tile_masks, num_sources, num_targets, K, c_in,
+  return conv_os_impl(feats, weights, packed, epilogue, grouped_map, row_of, tile_masks, num_sources, num_targets, K, c_in,
                       c_out, out, status, stream);
 }
 
@@ -1520,6 +1605,7 @@ extern "C" int spira_b200_set_option(const char *name, int value) {
   if (std::strcmp(name, "gather_tma") == 0) { g_gather_tma = value ? 1 : 0; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_n256") == 0) { g_os_n256 = value ? 1 : 0; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_n256_min_targets") == 0) { g_os_n256_min_targets = value < 0 ? 0 : value; return SPIRA_B200_OK; }
+  if (std::strcmp(name, "stem_variant") == 0) { g_stem_variant = (value < 0 || value > 2) ? 0 : value; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_team_threads") == 0) {
     SB_CHECK_ARG(value == 128 || value == 256 || value == 512, "set_option: os_team_threads must be 128, 256 or 512");
     g_os_team_threads = value;
@@ -1534,6 +1620,7 @@ extern "C" int spira_b200_get_option(const char *name) {
   if (std::strcmp(name, "os_n256") == 0) return g_os_n256;
   if (std::strcmp(name, "os_team_threads") == 0) return g_os_team_threads;
   if (std::strcmp(name, "os_n256_min_targets") == 0) return g_os_n256_min_targets;
+  if (std::strcmp(name, "stem_variant") == 0) return g_stem_variant;
   if (std::strcmp(name, "os_pack_mode") == 0) return g_gather_tma ? SPIRA_B200_PACK_WS : SPIRA_B200_PACK_OS;
   return -1;
 }

@@ -770,8 +770,8 @@ def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None
     ep, keep = _epilogue(bias, scale, shift, residual, relu)
     sb = getattr(out_in_map, "_sb", None)
     g = sb.get("grouped") if (sb is not None and grouped and GROUP_OS) else None
-    if g is not None and packed is not None:
-        _lib.call("spira_b200_conv_os_grouped", _ptr(sources), _ptr(packed), C.byref(ep) if ep is not None else None, g.map_ptr,
+    if g is not None and (packed is not None or _stem_shape(cin, cout, K)):
+        _lib.call("spira_b200_conv_os_grouped", _ptr(sources), _ptr(weights), _ptr(packed), C.byref(ep) if ep is not None else None, g.map_ptr,
                   g.row_of_ptr, g.tile_masks_ptr, int(num_sources), int(num_targets), K, cin, cout, _ptr(out),
                   _ptr(status_word(sources.device)), _stream(sources.device))
         return out
@@ -822,12 +822,17 @@ def _no_call():
     return None
 
 
+def _stem_shape(cin: int, cout: int, K: int) -> bool:
+    """Narrow-input layers (network stems) that the one-thread-per-row kernel covers, also on grouped maps."""
+    return cin <= 8 and cout in (16, 32, 64) and K * cin * cout * 4 + 128 * (2 if cout <= 32 else 1) * K * 4 <= 96 * 1024
+
+
 class ConvCall:
     """Everything about one layer that does not change between forwards: the packed weight images, the epilogue
     struct, the resolved C functions.  ``SparseConv`` keeps one and the two ``run_*`` functions below add only the
     per-call pointers, so that a forward costs a few microseconds of Python per layer."""
     __slots__ = ("stamp", "weights", "K", "cin", "cout", "w_ptr", "packed", "ep", "ep_ref", "keep", "dev_index", "status",
-                 "status_ptr", "fn_os", "fn_ws", "fn_os_grouped", "fn_ws_fused", "eligible")
+                 "status_ptr", "fn_os", "fn_ws", "fn_os_grouped", "fn_ws_fused", "eligible", "stem")
 
     def __init__(self, weights: torch.Tensor, bias, fused):
         lib = _lib.load()
@@ -837,6 +842,7 @@ class ConvCall:
         self.K, self.cin, self.cout = weights.shape
         self.w_ptr = weights.data_ptr()
         self.eligible = bool(lib.spira_b200_tensor_core_eligible(self.K, self.cin, self.cout))
+        self.stem = not self.eligible and _stem_shape(self.cin, self.cout, self.K)
         self.packed = {}
         scale = shift = None
         relu = False
@@ -891,9 +897,9 @@ def run_conv_os(call: ConvCall, num_sources: int, num_targets: int, out_in_map: 
     mode = _pack_mode[0]
     if mode < 0:
         mode = _pack_mode[0] = _lib.load().spira_b200_get_option(b"os_pack_mode")
-    if g is not None and call.eligible and GROUP_OS:
+    if g is not None and (call.eligible or call.stem) and GROUP_OS:
         name, fn = "spira_b200_conv_os_grouped", call.fn_os_grouped
-        args = (feats.data_ptr(), call.packed_ptr(mode), call.ep_ref, g.map_ptr, g.row_of_ptr, g.tile_masks_ptr,
+        args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(mode), call.ep_ref, g.map_ptr, g.row_of_ptr, g.tile_masks_ptr,
                 num_sources, num_targets, call.K, call.cin, call.cout, out.data_ptr(), call.status_ptr,
                 _raw_stream(call.dev_index))
     else:

@@ -219,7 +219,8 @@ def test_grouping_reorders_the_map_without_changing_it(C, scene):
         assert tm.sum() < 0.8 * (dense[:Tal].reshape(-1, 128, 27) >= 0).any(1).sum()
 
 
-@pytest.mark.parametrize("cin,cout", [(32, 32), (64, 64), (96, 96), (128, 96), (128, 128), (256, 256), (64, 48), (24, 16)])
+@pytest.mark.parametrize("cin,cout", [(32, 32), (64, 64), (96, 96), (128, 96), (128, 128), (256, 256), (64, 48), (24, 16),
+                                      (4, 32), (3, 32), (5, 16), (8, 64)])      # (the last four: network stems)
 def test_grouped_convolution_is_bit_identical(C, scene, cin, cout):
     keys, down = scene
     rng = np.random.default_rng(cin + cout)
@@ -293,7 +294,8 @@ def test_fused_weight_stationary_call_without_pairs(C):
 
 # ---- kernel variants selected by run-time options give the same results ----------------------------------------------
 @pytest.mark.parametrize("option,value", [("os_n256", 0), ("os_team_threads", 256), ("os_team_threads", 512),
-                                          ("os_n256_min_targets", 1 << 30), ("gather_tma", 1)])
+                                          ("os_n256_min_targets", 1 << 30), ("gather_tma", 1), ("stem_variant", 1),
+                                          ("stem_variant", 2)])
 def test_kernel_variants_agree_with_the_default(C, scene, option, value):
     keys, down = scene
     tk, td = keys_to_torch(keys), keys_to_torch(down)
@@ -302,7 +304,7 @@ def test_kernel_variants_agree_with_the_default(C, scene, option, value):
     m_dn = C.cuda_binary_search(tk, td, (3, 3, 3), (1, 1, 1), 0)
     m_ws = C.cuda_binary_search(tk, tk, (3, 3, 3), (1, 1, 1), 1)
     cases = []
-    for cin, cout in ((64, 64), (96, 96), (128, 96), (32, 128)):
+    for cin, cout in ((64, 64), (96, 96), (128, 96), (32, 128), (4, 32), (5, 16), (3, 64)):
         f, w = tensors(n, cin, cout, 27, cin + 3 * cout)
         cases.append((f.cuda(), w.cuda()))
 
