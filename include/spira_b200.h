@@ -100,8 +100,8 @@ int spira_b200_gather_probe(const void *rows, const int32_t *idx, int64_t n, int
 /* 1x1x1 layer with few output channels (a classification head): out[n][c_out] = feats[n][c_in] . weights[c_in][c_out]
  * (+ bias[c_out], may be null), fp16 in and out, fp32 accumulation, one rounding.  The reference sends every 1x1x1
  * layer to torch.mm and adds the bias in a second pass (spira/nn/conv.py:312-316); a head whose c_out is not a
- * multiple of 8 misses the library's aligned kernels there.  c_in a multiple of 8, c_out <= 32 and
- * c_in * roundup(c_out, 8) * 4 + 512 * c_out + 128 <= 48 KB, else SPIRA_B200_ERR_UNSUPPORTED (use the library GEMM). */
+ * multiple of 8 misses the library's aligned kernels there.  c_in a multiple of 8 up to 512 and c_out <= 32, else
+ * SPIRA_B200_ERR_UNSUPPORTED (use the library GEMM). */
 int spira_b200_pointwise(const void *feats, const void *weights, const void *bias, int64_t n, int c_in, int c_out,
                          void *out, void *stream);
 

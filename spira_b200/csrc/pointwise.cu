@@ -2,83 +2,111 @@
 //
 // The reference sends every 1x1x1 layer to torch.mm (spira/nn/conv.py:312-316).  For a head with e.g. 19 classes the
 // library GEMM cannot use its aligned kernels (c_out is not a multiple of 8) and a separate element-wise kernel adds
-// the bias.  The layer reads n*c_in*2 bytes and writes n*c_out*2: it is bound by HBM, not by arithmetic, so plain
-// fp32 FMAs are enough.  One thread per voxel: the row arrives with 16-byte loads, the weights sit in shared memory
-// as fp32 (every lane reads the same address: a broadcast), the c_out sums stay in registers, and the rows of a block
-// leave through shared memory so that the stores are contiguous.  fp32 accumulation, one rounding to fp16.
+// the bias.  The layer reads n*c_in*2 bytes and writes n*c_out*2: it is bound by HBM.  A reduction of 96 and 24
+// (padded) output columns is far too small for a tcgen05 pipeline (one 128-row MMA tile would wait longer for its
+// barriers than it computes), so each warp multiplies 16 voxels at a time with warp-level m16n8k16 MMAs: the A
+// fragments come straight from global memory (the four lanes of a quad read 16 contiguous bytes of a row), the
+// transposed weights sit in shared memory with a padded stride (conflict-free fragment loads), accumulation is fp32
+// with the bias as the initial value, and the 16 x c_out results leave through shared memory as one contiguous run.
 #include "common.cuh"
 
 namespace sb {
 
 constexpr int kPwThreads = 256;
+constexpr int kPwWarps = kPwThreads / 32;
+constexpr int kPwKGroup = 6;     // k-steps (of 16) whose row loads are issued together
 
-template <int CO>   // c_out rounded up to a multiple of 8
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int NT>   // 8-column tiles of the output: c_out <= 8 * NT
 __global__ void __launch_bounds__(kPwThreads) pointwise_kernel(const __half *__restrict__ feats, const __half *__restrict__ w,
                                                                 const __half *__restrict__ bias, int64_t n, int c_in, int c_out,
                                                                 __half *__restrict__ out) {
   extern __shared__ __align__(16) unsigned char pw_smem[];
-  float *s_w = reinterpret_cast<float *>(pw_smem);                         // [c_in][CO]
-  float *s_bias = s_w + c_in * CO;                                          // [CO]
-  __half *s_out = reinterpret_cast<__half *>(s_bias + CO);                  // [256][c_out]
-  const int tid = threadIdx.x;
-  for (int i = tid; i < c_in * CO; i += kPwThreads) {
-    const int k = i / CO, c = i - k * CO;
-    s_w[i] = c < c_out ? __half2float(w[k * c_out + c]) : 0.f;
+  const int k_pad = (c_in + 15) / 16 * 16;          // reduction length in whole k-steps (c_in is a multiple of 8)
+  const int ldw = k_pad + 8;                        // halfs per weight column: 4 * (odd number) words, no bank conflicts
+  __half *s_wt = reinterpret_cast<__half *>(pw_smem);                                  // [8 * NT][ldw]: W transposed
+  float *s_bias = reinterpret_cast<float *>(pw_smem + static_cast<size_t>(8 * NT) * ldw * 2);   // [8 * NT]
+  __half *s_out = reinterpret_cast<__half *>(s_bias + 8 * NT);                         // [warps][16 * c_out]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  for (int i = tid; i < 8 * NT * ldw; i += kPwThreads) {
+    const int col = i / ldw, k = i - col * ldw;
+    s_wt[i] = (col < c_out && k < c_in) ? w[k * c_out + col] : __float2half(0.f);
   }
-  if (tid < CO) s_bias[tid] = (bias != nullptr && tid < c_out) ? __half2float(bias[tid]) : 0.f;
+  if (tid < 8 * NT) s_bias[tid] = (bias != nullptr && tid < c_out) ? __half2float(bias[tid]) : 0.f;
   __syncthreads();
-  const int k8_end = c_in / 8;
-  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * kPwThreads; row0 < n; row0 += static_cast<int64_t>(gridDim.x) * kPwThreads) {
-    const int64_t row = row0 + tid;
-    float acc[CO];
+  const int k_steps = k_pad / 16;
+  const uint32_t *wt32 = reinterpret_cast<const uint32_t *>(s_wt);
+  __half *my_out = s_out + warp * 16 * c_out;
+  const int64_t n_tiles = (n + 15) / 16;
+  for (int64_t tile = static_cast<int64_t>(blockIdx.x) * kPwWarps + warp; tile < n_tiles;
+       tile += static_cast<int64_t>(gridDim.x) * kPwWarps) {
+    const int64_t r0 = tile * 16 + g, r1 = r0 + 8;
+    const uint32_t *p0 = reinterpret_cast<const uint32_t *>(feats + (r0 < n ? r0 : 0) * c_in);
+    const uint32_t *p1 = reinterpret_cast<const uint32_t *>(feats + (r1 < n ? r1 : 0) * c_in);
+    const bool ok0 = r0 < n, ok1 = r1 < n;
+    float acc[NT][4];
 #pragma unroll
-    for (int c = 0; c < CO; ++c) acc[c] = s_bias[c];
-    if (row < n) {
-      const uint4 *p = reinterpret_cast<const uint4 *>(feats + row * c_in);
-#pragma unroll 2
-      for (int k8 = 0; k8 < k8_end; ++k8) {
-        const uint4 v = __ldg(p + k8);
-        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+    for (int nt = 0; nt < NT; ++nt) {
+      acc[nt][0] = acc[nt][2] = s_bias[8 * nt + 2 * t];
+      acc[nt][1] = acc[nt][3] = s_bias[8 * nt + 2 * t + 1];
+    }
+    for (int kb = 0; kb < k_steps; kb += kPwKGroup) {
+      uint32_t a[kPwKGroup][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __half22float2(h[j]);
-          const float4 *w0 = reinterpret_cast<const float4 *>(s_w + (k8 * 8 + 2 * j) * CO);
+      for (int j = 0; j < kPwKGroup; ++j) {
+        // words of a row: k-step (kb + j) covers halfs [16 (kb + j), +16); this lane takes halfs 2t, 2t+1 and 2t+8, 2t+9
+        const int w_lo = 8 * (kb + j) + t, w_hi = w_lo + 4;
+        const bool in_lo = kb + j < k_steps, in_hi = in_lo && 2 * w_hi < c_in;   // (c_in % 16 == 8: the last half step is padding)
+        a[j][0] = (in_lo && ok0) ? __ldg(p0 + w_lo) : 0u;
+        a[j][1] = (in_lo && ok1) ? __ldg(p1 + w_lo) : 0u;
+        a[j][2] = (in_hi && ok0) ? __ldg(p0 + w_hi) : 0u;
+        a[j][3] = (in_hi && ok1) ? __ldg(p1 + w_hi) : 0u;
+      }
 #pragma unroll
-          for (int c4 = 0; c4 < CO / 4; ++c4) {
-            const float4 a = w0[c4], b = w0[CO / 4 + c4];
-            acc[4 * c4 + 0] = fmaf(f.x, a.x, acc[4 * c4 + 0]);
-            acc[4 * c4 + 1] = fmaf(f.x, a.y, acc[4 * c4 + 1]);
-            acc[4 * c4 + 2] = fmaf(f.x, a.z, acc[4 * c4 + 2]);
-            acc[4 * c4 + 3] = fmaf(f.x, a.w, acc[4 * c4 + 3]);
-            acc[4 * c4 + 0] = fmaf(f.y, b.x, acc[4 * c4 + 0]);
-            acc[4 * c4 + 1] = fmaf(f.y, b.y, acc[4 * c4 + 1]);
-            acc[4 * c4 + 2] = fmaf(f.y, b.z, acc[4 * c4 + 2]);
-            acc[4 * c4 + 3] = fmaf(f.y, b.w, acc[4 * c4 + 3]);
-          }
+      for (int j = 0; j < kPwKGroup; ++j) {
+        if (kb + j >= k_steps) break;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint32_t *col = wt32 + (8 * nt + g) * (ldw / 2) + 8 * (kb + j) + t;
+          mma_m16n8k16(acc[nt], a[j], col[0], col[4]);
         }
       }
     }
+    // accumulator layout: [0], [1] = row g, columns 2t, 2t+1 of the tile; [2], [3] = row g + 8
 #pragma unroll
-    for (int c = 0; c < CO; ++c)
-      if (c < c_out) s_out[tid * c_out + c] = __float2half_rn(acc[c]);
-    __syncthreads();
-    const int64_t rows_here = (n - row0 < kPwThreads) ? (n - row0) : kPwThreads;
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = 8 * nt + 2 * t + (e & 1), row = g + 8 * (e >> 1);
+        if (col < c_out) my_out[row * c_out + col] = __float2half_rn(acc[nt][e]);
+      }
+    }
+    __syncwarp();
+    const int64_t rows_here = n - tile * 16 < 16 ? n - tile * 16 : 16;
     const int total = static_cast<int>(rows_here) * c_out;
-    __half *dst = out + row0 * c_out;
-    for (int i = tid; i < total; i += kPwThreads) dst[i] = s_out[i];
-    __syncthreads();
+    __half *dst = out + tile * 16 * c_out;
+    for (int i = lane; i < total; i += 32) dst[i] = my_out[i];
+    __syncwarp();
   }
 }
 
-template <int CO>
+template <int NT>
 static int launch_pointwise(const __half *feats, const __half *w, const __half *bias, int64_t n, int c_in, int c_out, __half *out,
                             cudaStream_t st) {
-  const size_t smem = static_cast<size_t>(c_in) * CO * 4 + CO * 4 + static_cast<size_t>(kPwThreads) * c_out * 2;
+  const int k_pad = (c_in + 15) / 16 * 16;
+  const size_t smem = static_cast<size_t>(8 * NT) * (k_pad + 8) * 2 + 8 * NT * 4 + static_cast<size_t>(kPwWarps) * 16 * c_out * 2;
   if (smem > 48 * 1024) return fail(SPIRA_B200_ERR_UNSUPPORTED, "pointwise: c_in=%d, c_out=%d need %zu bytes of shared memory", c_in, c_out, smem);
-  int64_t blocks = div_up(n, kPwThreads);
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  int64_t blocks = div_up(div_up(n, 16), kPwWarps);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
   if (blocks > cap) blocks = cap;
-  pointwise_kernel<CO><<<static_cast<unsigned>(blocks), kPwThreads, smem, st>>>(feats, w, bias, n, c_in, c_out, out);
+  pointwise_kernel<NT><<<static_cast<unsigned>(blocks), kPwThreads, smem, st>>>(feats, w, bias, n, c_in, c_out, out);
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
 }
@@ -90,16 +118,16 @@ using namespace sb;
 extern "C" int spira_b200_pointwise(const void *feats, const void *weights, const void *bias, int64_t n, int c_in, int c_out,
                                     void *out, void *stream) {
   SB_CHECK_ARG(n >= 0 && n < (int64_t(1) << 31), "pointwise: n=%lld out of range", (long long)n);
-  if (c_in < 8 || c_in % 8 != 0 || c_out < 1 || c_out > 32)
-    return fail(SPIRA_B200_ERR_UNSUPPORTED, "pointwise: c_in=%d must be a multiple of 8 and c_out=%d at most 32", c_in, c_out);
+  if (c_in < 8 || c_in % 8 != 0 || c_in > 512 || c_out < 1 || c_out > 32)
+    return fail(SPIRA_B200_ERR_UNSUPPORTED, "pointwise: c_in=%d must be a multiple of 8 up to 512 and c_out=%d at most 32", c_in, c_out);
   if (n == 0) return SPIRA_B200_OK;
   SB_CHECK_ARG(feats && weights && out, "pointwise: null pointer");
   SB_CHECK_ARG(reinterpret_cast<uintptr_t>(feats) % 16 == 0, "pointwise: feature rows must be 16-byte aligned");
   const __half *f = static_cast<const __half *>(feats), *w = static_cast<const __half *>(weights), *b = static_cast<const __half *>(bias);
   __half *o = static_cast<__half *>(out);
   cudaStream_t st = as_stream(stream);
-  if (c_out <= 8) return launch_pointwise<8>(f, w, b, n, c_in, c_out, o, st);
-  if (c_out <= 16) return launch_pointwise<16>(f, w, b, n, c_in, c_out, o, st);
-  if (c_out <= 24) return launch_pointwise<24>(f, w, b, n, c_in, c_out, o, st);
-  return launch_pointwise<32>(f, w, b, n, c_in, c_out, o, st);
+  if (c_out <= 8) return launch_pointwise<1>(f, w, b, n, c_in, c_out, o, st);
+  if (c_out <= 16) return launch_pointwise<2>(f, w, b, n, c_in, c_out, o, st);
+  if (c_out <= 24) return launch_pointwise<3>(f, w, b, n, c_in, c_out, o, st);
+  return launch_pointwise<4>(f, w, b, n, c_in, c_out, o, st);
 }

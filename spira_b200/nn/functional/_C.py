@@ -924,9 +924,8 @@ def pointwise(feats: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     when the layer is outside what ``spira_b200_pointwise`` takes (the caller then uses the library GEMM, like the
     reference: spira/nn/conv.py:312-316)."""
     c_in, c_out = weight.shape
-    if not POINTWISE_HEAD or c_out > 32 or c_in % 8 != 0 or c_in < 8 or not feats.is_cuda or feats.dtype != torch.float16 \
-            or weight.dtype != torch.float16 or (bias is not None and bias.dtype != torch.float16) \
-            or c_in * ((c_out + 7) // 8 * 8) * 4 + 512 * c_out + 128 > 48 * 1024:
+    if not POINTWISE_HEAD or c_out > 32 or c_in % 8 != 0 or c_in < 8 or c_in > 512 or not feats.is_cuda \
+            or feats.dtype != torch.float16 or weight.dtype != torch.float16 or (bias is not None and bias.dtype != torch.float16):
         return None
     if not feats.is_contiguous():
         feats = feats.contiguous()

@@ -335,7 +335,8 @@ def test_kernel_variants_agree_with_the_default(C, scene, option, value):
 
 
 @pytest.mark.parametrize("n,cin,cout,bias", [(1, 8, 1, True), (255, 96, 19, True), (256, 96, 19, False), (25001, 64, 20, True),
-                                             (4097, 32, 32, True), (1000, 256, 13, False), (777, 16, 8, True)])
+                                             (4097, 32, 32, True), (1000, 256, 13, False), (777, 16, 8, True), (3000, 24, 5, True),
+                                             (100, 512, 32, True), (17, 40, 19, False)])
 def test_pointwise_head_matches_fp32_matmul(C, n, cin, cout, bias):
     """The 1x1x1 head kernel against a float32 product of the same fp16 inputs, rounded once (the reference computes
     this layer with torch.mm, spira/nn/conv.py:312-316): tolerance 2e-3 relative / 1e-3 absolute."""
@@ -354,7 +355,7 @@ def test_pointwise_head_declines_what_it_does_not_cover(C, lib):
     x = torch.zeros(10, 96, device="cuda").half()
     assert C.pointwise(x, torch.zeros(96, 64, device="cuda").half(), None) is None          # too many output channels
     assert C.pointwise(x[:, :4].contiguous(), torch.zeros(4, 8, device="cuda").half(), None) is None   # c_in not a multiple of 8
-    assert C.pointwise(torch.zeros(10, 512, device="cuda").half(), torch.zeros(512, 32, device="cuda").half(), None) is None
+    assert C.pointwise(torch.zeros(10, 1024, device="cuda").half(), torch.zeros(1024, 32, device="cuda").half(), None) is None
     assert C.pointwise(x.float(), torch.zeros(96, 8, device="cuda"), None) is None           # fp16 only
     out = torch.empty(10, 64, device="cuda").half()
     rc = lib.spira_b200_pointwise(x.data_ptr(), x.data_ptr(), None, 10, 96, 64, out.data_ptr(), None)
