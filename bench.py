@@ -418,7 +418,7 @@ def profile_kernels(engine, scene):
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the 42 convolution launches of one default step, from the
 # ncu launch list of that step (profiles/minkunet_step_launch_list.md); valid for the default workload only
-NCU_CONV_DRAM_BYTES_PER_STEP = {"minkunet": 659_276_544}
+NCU_CONV_DRAM_BYTES_PER_STEP = {"minkunet": 693_949_696}
 
 
 def roofline_from_layers(layers, pk, pk_kind, workload=None):
