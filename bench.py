@@ -492,15 +492,11 @@ def main():
     ap.add_argument("--steps", type=int, default=32)     # (scenes of ~2 ms: 32 steps keep one slow step from moving the mean)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap", "gather"])
+    ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap"])
     ap.add_argument("--no-group", action="store_true", help="output-stationary maps keep their target order (no grouping by neighbour pattern)")
     ap.add_argument("--no-defer", action="store_true", help="add_all_kernel_maps completes all maps before it returns")
     ap.add_argument("--n256-min-targets", type=int, default=-1, help="layers with fewer targets use 128-target tiles (-1 = library default)")
     ap.add_argument("--no-n256", action="store_true", help="output-stationary layers always use the targets-as-M kernel")
-    ap.add_argument("--team-threads", type=int, default=0, choices=[0, 128, 256, 512],
-                    help="producer threads per pipeline stage of the exchanged-operand kernel (0 = library default)")
-    ap.add_argument("--stem-variant", type=int, default=-1, choices=[-1, 0, 1, 2],
-                    help="narrow-input (stem) kernel: 0 offset by offset (library default), 1 row loads in batches, 2 two targets per thread")
     ap.add_argument("--gather", default="default", choices=["default", "tma", "cpasync"], help="row-gather engine of the tensor-core kernels")
     ap.add_argument("--cin", type=int, default=64)
     ap.add_argument("--cout", type=int, default=64)
@@ -537,22 +533,16 @@ def main():
     if args.impl == "ours" and args.no_n256:
         from spira_b200.nn.functional import _C as native_
         native_.set_option("os_n256", 0)
-    if args.impl == "ours" and args.team_threads:
-        from spira_b200.nn.functional import _C as native_
-        native_.set_option("os_team_threads", args.team_threads)
-    if args.impl == "ours" and args.stem_variant >= 0:
-        from spira_b200.nn.functional import _C as native_
-        native_.set_option("stem_variant", args.stem_variant)
     if args.impl == "ours" and args.gather != "default":
         from spira_b200 import build
         build.build()
         from spira_b200.nn.functional import _C as native
         native.set_option("gather_tma", 1 if args.gather == "tma" else 0)
-    if args.workload in ("layer", "kmap", "gather"):
+    if args.workload in ("layer", "kmap"):
         from spira_b200 import build, _lib
         build.build()
         _lib.load()
-        line = {"layer": run_layer, "kmap": run_kmap, "gather": run_gather}[args.workload](args, device, pk, pk_kind)
+        line = {"layer": run_layer, "kmap": run_kmap}[args.workload](args, device, pk, pk_kind)
         line["n_gpus"] = n_gpus
         if rank == 0:
             print(json.dumps(line))
@@ -802,51 +792,6 @@ def _time_calls(fn, steps, warmup, l2buf):
     return sum(t) / len(t), min(t)
 
 
-def run_gather(args, device, pk, pk_kind):
-    """Ceiling of the row-gather pattern of the output-stationary kernels: the neighbour rows of one 3^3 layer of a
-    LiDAR-like scene (``--cin`` channels, 64 of them = 128 bytes taken per row, like one pipeline stage) are read through
-    the library's probe kernel in four orders and folded away, nothing is written."""
-    from spira_b200 import scenes as sc, _lib
-    from spira_b200.nn.functional import _C
-    c = sc.lidar_scene(1)
-    n = len(c)
-    keys, _ = _C.cuda_flatten_sort(torch.from_numpy(c).to(device), False)
-    feats = torch.from_numpy(sc.features(n, args.cin, 0)).to(device)
-    m = _C.cuda_binary_search(keys, keys, (3, 3, 3), (1, 1, 1), 0)
-    dense, grouped = m[2][:n], m[2]._sb["grouped"].map[:n]
-    def pairs_in_tile_order(mp):           # present entries, tile by tile (256 rows), offset by offset, row by row
-        pad = (-mp.shape[0]) % 256
-        t = torch.cat([mp, mp.new_full((pad, mp.shape[1]), -1)]).view(-1, 256, mp.shape[1]).permute(0, 2, 1).reshape(-1)
-        return t[t >= 0].contiguous()
-    orders = {
-        "order of the output-stationary kernel, targets in spatial order": pairs_in_tile_order(dense),
-        "order of the output-stationary kernel, grouped map": pairs_in_tile_order(grouped),
-    }
-    nnz = int((dense >= 0).sum().item())
-    g = torch.Generator(device=device).manual_seed(0)
-    orders["random rows"] = torch.randint(0, n, (nnz,), device=device, generator=g, dtype=torch.int32)
-    orders["consecutive rows"] = (torch.arange(nnz, device=device, dtype=torch.int32) % n).contiguous()
-    taken = min(128, args.cin * 2)
-    sink = torch.zeros(16 * 1024, dtype=torch.int32, device=device)
-    l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
-    stream = torch.cuda.current_stream().cuda_stream
-    results = {}
-    for name, idx in orders.items():
-        idx = idx.contiguous()
-        rows = int((idx >= 0).sum().item())
-        fn = lambda: _lib.call("spira_b200_gather_probe", feats.data_ptr(), idx.data_ptr(), idx.numel(), args.cin * 2, taken,
-                               sink.data_ptr(), stream)
-        mean_ms, min_ms = _time_calls(fn, args.steps, args.warmup, l2buf)
-        results[name] = {"rows": rows, "ms": round(mean_ms, 5), "gathered_gbs": round(rows * taken / (min_ms * 1e-3) / 1e9, 1)}
-    best = max(v["gathered_gbs"] for v in results.values())
-    return {"metric": "row gather bandwidth (bytes gathered / time, nothing written)", "value": best, "unit": "GB/s", "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": min(v["ms"] for v in results.values()), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16 rows", "data": "synthetic",
-            "config": {"workload": f"gather probe: {n} voxels, rows of {args.cin * 2} bytes, {taken} bytes taken per row, {nnz} pairs of a 3^3 map",
-                       "l2": "256 MiB buffer rewritten between timed steps"},
-            "orders": results, "gpu_launches": args.steps * len(orders)}
-
-
 def run_layer(args, device, pk, pk_kind):
     """Single-layer workload: one submanifold 3^3 layer, c_in -> c_out, 50,000 voxels in a 512^3 grid (64-bit keys)."""
     from spira_b200 import scenes as sc, _lib
@@ -882,23 +827,14 @@ def run_layer(args, device, pk, pk_kind):
         roof = {"bound": "tensor", "achieved": round(ach, 2), "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": round(ach / pk["bf16_tflops"], 4), "traffic": None}
     kernel = "conv_tc_kernel<WS>" if df else ("conv_os_n256_kernel" if 64 < args.cout <= 96 else "conv_tc_kernel<OS>")
     if df == 0 and m[2]._sb.get("grouped") is not None and args.cin % 8 == 0:
-        # What actually bounds the output-stationary kernels: bytes that cross from L2 into the SMs (gathered rows + one
-        # weight chunk per visited (tile, 64-wide reduction chunk) + the map), against the rate a dedicated gather probe
-        # reaches for the same access pattern, measured here.
+        # Bytes that cross from L2 into the SMs per launch: gathered rows + one weight chunk per visited (tile, 64-wide
+        # reduction chunk) + the map.  This, not HBM, is what the output-stationary kernels move most of.
         stats = m[2]._sb["grouped"].stats.cpu().tolist()
         tile_rows = 256 if kernel == "conv_os_n256_kernel" else 128
         visited = stats[1] if tile_rows == 256 else stats[0]              # non-empty (tile, offset) pairs of the grouped map
         xbar = nnz * args.cin * 2 + visited * (args.cin / 64.0) * args.cout * 128 + m[2].numel() * 4
-        taken = min(128, args.cin * 2)
-        idx = torch.randint(0, n, (nnz,), device=device, dtype=torch.int32)
-        sink = torch.zeros(16 * 1024, dtype=torch.int32, device=device)
-        st = torch.cuda.current_stream().cuda_stream
-        _, probe_ms = _time_calls(lambda: _lib.call("spira_b200_gather_probe", feats.data_ptr(), idx.data_ptr(), nnz, args.cin * 2, taken,
-                                                    sink.data_ptr(), st), args.steps, args.warmup, l2buf)
-        probe_gbs = nnz * taken / (probe_ms * 1e-3) / 1e9
         roof["l2_to_sm"] = {"bytes_per_launch": int(xbar), "achieved_gbs": round(xbar / (min_ms * 1e-3) / 1e9, 1),
-                            "probe_gbs": round(probe_gbs, 1), "frac_of_probe": round(xbar / (min_ms * 1e-3) / 1e9 / probe_gbs, 3),
-                            "note": "gathered rows + weight chunks + map, over the fastest launch; probe = row gather at full occupancy"}
+                            "note": "gathered rows + weight chunks + map, over the fastest launch"}
     # DRAM bytes per launch from an ncu capture of exactly this case (dram__bytes_read.sum + dram__bytes_write.sum)
     if args.scene == "lidar" and (args.cin, args.cout, df) == (96, 96, 0):
         roof["traffic"] = 39_471_000

@@ -59,15 +59,20 @@ int spira_b200_read_back(const void *device_src, void *pinned_dst, size_t bytes,
  *                       on the MMA's N side and the weights on its M side; 0: always 128 targets as M
  *   "os_n256_min_targets" layers with fewer targets than this use the 128-target tiles even where the 256-target kernel
  *                       applies: with few tiles per SM the heaviest tile sets the time and smaller tiles balance better
- *   "os_team_threads"   128 (default), 256 or 512: producer threads that fill one pipeline stage of that kernel
- *                       together (4, 2 or 1 teams); measured equal within noise for 128 and 256, slower for 512
- *   "stem_variant"      narrow-input layers (c_in <= 8) on the one-thread-per-target kernel: 0 (default) offset by
- *                       offset, 1 the row loads of nine offsets issued together, 2 two targets per thread (measured
- *                       28.7 / 30.8 / 33.4 us on a 4 -> 32 stem over 127 k voxels)
+ *   "wait_limit_us"     limit, in microseconds, of every wait inside the tensor-core kernels (mbarriers, the grid
+ *                       barrier of spira_b200_conv_ws_fused); default 1500000.  A kernel whose wait runs out sets its
+ *                       `status` word, lets its copies land, releases its tensor memory and returns
+ *   "ws_barrier_skew_once"  test aid: added to the grid-barrier target of the NEXT spira_b200_conv_ws_fused launch only,
+ *                       so that its barrier cannot be met and the wait limit is exercised without any fault
  * get_option additionally answers "os_pack_mode": the SPIRA_B200_PACK_* image spira_b200_conv_os expects under
  * the current options.  Unknown names: set_option fails, get_option returns -1. */
 int spira_b200_set_option(const char *name, int value);
 int spira_b200_get_option(const char *name);
+
+/* Recovery after a spira_b200_conv_ws_fused launch reported an expired wait, and the way to move the fused calls of
+ * a device to another stream: synchronises the current device, sets the host's count of grid-barrier arrivals to the
+ * device's, and forgets which stream the device's fused calls were bound to.  No reference counterpart. */
+int spira_b200_ws_barrier_resync(void);
 
 /* ---- packed keys ------------------------------------------------------------------------- */
 
@@ -90,12 +95,6 @@ int spira_b200_flatten_sort(const int32_t *coords, int64_t n, int key_bytes, voi
  * SparseTensor.order (spira/tensors.py:55-65). */
 int spira_b200_permute_rows(const void *rows_in, const int32_t *perm, int64_t n, int64_t row_bytes, void *rows_out,
                             void *stream);
-
-/* Measurement aid (no reference counterpart): gathers bytes_taken bytes of each of n rows rows[idx[i]] (idx < 0 skipped),
- * 16 bytes per thread on 8 x SM-count blocks of 256 threads, and folds them away (`sink`: at least 8 x SM-count words,
- * practically never written).  Timing it gives the ceiling of the row-gather pattern of the convolution kernels. */
-int spira_b200_gather_probe(const void *rows, const int32_t *idx, int64_t n, int64_t row_bytes, int64_t bytes_taken,
-                            uint32_t *sink, void *stream);
 
 /* 1x1x1 layer with few output channels (a classification head): out[n][c_out] = feats[n][c_in] . weights[c_in][c_out]
  * (+ bias[c_out], may be null), fp16 in and out, fp32 accumulation, one rounding.  The reference sends every 1x1x1
@@ -294,7 +293,9 @@ int spira_b200_conv_ws(const void *feats, const void *weights, const void *packe
  * cooperatively: after their last tile the CTAs meet at a grid barrier (bounded wait, reported through `status`), then
  * every CTA converts its slice of the scratch to fp16 with the epilogue applied and writes zeros back.  Contract:
  *   zeroed_accum[0 .. num_targets * c_out) holds zeros on entry and holds zeros again when the call has completed;
- *   calls on one device must be ordered on one stream (they share the arrival counter of the grid barrier). */
+ *   calls on one device must be ordered on one stream (they share the arrival counter of the grid barrier): the first
+ *   call binds the device to its stream, a call on another stream returns SPIRA_B200_ERR_ARGUMENT until
+ *   spira_b200_ws_barrier_resync() releases the binding. */
 int spira_b200_conv_ws_fused(const void *feats, const void *packed, const spira_b200_epilogue *epilogue,
                              const int32_t *in_idx, const int32_t *out_idx, const int32_t *naddrs, const int32_t *qnaddrs,
                              int rows, int64_t num_tiles128, int mirror, int swap, int64_t num_sources, int64_t num_targets,

@@ -83,6 +83,7 @@ struct ConvParams {
   int T, n_tiles, K, c_in, c_out, R, n_chunks;  // n_chunks: OS = ceil(R/64); WS = ceil(c_in/64) per offset
   int stages, teams, slab_bufs, b_bytes, acc_stride, tmem_cols;
   int off_b, off_slab, off_flags, off_cm, off_meta, off_bar;
+  unsigned long long wait_ns;   // limit of every internal wait (mbarriers, grid barrier)
 };
 
 __device__ __forceinline__ float epilogue_apply(float v, int c, const Epilogue &ep) {
@@ -252,7 +253,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
             }
             for (int jj = 0; jj < cpo; ++jj) {
               ++sent;
-              if (!mbar_wait(bar_empty(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+              if (!mbar_wait(bar_empty(stage), phase ^ 1, abort_flag, P.wait_ns)) { ok = false; break; }
               if (lane == 0) {
                 const int valid = min(kChunk, P.c_in - jj * kChunk);
                 meta[stage] = ((valid + 15) >> 4) | ((sent == 1) << 8) | ((sent == total) << 9);
@@ -330,7 +331,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
             slab[kRows + (tile_i & (kScatterRing - 1)) * kRows + r] = r < n ? (mirrored ? P.in_idx : P.out_idx)[p0 + r] : -1;
         }
         const int stage = my_stage;
-        if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag, P.wait_ns)) { ok = false; break; }
         if (r == 0) post_weights(stage, w_row * cpo + jj, min(kChunk, P.c_in - jj * kChunk), jj == 0, jj == cpo - 1);
         const uint32_t dst = sbase + stage * kABytes + dst_off;
         const int c = jj * kChunk + piece * 8;
@@ -378,7 +379,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         const int32_t *my_slab = slab + buf * kRows * P.K;
         uint32_t *my_cmask = cmask + (tile_i & 1) * n_words;
         if (P.slab_bufs == 2) {
-          if (!mbar_wait(bar_slab0 + 8u * buf, (tile_i >> 1) & 1, abort_flag)) ok = false;
+          if (!mbar_wait(bar_slab0 + 8u * buf, (tile_i >> 1) & 1, abort_flag, P.wait_ns)) ok = false;
           // all warps have issued their share of the previous tile: the other slab and chunk mask are free
           if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
           if (tid == 0 && next < n_tiles) {
@@ -392,7 +393,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
             mbar_arrive_expect_tx(bar_slab0, slab_bytes);
             bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(tile) * kRows * P.K, slab_bytes, bar_slab0);
           }
-          if (!mbar_wait(bar_slab0, tile_i & 1, abort_flag)) ok = false;
+          if (!mbar_wait(bar_slab0, tile_i & 1, abort_flag, P.wait_ns)) ok = false;
         }
         // which 64-wide reduction chunks touch at least one neighbour of this tile: one bit per chunk, the
         // chunks are spread over the warps
@@ -434,7 +435,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           }
           const int j = (word << 5) + __ffs(bits) - 1;
           const int stage = my_stage, slot_shift = my_slot * 8;
-          if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag, P.wait_ns)) { ok = false; break; }
           my_stage += teams;
           ++my_slot;
           if (my_stage >= stages) { my_stage -= stages; my_slot = 0; my_phase ^= 1; }
@@ -480,12 +481,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       int tile_i = 0;
       for (int tile = tile_at(0); ok && tile < n_tiles; tile = tile_at(++tile_i)) {
         const int b = tile_i & 1;
-        if (!mbar_wait(bar_acc_empty(b), ((acc_phase >> b) & 1u) ^ 1u, abort_flag)) break;
+        if (!mbar_wait(bar_acc_empty(b), ((acc_phase >> b) & 1u) ^ 1u, abort_flag, P.wait_ns)) break;
         acc_phase ^= 1u << b;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * P.acc_stride;
         while (true) {
-          if (!mbar_wait(bar_full(stage), phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar_full(stage), phase, abort_flag, P.wait_ns)) { ok = false; break; }
           fence_proxy_async();     // the rows were written by cp.async (generic proxy), the MMA reads them through the async proxy
           tc_fence_after();
           const int m = meta[stage];
@@ -514,7 +515,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     int tile_i = 0;
     for (int tile = tile_at(0); tile < n_tiles; tile = tile_at(++tile_i)) {
       const int b = tile_i & 1;
-      if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag)) break;
+      if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag, P.wait_ns)) break;
       acc_phase ^= 1u << b;
       tc_fence_after();
       const uint32_t taddr = tmem_base + b * P.acc_stride + (static_cast<uint32_t>(q * 32) << 16);
@@ -605,7 +606,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           while (true) {
             const unsigned seen = *reinterpret_cast<volatile unsigned *>(&g_grid_arrivals);
             if (static_cast<int>(seen - P.barrier_target) >= 0) { arrived = true; break; }
-            if (global_timer_ns() - t0 > kWaitLimitNs) break;
+            if (global_timer_ns() - t0 > P.wait_ns) break;
           }
           if (!arrived && P.status) atomicExch(P.status, 1);
         }
@@ -671,15 +672,15 @@ struct ConvN2Params {
   int T, T_al, n_tiles, K, c_in, c_out, R, n_chunks;
   int stages, w_bytes, w_stride;
   int off_feat, off_slab, off_tr, off_cm, off_meta, off_bar;
+  unsigned long long wait_ns;   // limit of every internal wait
 };
 
-// kTeamThreads: producer threads that fill one stage together (128, 256 or 512: 4, 2 or 1 teams; 8 lanes per row, so a
-// thread owns one 16-byte piece of 16, 8 or 4 rows).  Stage s is filled by team s % teams.
-template <int kTeamThreads>
+// Producer teams of 128 threads fill one stage together (4 teams; 8 lanes per row, so a thread owns one 16-byte piece
+// of 16 rows).  Stage s is filled by team s % 4.  (Teams of 256 or 512 threads were measured equal or slower.)
+constexpr int kN2TeamThreads = 128;
 __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __grid_constant__ ConvN2Params P) {
-  constexpr int kN2TeamThreads = kTeamThreads;
-  constexpr int kRowsPerThread = kN2Rows * 8 / kTeamThreads;     // 16, 8, 4
-  constexpr int kRowStep = kTeamThreads / 8;                     // rows between two places of a thread
+  constexpr int kRowsPerThread = kN2Rows * 8 / kN2TeamThreads;   // 16
+  constexpr int kRowStep = kN2TeamThreads / 8;                   // rows between two places of a thread
   constexpr uint32_t kSlotMask = (1u << kRowsPerThread) - 1u;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -699,7 +700,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int stages = P.stages;
-  constexpr int kTeams = kProducers / kN2TeamThreads;   // 4, 2, 1
+  constexpr int kTeams = kProducers / kN2TeamThreads;   // 4
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -724,7 +725,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < kProducerWarps) {
-    // =========================== producers: teams of kTeamThreads threads, stage s is filled by team s % kTeams ======
+    // =========================== producers: teams of 128 threads, stage s is filled by team s % kTeams ======
     // Thread r of a team owns ONE 16-byte piece (r & 7) of kRowsPerThread rows (r >> 3, + kRowStep, ...): the eight lanes
     // that share a row read 128 contiguous bytes, so a warp-level copy touches 4 rows instead of 32 different cache lines
     // (the L1 processes one line per cycle: a thread-per-row mapping is bound by that, not by bandwidth).
@@ -765,7 +766,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
         bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(t0) * P.K, bytes, bar_slab);
       }
       for (int i = rows_here * P.K + tid; i < kN2Rows * P.K; i += kProducers) slab[i] = -1;
-      if (!mbar_wait(bar_slab, tile_i & 1, abort_flag)) ok = false;
+      if (!mbar_wait(bar_slab, tile_i & 1, abort_flag, P.wait_ns)) ok = false;
       if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
       // non-empty 64-wide reduction chunks of this tile (one bit per chunk), spread over the warps
       for (int j = warp; j < P.n_chunks; j += kProducerWarps) {
@@ -802,7 +803,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
         }
         const int j = (word << 5) + __ffs(bits) - 1;
         const int stage = my_stage, slot_shift = my_slot * kRowsPerThread;
-        if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar_empty(stage), my_phase ^ 1, abort_flag, P.wait_ns)) { ok = false; break; }
         my_stage += kTeams;
         ++my_slot;
         if (my_stage >= stages) { my_stage -= stages; my_slot = 0; my_phase ^= 1; }
@@ -851,12 +852,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
       int tile_i = 0;
       for (int tile = snake_tile(0); ok && tile < P.n_tiles; tile = snake_tile(++tile_i)) {
         const int b = tile_i & 1;
-        if (!mbar_wait(bar_acc_empty(b), ((acc_phase >> b) & 1u) ^ 1u, abort_flag)) break;
+        if (!mbar_wait(bar_acc_empty(b), ((acc_phase >> b) & 1u) ^ 1u, abort_flag, P.wait_ns)) break;
         acc_phase ^= 1u << b;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * kN2Rows;
         while (true) {
-          if (!mbar_wait(bar_full(stage), phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar_full(stage), phase, abort_flag, P.wait_ns)) { ok = false; break; }
           fence_proxy_async();     // the rows were written by cp.async (generic proxy), the MMA reads them through the async proxy
           tc_fence_after();
           const int m = meta[stage];
@@ -878,10 +879,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     __syncwarp();
   } else {
     // =========================== epilogue ===========================
-    // Accumulator lane = output channel, column = target.  Thread c applies the per-channel affine (its own constants)
-    // to 32 targets, rounds to fp16 and parks the values in a small per-warp tile; the warp then reads the tile
-    // transposed, so that thread t holds the 32 channels of ONE target: residual add and ReLU in fp16 pairs, four
-    // 16-byte stores per target row instead of 32 two-byte ones.
+    // Accumulator lane = output channel, column = target.  Thread c applies everything to the fp32 accumulator of
+    // channel c for 32 targets at a time: the per-channel affine (its own constants), the residual (read channel-major:
+    // for one target the lanes of the warp read 32 consecutive channels, 64 contiguous bytes) and the ReLU; the value is
+    // then rounded ONCE to fp16 and parked in a small per-warp tile, which the warp reads transposed, so that thread t
+    // holds the 32 channels of ONE target and writes them with four 16-byte stores.
     const int q = warp & 3;
     const int c = q * 32 + lane;
     const bool has_channel = c < P.c_out;
@@ -889,12 +891,15 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     const float bias = (has_channel && P.ep.bias) ? __half2float(P.ep.bias[c]) : 0.f;
     const float scale = (has_channel && P.ep.scale) ? P.ep.scale[c] : 1.f;
     const float shift = (has_channel && P.ep.shift) ? P.ep.shift[c] : 0.f;
+    const __half *res_col = (has_channel && P.ep.residual) ? P.ep.residual + c : nullptr;
+    const bool with_residual = P.ep.residual != nullptr;    // warp-uniform
+    const bool relu = P.ep.relu != 0;
     uint32_t *tr = reinterpret_cast<uint32_t *>(smem + P.off_tr) + q * (32 * 17);
     uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
     for (int tile = snake_tile(0); tile < P.n_tiles; tile = snake_tile(++tile_i)) {
       const int b = tile_i & 1;
-      if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag)) break;
+      if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag, P.wait_ns)) break;
       acc_phase ^= 1u << b;
       tc_fence_after();
       if (n_valid > 0) {
@@ -902,19 +907,31 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
         const int64_t t0 = static_cast<int64_t>(tile) * kN2Rows;
         for (int jb = 0; jb < kN2Rows / 32; ++jb) {
           if (t0 + jb * 32 >= P.T) break;                       // warp-uniform: no target left in this block
+          // thread `lane` = target jb*32 + lane in the second half; its output row is needed by every lane before that
+          const int64_t t = t0 + jb * 32 + lane;
+          const int orow = t < P.T ? (P.row_of ? P.row_of[t] : static_cast<int>(t)) : -1;
           uint32_t v[32];
           tmem_ld_32x32(taddr + jb * 32, v);
           tmem_ld_wait();
 #pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint((__uint_as_float(v[i]) + bias) * scale + shift);
+          if (with_residual) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int oj = __shfl_sync(0xffffffffu, orow, i);  // output row of target jb*32 + i
+              if (res_col != nullptr && oj >= 0)
+                v[i] = __float_as_uint(__uint_as_float(v[i]) + __half2float(res_col[static_cast<int64_t>(oj) * P.c_out]));
+            }
+          }
+#pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float x0 = (__uint_as_float(v[2 * i]) + bias) * scale + shift;
-            const float x1 = (__uint_as_float(v[2 * i + 1]) + bias) * scale + shift;
-            const __half2 h = __floats2half2_rn(x0, x1);            // targets 2i, 2i+1 of channel `lane`
+            float x0 = __uint_as_float(v[2 * i]), x1 = __uint_as_float(v[2 * i + 1]);
+            if (relu) { x0 = fmaxf(x0, 0.f); x1 = fmaxf(x1, 0.f); }
+            const __half2 h = __floats2half2_rn(x0, x1);            // targets 2i, 2i+1 of channel `lane`: the single rounding
             tr[lane * 17 + i] = *reinterpret_cast<const uint32_t *>(&h);
           }
           __syncwarp();
-          // thread `lane` = target jb*32 + lane: channel cc sits in word (lane >> 1) of row cc, low or high half
-          const int64_t t = t0 + jb * 32 + lane;
+          // channel cc of this thread's target sits in word (lane >> 1) of row cc, low or high half
           const uint32_t sel = (lane & 1) ? 0x7632u : 0x5410u;      // PRMT: take the high / low halves of two words
           uint32_t y[16];
 #pragma unroll
@@ -924,29 +941,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
             y[m2] = __byte_perm(w0, w1, sel);                       // (channel 2*m2, channel 2*m2+1) of this target
           }
           __syncwarp();
-          if (t < P.T) {
-            const int64_t orow = P.row_of ? P.row_of[t] : t;
-            __half *dst = P.out + orow * P.c_out + q * 32;
-            const __half *res = P.ep.residual ? P.ep.residual + orow * P.c_out + q * 32 : nullptr;
+          if (orow >= 0) {
+            __half *dst = P.out + static_cast<int64_t>(orow) * P.c_out + q * 32;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (g * 8 < n_valid) {
-                uint4 o = make_uint4(y[4 * g], y[4 * g + 1], y[4 * g + 2], y[4 * g + 3]);
-                __half2 *oh = reinterpret_cast<__half2 *>(&o);
-                if (res) {
-                  const uint4 rv = *reinterpret_cast<const uint4 *>(res + g * 8);
-                  const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
-#pragma unroll
-                  for (int e2 = 0; e2 < 4; ++e2) oh[e2] = __hadd2(oh[e2], rh[e2]);
-                }
-                if (P.ep.relu) {
-                  const __half2 zero = __float2half2_rn(0.f);
-#pragma unroll
-                  for (int e2 = 0; e2 < 4; ++e2) oh[e2] = __hmax2(oh[e2], zero);
-                }
-                *reinterpret_cast<uint4 *>(dst + g * 8) = o;
-              }
-            }
+            for (int g = 0; g < 4; ++g)
+              if (g * 8 < n_valid)
+                *reinterpret_cast<uint4 *>(dst + g * 8) = make_uint4(y[4 * g], y[4 * g + 1], y[4 * g + 2], y[4 * g + 3]);
           }
         }
       }
@@ -1030,20 +1030,19 @@ __global__ void __launch_bounds__(128) conv_os_simt_kernel(const __half *__restr
 
 // Output-stationary kernel for the network stems (3-8 input channels, 16/32/64 output channels): far too little
 // arithmetic for the tensor cores and rows too short for 16-byte gathers.  One thread keeps all COUT accumulators of
-// ROWS targets (rows tid, tid + 128, ... of the block's tile) in registers; the weights sit in shared memory as fp32
-// and are read as broadcast float4; the tile's map slab is staged with coalesced 16-byte loads; the row loads of
-// BATCH offsets are issued together.  On a grouped map (rows sorted by neighbour pattern) the lanes of a warp skip
-// the same offsets: 36 -> 26 us on the 4 -> 32 stem of a 127 k-voxel scene.  ROWS = BATCH = 1 is the default: more
-// rows per thread or more loads in flight cost registers and shared memory, and the resident warps they displace
-// were worth more (see the launch code).
-template <int COUT, int ROWS, int BATCH>
+// one target (row tid of the block's 128-row tile) in registers; the weights sit in shared memory as fp32 and are read
+// as broadcast float4; the tile's map slab is staged with coalesced 16-byte loads.  On a grouped map (rows sorted by
+// neighbour pattern) the lanes of a warp skip the same offsets: 36 -> 26 us on the 4 -> 32 stem of a 127 k-voxel
+// scene.  (Two targets per thread, or the row loads of nine offsets issued together, were measured slower: they cost
+// registers and shared memory, and the resident warps they displace were worth more.)
+template <int COUT>
 __global__ void __launch_bounds__(128) conv_os_stem_kernel(const __half *__restrict__ feats, const __half *__restrict__ w,
                                                             Epilogue ep, const int32_t *__restrict__ map,
                                                             const int32_t *__restrict__ row_of, int64_t T, int K,
                                                             int c_in, __half *__restrict__ out) {
   extern __shared__ __align__(16) unsigned char stem_smem[];
   float *ws = reinterpret_cast<float *>(stem_smem);                              // [K][c_in][COUT]
-  int32_t *slab = reinterpret_cast<int32_t *>(stem_smem + static_cast<size_t>(K) * c_in * COUT * 4);   // [128 * ROWS][K]
+  int32_t *slab = reinterpret_cast<int32_t *>(stem_smem + static_cast<size_t>(K) * c_in * COUT * 4);   // [128][K]
   const int tid = threadIdx.x;
   if (reinterpret_cast<uintptr_t>(w) % 16 == 0) {                               // (COUT is a multiple of 16: whole 8-value groups)
     for (int i = tid; i < K * c_in * COUT / 8; i += 128) {
@@ -1059,104 +1058,68 @@ __global__ void __launch_bounds__(128) conv_os_stem_kernel(const __half *__restr
   } else {
     for (int i = tid; i < K * c_in * COUT; i += 128) ws[i] = __half2float(w[i]);
   }
-  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * (128 * ROWS);
-  // the map has T_al rows (T rounded up to 128): the last tile may hold fewer than 128 * ROWS of them
-  const int64_t T_al = (T + 127) / 128 * 128;
-  const int rows_here = static_cast<int>(T_al - t0 < 128 * ROWS ? T_al - t0 : 128 * ROWS);
+  // the map has T_al rows (T rounded up to 128): every block finds its 128 rows
+  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * 128;
   const int4 *s4 = reinterpret_cast<const int4 *>(map + t0 * K);
-  const int valid4 = rows_here * K / 4;                                         // (rows_here is a multiple of 128)
-  for (int i = tid; i < 32 * ROWS * K; i += 128)
-    reinterpret_cast<int4 *>(slab)[i] = i < valid4 ? s4[i] : make_int4(-1, -1, -1, -1);
+  for (int i = tid; i < 32 * K; i += 128) reinterpret_cast<int4 *>(slab)[i] = s4[i];
   __syncthreads();
-  float acc[ROWS][COUT];
+  float acc[COUT];
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r)
+  for (int co = 0; co < COUT; ++co) acc[co] = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int idx = slab[tid * K + k];
+    if (idx < 0) continue;
+    const __half *f = feats + static_cast<int64_t>(idx) * c_in;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    // the row in one load where its size allows it (4 channels: 8 bytes, 8 channels: 16 bytes)
+    if (c_in == 4) {
+      const uint2 v = __ldg(reinterpret_cast<const uint2 *>(f));
+      raw.x = v.x; raw.y = v.y;
+    } else if (c_in == 8) {
+      raw = __ldg(reinterpret_cast<const uint4 *>(f));
+    } else {
+      __half *xs = reinterpret_cast<__half *>(&raw);
 #pragma unroll
-    for (int co = 0; co < COUT; ++co) acc[r][co] = 0.f;
-  // Offsets in batches of BATCH: first all row loads of the batch (independent of one another, so that a target with
-  // many neighbours waits for K / BATCH round trips to L2 instead of K), then the arithmetic in offset order.
-  for (int k0 = 0; k0 < K; k0 += BATCH) {
-    int idx[BATCH][ROWS];
-    uint4 raw[BATCH][ROWS];
-#pragma unroll
-    for (int j = 0; j < BATCH; ++j)
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) idx[j][r] = (k0 + j < K) ? slab[(tid + 128 * r) * K + k0 + j] : -1;
-#pragma unroll
-    for (int j = 0; j < BATCH; ++j) {
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        raw[j][r] = make_uint4(0, 0, 0, 0);
-        if (idx[j][r] < 0) continue;
-        const __half *f = feats + static_cast<int64_t>(idx[j][r]) * c_in;
-        // the row in one load where its size allows it (4 channels: 8 bytes, 8 channels: 16 bytes)
-        if (c_in == 4) {
-          const uint2 v = __ldg(reinterpret_cast<const uint2 *>(f));
-          raw[j][r].x = v.x; raw[j][r].y = v.y;
-        } else if (c_in == 8) {
-          raw[j][r] = __ldg(reinterpret_cast<const uint4 *>(f));
-        } else {
-          __half *xs = reinterpret_cast<__half *>(&raw[j][r]);
-#pragma unroll
-          for (int ci = 0; ci < 8; ++ci)
-            if (ci < c_in) xs[ci] = f[ci];
-        }
-      }
+      for (int ci = 0; ci < 8; ++ci)
+        if (ci < c_in) xs[ci] = f[ci];
     }
+    const float4 *wk = reinterpret_cast<const float4 *>(ws + static_cast<size_t>(k) * c_in * COUT);
 #pragma unroll
-    for (int j = 0; j < BATCH; ++j) {
-      bool any = false;
+    for (int ci = 0; ci < 8; ++ci) {
+      if (ci >= c_in) break;
+      const float x = __half2float(reinterpret_cast<const __half *>(&raw)[ci]);
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) any = any || idx[j][r] >= 0;
-      if (!any) continue;
-      const float4 *wk = reinterpret_cast<const float4 *>(ws + static_cast<size_t>(k0 + j) * c_in * COUT);
-#pragma unroll
-      for (int ci = 0; ci < 8; ++ci) {
-        if (ci >= c_in) break;
-        float x[ROWS];
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) x[r] = __half2float(reinterpret_cast<const __half *>(&raw[j][r])[ci]);
-#pragma unroll
-        for (int c4 = 0; c4 < COUT / 4; ++c4) {
-          const float4 wv = wk[ci * (COUT / 4) + c4];
-#pragma unroll
-          for (int r = 0; r < ROWS; ++r) {
-            if (idx[j][r] < 0) continue;
-            acc[r][4 * c4 + 0] = fmaf(x[r], wv.x, acc[r][4 * c4 + 0]);
-            acc[r][4 * c4 + 1] = fmaf(x[r], wv.y, acc[r][4 * c4 + 1]);
-            acc[r][4 * c4 + 2] = fmaf(x[r], wv.z, acc[r][4 * c4 + 2]);
-            acc[r][4 * c4 + 3] = fmaf(x[r], wv.w, acc[r][4 * c4 + 3]);
-          }
-        }
+      for (int c4 = 0; c4 < COUT / 4; ++c4) {
+        const float4 wv = wk[ci * (COUT / 4) + c4];
+        acc[4 * c4 + 0] = fmaf(x, wv.x, acc[4 * c4 + 0]);
+        acc[4 * c4 + 1] = fmaf(x, wv.y, acc[4 * c4 + 1]);
+        acc[4 * c4 + 2] = fmaf(x, wv.z, acc[4 * c4 + 2]);
+        acc[4 * c4 + 3] = fmaf(x, wv.w, acc[4 * c4 + 3]);
       }
     }
   }
+  const int64_t t = t0 + tid;
+  // a grouped map names the output row of each of its rows; its padding rows carry -1
+  const int64_t out_row = row_of != nullptr ? static_cast<int64_t>(row_of[t]) : (t < T ? t : -1);
+  if (out_row < 0) return;
+  __half *dst = out + out_row * COUT;
+  const __half *res = ep.residual ? ep.residual + out_row * COUT : nullptr;
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) {
-    const int64_t t = t0 + tid + 128 * r;
-    // a grouped map names the output row of each of its rows; its padding rows carry -1
-    int64_t out_row = -1;
-    if (t < T_al) out_row = row_of != nullptr ? static_cast<int64_t>(row_of[t]) : (t < T ? t : -1);
-    if (out_row < 0) continue;
-    __half *dst = out + out_row * COUT;
-    const __half *res = ep.residual ? ep.residual + out_row * COUT : nullptr;
+  for (int c8 = 0; c8 < COUT / 8; ++c8) {
+    uint4 pack, rv = make_uint4(0, 0, 0, 0);
+    if (res) rv = *reinterpret_cast<const uint4 *>(res + 8 * c8);
+    const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+    uint32_t *pw = reinterpret_cast<uint32_t *>(&pack);
 #pragma unroll
-    for (int c8 = 0; c8 < COUT / 8; ++c8) {
-      uint4 pack, rv = make_uint4(0, 0, 0, 0);
-      if (res) rv = *reinterpret_cast<const uint4 *>(res + 8 * c8);
-      const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
-      uint32_t *pw = reinterpret_cast<uint32_t *>(&pack);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int co = 8 * c8 + 2 * e;
-        float v0 = epilogue_apply(acc[r][co], co, ep), v1 = epilogue_apply(acc[r][co + 1], co + 1, ep);
-        if (res) { v0 += __low2float(rh[e]); v1 += __high2float(rh[e]); }
-        if (ep.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
-        const __half2 hv = __floats2half2_rn(v0, v1);
-        pw[e] = *reinterpret_cast<const uint32_t *>(&hv);
-      }
-      *reinterpret_cast<uint4 *>(dst + 8 * c8) = pack;
+    for (int e = 0; e < 4; ++e) {
+      const int co = 8 * c8 + 2 * e;
+      float v0 = epilogue_apply(acc[co], co, ep), v1 = epilogue_apply(acc[co + 1], co + 1, ep);
+      if (res) { v0 += __low2float(rh[e]); v1 += __high2float(rh[e]); }
+      if (ep.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
+      const __half2 hv = __floats2half2_rn(v0, v1);
+      pw[e] = *reinterpret_cast<const uint32_t *>(&hv);
     }
+    *reinterpret_cast<uint4 *>(dst + 8 * c8) = pack;
   }
 }
 
@@ -1219,6 +1182,10 @@ static int round16(int x) { return (x + 15) / 16 * 16; }
 
 // ---- run-time options -----------------------------------------------------------------------------
 static int g_gather_tma = 0;      // 1: producers use TMA gather4, 0: cp.async
+static int g_wait_limit_us = kDefaultWaitLimitUs;   // limit of every wait inside the tensor-core kernels
+static int g_ws_barrier_skew_once = 0;              // added to the grid-barrier target of the NEXT fused launch only
+
+static unsigned long long wait_limit_ns() { return static_cast<unsigned long long>(g_wait_limit_us) * 1000ull; }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1250,7 +1217,13 @@ static int make_feats_tensor_map(CUtensorMap *map, const void *feats, int64_t nu
   return SPIRA_B200_OK;
 }
 
+// Fused weight-stationary launches of one device share the arrival counter of their grid barrier (and, by contract,
+// the caller's zero scratch), so they must be ordered on ONE stream.  The first fused launch binds the device to its
+// stream; a launch on another stream is refused instead of being left to run into the wait limit.
+// spira_b200_ws_barrier_resync() releases the binding.
 static unsigned g_arrivals_host[64] = {0};   // per device: sum of the grid sizes of all fused launches so far
+static cudaStream_t g_fused_stream[64] = {nullptr};
+static bool g_fused_bound[64] = {false};
 
 template <bool kWS>
 static int launch_conv_tc(ConvParams &P, bool tma, size_t smem, int64_t num_sources, cudaStream_t st) {
@@ -1263,9 +1236,16 @@ static int launch_conv_tc(ConvParams &P, bool tma, size_t smem, int64_t num_sour
     int dev = 0;
     SB_CHECK_CUDA(cudaGetDevice(&dev));
     SB_CHECK_ARG(dev >= 0 && dev < 64, "conv_ws_fused: device %d out of range", dev);
+    SB_CHECK_ARG(!g_fused_bound[dev] || g_fused_stream[dev] == st,
+                 "conv_ws_fused: device %d runs its fused weight-stationary calls on another stream; they share one grid-barrier "
+                 "counter and must stay on one stream (spira_b200_ws_barrier_resync() rebinds, spira_b200_conv_ws has no such limit)",
+                 dev);
     SB_CHECK_CUDA(cudaFuncSetAttribute(conv_tc_kernel<kWS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    g_fused_bound[dev] = true;
+    g_fused_stream[dev] = st;
     g_arrivals_host[dev] += static_cast<unsigned>(grid);
-    P.barrier_target = g_arrivals_host[dev];
+    P.barrier_target = g_arrivals_host[dev] + static_cast<unsigned>(g_ws_barrier_skew_once);
+    g_ws_barrier_skew_once = 0;
     void *args[] = {&P, &tmap};
     cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(&conv_tc_kernel<kWS, false>), dim3(grid),
                                                 dim3(kConvThreads), args, smem, st);
@@ -1345,8 +1325,6 @@ static size_t plan_smem_n256(ConvN2Params &P, int teams) {
 }
 
 static int g_os_n256 = 1;          // 1: layers with 64 < c_out <= 128 use the exchanged-operand kernel
-static int g_os_team_threads = 128;   // producer threads per stage of that kernel: 128, 256 or 512
-static int g_stem_variant = 0;        // stem kernel: 0 offset by offset, 1 row loads in batches, 2 two targets per thread
 static int g_os_n256_min_targets = 0; // layers with fewer targets use the 128-target tiles (finer load balance)
 
 }  // namespace sb
@@ -1394,16 +1372,11 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
   SB_CHECK_ARG((ep.scale == nullptr) == (ep.shift == nullptr), "conv_os: scale and shift must be given together");
   if (packed == nullptr) {
     SB_CHECK_ARG(weights != nullptr, "conv_os: neither weights nor a packed image given");
-    // g_stem_variant (option "stem_variant", a measurement aid): 0 (default) one target per thread and offset by offset,
-    // 1 one target per thread with the row loads in batches of 9, 2 two targets per thread offset by offset.  Measured
-    // on the 4 -> 32 stem of a 127 k-voxel scene: 28.7 / 30.8 / 33.4 us -- the variant with the most resident warps wins.
-    const int variant = (c_out <= 32) ? g_stem_variant : (g_stem_variant == 2 ? 1 : g_stem_variant);
-    const int stem_rows = variant == 2 ? 2 : 1;
-    const size_t stem_smem = static_cast<size_t>(K) * c_in * c_out * 4 + static_cast<size_t>(128) * stem_rows * K * 4;
+    const size_t stem_smem = static_cast<size_t>(K) * c_in * c_out * 4 + static_cast<size_t>(128) * K * 4;
     const bool aligned16 = reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(map_os) % 16 == 0 &&
                            (ep.residual == nullptr || reinterpret_cast<uintptr_t>(ep.residual) % 16 == 0);
     if (c_in <= 8 && (c_out == 16 || c_out == 32 || c_out == 64) && stem_smem <= 96 * 1024 && aligned16) {
-      const unsigned grid = static_cast<unsigned>(div_up(num_targets, 128 * stem_rows));
+      const unsigned grid = static_cast<unsigned>(div_up(num_targets, 128));
       auto launch = [&](auto kernel) -> int {
         SB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(stem_smem)));
         kernel<<<grid, 128, stem_smem, as_stream(stream)>>>(static_cast<const __half *>(feats), static_cast<const __half *>(weights),
@@ -1411,15 +1384,9 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
         SB_CHECK_LAUNCH();
         return SPIRA_B200_OK;
       };
-      if (variant == 2) return c_out == 16 ? launch(conv_os_stem_kernel<16, 2, 1>) : launch(conv_os_stem_kernel<32, 2, 1>);
-      if (variant == 0) {
-        if (c_out == 16) return launch(conv_os_stem_kernel<16, 1, 1>);
-        if (c_out == 32) return launch(conv_os_stem_kernel<32, 1, 1>);
-        return launch(conv_os_stem_kernel<64, 1, 1>);
-      }
-      if (c_out == 16) return launch(conv_os_stem_kernel<16, 1, 9>);
-      if (c_out == 32) return launch(conv_os_stem_kernel<32, 1, 9>);
-      return launch(conv_os_stem_kernel<64, 1, 9>);
+      if (c_out == 16) return launch(conv_os_stem_kernel<16>);
+      if (c_out == 32) return launch(conv_os_stem_kernel<32>);
+      return launch(conv_os_stem_kernel<64>);
     }
     SB_CHECK_ARG(row_of == nullptr, "conv_os_grouped: without a packed weight image only c_in <= 8 with c_out 16, 32 or 64 is covered");
     conv_os_simt_kernel<<<static_cast<unsigned>(div_up(num_targets, 4)), 128, 0, as_stream(stream)>>>(
@@ -1451,18 +1418,14 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
     Q.K = K; Q.c_in = c_in; Q.c_out = c_out;
     Q.R = K * c_in;
     Q.n_chunks = static_cast<int>(div_up(Q.R, kChunk));
-    size_t smem2 = plan_smem_n256(Q, kProducers / g_os_team_threads);
+    Q.wait_ns = wait_limit_ns();
+    size_t smem2 = plan_smem_n256(Q, kProducers / kN2TeamThreads);
     if (smem2 != 0) {
       const int grid = Q.n_tiles < sm_count() ? Q.n_tiles : sm_count();
-      auto launch = [&](auto kernel) -> int {
-        SB_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
-        kernel<<<grid, kConvThreads, smem2, as_stream(stream)>>>(Q);
-        SB_CHECK_LAUNCH();
-        return SPIRA_B200_OK;
-      };
-      if (g_os_team_threads == 512) return launch(conv_os_n256_kernel<512>);
-      if (g_os_team_threads == 256) return launch(conv_os_n256_kernel<256>);
-      return launch(conv_os_n256_kernel<128>);
+      SB_CHECK_CUDA(cudaFuncSetAttribute(conv_os_n256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem2)));
+      conv_os_n256_kernel<<<grid, kConvThreads, smem2, as_stream(stream)>>>(Q);
+      SB_CHECK_LAUNCH();
+      return SPIRA_B200_OK;
     }
   }
   ConvParams P{};
@@ -1477,6 +1440,7 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
   P.T = static_cast<int>(num_targets);
   P.n_tiles = static_cast<int>(align128(num_targets) / kRows);
   P.K = K; P.c_in = c_in; P.c_out = c_out;
+  P.wait_ns = wait_limit_ns();
   const bool tma = g_gather_tma != 0 && num_sources > 0 && K <= 512;
   P.R = K * c_in;
   // TMA gather: every offset owns ceil(c_in/64) chunks (PACK_WS image); cp.async: 64-wide chunks over the whole reduction
@@ -1552,6 +1516,7 @@ static int conv_ws_impl(const void *feats, const void *weights, const void *pack
       P.ep = ep;
       P.fused = fused ? 1 : 0;
       P.status = status;
+      P.wait_ns = wait_limit_ns();
       P.in_idx = gi; P.out_idx = go; P.naddrs = naddrs; P.qnaddrs = qnaddrs;
       P.rows = rows; P.mirror = mirror;
       // the centre row (last of the half list) is its own mirror image: its tiles are not repeated
@@ -1605,22 +1570,35 @@ extern "C" int spira_b200_set_option(const char *name, int value) {
   if (std::strcmp(name, "gather_tma") == 0) { g_gather_tma = value ? 1 : 0; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_n256") == 0) { g_os_n256 = value ? 1 : 0; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_n256_min_targets") == 0) { g_os_n256_min_targets = value < 0 ? 0 : value; return SPIRA_B200_OK; }
-  if (std::strcmp(name, "stem_variant") == 0) { g_stem_variant = (value < 0 || value > 2) ? 0 : value; return SPIRA_B200_OK; }
-  if (std::strcmp(name, "os_team_threads") == 0) {
-    SB_CHECK_ARG(value == 128 || value == 256 || value == 512, "set_option: os_team_threads must be 128, 256 or 512");
-    g_os_team_threads = value;
+  if (std::strcmp(name, "wait_limit_us") == 0) {
+    SB_CHECK_ARG(value >= 100 && value <= 60 * 1000 * 1000, "set_option: wait_limit_us must lie in [100, 60000000]");
+    g_wait_limit_us = value;
     return SPIRA_B200_OK;
   }
+  if (std::strcmp(name, "ws_barrier_skew_once") == 0) { g_ws_barrier_skew_once = value; return SPIRA_B200_OK; }
   return fail(SPIRA_B200_ERR_ARGUMENT, "set_option: unknown option '%s'", name);
+}
+
+extern "C" int spira_b200_ws_barrier_resync(void) {
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  SB_CHECK_ARG(dev >= 0 && dev < 64, "ws_barrier_resync: device %d out of range", dev);
+  SB_CHECK_CUDA(cudaDeviceSynchronize());
+  unsigned seen = 0;
+  SB_CHECK_CUDA(cudaMemcpyFromSymbol(&seen, g_grid_arrivals, sizeof(seen)));
+  g_arrivals_host[dev] = seen;
+  g_fused_bound[dev] = false;
+  g_fused_stream[dev] = nullptr;
+  return SPIRA_B200_OK;
 }
 
 extern "C" int spira_b200_get_option(const char *name) {
   if (name == nullptr) return -1;
   if (std::strcmp(name, "gather_tma") == 0) return g_gather_tma;
   if (std::strcmp(name, "os_n256") == 0) return g_os_n256;
-  if (std::strcmp(name, "os_team_threads") == 0) return g_os_team_threads;
+  if (std::strcmp(name, "wait_limit_us") == 0) return g_wait_limit_us;
+  if (std::strcmp(name, "ws_barrier_skew_once") == 0) return g_ws_barrier_skew_once;
   if (std::strcmp(name, "os_n256_min_targets") == 0) return g_os_n256_min_targets;
-  if (std::strcmp(name, "stem_variant") == 0) return g_stem_variant;
   if (std::strcmp(name, "os_pack_mode") == 0) return g_gather_tma ? SPIRA_B200_PACK_WS : SPIRA_B200_PACK_OS;
   return -1;
 }

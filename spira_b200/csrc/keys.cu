@@ -44,35 +44,6 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const VecT *__restric
   out[row * vecs_per_row + v] = in[int64_t(perm[row]) * vecs_per_row + v];
 }
 
-// Measurement aid: reads `n` rows of `row_bytes` (a multiple of 16) through an index list, 16 bytes per thread, and
-// folds them into one word per block, i.e. a row gather without the matching write.  It gives the ceiling of the access
-// pattern the convolution producers use (L2 -> SM, one row piece per lane) at full occupancy.
-__global__ void __launch_bounds__(256) gather_probe_kernel(const uint4 *__restrict__ rows, const int32_t *__restrict__ idx,
-                                                            int64_t n, int vecs_per_row, int vecs_taken,
-                                                            uint32_t *__restrict__ sink) {
-  uint32_t acc = 0;
-  const int64_t total = n * vecs_taken, step = int64_t(gridDim.x) * blockDim.x;
-  // four independent loads per thread and iteration (memory-level parallelism like the 16 copies a producer thread issues)
-  for (int64_t g0 = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; g0 < total; g0 += 4 * step) {
-    uint4 q[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int64_t g = g0 + u * step;
-      q[u] = make_uint4(0, 0, 0, 0);
-      if (g < total) {
-        const int64_t r = g / vecs_taken;
-        const int v = static_cast<int>(g - r * vecs_taken);
-        const int32_t src = idx[r];
-        if (src >= 0) q[u] = __ldcg(rows + int64_t(src) * vecs_per_row + v);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) acc ^= q[u].x ^ q[u].y ^ q[u].z ^ q[u].w;
-  }
-  acc = __reduce_xor_sync(0xffffffffu, acc);
-  if ((threadIdx.x & 31) == 0 && acc == 0x9e3779b9u) sink[blockIdx.x] = acc;   // (keeps the loads alive; practically never taken)
-}
-
 template <typename KeyT, int L>
 struct MaskPack {
   KeyT mask[L];
@@ -442,17 +413,4 @@ extern "C" int spira_b200_downsample_sorted(const void *sorted_keys, int64_t n, 
     return downsample_sorted_impl<KeyT>(static_cast<const KeyT *>(sorted_keys), n, n_levels, host_strides, host_out_keys,
                                         counts, workspace, workspace_bytes, status, as_stream(stream));
   })
-}
-
-extern "C" int spira_b200_gather_probe(const void *rows, const int32_t *idx, int64_t n, int64_t row_bytes, int64_t bytes_taken,
-                                       uint32_t *sink, void *stream) {
-  SB_CHECK_ARG(n >= 0 && row_bytes > 0 && row_bytes % 16 == 0 && bytes_taken > 0 && bytes_taken % 16 == 0 && bytes_taken <= row_bytes,
-               "gather_probe: row_bytes and bytes_taken must be multiples of 16 with bytes_taken <= row_bytes");
-  if (n == 0) return SPIRA_B200_OK;
-  SB_CHECK_ARG(rows && idx && sink && reinterpret_cast<uintptr_t>(rows) % 16 == 0, "gather_probe: null or unaligned pointer");
-  const int grid = sm_count() * 8;                       // `sink` holds one word per block
-  gather_probe_kernel<<<grid, 256, 0, as_stream(stream)>>>(static_cast<const uint4 *>(rows), idx, n, static_cast<int>(row_bytes / 16),
-                                                           static_cast<int>(bytes_taken / 16), sink);
-  SB_CHECK_LAUNCH();
-  return SPIRA_B200_OK;
 }

@@ -1,13 +1,13 @@
 // Thin inline-PTX wrappers for the sm_100a features the feature-compute kernels use:
 // mbarrier, cp.async, bulk async copies, tcgen05 (MMA / TMEM), proxy fences.
-// Every wait is bounded: it gives up after kWaitLimitNs and reports failure to the caller.
+// Every wait is bounded: it gives up after the limit the launch was given and reports failure to the caller.
 #pragma once
 
 #include <cstdint>
 
 namespace sb::ptx {
 
-constexpr unsigned long long kWaitLimitNs = 1500ull * 1000ull * 1000ull;  // 1.5 s
+constexpr int kDefaultWaitLimitUs = 1500 * 1000;  // 1.5 s; the host may choose another limit per launch
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -45,7 +45,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false if `*abort_flag` became non-zero or the time limit expired (and
 // then raises the abort flag itself so that every other role of the CTA leaves its loops too).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   int spins = 0;
@@ -53,7 +54,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63) == 0) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }

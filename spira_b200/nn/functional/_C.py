@@ -71,6 +71,8 @@ def check_status(device=None) -> None:
         if int(t.item()) != 0:
             t.zero_()
             _zero_scratch.pop(idx, None)     # a kernel that gave up may have left sums behind: start from a fresh zero scratch
+            with torch.cuda.device(idx):     # and bring the host's count of grid-barrier arrivals back in step with the device's
+                _lib.call("spira_b200_ws_barrier_resync")
             raise RuntimeError("[spira_b200] a tensor-core kernel gave up on an internal wait (status word set)")
 
 
@@ -175,11 +177,40 @@ def _strides_double(strides) -> bool:
 
 
 class PendingLevels:
-    """Down-sampling whose kernels are enqueued and whose level sizes are on their way to the host."""
-    __slots__ = ("coordinates", "strides", "bufs", "counts", "host", "done", "levels")
+    """Down-sampling whose kernels are enqueued and whose level sizes are on their way to the host.  Every pending
+    build owns its landing slot (pinned buffer + event) until its sizes have been read, so that several builds --
+    other caches, models or scenes -- can be in flight at once."""
+    __slots__ = ("coordinates", "strides", "bufs", "counts", "host", "done", "levels", "slot", "device_index")
+
+    def __del__(self):          # a build that was dropped without being completed gives its slot back
+        _release_slot(self)
 
 
-_side_channel = {}      # device index -> (side stream, pinned int32 buffer, its address, "sizes arrived" event, event handle)
+_side_stream = {}       # device index -> side stream of the size read-backs
+_free_slots = {}        # device index -> [(pinned int32 buffer, its address, "sizes arrived" event, event handle), ...]
+
+
+def _take_slot(idx: int, dev, side):
+    free = _free_slots.setdefault(idx, [])
+    if free:
+        return free.pop()
+    host = torch.zeros(MAX_LEVELS + 1, dtype=torch.int32).pin_memory()
+    done = torch.cuda.Event()
+    done.record(side)                       # creates the underlying event, whose handle the library records later
+    return (host, host.data_ptr(), done, done.cuda_event)
+
+
+def _release_slot(p) -> None:
+    slot = getattr(p, "slot", None)
+    if slot is not None:
+        p.slot = None
+        try:
+            slot[2].synchronize()           # the copy into the buffer (if one is in flight) has landed
+            _free_slots.setdefault(p.device_index, []).append(slot)
+        except Exception:                   # interpreter shutdown: nothing to recycle
+            pass
+
+
 _ds_ws_bytes = {}       # (n, key bytes) -> workspace bytes of the sort-free down-sampling
 _ds_strides = {}        # strides tuple -> ctypes int32 array
 
@@ -204,14 +235,9 @@ def streamed_output_generate_begin(coordinates: torch.Tensor, target_strides) ->
     coordinates = coordinates.contiguous()
     n, kb, dev = coordinates.shape[0], _key_bytes(coordinates), coordinates.device
     idx = dev.index if dev.index is not None else torch.cuda.current_device()
-    chan = _side_channel.get(idx)
-    if chan is None:
-        side = torch.cuda.Stream(device=dev)
-        host = torch.zeros(MAX_LEVELS + 1, dtype=torch.int32).pin_memory()
-        done = torch.cuda.Event()
-        done.record(side)                       # creates the underlying event, whose handle the library records later
-        chan = _side_channel[idx] = (side, host, host.data_ptr(), done, done.cuda_event)
-    side, host, host_ptr, done, done_handle = chan
+    side = _side_stream.get(idx)
+    if side is None:
+        side = _side_stream[idx] = torch.cuda.Stream(device=dev)
     need = _ds_ws_bytes.get((n, kb))
     if need is None:
         size = C.c_size_t()
@@ -220,6 +246,8 @@ def streamed_output_generate_begin(coordinates: torch.Tensor, target_strides) ->
             _ds_ws_bytes.clear()
         need = _ds_ws_bytes[(n, kb)] = size.value
     p = PendingLevels()
+    p.device_index, p.slot = idx, _take_slot(idx, dev, side)
+    host, host_ptr, done, done_handle = p.slot
     p.coordinates, p.strides, p.levels = coordinates, strides, L
     p.bufs = torch.empty((L, n), dtype=coordinates.dtype, device=dev)
     p.counts = torch.empty(L + 1, dtype=torch.int32, device=dev)      # [L] = "the input was not sorted"
@@ -239,6 +267,7 @@ def streamed_output_generate_end(p: PendingLevels) -> List[torch.Tensor]:
     p.done.synchronize()
     L = p.levels
     host_counts = p.host[:L + 1].tolist()
+    _release_slot(p)
     if host_counts[L] != 0:      # the keys were not sorted: take the sorting path
         global SORT_FREE_DOWNSAMPLE
         SORT_FREE_DOWNSAMPLE, keep = False, SORT_FREE_DOWNSAMPLE

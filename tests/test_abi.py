@@ -67,7 +67,7 @@ def test_more_argument_errors_without_a_gpu(lib):
     assert lib.spira_b200_kmap_ws_lists(None, 17, None) != 0 and b"n_maps" in lib.spira_b200_last_error()
     assert lib.spira_b200_kmap_group(None, 0, None, 0, None) == 0       # nothing to do
     assert lib.spira_b200_downsample_sorted_workspace(10, 3, ctypes.byref(n)) != 0
-    assert lib.spira_b200_set_option(b"os_team_threads", 100) != 0
+    assert lib.spira_b200_set_option(b"wait_limit_us", 1) != 0 and b"wait_limit_us" in lib.spira_b200_last_error()
     assert lib.spira_b200_set_option(b"no_such_option", 1) != 0 and lib.spira_b200_get_option(b"no_such_option") == -1
-    assert lib.spira_b200_get_option(b"os_team_threads") == 128 and lib.spira_b200_get_option(b"os_n256") == 1
+    assert lib.spira_b200_get_option(b"wait_limit_us") == 1500000 and lib.spira_b200_get_option(b"os_n256") == 1
     assert lib.spira_b200_read_back(None, None, 4, None, None, None) != 0

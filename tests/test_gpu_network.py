@@ -285,3 +285,28 @@ def test_network_on_64_bit_keys_matches_32_bit_keys(lib, dataflow):
     else:
         assert_features_close(y64, y32, rtol=1e-2, atol=4e-3)
     _C.check_status()
+
+
+def test_two_map_builds_in_flight_keep_their_own_level_sizes(lib):
+    """Two caches start their network-wide builds before either reads its level sizes back: every pending build owns
+    its pinned landing buffer, so neither sees the other scene's sizes."""
+    from spira_b200 import models, scenes, nn as spnn
+    from spira_b200.nn.functional import _C
+    ks, ss, ts = models.map_schedule(3, 3, 3)
+    scenes_k, caches = [], []
+    for seed, n in ((7, 30000), (8, 9000)):
+        c = scenes.lidar_scene(seed)[:n]
+        keys, _ = _C.cuda_flatten_sort(torch.from_numpy(c).cuda(), False)
+        scenes_k.append(keys)
+    for keys in scenes_k:                    # both builds are pending now
+        cache = spnn.KernelMapCache()
+        cache.add_all_kernel_maps(keys, ks, ss, ts, (1, 1, 1), [0] * len(ks))
+        assert cache._pending is not None
+        caches.append(cache)
+    for keys, cache in zip(scenes_k, caches):
+        host = keys.cpu().numpy().view(np.uint32)
+        for stride in ts:
+            want = O.downsample(host, stride)
+            got = cache._coordinates_cache[stride].cpu().numpy().view(np.uint32)
+            assert np.array_equal(got, want), f"level {stride} of a scene with {len(host)} voxels"
+    _C.check_status()
