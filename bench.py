@@ -9,9 +9,11 @@ forward pass.  Default workload: MinkUNet18-style network, fp16, random init, on
 (the headline workload).  With N > 1 (launched by torch.distributed.run) every rank owns one GPU and its own
 scenes; nothing is exchanged on the data path, so scaling is weak and ``value`` = scenes of all ranks / slowest rank.
 
-``--impl reference`` drives the reference's own native module (built from its unmodified sources into
-``oracle/_ref/_C.so``) through the same Python glue, model definition and timing loop.  The reference has no CPU
-implementation of this path; if its module is unavailable the arm times the CPU oracle port instead.
+``--impl reference`` is the stock reference: its own Python package (``SparseTensor``, ``KernelMapCache``, ``SparseConv``,
+``tune`` over all nine dataflows) driving its own native module, both taken from ``oracle/_ref`` (built and staged from the
+unmodified sources by ``oracle/build_ref.py``), on a network assembled from the reference's own blocks.
+``--impl reference-kernels`` runs the same native module behind this repository's Python glue and model classes instead.
+The reference has no CPU implementation of this path; if its module is unavailable the arm times the CPU oracle port.
 
 Prints ONE JSON line (rank 0).
 """
@@ -71,65 +73,91 @@ def make_workload(name: str):
 
 
 # ------------------------------------------------------------------------------------------------
-# the reference's native module behind this repo's Python glue
+# the reference (test infrastructure under oracle/: only the reference arm touches it)
 # ------------------------------------------------------------------------------------------------
-class ReferenceModule:
-    """Adapter: the reference's pybind module plus the three helpers this repo's glue calls that are plain torch
-    operations in the reference's own Python (feature permutation ``features[index]``, ``map.T.contiguous()``)."""
-    LAYOUT_OS, LAYOUT_WS = 0, 1
-    CACHE_DERIVED = False   # the reference rebuilds the inverted map of a transposed layer on every forward
-
-    def __init__(self, mod):
-        self._mod = mod
-
-    def __getattr__(self, name):
-        return getattr(self._mod, name)
-
-    def cuda_flatten_sort(self, coords, double=False):
-        keys, perm = self._mod.cuda_flatten_sort(coords, double)
-        if (keys.numel() * keys.element_size()) % 512 == 0:
-            # the reference's search reads sources[num_sources] (kernels/query_sorted.cuh:42,48); keep that read
-            # inside an allocation when the tensor ends exactly on an allocator block boundary
-            big = torch.empty(keys.numel() + 64, dtype=keys.dtype, device=keys.device)
-            big[:keys.numel()] = keys
-            keys = big[:keys.numel()]
-        return keys, perm
-
-    @staticmethod
-    def permute_rows(rows, perm):
-        return rows[perm.to(torch.int64)]
-
-    @staticmethod
-    def transpose_map(m):
-        return m.T.contiguous()
-
-    @staticmethod
-    def _aligned(n):
-        return (n + 127) // 128 * 128
-
-    @staticmethod
-    def check_status(device=None):
-        return None
+def reference_tools():
+    """``oracle/reference_module.py``: loaders for the reference's native module, Python package and model blocks."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import reference_module
+    return reference_module
 
 
-def load_reference_module():
-    so = ROOT / "oracle" / "_ref" / "_C.so"
-    if not so.exists():
-        return None
-    import importlib.util
-    spec = importlib.util.spec_from_file_location("_C", str(so))
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    return ReferenceModule(mod)
+def schedule(n_down: int, kernel: int = 3, resample_kernel: int = 3):
+    """(kernel_sizes, source_strides, target_strides) of ``KernelMapCache.add_all_kernel_maps`` for a network with
+    ``n_down`` stride-2 levels, in the builder's alternating order (scripts/end_to_end_experiment.py:107-112)."""
+    kernel_sizes, source_strides, target_strides = [], [(1, 1, 1)], []
+    s = 1
+    for level in range(n_down + 1):
+        kernel_sizes.append((kernel,) * 3)
+        source_strides.append((s,) * 3)
+        if level < n_down:
+            kernel_sizes.append((resample_kernel,) * 3)
+            s *= 2
+            source_strides.append((s,) * 3)
+            target_strides.append((s,) * 3)
+    return kernel_sizes, source_strides, target_strides
 
 
-def install_native(module) -> None:
-    """Points every glue module of the package at ``module`` instead of the built-in binding."""
-    import spira_b200.nn.functional as F
-    from spira_b200.nn import conv
-    from spira_b200.nn.functional import indexing, convolution, memory
-    for m in (F, conv, indexing, convolution, memory):
-        m._C = module
+class StockReferenceEngine:
+    """The reference as its users run it: its own Python package on its own native module, a network assembled from its
+    own blocks, dataflows chosen by its own ``spira.tune`` (spira/utils/helpers.py:388-618)."""
+
+    def __init__(self, workload_name, workload, device):
+        self.R = reference_tools()
+        self.sp = self.R.load_package()
+        torch.manual_seed(0)
+        self.model = self.R.build_network(workload_name, self.sp).to(device).half().eval()
+        self.cache = self.sp.nn.KernelMapCache()
+        self.sp.set_kernel_map_cache(self.model, self.cache)
+        self.ks, self.ss, self.ts = schedule(workload["n_down"], 3, 3)
+        self.layer_strides = [tuple(b // a for a, b in zip(self.ss[i], self.ss[i + 1])) for i in range(len(self.ks))]
+        self.dataflows = [0] * len(self.ks)
+        self.tune_note = None
+
+    def tune(self, dev_scenes, save_dir, n_samples=5):
+        """``spira.tune`` as scripts/end_to_end_experiment.py:122-151 calls it.  The tuner needs more than three samples
+        (it discards the first three of every configuration, helpers.py:236), so the scenes are cycled.  Layers with 3 or
+        5 input channels cannot run the mask-format dataflows (the gather tile sizes must be multiples of four,
+        spira/nn/conv.py:261): if the full search fails, it is repeated without them."""
+        sp = self.sp
+
+        def loader():
+            i = 0
+            while True:
+                c, f = dev_scenes[i % len(dev_scenes)]
+                yield sp.SparseTensor(features=f.clone(), coordinates=c.clone()).order()
+                i += 1
+
+        last = None
+        for options, gs in ((None, True), ([0, 1, 3, 5, 7], False), ([0, 1], False)):
+            self.cache.reset()  # (the tuner's structure pass runs on whatever maps a failed attempt left behind)
+            if not gs:          # a restricted search starts from a dataflow every layer can run
+                for m in self.model.modules():
+                    if hasattr(m, "_tunable_config"):
+                        m._tunable_config["map_dataflow"], m._tunable_config["force_os"] = 0, False
+            try:
+                _, chosen = sp.tune(model=self.model, data_loader=loader(), kernel_map_cache=self.cache, map_dataflow_options=options,
+                                    test_force_os=True, n_samples=n_samples, force_retune=True, save_dir=save_dir, verbose=False,
+                                    allow_gs_tuning=gs, return_dataflows=True)
+            except (RuntimeError, ValueError, KeyError) as e:
+                last = e
+                try:
+                    sp.nn.functional.cuda_reset_error()
+                except Exception:
+                    pass
+                continue
+            self.dataflows = [chosen.get((self.ss[i], self.ks[i], self.layer_strides[i]), 0) for i in range(len(self.ks))]
+            self.tune_note = {"tuner": "spira.tune (reference)", "map_dataflow_options": options or list(range(9)),
+                              "per_group": {str(k): v for k, v in chosen.items()}}
+            return
+        raise RuntimeError(f"the reference's tuner failed on every option set: {last}")
+
+    def step(self, coords, feats):
+        x = self.sp.SparseTensor(features=feats, coordinates=coords).order()
+        self.cache.reset()
+        self.cache.add_all_kernel_maps(x._coordinates, self.ks, self.ss, self.ts, (1, 1, 1), self.dataflows)
+        with torch.no_grad():
+            return self.model(x)._features
 
 
 # ------------------------------------------------------------------------------------------------
@@ -347,8 +375,10 @@ def timed_loop(step_fn, n_steps, warmup, l2buf, dist_ctx, drain_fn=None):
     from spira_b200 import sharding
     gc.unfreeze()
     per_step = [a.elapsed_time(b) for a, b in evs]
-    total_ms = sharding.max_over_ranks(sum(per_step), torch.device("cuda"))
-    return total_ms, wall + (per_step,)
+    dev_ = torch.device("cuda")
+    return {"median_ms": sharding.max_over_ranks(statistics.median(per_step), dev_),
+            "mean_ms": sharding.max_over_ranks(sum(per_step) / len(per_step), dev_),
+            "steps": per_step, "enqueue_ms": wall[1] * 1e3 / n_steps, "wall_s": wall[0]}
 
 
 def profile_kernels(engine, scene):
@@ -416,33 +446,78 @@ def profile_kernels(engine, scene):
     return out, layers
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the 42 convolution launches of one default step, from the
-# ncu launch list of that step (profiles/minkunet_step_launch_list.md); valid for the default workload only
-NCU_CONV_DRAM_BYTES_PER_STEP = {"minkunet": 693_949_696}
+def kernel_source_sha() -> str:
+    """Hash of the CUDA sources of the library: a captured DRAM-traffic figure is only valid for the kernels it was
+    captured from."""
+    import hashlib
+    h = hashlib.sha256()
+    for f in sorted((ROOT / "spira_b200" / "csrc").glob("*.cu*")):
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()[:16]
 
 
-def roofline_from_layers(layers, pk, pk_kind, workload=None):
-    if not layers:
+def captured_traffic(kernel: str, workload: str):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of ``kernel`` on ``workload`` from the ncu
+    capture recorded in ``profiles/dram_traffic.json``, or None when there is no capture of the CURRENT kernel sources."""
+    p = ROOT / "profiles" / "dram_traffic.json"
+    if not p.exists():
         return None
+    try:
+        table = json.loads(p.read_text())
+    except Exception:
+        return None
+    sha = kernel_source_sha()
+    for e in table.get("captures", []):
+        if e.get("kernel") == kernel and e.get("workload") == workload and e.get("source_sha") == sha:
+            return int(e["dram_bytes_per_launch"])
+    return None
+
+
+def roofline_of(layers, pk, pk_kind, peak_key):
+    """achieved / peak of a set of layers from their live CUDA-event times: FLOPs against the tensor peak or algorithmic
+    bytes against the HBM peak, whichever ideal time is larger."""
     t_ms = sum(l["ms"] for l in layers)
-    step_traffic = NCU_CONV_DRAM_BYTES_PER_STEP.get(workload)
-    traffic = None if step_traffic is None else int(step_traffic / len(layers))      # per launch, like `achieved`
     flops = sum(l["flops"] for l in layers)
     byts = sum(l["bytes"] for l in layers)
-    ideal_tensor_ms = flops / (pk["bf16_tflops_sustained"] * 1e12) * 1e3
+    ideal_tensor_ms = flops / (pk[peak_key] * 1e12) * 1e3
     ideal_hbm_ms = byts / (pk["hbm_gbs"] * 1e9) * 1e3
+    common = {"peak_source": f"of {pk_kind}", "launches": len(layers), "kernel_ms": round(t_ms, 4),
+              "algorithmic_flops": int(flops), "algorithmic_bytes": int(byts),
+              "tflops": round(flops / (t_ms * 1e-3) / 1e12, 2), "gbs": round(byts / (t_ms * 1e-3) / 1e9, 1)}
     if ideal_hbm_ms >= ideal_tensor_ms:
         ach = byts / (t_ms * 1e-3) / 1e9
-        return {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(ach / pk["hbm_gbs"], 4),
-                "traffic": traffic, "kernel": "conv_os_n256_kernel / conv_tc_kernel / conv_os_stem_kernel (all sparse-convolution layers of one scene)",
-                "peak_source": f"of {pk_kind}", "launches": len(layers), "kernel_ms_per_step": round(t_ms, 4),
-                "algorithmic_bytes_per_step": int(byts), "tflops": round(flops / (t_ms * 1e-3) / 1e12, 2)}
+        return dict({"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(ach / pk["hbm_gbs"], 4)}, **common)
     ach = flops / (t_ms * 1e-3) / 1e12
-    return {"bound": "tensor", "achieved": round(ach, 2), "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
-            "frac": round(ach / pk["bf16_tflops_sustained"], 4), "traffic": traffic,
-            "kernel": "conv_os_n256_kernel / conv_tc_kernel / conv_os_stem_kernel (all sparse-convolution layers of one scene)", "peak_source": f"of {pk_kind}",
-            "launches": len(layers), "kernel_ms_per_step": round(t_ms, 4), "algorithmic_flops_per_step": int(flops),
-            "gbs": round(byts / (t_ms * 1e-3) / 1e9, 1)}
+    return dict({"bound": "tensor", "achieved": round(ach, 2), "peak": pk[peak_key], "unit": "TFLOP/s", "frac": round(ach / pk[peak_key], 4)}, **common)
+
+
+def roofline_from_layers(layers, pk, pk_kind, workload_label):
+    """Roofline of the DOMINANT kernel of a step (largest share of the measured convolution time) with its own achieved /
+    peak; ``conv_class`` carries the aggregate over all sparse-convolution launches and ``per_kernel`` the shares."""
+    if not layers:
+        return None
+    from spira_b200 import _lib
+    lib = _lib.load()
+    by_kernel = {}
+    for l in layers:
+        ws = 0 if "conv_os" in l["kernel"] else 1
+        kid = lib.spira_b200_conv_kernel_choice(ws, l["K"], l["cin"], l["cout"], l["T"])
+        by_kernel.setdefault(_lib.KERNEL_NAMES.get(kid, "unknown"), []).append(l)
+    total_ms = sum(l["ms"] for l in layers)
+    name, group = max(by_kernel.items(), key=lambda kv: sum(l["ms"] for l in kv[1]))
+    # the kernels run inside a long step: the sustained figure is the denominator
+    roof = roofline_of(group, pk, pk_kind, "bf16_tflops_sustained")
+    roof["kernel"] = name
+    roof["share_of_conv_time"] = round(sum(l["ms"] for l in group) / total_ms, 3)
+    traffic = captured_traffic(name, workload_label)
+    roof["traffic"] = traffic
+    roof["traffic_source"] = None if traffic is None else "profiles/dram_traffic.json (ncu capture of the current kernel sources, mean per launch)"
+    roof["per_kernel"] = {k: {"launches": len(v), "ms": round(sum(l["ms"] for l in v), 4),
+                              "frac": roofline_of(v, pk, pk_kind, "bf16_tflops_sustained")["frac"]} for k, v in by_kernel.items()}
+    roof["conv_class"] = roofline_of(layers, pk, pk_kind, "bf16_tflops_sustained")
+    roof["kernel_ms_per_step"] = round(total_ms, 4)
+    return roof
 
 
 # ------------------------------------------------------------------------------------------------
@@ -491,7 +566,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)     # (scenes of ~2 ms: 32 steps keep one slow step from moving the mean)
     ap.add_argument("--warmup", type=int, default=4)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-kernels"])
+    ap.add_argument("--no-batch16", action="store_true", help="skip the 16-scene sharded SECOND-style batch reported as c4_batch16")
     ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap"])
     ap.add_argument("--no-group", action="store_true", help="output-stationary maps keep their target order (no grouping by neighbour pattern)")
     ap.add_argument("--no-defer", action="store_true", help="add_all_kernel_maps completes all maps before it returns")
@@ -539,6 +615,17 @@ def main():
         from spira_b200.nn.functional import _C as native
         native.set_option("gather_tma", 1 if args.gather == "tma" else 0)
     if args.workload in ("layer", "kmap"):
+        if args.impl != "ours":
+            if rank == 0:
+                if reference_tools().available():
+                    line = {"layer": run_layer_reference, "kmap": run_kmap_reference}[args.workload](args, device, pk, pk_kind)
+                    line.update(n_gpus=n_gpus, impl="reference")
+                else:
+                    line = {"impl": "reference", "unavailable": "the reference's native module is not built (oracle/_ref/_C.so missing)"}
+                print(json.dumps(line))
+            if dist_ctx:
+                torch.distributed.destroy_process_group()
+            return
         from spira_b200 import build, _lib
         build.build()
         _lib.load()
@@ -550,34 +637,122 @@ def main():
             torch.distributed.destroy_process_group()
         return
     wl = make_workload(args.workload)
-    from spira_b200 import scenes as sc
-
-    ref_mod = None
-    if args.impl == "reference":
-        ref_mod = load_reference_module()
-        if ref_mod is None:
-            if rank == 0:
-                run_reference_port(args, wl, n_gpus)
-            if dist_ctx:
-                torch.distributed.destroy_process_group()
-            return
-        install_native(ref_mod)
-    else:
+    if args.impl != "ours" and not reference_tools().available():
+        if rank == 0:
+            run_reference_port(args, wl, n_gpus)
+        if dist_ctx:
+            torch.distributed.destroy_process_group()
+        return
+    if args.impl == "ours":
         from spira_b200 import build, _lib
         build.build()
         _lib.load()
 
-    # scenes of this rank: resident on the device AND in pinned host memory (for the end-to-end number)
-    seeds = [s + 100 * rank for s in wl["seeds"]]
+    host, dev = load_scenes(wl, [s + 100 * rank for s in wl["seeds"]], device)
+    n_vox = [len(h[0]) for h in host]
+    engine, chosen_note = make_engine(args, args.workload, wl, device, dev, rank)
+    l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+    from spira_b200 import _lib
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    m = measure(engine, host, dev, args, l2buf, dist_ctx, device)
+    clocks = sampler.stop() if rank == 0 else None
+
+    line = {
+        "metric": "MinkUNet scene throughput (scene latency = ms_per_step)" if args.workload == "minkunet" else f"{args.workload} scene throughput",
+        "value": round(n_gpus * 1e3 / m["median_ms"], 3), "unit": "scenes/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(m["median_ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 (fp32 accumulate); u32 packed keys", "data": "synthetic",
+        "config": {"workload": wl["label"], "voxels_per_scene": n_vox, "scenes_per_rank": len(dev),
+                   "timed_region": "order() + add_all_kernel_maps() + model forward, per scene",
+                   "statistic": "median of the K per-step device times, slowest rank (the mean is in mean_ms_per_step); both arms alike",
+                   "l2": "256 MiB buffer rewritten between timed steps",
+                   "setup": "tune / compile, then every scene once untimed (allocator priming), then the W warm-up steps",
+                   "dataflows": chosen_note, "sharding": "independent scenes per GPU, no collective",
+                   "fused_epilogue": bool(args.impl == "ours" and not args.no_fuse),
+                   "recorded_tape": bool(args.impl == "ours" and not args.no_compile)},
+        "e2e": {"value": round(n_gpus * 1e3 / m["e2e_median_ms"], 3), "unit": "scenes/s", "ms_per_step": round(m["e2e_median_ms"], 4),
+                "mean_ms_per_step": round(m["e2e_mean_ms"], 4), "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"]},
+        "mean_ms_per_step": round(m["mean_ms"], 4),
+        "gpu_launches": m["launches"] if args.impl == "ours" else 0,
+        "host_enqueue_ms_per_step": round(m["enqueue_ms"], 4),
+        "step_ms_min_median_max": [round(min(m["steps"]), 4), round(statistics.median(m["steps"]), 4), round(max(m["steps"]), 4)],
+        "step_ms_first": [round(v, 4) for v in m["steps"][:8]],
+        "clocks": clocks,
+    }
+    if args.impl != "ours":
+        line["impl"] = args.impl
+        line["cpu_baseline"] = {"value": line["value"], "unit": "scenes/s", "cores": 0, "kind": "reference",
+                                "sample": "the reference's own CUDA kernels (its unmodified sources built for sm_100) on the GPU: it has no CPU path"}
+    else:
+        # roofline of the dominant kernel + secondary metrics, measured live with CUDA events
+        per_call, layers = profile_kernels(engine, dev[0])
+        line["roofline"] = roofline_from_layers(layers, pk, pk_kind, wl["label"])
+        if args.dump_layers and rank == 0:
+            Path(args.dump_layers).parent.mkdir(parents=True, exist_ok=True)
+            Path(args.dump_layers).write_text(json.dumps([{k: (list(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in layers], indent=0))
+        km = per_call.get("spira_b200_kmap_search")
+        if km:
+            maps_bytes = 0
+            for key, entry in engine.cache._kernel_maps_cache.items():
+                S, T = entry[1], entry[2]
+                K = int(np.prod(key[2]))
+                maps_bytes += (S + T) * 4 + K * ((T + 127) // 128 * 128) * 4
+            line["kernel_map_build"] = {"search_kernel_ms": round(km["ms"], 4), "maps": len(engine.cache._kernel_maps_cache),
+                                        "algorithmic_bytes": maps_bytes, "gbs": round(maps_bytes / (km["ms"] * 1e-3) / 1e9, 1),
+                                        "frac_of_hbm_peak": round(maps_bytes / (km["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+        line["native_calls_ms"] = {k.replace("spira_b200_", ""): round(v["ms"], 4) for k, v in per_call.items()}
+        if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+            # bounded sample: whole scenes (the layer shapes of scene 0 on the coordinates of every scene in turn) until
+            # about ten seconds of CPU work are done
+            scenes_done, cpu_s, n_done, share = 0.0, 0.0, 0, 1.0
+            while cpu_s < 10.0 and scenes_done < 64:
+                est, spent, n_done, share = cpu_scene_pass(host[int(scenes_done) % len(host)][0].numpy(), layers)
+                cpu_s += spent
+                scenes_done += share
+                if share < 1.0:
+                    break
+            line["cpu_baseline"] = {"value": round(scenes_done / cpu_s, 5), "unit": "scenes/s", "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": f"oracle port: sort + kernel maps (numpy) + {n_done}/{len(layers)} conv layers "
+                                              f"(torch-CPU gather-GEMM-scatter) per scene, {scenes_done:.2f} scenes in {cpu_s:.1f} s; BN/ReLU omitted"}
+    if not args.no_batch16:
+        del engine
+        line["c4_batch16"] = run_batch16(args, device, rank, world, dist_ctx, l2buf)
+    if rank == 0:
+        print(json.dumps(line))
+    if dist_ctx:
+        torch.distributed.destroy_process_group()
+
+
+def load_scenes(wl, seeds, device):
+    """Scenes resident on the device AND in pinned host memory (for the end-to-end number).  A scene whose key tensor
+    would end exactly on an allocator block boundary loses its last voxel, both arms alike: the reference's search reads
+    one key past its source array (csrc/spira/cuda/kernels/query_sorted.cuh:42,48)."""
+    from spira_b200 import scenes as sc
     host, dev = [], []
     for s in seeds:
         c = wl["scene"](s)
+        if len(c) % 64 == 0:
+            c = c[:-1]
         f = sc.features(len(c), wl["channels"], s, wl["feat_kind"])
         hc, hf = torch.from_numpy(c).pin_memory(), torch.from_numpy(f).pin_memory()
         host.append((hc, hf))
         dev.append((hc.to(device), hf.to(device)))
-    n_vox = [len(h[0]) for h in host]
+    return host, dev
 
+
+def make_engine(args, workload_name, wl, device, dev, rank):
+    """The engine of the chosen arm with its dataflows selected: (engine, note for the JSON line)."""
+    if args.impl == "reference":
+        engine = StockReferenceEngine(workload_name, wl, device)
+        engine.tune(dev, os.path.join(tempfile.gettempdir(), f"spira_ref_tune_{workload_name}_r{rank}"))
+        return engine, engine.tune_note
+    if args.impl == "reference-kernels":
+        R = reference_tools()
+        ref_mod = R.ReferenceModule()
+        R.install_native(ref_mod)
     engine = Engine(wl, device)
     if args.impl == "ours" and not args.no_fuse:
         import spira_b200 as sp_
@@ -593,11 +768,11 @@ def main():
             for c, f in dev:
                 yield sp.SparseTensor(c, f).order()
         _, chosen = sp.tune(engine.model, loader(), engine.cache, n_samples=2, save_dir=os.path.join(tempfile.gettempdir(), "spira_b200_tune"),
-                            tune_tag=f"{args.workload}_r{rank}", force_retune=True, return_dataflows=True, verify=False)
+                            tune_tag=f"{workload_name}_r{rank}", force_retune=True, return_dataflows=True, verify=False)
         engine.apply_groups(chosen)
         chosen_note = {str(k): v for k, v in chosen.items()}
     else:
-        # the reference tunes per layer group with dozens of whole-model runs; here: the best UNIFORM dataflow of 0/1/2
+        # the reference's kernels behind this repository's glue: the best UNIFORM dataflow of 0/1/2 first
         best = None
         for df in (0, 1, 2):
             try:
@@ -618,8 +793,7 @@ def main():
                 best = (df, t)
         engine.set_uniform_dataflow(best[0])
         chosen_note = {"uniform_map_dataflow": best[0]}
-        # then, like the reference's own tuner (spira/utils/helpers.py:388-618), per layer group: every group tries the
-        # other dataflows on whole-model runs and keeps what is faster
+        # then per layer group: every group tries the other dataflows on whole-model runs and keeps what is faster
         try:
             tuned = tune_reference_groups(engine, dev, best[0])
             if tuned is not None:
@@ -627,10 +801,13 @@ def main():
         except RuntimeError:
             ref_mod.cuda_reset_error()
             engine.set_uniform_dataflow(best[0])
-
     if args.impl == "ours" and not args.no_compile:
         engine.compile(*dev[0])
-    l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+    return engine, chosen_note
+
+
+def measure(engine, host, dev, args, l2buf, dist_ctx, device):
+    """The two timed loops of an arm: scenes resident in HBM, then end to end through pinned host buffers."""
     from spira_b200 import _lib
 
     def step_resident(i):
@@ -701,80 +878,43 @@ def main():
         step_resident(i)
         step_e2e(i)
     torch.cuda.synchronize()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches0 = _lib.launch_count
-    total_ms, wall = timed_loop(step_resident, args.steps, args.warmup, l2buf, dist_ctx)
+    res = timed_loop(step_resident, args.steps, args.warmup, l2buf, dist_ctx)
     launches = _lib.launch_count - launches0
-    e2e_ms, _ = timed_loop(step_e2e, args.steps, args.warmup, l2buf, dist_ctx, drain_e2e)
-    clocks = sampler.stop() if rank == 0 else None
+    e2e = timed_loop(step_e2e, args.steps, args.warmup, l2buf, dist_ctx, drain_e2e)
+    return {"median_ms": res["median_ms"], "mean_ms": res["mean_ms"], "steps": res["steps"], "enqueue_ms": res["enqueue_ms"],
+            "e2e_median_ms": e2e["median_ms"], "e2e_mean_ms": e2e["mean_ms"], "launches": launches,
+            "h2d": int(np.mean([h[0].numel() * 4 + h[1].numel() * 2 for h in host])), "d2h": int(d2h_bytes[0])}
 
-    ms_per_step = total_ms / args.steps
-    value = n_gpus * args.steps / (total_ms / 1e3)
-    e2e_value = n_gpus * args.steps / (e2e_ms / 1e3)
-    h2d = int(np.mean([h[0].numel() * 4 + h[1].numel() * 2 for h in host]))
-    d2h = int(d2h_bytes[0])
 
-    line = {
-        "metric": "MinkUNet scene throughput (scene latency = ms_per_step)" if args.workload == "minkunet" else f"{args.workload} scene throughput",
-        "value": round(value, 3), "unit": "scenes/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16 (fp32 accumulate); u32 packed keys", "data": "synthetic",
-        "config": {"workload": wl["label"], "voxels_per_scene": n_vox, "scenes_per_rank": len(dev),
-                   "timed_region": "order() + add_all_kernel_maps() + model forward, per scene",
-                   "l2": "256 MiB buffer rewritten between timed steps",
-                   "setup": "tune / compile, then every scene once untimed (allocator priming), then the W warm-up steps",
-                   "dataflows": chosen_note, "sharding": "independent scenes per GPU, no collective",
-                   "fused_epilogue": bool(args.impl == "ours" and not args.no_fuse),
-                   "recorded_tape": bool(args.impl == "ours" and not args.no_compile)},
-        "e2e": {"value": round(e2e_value, 3), "unit": "scenes/s", "ms_per_step": round(e2e_ms / args.steps, 4),
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches if args.impl == "ours" else 0,
-        "host_enqueue_ms_per_step": round(wall[1] * 1e3 / args.steps, 4),
-        "step_ms_min_median_max": [round(min(wall[2]), 4), round(statistics.median(wall[2]), 4), round(max(wall[2]), 4)],
-        "step_ms_first": [round(v, 4) for v in wall[2][:8]],
-        "clocks": clocks,
-    }
-    if args.impl == "reference":
-        line["impl"] = "reference"
-        line["cpu_baseline"] = {"value": line["value"], "unit": "scenes/s", "cores": 0, "kind": "reference",
-                                "sample": "the reference's own CUDA kernels (its unmodified sources built for sm_100) on the GPU: it has no CPU path"}
-    else:
-        # roofline of the dominant kernel class + secondary metrics, measured live with CUDA events
-        per_call, layers = profile_kernels(engine, dev[0])
-        line["roofline"] = roofline_from_layers(layers, pk, pk_kind, args.workload if args.dataflow == "auto" else None)
-        if args.dump_layers and rank == 0:
-            Path(args.dump_layers).parent.mkdir(parents=True, exist_ok=True)
-            Path(args.dump_layers).write_text(json.dumps([{k: (list(v) if isinstance(v, tuple) else v) for k, v in l.items()} for l in layers], indent=0))
-        km = per_call.get("spira_b200_kmap_search")
-        if km:
-            maps_bytes = 0
-            for key, entry in engine.cache._kernel_maps_cache.items():
-                S, T = entry[1], entry[2]
-                K = int(np.prod(key[2]))
-                maps_bytes += (S + T) * 4 + K * ((T + 127) // 128 * 128) * 4
-            line["kernel_map_build"] = {"search_kernel_ms": round(km["ms"], 4), "maps": len(engine.cache._kernel_maps_cache),
-                                        "algorithmic_bytes": maps_bytes, "gbs": round(maps_bytes / (km["ms"] * 1e-3) / 1e9, 1),
-                                        "frac_of_hbm_peak": round(maps_bytes / (km["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
-        line["native_calls_ms"] = {k.replace("spira_b200_", ""): round(v["ms"], 4) for k, v in per_call.items()}
-        if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
-            # bounded sample: whole scenes (the layer shapes of scene 0 on the coordinates of every scene in turn) until
-            # about ten seconds of CPU work are done
-            scenes_done, cpu_s, n_done, share = 0.0, 0.0, 0, 1.0
-            while cpu_s < 10.0 and scenes_done < 64:
-                est, spent, n_done, share = cpu_scene_pass(host[int(scenes_done) % len(host)][0].numpy(), layers)
-                cpu_s += spent
-                scenes_done += share
-                if share < 1.0:
-                    break
-            line["cpu_baseline"] = {"value": round(scenes_done / cpu_s, 5), "unit": "scenes/s", "cores": torch.get_num_threads(), "kind": "port",
-                                    "sample": f"oracle port: sort + kernel maps (numpy) + {n_done}/{len(layers)} conv layers "
-                                              f"(torch-CPU gather-GEMM-scatter) per scene, {scenes_done:.2f} scenes in {cpu_s:.1f} s; BN/ReLU omitted"}
-    if rank == 0:
-        print(json.dumps(line))
+def run_batch16(args, device, rank, world, dist_ctx, l2buf):
+    """Sixteen multi-sweep scenes (seeds 10-25) through the SECOND-style backbone, scene i on rank i mod G
+    (``spira_b200.sharding.assign_scenes``), no collective on the data path: scenes/s = 16 / the slowest rank's device time
+    for its share, after one untimed pass over the same scenes."""
+    from spira_b200 import sharding
+    wl = make_workload("second")
+    mine = sharding.assign_scenes(16, world, rank)
+    host, dev = load_scenes(wl, [10 + i for i in mine], device)
+    engine, note = make_engine(args, "second", wl, device, dev[:2], rank)
+    for c, f in dev:                       # untimed pass: allocator priming and warm-up
+        engine.step(c, f)
+    torch.cuda.synchronize()
     if dist_ctx:
-        torch.distributed.destroy_process_group()
+        torch.distributed.barrier()
+    flush_l2(l2buf)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for c, f in dev:
+        engine.step(c, f)
+    b.record()
+    torch.cuda.synchronize()
+    if dist_ctx:
+        torch.distributed.barrier()
+    local_ms = a.elapsed_time(b)
+    worst = sharding.max_over_ranks(local_ms, torch.device("cuda"))
+    return {"value": round(16 / (worst / 1e3), 2), "unit": "scenes/s", "scenes": 16, "scenes_on_rank0": len(mine),
+            "slowest_rank_ms": round(worst, 3), "workload": wl["label"], "voxels_per_scene_rank0": [len(h[0]) for h in host],
+            "assignment": "scene i -> rank i mod n_gpus", "dataflows": note}
 
 
 def _time_calls(fn, steps, warmup, l2buf):
@@ -825,7 +965,7 @@ def run_layer(args, device, pk, pk_kind):
     else:
         ach = flops / (mean_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": round(ach, 2), "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": round(ach / pk["bf16_tflops"], 4), "traffic": None}
-    kernel = "conv_tc_kernel<WS>" if df else ("conv_os_n256_kernel" if 64 < args.cout <= 96 else "conv_tc_kernel<OS>")
+    kernel = _lib.KERNEL_NAMES[_lib.load().spira_b200_conv_kernel_choice(df, 27, args.cin, args.cout, n)]
     if df == 0 and m[2]._sb.get("grouped") is not None and args.cin % 8 == 0:
         # Bytes that cross from L2 into the SMs per launch: gathered rows + one weight chunk per visited (tile, 64-wide
         # reduction chunk) + the map.  This, not HBM, is what the output-stationary kernels move most of.
@@ -835,14 +975,13 @@ def run_layer(args, device, pk, pk_kind):
         xbar = nnz * args.cin * 2 + visited * (args.cin / 64.0) * args.cout * 128 + m[2].numel() * 4
         roof["l2_to_sm"] = {"bytes_per_launch": int(xbar), "achieved_gbs": round(xbar / (min_ms * 1e-3) / 1e9, 1),
                             "note": "gathered rows + weight chunks + map, over the fastest launch"}
-    # DRAM bytes per launch from an ncu capture of exactly this case (dram__bytes_read.sum + dram__bytes_write.sum)
-    if args.scene == "lidar" and (args.cin, args.cout, df) == (96, 96, 0):
-        roof["traffic"] = 39_471_000
+    workload_label = f"single submanifold 3^3 layer {args.cin}->{args.cout}, {n} voxels ({args.scene}), dataflow {'WS' if df else 'OS'}"
+    roof["traffic"] = captured_traffic(kernel, workload_label)
     roof.update(kernel=kernel, peak_source=f"of {pk_kind}", algorithmic_bytes=int(byts), algorithmic_flops=int(flops))
     return {"metric": "SpC layer TFLOP/s (FLOPs = 2*nnz*c_in*c_out)", "value": round(flops / (mean_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s",
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(mean_ms, 5), "min_ms": round(min_ms, 5), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"single submanifold 3^3 layer {args.cin}->{args.cout}, {n} voxels ({args.scene}), dataflow {'WS' if df else 'OS'}",
+            "config": {"workload": workload_label,
                        "nnz": nnz, "nnz_per_voxel": round(nnz / n, 2), "l2": "256 MiB buffer rewritten between timed steps"},
             "kernel_map_build_ms": round(map_ms, 5), "roofline": roof, "gpu_launches": args.steps * (2 if df else 1)}
 
@@ -909,6 +1048,112 @@ def run_kmap(args, device, pk, pk_kind):
                          "traffic": None, "kernel": "kmap_search_kernel<u32>, 5^3 map of scene 0", "peak_source": f"of {pk_kind}",
                          "algorithmic_bytes": byts5, "kernel_ms": round(k_ms, 5), "kernel_min_ms": round(k_min, 5)},
             "gpu_launches": args.steps * 4 * 4}
+
+
+def _padded(t):
+    """Same values with slack behind them: the reference's search reads ``sources[num_sources]``
+    (csrc/spira/cuda/kernels/query_sorted.cuh:42,48)."""
+    big = torch.zeros(t.shape[0] + 64, dtype=t.dtype, device=t.device)
+    big[:t.shape[0]] = t
+    return big[:t.shape[0]]
+
+
+def run_layer_reference(args, device, pk, pk_kind):
+    """The single-layer workload on the reference's own kernels: every dataflow's forward call on the map the reference
+    builds for it (scripts/layerwise_experiment.py times the same calls through its module)."""
+    from spira_b200 import scenes as sc
+    ref = reference_tools().load_native()
+    if args.scene == "c0":
+        c, double = sc.planes_and_spheres(0), True
+    else:
+        c, double = sc.lidar_scene(1), False
+    n = len(c)
+    keys, _ = ref.cuda_flatten_sort(torch.from_numpy(c).to(device), double)
+    keys = _padded(keys)
+    feats = torch.from_numpy(sc.features(n, args.cin, 0)).to(device)
+    rng = np.random.default_rng(0)
+    w = torch.from_numpy((rng.normal(size=(27, args.cin, args.cout)) / np.sqrt(27 * args.cin)).astype(np.float16)).to(device)
+    l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+    gt, st_ = min(args.cin, 16), min(args.cout, 16)
+    per_df, nnz = {}, None
+    for df in range(9):
+        try:
+            m = ref.cuda_binary_search(keys, keys, (3, 3, 3), (1, 1, 1), df)
+            if df == 0:
+                nnz = int((m[2] >= 0).sum().item())
+                fn = lambda: ref.cuda_sparse_convolution_forward_os(n, n, m[2], feats, w)
+            elif df == 1:
+                fn = lambda: ref.cuda_sparse_convolution_forward_ws_merged(n, n, feats, w, m[5], m[6], m[3], m[7], m[8], False)
+            elif df == 2:
+                fn = lambda: ref.cuda_sparse_convolution_forward_ws(n, n, gt, st_, 4, -1, feats, w, m[3], m[4], m[5])
+            elif df % 2 == 1:
+                fn = lambda: ref.cuda_sparse_convolution_forward_hs_merged(n, n, feats, w, m[5], m[6], m[3], None if df == 3 else m[2],
+                                                                           m[7], m[8], False)
+            else:
+                fn = lambda: ref.cuda_sparse_convolution_forward_hs(n, n, gt, st_, 4, -1, feats, w, m[3], m[4], m[5],
+                                                                    None if df == 4 else m[2])
+            mean_ms, min_ms = _time_calls(fn, args.steps, args.warmup, l2buf)
+            map_ms, _ = _time_calls(lambda: ref.cuda_binary_search(keys, keys, (3, 3, 3), (1, 1, 1), df), args.steps, args.warmup, l2buf)
+            per_df[df] = {"ms": round(mean_ms, 5), "min_ms": round(min_ms, 5), "kernel_map_build_ms": round(map_ms, 5)}
+        except RuntimeError as e:
+            ref.cuda_reset_error()
+            per_df[df] = {"error": str(e).splitlines()[0][:120]}
+    ok = {d: v for d, v in per_df.items() if "ms" in v}
+    best = min(ok, key=lambda d: ok[d]["ms"])
+    flops = 2.0 * nnz * args.cin * args.cout
+    mean_ms = ok[best]["ms"]
+    return {"metric": "SpC layer TFLOP/s (FLOPs = 2*nnz*c_in*c_out)", "value": round(flops / (mean_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s",
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"single submanifold 3^3 layer {args.cin}->{args.cout}, {n} voxels ({args.scene}), the reference's best dataflow",
+                       "nnz": nnz, "best_dataflow": best, "l2": "256 MiB buffer rewritten between timed steps"},
+            "kernel_map_build_ms": ok[best]["kernel_map_build_ms"], "per_dataflow": {str(k): v for k, v in per_df.items()},
+            "cpu_baseline": {"value": round(flops / (mean_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                             "sample": "the reference's own CUDA kernels on the GPU: it has no CPU path"},
+            "e2e": {"value": round(flops / (mean_ms * 1e-3) / 1e12, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
+def run_kmap_reference(args, device, pk, pk_kind):
+    """The kernel-map workload on the reference's own builder, with the protocol of scripts/mapping_experiment.py:84-105
+    (the map-building call between two events) on the same four scenes and map kinds as this engine's leg."""
+    from spira_b200 import scenes as sc
+    ref = reference_tools().load_native()
+    scenes_k = []
+    for seed in (1, 2, 3, 4):
+        keys, _ = ref.cuda_flatten_sort(torch.from_numpy(sc.lidar_scene(seed)).to(device), False)
+        keys = _padded(keys)
+        scenes_k.append((keys, ref.cuda_downsample(keys, 2, 2, 2)))
+    l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+    out = {}
+    for name, ks, strided, df in (("3x3x3_os", (3, 3, 3), False, 0), ("3x3x3_ws", (3, 3, 3), False, 1), ("5x5x5_os", (5, 5, 5), False, 0),
+                                  ("down_3x3x3_os", (3, 3, 3), True, 0), ("down_3x3x3_ws", (3, 3, 3), True, 1)):
+        def fn():
+            for keys, down in scenes_k:
+                ref.cuda_binary_search(keys, down if strided else keys, ks, (1, 1, 1), df)
+        mean_ms, min_ms = _time_calls(fn, args.steps, args.warmup, l2buf)
+        K = ks[0] * ks[1] * ks[2]
+        byts = sum((k.numel() + (d.numel() if strided else k.numel())) * 4 + K * ((((d.numel() if strided else k.numel()) + 127) // 128) * 128) * 4
+                   for k, d in scenes_k)
+        out[name] = {"ms_per_scene": round(mean_ms / 4, 5), "min_ms_per_scene": round(min_ms / 4, 5), "algorithmic_bytes_per_scene": byts // 4,
+                     "gbs": round(byts / (mean_ms * 1e-3) / 1e9, 1)}
+
+    def all_maps():
+        for keys, down in scenes_k:
+            maps = ref.cuda_binary_search_streamed([keys, down], [(3, 3, 3), (3, 3, 3)], [(1, 1, 1), (1, 1, 1)], [0, 0])
+            ref.cuda_binary_search(keys, keys, (5, 5, 5), (1, 1, 1), 0)
+            ref.cuda_convert_transposed_os(maps[1][2], keys.numel())
+    mean_ms, min_ms = _time_calls(all_maps, args.steps, args.warmup, l2buf)
+    v = round(4 / (mean_ms * 1e-3), 2)
+    return {"metric": "kernel-map build (3^3 + 5^3 + stride-2 + transposed inverse)", "value": v, "unit": "scenes/s",
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(mean_ms, 5), "ms_per_scene": round(mean_ms / 4, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+            "config": {"workload": "kernel maps only, 4 LiDAR-like scenes ~125k voxels each", "voxels": [k.numel() for k, _ in scenes_k],
+                       "l2": "256 MiB buffer rewritten between timed steps"},
+            "maps": out,
+            "cpu_baseline": {"value": v, "unit": "scenes/s", "cores": 0, "kind": "reference",
+                             "sample": "the reference's own CUDA map builder on the GPU: it has no CPU path"},
+            "e2e": {"value": v, "unit": "scenes/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
 
 
 def run_reference_port(args, wl, n_gpus):

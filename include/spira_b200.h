@@ -141,6 +141,10 @@ typedef struct spira_b200_kmap_desc {
   int32_t reserved;
   int32_t *map;            /* dense int32 map, T_al = ceil(T/128)*128 rows/columns, -1 = no neighbour */
   int32_t *tile_counts;    /* optional [K][T_al/128] (row order as LAYOUT_WS): hits per 128 targets, or NULL */
+  const int32_t *row_perm; /* LAYOUT_WS only, device int32[K] or NULL: natural row k = kz*o + iz is stored as row
+                              row_perm[k] of map and tile_counts -- the L1-norm order of the hybrid dataflows
+                              (generate_indexes_L1, csrc/spira/torch/cuda_sparse_convolution_mapping.cu:159-209,
+                              BinarySearch_kz_hybrid, csrc/spira/cuda/kernels/query_sorted.cuh:58-113) */
 } spira_b200_kmap_desc;
 
 /* Builds up to SPIRA_B200_MAX_MAPS kernel maps in ONE launch.  Replaces cuda_binary_search and
@@ -189,6 +193,27 @@ int spira_b200_kmap_masks(const int32_t *map_ws, int rows_total, int64_t num_sou
                           int64_t aligned_targets, const int32_t *tile_base, int32_t *source_masks,
                           int32_t *target_masks, void *stream);
 
+/* Mask format of a MIRRORED map: map_rows / tile_base_rows point at the first of `rows_listed` consecutive rows of a
+ * LAYOUT_WS map (and of its tile_base); the masks have rows_masks rows (rows_listed = rows_masks / 2, rounded up).  Row o
+ * is ranked like spira_b200_kmap_masks does; the pair (s, t) with rank r also enters row rows_masks - 1 - o as
+ * source_masks[..][t] = target_masks[..][s] = r.  num_sources must equal num_targets.  Replaces
+ * GenerateMasksFromKernelMap_Half (csrc/spira/cuda/kernels/generate_masks_from_kernel_map.cuh:36-62) as used by the
+ * submanifold mask dataflow and the hybrid dataflows (csrc/spira/cuda/functions/query_sorted_index.cu:516-640, 647-775). */
+int spira_b200_kmap_masks_half(const int32_t *map_rows, const int32_t *tile_base_rows, int rows_listed, int rows_masks,
+                               int64_t num_sources, int64_t num_targets, int64_t aligned_targets, int32_t *source_masks,
+                               int32_t *target_masks, void *stream);
+
+/* Pair lists from the mask format alone, so that masks built by ANY producer (the reference's own builder included) can
+ * feed spira_b200_conv_ws: for all `rows` mask rows, in_idx[naddrs[k] + r] = s where source_masks[k][s] = r >= 0 and
+ * out_idx[naddrs[k] + r] = t where target_masks[k][t] = r.  nbsizes holds the list sizes of all rows (n_sizes == rows) or
+ * of the first half of a mirrored map (n_sizes == (rows + 1) / 2: row k >= n_sizes has the size of row rows - 1 - k).
+ * naddrs / qnaddrs [rows + 1] are written by the call; in_idx / out_idx need room for every pair (at most
+ * rows * min(num_sources, num_targets)).  This is what the gather and scatter stages of the reference's mask-format call
+ * read the masks for (csrc/spira/cuda/functions/sparse_convolution.cu:1002-1124). */
+int spira_b200_kmap_lists_from_masks(const int32_t *source_masks, const int32_t *target_masks, const int32_t *nbsizes,
+                                     int n_sizes, int rows, int64_t num_sources, int64_t num_targets, int32_t *naddrs,
+                                     int32_t *qnaddrs, int32_t *in_idx, int32_t *out_idx, void *stream);
+
 /* out[S_al][K] (fully written) = inverse of map_os[T_al][K] per column; replaces
  * cuda_convert_transposed_os (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:1809-1830). */
 int spira_b200_convert_transposed_os(const int32_t *map_os, int64_t aligned_targets, int K, int32_t *out,
@@ -218,6 +243,17 @@ typedef struct spira_b200_epilogue {
 
 /* 1 if (c_in, c_out, K) can run on the tcgen05 tensor-core kernels, else 0 (SIMT kernels are used). */
 int spira_b200_tensor_core_eligible(int K, int c_in, int c_out);
+
+/* Which kernel a layer of this shape runs on under the current options (the dispatch rule of spira_b200_conv_os* /
+ * spira_b200_conv_ws* given a packed weight image where one exists); -1 for invalid sizes.  No reference counterpart;
+ * the benchmark uses it to attribute measured times to kernels. */
+#define SPIRA_B200_KERNEL_SIMT_OS 0 /* conv_os_simt_kernel */
+#define SPIRA_B200_KERNEL_STEM_OS 1 /* conv_os_stem_kernel: c_in <= 8, c_out in {16, 32, 64} */
+#define SPIRA_B200_KERNEL_TC_OS 2   /* conv_tc_kernel<output-stationary>: 128 targets as the MMA's M operand */
+#define SPIRA_B200_KERNEL_N256_OS 3 /* conv_os_n256_kernel: 256 targets as the MMA's N operand */
+#define SPIRA_B200_KERNEL_TC_WS 4   /* conv_tc_kernel<weight-stationary> */
+#define SPIRA_B200_KERNEL_SIMT_WS 5 /* conv_ws_simt_kernel */
+int spira_b200_conv_kernel_choice(int weight_stationary, int K, int c_in, int c_out, int64_t num_targets);
 
 /* Bytes of the pre-packed weight image for spira_b200_conv_*. */
 int spira_b200_packed_weight_bytes(int K, int c_in, int c_out, int pack_mode, size_t *bytes);
@@ -273,8 +309,9 @@ int spira_b200_conv_os_grouped(const void *feats, const void *weights, const voi
 
 /* Weight-stationary gather-GEMM-scatter over compacted pair lists: for row k and pair p in
  * [naddrs[k], naddrs[k+1]):  accum[out_idx[p]][:] += feats[in_idx[p]][:] @ W[k].  With
- * `mirror` != 0 (submanifold, odd K, rows == (K+1)/2) every row k < rows-1 is also applied with
- * in/out swapped and weight K-1-k (csrc/spira/cuda/kernels/weight_stat.cuh:786-798).  With
+ * `mirror` != 0 (submanifold map, rows == (K+1)/2) every row k is also applied with in/out swapped
+ * and weight K-1-k, except the centre row (K-1)/2 of an odd K, which is its own mirror image
+ * (csrc/spira/cuda/kernels/weight_stat.cuh:786-798; even K: the weight-stationary part of a hybrid map).  With
  * `swap` != 0 the roles of in_idx and out_idx are exchanged (transposed layer on the map of its
  * non-transposed twin, spira/nn/conv.py:341-348).  accum is fp32 [num_targets][c_out] scratch,
  * zeroed by the call; out is fp16 [num_targets][c_out].  `qnaddrs` holds the 128-rounded prefix

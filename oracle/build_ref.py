@@ -7,6 +7,12 @@ Python shim imports as ``spira.nn.functional._C``.  No reference source is copie
 object files and the final shared object are written, all under ``oracle/_ref/``.
 The reference's CMake build is not run: this script is the whole recipe.
 
+The reference's Python package (``source/spira``) and its model definitions
+(``scripts/models/spira``) are staged next to the module, under ``oracle/_ref/spira`` and
+``oracle/_ref/models``, so that the reference's own Python can drive its module on the GPU
+box, where the checkout does not exist.  ``oracle/_ref/`` is not tracked: nothing of the
+reference enters the repository's history.
+
 The resulting module runs only on a machine with a GPU.  It is used by the GPU parity
 tests (kernel maps and features against the reference's own kernels) and by
 ``bench.py --impl reference``.
@@ -14,6 +20,7 @@ tests (kernel maps and features against the reference's own kernels) and by
 import argparse
 import concurrent.futures as cf
 import os
+import shutil
 import subprocess
 import sys
 import sysconfig
@@ -58,11 +65,25 @@ def _flags(csrc: Path):
     return flags, link
 
 
+def stage_python(src: str) -> None:
+    """Copies the reference's Python files (package ``spira`` and the ``models/spira`` definitions of its scripts) into
+    ``oracle/_ref/`` -- an untracked directory that travels to the GPU box with the built module."""
+    root = Path(src)
+    for rel_src, rel_dst in (("source/spira", "spira"), ("scripts/models/spira", "models/spira")):
+        a, b = root / rel_src, OUT / rel_dst
+        if not a.is_dir():
+            raise FileNotFoundError(f"reference Python sources not found under {a}")
+        if b.exists():
+            shutil.rmtree(b)
+        shutil.copytree(a, b, ignore=shutil.ignore_patterns("__pycache__", "*.pyc", "*.so"))
+
+
 def build(src: str, jobs: int = 8, force: bool = False) -> Path:
     csrc = Path(src) / "source" / "csrc"
     if not csrc.is_dir():
         raise FileNotFoundError(f"reference sources not found under {csrc}")
     OUT.mkdir(exist_ok=True)
+    stage_python(src)
     target = OUT / "_C.so"
     sources = sorted(list(csrc.glob("spira/**/*.cu")) + list(csrc.glob("spira/**/*.cpp")))
     if target.exists() and not force and all(target.stat().st_mtime > s.stat().st_mtime for s in sources):

@@ -238,6 +238,99 @@ def gs_masks(dense_ws: np.ndarray, num_sources: int, num_targets: int):
     return sm, tm, sizes
 
 
+def gs_masks_half(rows_map: np.ndarray, rows_masks: int, num_sources: int, num_targets: int):
+    """Mask format of a mirrored map: ``rows_map`` holds the listed rows (the first half of ``rows_masks`` rows, centre
+    included when ``rows_masks`` is odd).  The pair (s, t) with rank r of listed row o is written to row o as in
+    :func:`gs_masks` and to the mirrored row ``rows_masks - 1 - o`` with the roles exchanged, unless o is its own image.
+
+    ``source/csrc/spira/cuda/kernels/generate_masks_from_kernel_map.cuh:36-62``."""
+    listed = rows_map.shape[0]
+    sm = np.full((rows_masks, num_sources), -1, dtype=np.int32)
+    tm = np.full((rows_masks, num_targets), -1, dtype=np.int32)
+    sizes = np.zeros(listed, dtype=np.int32)
+    for o in range(listed):
+        t = np.nonzero(rows_map[o, :num_targets] >= 0)[0]
+        s_ = rows_map[o, t]
+        r = np.arange(len(t), dtype=np.int32)
+        sm[o, s_] = r
+        tm[o, t] = r
+        if 2 * o + 1 != rows_masks:
+            sm[rows_masks - 1 - o, t] = r
+            tm[rows_masks - 1 - o, s_] = r
+        sizes[o] = len(t)
+    return sm, tm, sizes
+
+
+def l1_permutation(kernel_size: Sequence[int], dataflow: int):
+    """``position[k]`` of natural offset ``k = (ix*ky + iy)*kz + iz`` in the row order of the hybrid dataflows 3-8: offsets
+    with L1 norm below ``(dataflow - 1) // 2`` first, the others behind them, both in natural order.  The number of
+    dense rows is what the reference reads from ``position[0]``.
+
+    ``source/csrc/spira/torch/cuda_sparse_convolution_mapping.cu:159-209`` (``generate_indexes_L1``) and ``:682`` / ``:788``."""
+    threshold = (int(dataflow) - 1) // 2
+    l1 = []
+    (x0, x1), (y0, y1), (z0, z1) = (axis_range(k) for k in kernel_size)
+    for x in range(x0, x1 + 1):
+        for y in range(y0, y1 + 1):
+            for z in range(z0, z1 + 1):
+                l1.append(abs(x) + abs(y) + abs(z))
+    front = sum(1 for v in l1 if v < threshold)
+    position, f, b = [], 0, front
+    for v in l1:
+        if v < threshold:
+            position.append(f)
+            f += 1
+        else:
+            position.append(b)
+            b += 1
+    return np.asarray(position, dtype=np.int32), int(position[0])
+
+
+def hybrid_structures(dense_ws: np.ndarray, num_sources: int, num_targets: int, kernel_size, dataflow: int):
+    """The 9-tuple slots of a hybrid dataflow (3-8) from the natural-order ``[K, T_al]`` map.
+
+    Rows are permuted to L1-norm order (``BinarySearch_kz_hybrid``, ``source/csrc/spira/cuda/kernels/query_sorted.cuh:58-113``);
+    the first half of the rows behind the ``dense`` leading ones is compacted into pair lists for odd dataflows
+    (``query_sorted_index.cu:777-908``) or ranked into mirrored masks for even ones (``:647-775``); dataflows above 4 return
+    the leading rows transposed, ``[T_al, dense]`` (``cuda_sparse_convolution_mapping.cu:770-773,884-887``).
+    Returns a dict with ``map`` and, by parity of the dataflow, ``nbmaps / nbsizes / naddrs / qnaddrs / sizes`` or
+    ``smask / tmask / nbsizes``, plus ``permuted`` (the whole permuted map) and ``dense``."""
+    K = dense_ws.shape[0]
+    position, dense = l1_permutation(kernel_size, dataflow)
+    permuted = np.empty_like(dense_ws)
+    permuted[position] = dense_ws
+    half = (K - dense) // 2
+    rows = permuted[dense:dense + half]
+    out = dict(permuted=permuted, dense=dense,
+               map=np.ascontiguousarray(permuted[:dense].T) if dataflow > 4 else permuted)
+    if dataflow % 2 == 1:
+        ins, outs, sizes = [], [], []
+        for o in range(half):
+            t = np.nonzero(rows[o] >= 0)[0]
+            ins.append(rows[o, t])
+            outs.append(t.astype(np.int32))
+            sizes.append(len(t))
+        nbsizes = np.asarray(sizes, dtype=np.int32)
+        naddrs = np.concatenate([[0], np.cumsum(nbsizes)]).astype(np.int32)
+        q = (nbsizes + 127) // 128 * 128
+        qnaddrs = np.concatenate([[0], np.cumsum(q)]).astype(np.int32)
+        cat = (lambda parts: np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32))
+        out.update(nbmaps=np.stack([cat(ins), cat(outs)]).astype(np.int32), nbsizes=nbsizes, naddrs=naddrs, qnaddrs=qnaddrs,
+                   sizes=np.asarray([naddrs[-1], qnaddrs[-1]], dtype=np.int32))
+    else:
+        sm, tm, sizes = gs_masks_half(rows, K - dense, num_sources, num_targets)
+        out.update(smask=sm, tmask=tm, nbsizes=sizes)
+    return out
+
+
+def natural_weights_from_l1(weights, kernel_size, dataflow: int):
+    """The kernel tensor in natural offset order that means what ``weights`` means in the L1-norm order a hybrid dataflow
+    reads (``scripts/models/convert_weights.py:30-55``): ``w_nat[k] = weights[position[k]]``."""
+    import torch
+    position, _ = l1_permutation(kernel_size, dataflow)
+    return torch.as_tensor(weights)[torch.as_tensor(position.astype(np.int64))]
+
+
 def convert_transposed_os(out_in_map: np.ndarray, num_inputs: int) -> np.ndarray:
     """Invert a ``[T_al, K]`` out->in map into ``[S_al, K]`` in->out, same column.
 

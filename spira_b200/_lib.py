@@ -20,7 +20,7 @@ class KmapDesc(C.Structure):
         ("num_sources", c_int64), ("num_targets", c_int64),
         ("kernel_size", c_int32 * 3), ("source_stride", c_int32 * 3),
         ("layout", c_int32), ("reserved", c_int32),
-        ("map", c_void_p), ("tile_counts", c_void_p),
+        ("map", c_void_p), ("tile_counts", c_void_p), ("row_perm", c_void_p),
     ]
 
 
@@ -44,6 +44,8 @@ class Epilogue(C.Structure):
 
 
 LAYOUT_OS, LAYOUT_WS = 0, 1
+KERNEL_NAMES = {0: "conv_os_simt_kernel", 1: "conv_os_stem_kernel", 2: "conv_tc_kernel<OS>", 3: "conv_os_n256_kernel",
+                4: "conv_tc_kernel<WS>", 5: "conv_ws_simt_kernel"}
 PACK_OS, PACK_WS = 0, 1
 MAX_MAPS, MAX_LEVELS = 16, 8
 
@@ -72,9 +74,13 @@ SIGNATURES = {
     "spira_b200_kmap_ws_pairs": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "spira_b200_kmap_ws_lists": [C.POINTER(WsDesc), c_int, c_void_p],
     "spira_b200_kmap_masks": [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
+    "spira_b200_kmap_masks_half": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p],
+    "spira_b200_kmap_lists_from_masks": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p],
     "spira_b200_convert_transposed_os": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p],
     "spira_b200_transpose_map": [c_void_p, c_int64, c_int64, c_void_p, c_void_p],
     "spira_b200_tensor_core_eligible": [c_int, c_int, c_int],
+    "spira_b200_conv_kernel_choice": [c_int, c_int, c_int, c_int, c_int64],
     "spira_b200_packed_weight_bytes": [c_int, c_int, c_int, c_int, C.POINTER(c_size_t)],
     "spira_b200_pack_weights": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "spira_b200_conv_os": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_int64, c_int64, c_int, c_int,
@@ -128,7 +134,7 @@ def check(code: int) -> None:
 KERNELS_PER_CALL = {
     "spira_b200_pack": 1, "spira_b200_unpack": 1, "spira_b200_flatten_sort": 1, "spira_b200_permute_rows": 1,
     "spira_b200_downsample": 1, "spira_b200_pointwise": 1, "spira_b200_downsample_sorted": 4, "spira_b200_kmap_search": 1, "spira_b200_kmap_ws_sizes": 2, "spira_b200_kmap_ws_pairs": 1, "spira_b200_kmap_ws_lists": 3,
-    "spira_b200_kmap_masks": 1, "spira_b200_convert_transposed_os": 1, "spira_b200_transpose_map": 1,
+    "spira_b200_kmap_masks": 1, "spira_b200_kmap_masks_half": 1, "spira_b200_kmap_lists_from_masks": 3, "spira_b200_convert_transposed_os": 1, "spira_b200_transpose_map": 1,
     "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_os_grouped": 1, "spira_b200_kmap_group": 2,
     "spira_b200_conv_ws": 2, "spira_b200_conv_ws_fused": 1, "spira_b200_conv_ws_static": 2,
 }

@@ -134,6 +134,11 @@ class CompiledModel:
                         y = torch.mm(x, module.kernel.view(module.in_channels, module.out_channels))
                         slots[o] = y if module.bias is None else y + module.bias
                     continue
+                if dataflow >= 3 and not os_flow:
+                    # hybrid dataflows run through the module's reference-shaped calls
+                    xin = SparseTensor(coordinates=cache._coordinates_cache.get(in_stride), features=x, stride=in_stride)
+                    slots[o] = module._forward(xin, None if r is None else slots[r])._features
+                    continue
                 m = None
                 if fast:
                     e = cache._maps.get(key)

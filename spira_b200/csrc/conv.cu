@@ -879,11 +879,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     __syncwarp();
   } else {
     // =========================== epilogue ===========================
-    // Accumulator lane = output channel, column = target.  Thread c applies everything to the fp32 accumulator of
-    // channel c for 32 targets at a time: the per-channel affine (its own constants), the residual (read channel-major:
-    // for one target the lanes of the warp read 32 consecutive channels, 64 contiguous bytes) and the ReLU; the value is
-    // then rounded ONCE to fp16 and parked in a small per-warp tile, which the warp reads transposed, so that thread t
-    // holds the 32 channels of ONE target and writes them with four 16-byte stores.
+    // Accumulator lane = output channel, column = target.  Thread c applies the per-channel affine (its own constants)
+    // to the fp32 accumulator of channel c for 32 targets at a time and parks the fp32 values, 16 targets per pass, in a
+    // small per-warp tile.  The warp reads the tile transposed: thread (target tl = lane & 15, channel half lane >> 4)
+    // then holds 16 consecutive channels of ONE target in fp32, adds the residual (two 16-byte loads), applies the
+    // ReLU, rounds ONCE to fp16 and writes two 16-byte stores.
     const int q = warp & 3;
     const int c = q * 32 + lane;
     const bool has_channel = c < P.c_out;
@@ -891,9 +891,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     const float bias = (has_channel && P.ep.bias) ? __half2float(P.ep.bias[c]) : 0.f;
     const float scale = (has_channel && P.ep.scale) ? P.ep.scale[c] : 1.f;
     const float shift = (has_channel && P.ep.shift) ? P.ep.shift[c] : 0.f;
-    const __half *res_col = (has_channel && P.ep.residual) ? P.ep.residual + c : nullptr;
-    const bool with_residual = P.ep.residual != nullptr;    // warp-uniform
     const bool relu = P.ep.relu != 0;
+    const int tl = lane & 15, ch0 = (lane >> 4) * 16;       // second half of a pass: this thread's target and first channel
     uint32_t *tr = reinterpret_cast<uint32_t *>(smem + P.off_tr) + q * (32 * 17);
     uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
@@ -907,46 +906,46 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
         const int64_t t0 = static_cast<int64_t>(tile) * kN2Rows;
         for (int jb = 0; jb < kN2Rows / 32; ++jb) {
           if (t0 + jb * 32 >= P.T) break;                       // warp-uniform: no target left in this block
-          // thread `lane` = target jb*32 + lane in the second half; its output row is needed by every lane before that
+          // output row of target jb*32 + lane (-1: none); the transposed halves fetch theirs with a shuffle
           const int64_t t = t0 + jb * 32 + lane;
-          const int orow = t < P.T ? (P.row_of ? P.row_of[t] : static_cast<int>(t)) : -1;
+          const int orow_lane = t < P.T ? (P.row_of ? P.row_of[t] : static_cast<int>(t)) : -1;
           uint32_t v[32];
           tmem_ld_32x32(taddr + jb * 32, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint((__uint_as_float(v[i]) + bias) * scale + shift);
-          if (with_residual) {
+          for (int h = 0; h < 2; ++h) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int oj = __shfl_sync(0xffffffffu, orow, i);  // output row of target jb*32 + i
-              if (res_col != nullptr && oj >= 0)
-                v[i] = __float_as_uint(__uint_as_float(v[i]) + __half2float(res_col[static_cast<int64_t>(oj) * P.c_out]));
+            for (int i = 0; i < 16; ++i)
+              tr[lane * 17 + i] = __float_as_uint((__uint_as_float(v[16 * h + i]) + bias) * scale + shift);
+            __syncwarp();
+            const int orow = __shfl_sync(0xffffffffu, orow_lane, 16 * h + tl);
+            float x[16];
+#pragma unroll
+            for (int m = 0; m < 16; ++m) x[m] = __uint_as_float(tr[(ch0 + m) * 17 + tl]);
+            __syncwarp();
+            if (orow >= 0 && ch0 < n_valid) {
+              const int64_t base = static_cast<int64_t>(orow) * P.c_out + q * 32 + ch0;
+              if (P.ep.residual) {
+                const uint4 r0 = *reinterpret_cast<const uint4 *>(P.ep.residual + base);
+                const uint4 r1 = *reinterpret_cast<const uint4 *>(P.ep.residual + base + 8);
+                const __half2 *rh0 = reinterpret_cast<const __half2 *>(&r0), *rh1 = reinterpret_cast<const __half2 *>(&r1);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  x[2 * e] += __low2float(rh0[e]); x[2 * e + 1] += __high2float(rh0[e]);
+                  x[8 + 2 * e] += __low2float(rh1[e]); x[8 + 2 * e + 1] += __high2float(rh1[e]);
+                }
+              }
+              uint32_t y[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float a0 = x[2 * e], a1 = x[2 * e + 1];
+                if (relu) { a0 = fmaxf(a0, 0.f); a1 = fmaxf(a1, 0.f); }
+                const __half2 hv = __floats2half2_rn(a0, a1);       // the single rounding
+                y[e] = *reinterpret_cast<const uint32_t *>(&hv);
+              }
+              *reinterpret_cast<uint4 *>(P.out + base) = make_uint4(y[0], y[1], y[2], y[3]);
+              *reinterpret_cast<uint4 *>(P.out + base + 8) = make_uint4(y[4], y[5], y[6], y[7]);
             }
-          }
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float x0 = __uint_as_float(v[2 * i]), x1 = __uint_as_float(v[2 * i + 1]);
-            if (relu) { x0 = fmaxf(x0, 0.f); x1 = fmaxf(x1, 0.f); }
-            const __half2 h = __floats2half2_rn(x0, x1);            // targets 2i, 2i+1 of channel `lane`: the single rounding
-            tr[lane * 17 + i] = *reinterpret_cast<const uint32_t *>(&h);
-          }
-          __syncwarp();
-          // channel cc of this thread's target sits in word (lane >> 1) of row cc, low or high half
-          const uint32_t sel = (lane & 1) ? 0x7632u : 0x5410u;      // PRMT: take the high / low halves of two words
-          uint32_t y[16];
-#pragma unroll
-          for (int m2 = 0; m2 < 16; ++m2) {
-            const uint32_t w0 = tr[(2 * m2) * 17 + (lane >> 1)];
-            const uint32_t w1 = tr[(2 * m2 + 1) * 17 + (lane >> 1)];
-            y[m2] = __byte_perm(w0, w1, sel);                       // (channel 2*m2, channel 2*m2+1) of this target
-          }
-          __syncwarp();
-          if (orow >= 0) {
-            __half *dst = P.out + static_cast<int64_t>(orow) * P.c_out + q * 32;
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-              if (g * 8 < n_valid)
-                *reinterpret_cast<uint4 *>(dst + g * 8) = make_uint4(y[4 * g], y[4 * g + 1], y[4 * g + 2], y[4 * g + 3]);
           }
         }
       }
@@ -1359,6 +1358,29 @@ extern "C" int spira_b200_pack_weights(const void *weights, int K, int c_in, int
   return SPIRA_B200_OK;
 }
 
+// Does the 256-target kernel take this output-stationary layer?  (Its shared-memory plan must hold four stages.)
+static bool os_n256_applies(int K, int c_in, int c_out, int64_t num_targets) {
+  if (!(g_os_n256 && !g_gather_tma && c_out > 64 && c_out <= 128 && K <= 32 && num_targets >= g_os_n256_min_targets)) return false;
+  ConvN2Params Q{};
+  Q.K = K; Q.c_in = c_in; Q.c_out = c_out;
+  Q.R = K * c_in;
+  Q.n_chunks = static_cast<int>(div_up(Q.R, kChunk));
+  return plan_smem_n256(Q, kProducers / kN2TeamThreads) != 0;
+}
+
+static bool stem_applies(int K, int c_in, int c_out) {
+  const size_t stem_smem = static_cast<size_t>(K) * c_in * c_out * 4 + static_cast<size_t>(128) * K * 4;
+  return c_in <= 8 && (c_out == 16 || c_out == 32 || c_out == 64) && stem_smem <= 96 * 1024;
+}
+
+extern "C" int spira_b200_conv_kernel_choice(int weight_stationary, int K, int c_in, int c_out, int64_t num_targets) {
+  if (K < 1 || c_in < 1 || c_out < 1 || num_targets < 0) return -1;
+  const bool tc = tc_eligible(K, c_in, c_out);
+  if (weight_stationary) return tc ? SPIRA_B200_KERNEL_TC_WS : SPIRA_B200_KERNEL_SIMT_WS;
+  if (!tc) return stem_applies(K, c_in, c_out) ? SPIRA_B200_KERNEL_STEM_OS : SPIRA_B200_KERNEL_SIMT_OS;
+  return os_n256_applies(K, c_in, c_out, num_targets) ? SPIRA_B200_KERNEL_N256_OS : SPIRA_B200_KERNEL_TC_OS;
+}
+
 static int conv_os_impl(const void *feats, const void *weights, const void *packed, const spira_b200_epilogue *epilogue,
                         const int32_t *map_os, const int32_t *row_of, const uint32_t *tile_masks, int64_t num_sources,
                         int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status, void *stream) {
@@ -1402,7 +1424,7 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
                "conv_os: feats, packed, out, map and residual must be 16-byte aligned");
   // On grouped maps both kernels run at the speed of the row gathers; the 256-target tiles then only pay off for the
   // wider layers (measured: 32 channels 20 % slower, 64 equal, 96 5 % faster than 128-target tiles).
-  if (g_os_n256 && !g_gather_tma && c_out > 64 && c_out <= 128 && K <= 32 && num_targets >= g_os_n256_min_targets) {
+  if (os_n256_applies(K, c_in, c_out, num_targets)) {
     ConvN2Params Q{};
     Q.feats = static_cast<const __half *>(feats);
     Q.packed = static_cast<const unsigned char *>(packed);
@@ -1477,7 +1499,7 @@ static int conv_ws_impl(const void *feats, const void *weights, const void *pack
                "conv_ws: sizes out of range");
   SB_CHECK_ARG(K >= 1 && c_in >= 1 && c_out >= 1 && rows >= 1 && rows <= K, "conv_ws: K=%d c_in=%d c_out=%d rows=%d", K, c_in,
                c_out, rows);
-  SB_CHECK_ARG(!mirror || (rows == (K + 1) / 2 && K % 2 == 1 && !swap), "conv_ws: mirror needs odd K, rows == (K+1)/2 and no swap");
+  SB_CHECK_ARG(!mirror || (rows == (K + 1) / 2 && !swap), "conv_ws: mirror needs rows == (K+1)/2 and no swap");
   SB_CHECK_ARG(num_tiles128 >= -1 && num_tiles128 < (int64_t(1) << 30), "conv_ws: num_tiles128 out of range");
   if (num_targets == 0) return SPIRA_B200_OK;
   SB_CHECK_ARG(accum && out && naddrs, "conv_ws: null pointer");
@@ -1498,7 +1520,7 @@ static int conv_ws_impl(const void *feats, const void *weights, const void *pack
     SB_CHECK_ARG((num_tiles128 == 0 || (gi && go)) && (feats || num_sources == 0), "conv_ws: null pointer");
     if (packed == nullptr) {
       SB_CHECK_ARG(weights != nullptr, "conv_ws: neither weights nor a packed image given");
-      dim3 grid(static_cast<unsigned>(sm_count() * 2), static_cast<unsigned>(mirror ? 2 * rows - 1 : rows));
+      dim3 grid(static_cast<unsigned>(sm_count() * 2), static_cast<unsigned>(mirror ? K : rows));
       conv_ws_simt_kernel<<<grid, 128, 0, st>>>(static_cast<const __half *>(feats), static_cast<const __half *>(weights), gi,
                                                 go, naddrs, rows, K, c_in, c_out, accum);
       SB_CHECK_LAUNCH();
@@ -1519,8 +1541,8 @@ static int conv_ws_impl(const void *feats, const void *weights, const void *pack
       P.wait_ns = wait_limit_ns();
       P.in_idx = gi; P.out_idx = go; P.naddrs = naddrs; P.qnaddrs = qnaddrs;
       P.rows = rows; P.mirror = mirror;
-      // the centre row (last of the half list) is its own mirror image: its tiles are not repeated
-      P.centre_tiles = static_cast<int>(div_up(num_targets, kRows));
+      // the centre row of an odd kernel volume (last of the half list) is its own mirror image: its tiles are not repeated
+      P.centre_tiles = (K % 2 == 1) ? static_cast<int>(div_up(num_targets, kRows)) : 0;
       if (num_tiles128 < 0) {
         P.n_tiles_plain = -1;      // the kernel reads qnaddrs[rows] itself
         P.n_tiles = -1;

@@ -29,6 +29,7 @@ struct MapDesc {
   const KeyT *tgt;
   int32_t *map;
   int32_t *tile_counts;
+  const int32_t *row_perm;   // weight-stationary layout: natural row k is stored as row row_perm[k] (null: identity)
   int32_t S, T, T_al, n_tiles;
   int32_t kx, ky, kz, nxy, K;
   int32_t x0, y0, z0;  // lowest offset per axis, in units of the source stride
@@ -176,7 +177,8 @@ __global__ void __launch_bounds__(kTile) kmap_search_kernel(const __grid_constan
           }
           if (i < len && W[i] == q) r = lo + i;
         }
-        const int k_ws = kz * o + iz;
+        const int k_nat = kz * o + iz;
+        const int k_ws = D.row_perm ? D.row_perm[k_nat] : k_nat;     // (the output-stationary layout never carries one)
         if (count) {
           unsigned m = __ballot_sync(0xffffffffu, r >= 0);
           if (lane == 0 && m) atomicAdd(&s_cnt[k_ws], __popc(m));
@@ -343,6 +345,61 @@ __global__ void __launch_bounds__(kTile) masks_kernel(const int32_t *__restrict_
   target_masks[k * T + t] = rank;
 }
 
+// Mask format of a mirrored map (csrc/spira/cuda/kernels/generate_masks_from_kernel_map.cuh:36-62): only the first
+// `rows_listed` rows of the `rows_masks` mask rows are ranked; the pair (s, t) of listed row o with rank r also enters the
+// mirrored row rows_masks - 1 - o with the roles exchanged (source t, target s), unless o is its own mirror image.
+__global__ void __launch_bounds__(kTile) masks_half_kernel(const int32_t *__restrict__ map_rows, int rows_masks, int64_t S,
+                                                            int64_t T, int64_t T_al, int64_t n_tiles,
+                                                            const int32_t *__restrict__ tile_base,
+                                                            int32_t *__restrict__ source_masks,
+                                                            int32_t *__restrict__ target_masks) {
+  __shared__ int s_warp[kTile / 32];
+  const int tile = blockIdx.x, k = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t t = static_cast<int64_t>(tile) * kTile + tid;
+  const int v = map_rows[k * T_al + t];
+  const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
+  if (lane == 0) s_warp[warp] = __popc(m);
+  __syncthreads();
+  if (v < 0) return;
+  int rank = __popc(m & ((1u << lane) - 1)) + tile_base[k * n_tiles + tile];
+  for (int w = 0; w < warp; ++w) rank += s_warp[w];
+  source_masks[k * S + v] = rank;
+  target_masks[k * T + t] = rank;
+  const int km = rows_masks - 1 - k;
+  if (km != k) {
+    source_masks[km * S + t] = rank;
+    target_masks[km * T + v] = rank;
+  }
+}
+
+// Pair lists from the mask format alone (the inverse of the kernels above): sizes[k] for all `rows` mask rows from
+// nbsizes[n_sizes] (n_sizes == rows, or a mirrored half whose missing rows repeat the listed ones back to front), prefix
+// sums naddrs / qnaddrs, then in_idx[naddrs[k] + r] = s for source_masks[k][s] = r and likewise out_idx from the targets.
+__global__ void masks_addr_kernel(const int32_t *__restrict__ nbsizes, int n_sizes, int rows, int32_t *__restrict__ naddrs,
+                                  int32_t *__restrict__ qnaddrs) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int acc = 0, qacc = 0;
+  for (int k = 0; k < rows; ++k) {
+    naddrs[k] = acc;
+    qnaddrs[k] = qacc;
+    const int v = nbsizes[k < n_sizes ? k : rows - 1 - k];
+    acc += v;
+    qacc += (v + 127) / 128 * 128;
+  }
+  naddrs[rows] = acc;
+  qnaddrs[rows] = qacc;
+}
+
+__global__ void __launch_bounds__(256) lists_from_masks_kernel(const int32_t *__restrict__ masks, int64_t n,
+                                                                const int32_t *__restrict__ naddrs,
+                                                                int32_t *__restrict__ idx) {
+  const int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  const int k = blockIdx.y;
+  if (i >= n) return;
+  const int r = masks[k * n + i];
+  if (r >= 0) idx[naddrs[k] + r] = static_cast<int32_t>(i);
+}
+
 __global__ void __launch_bounds__(256) invert_os_kernel(const int32_t *__restrict__ map_os, int64_t n, int K,
                                                          int32_t *__restrict__ out) {
   int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
@@ -393,6 +450,7 @@ int search_impl(const spira_b200_kmap_desc *descs, int n_maps, cudaStream_t stre
     m.tgt = static_cast<const KeyT *>(d.targets);
     m.map = d.map;
     m.tile_counts = d.tile_counts;
+    m.row_perm = d.layout == SPIRA_B200_LAYOUT_WS ? d.row_perm : nullptr;
     m.S = static_cast<int32_t>(d.num_sources);
     m.T = static_cast<int32_t>(d.num_targets);
     m.T_al = static_cast<int32_t>(align128(d.num_targets));
@@ -510,6 +568,47 @@ extern "C" int spira_b200_kmap_masks(const int32_t *map_ws, int rows_total, int6
   masks_kernel<<<grid, kTile, 0, as_stream(stream)>>>(map_ws, num_sources, num_targets, aligned_targets, n_tiles,
                                                       tile_base, source_masks, target_masks);
   SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_kmap_masks_half(const int32_t *map_rows, const int32_t *tile_base_rows, int rows_listed,
+                                          int rows_masks, int64_t num_sources, int64_t num_targets, int64_t aligned_targets,
+                                          int32_t *source_masks, int32_t *target_masks, void *stream) {
+  SB_CHECK_ARG(rows_masks >= 1 && rows_masks <= kMaxK && rows_listed >= 0 && 2 * rows_listed <= rows_masks + 1 &&
+                   2 * rows_listed >= rows_masks && aligned_targets % 128 == 0 && num_targets <= aligned_targets,
+               "kmap_masks_half: bad sizes (rows_listed must be rows_masks / 2, rounded up)");
+  SB_CHECK_ARG(num_sources == num_targets, "kmap_masks_half: a mirrored map has as many sources as targets");
+  SB_CHECK_ARG(source_masks && target_masks, "kmap_masks_half: null pointer");
+  SB_CHECK_CUDA(cudaMemsetAsync(source_masks, 0xFF, sizeof(int32_t) * rows_masks * num_sources, as_stream(stream)));
+  SB_CHECK_CUDA(cudaMemsetAsync(target_masks, 0xFF, sizeof(int32_t) * rows_masks * num_targets, as_stream(stream)));
+  if (aligned_targets == 0 || rows_listed == 0) return SPIRA_B200_OK;
+  SB_CHECK_ARG(map_rows && tile_base_rows, "kmap_masks_half: null pointer");
+  const int64_t n_tiles = aligned_targets / kTile;
+  dim3 grid(static_cast<unsigned>(n_tiles), static_cast<unsigned>(rows_listed));
+  masks_half_kernel<<<grid, kTile, 0, as_stream(stream)>>>(map_rows, rows_masks, num_sources, num_targets, aligned_targets, n_tiles,
+                                                           tile_base_rows, source_masks, target_masks);
+  SB_CHECK_LAUNCH();
+  return SPIRA_B200_OK;
+}
+
+extern "C" int spira_b200_kmap_lists_from_masks(const int32_t *source_masks, const int32_t *target_masks, const int32_t *nbsizes,
+                                                int n_sizes, int rows, int64_t num_sources, int64_t num_targets, int32_t *naddrs,
+                                                int32_t *qnaddrs, int32_t *in_idx, int32_t *out_idx, void *stream) {
+  SB_CHECK_ARG(rows >= 1 && rows <= kMaxK && (n_sizes == rows || n_sizes == (rows + 1) / 2) && num_sources >= 0 && num_targets >= 0,
+               "kmap_lists_from_masks: rows=%d n_sizes=%d (the sizes cover all mask rows or their first half)", rows, n_sizes);
+  SB_CHECK_ARG(nbsizes && naddrs && qnaddrs, "kmap_lists_from_masks: null pointer");
+  cudaStream_t st = as_stream(stream);
+  masks_addr_kernel<<<1, 32, 0, st>>>(nbsizes, n_sizes, rows, naddrs, qnaddrs);
+  SB_CHECK_LAUNCH();
+  if (num_sources > 0 && num_targets > 0) {
+    SB_CHECK_ARG(source_masks && target_masks && in_idx && out_idx, "kmap_lists_from_masks: null pointer");
+    lists_from_masks_kernel<<<dim3(static_cast<unsigned>(div_up(num_sources, 256)), static_cast<unsigned>(rows)), 256, 0, st>>>(
+        source_masks, num_sources, naddrs, in_idx);
+    SB_CHECK_LAUNCH();
+    lists_from_masks_kernel<<<dim3(static_cast<unsigned>(div_up(num_targets, 256)), static_cast<unsigned>(rows)), 256, 0, st>>>(
+        target_masks, num_targets, naddrs, out_idx);
+    SB_CHECK_LAUNCH();
+  }
   return SPIRA_B200_OK;
 }
 

@@ -370,7 +370,10 @@ class SparseConv(Module):
                         self._tuning_data.append(((m[4], m[3]) if self.transposed else (m[3], m[4])) + (m[5],))
                     target_features = _C.run_conv_ws(call, n_src, n_tgt, sb["ws"], source_features, self.transposed, residual)
                 return SparseTensor(features=target_features, coordinates=target_coordinates, stride=target_stride)
-            if self._fused is not None or residual is not None:
+            # reference-shaped calls: maps from another builder, and the hybrid dataflows 3-8 (an output-stationary and a
+            # weight-stationary call per layer; a fused epilogue is applied as separate passes afterwards)
+            epilogue_after = self._fused is not None or residual is not None
+            if epilogue_after and not (sb is not None and map_dataflow >= 3):
                 raise RuntimeError("[spira_b200] the fused epilogue needs kernel maps built by this engine")
             if map_dataflow == 0 or force_os:
                 target_features = F.sparse_convolution_forward_os(n_src, n_tgt, m[2], source_features, self.kernel)
@@ -397,6 +400,18 @@ class SparseConv(Module):
                         None if map_dataflow == 4 else m[2],
                         self._tunable_config['gather_tile_size'], self._tunable_config['scatter_tile_size'],
                         None, self._tunable_config['threshold'])
+
+            if epilogue_after:
+                y = target_features.float()
+                if self.bias is not None:
+                    y = y + self.bias.float()
+                if self._fused is not None and self._fused["scale"] is not None:
+                    y = y * self._fused["scale"] + self._fused["shift"]
+                if residual is not None:
+                    y = y + residual.float()
+                if self._fused is not None and self._fused["relu"]:
+                    y = torch.relu(y)
+                return SparseTensor(features=y.to(target_features.dtype), coordinates=target_coordinates, stride=target_stride)
 
         if self.bias is not None:
             target_features += self.bias

@@ -317,6 +317,45 @@ def _dataflow_layout(dataflow: int) -> int:
     return LAYOUT_OS if dataflow == 0 else LAYOUT_WS
 
 
+def _axis_range(k: int):
+    lo = -(k // 2) if k % 2 == 1 else -(k // 2) + 1
+    return range(lo, lo + k)
+
+
+def l1_permutation(kernel_size, dataflow: int):
+    """Row order of the hybrid dataflows 3-8 (``generate_indexes_L1``,
+    csrc/spira/torch/cuda_sparse_convolution_mapping.cu:159-209): ``position[k]`` of every offset in natural order
+    ``k = (ix*ky + iy)*kz + iz``.  Offsets whose L1 norm is below ``(dataflow - 1) // 2`` come first (the rows the
+    output-stationary part takes), the others follow, both in natural order.  Returns ``(position, dense_offsets)``;
+    like the reference, ``dense_offsets`` is read from ``position[0]`` (mapping.cu:682: the first natural offset is a
+    corner, which is never among the leading rows of an odd kernel)."""
+    threshold = (int(dataflow) - 1) // 2
+    l1 = [abs(x) + abs(y) + abs(z) for x in _axis_range(kernel_size[0]) for y in _axis_range(kernel_size[1])
+          for z in _axis_range(kernel_size[2])]
+    front = sum(1 for v in l1 if v < threshold)
+    position, f, b = [], 0, front
+    for v in l1:
+        if v < threshold:
+            position.append(f)
+            f += 1
+        else:
+            position.append(b)
+            b += 1
+    return position, position[0]
+
+
+_l1_device = {}
+
+
+def _l1_device_tensor(kernel_size, dataflow, device):
+    key = (tuple(kernel_size), int(dataflow), str(device))
+    t = _l1_device.get(key)
+    if t is None:
+        position, dense = l1_permutation(kernel_size, dataflow)
+        t = _l1_device[key] = (torch.tensor(position, dtype=torch.int32, device=device), dense)
+    return t
+
+
 LAZY_SIZES = True   # cuda_binary_search_streamed(..., exact_sizes=False) keeps the list sizes on the device
 WS_FUSED = True     # weight-stationary layers run as ONE cooperative launch over a persistent, always-zero scratch
 DEFER_MAPS = True   # KernelMapCache.add_all_kernel_maps returns after the level-0 map; the rest is completed on first use
@@ -427,8 +466,20 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
         shape = (Tal, K) if layout == LAYOUT_OS else (K, Tal)
         dense = torch.empty(shape, dtype=torch.int32, device=dev)
         counts = torch.empty((K, Tal // 128), dtype=torch.int32, device=dev)
+        perm, n_dense = (None, 0)
+        if df >= 3:
+            # hybrid dataflows: the rows of the [K, T_al] map come in L1-norm order; the compacted half behind the leading
+            # rows is mirrored, which presumes a submanifold map (the reference's tuner tries them on stride-1 layers only,
+            # spira/utils/helpers.py:187-197)
+            if S != T:
+                raise RuntimeError(f"[spira_b200] map dataflow {df} (hybrid) needs a submanifold map: {S} sources, {T} targets")
+            if ks[2] not in (3, 5):      # (csrc/spira/cuda/functions/query_sorted_index.cu:698-700)
+                raise RuntimeError("[spira_b200] Currently Kernel Size in Z axis can only be 3, 5 for the hybrid dataflows")
+            perm, n_dense = _l1_device_tensor(ks, df, dev)
+            if (K - n_dense) % 2 != 0:
+                raise RuntimeError(f"[spira_b200] map dataflow {df}: kernel size {ks} leaves an odd number of rows to mirror")
         info.append(dict(src=src, tgt=tgt, S=S, T=T, K=K, Tal=Tal, ks=ks, st=st, df=df, layout=layout, dense=dense,
-                         counts=counts))
+                         counts=counts, perm=perm, n_dense=n_dense))
     for first in range(0, n, MAX_MAPS):
         batch = info[first:first + MAX_MAPS]
         descs = (KmapDesc * len(batch))()
@@ -439,10 +490,15 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
             d.source_stride[:] = m["st"]
             d.layout = m["layout"]
             d.map, d.tile_counts = m["dense"].data_ptr(), m["counts"].data_ptr()
+            d.row_perm = None if m["perm"] is None else m["perm"].data_ptr()
         _lib.call("spira_b200_kmap_search", descs, len(batch), kb, stream)
 
+    hybrid_maps = [m for m in info if m["df"] >= 3]
+    if hybrid_maps:
+        _build_hybrid(hybrid_maps, dev, stream)
+
     # weight-stationary post-processing
-    ws_maps = [m for m in info if m["layout"] == LAYOUT_WS]
+    ws_maps = [m for m in info if m["layout"] == LAYOUT_WS and m["df"] < 3]
     for m in ws_maps:
         # submanifold map with an odd kernel volume: only the first (K+1)/2 rows are listed, the rest is applied by
         # symmetry (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:269)
@@ -524,9 +580,11 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
     for m in info:
         df, dense = m["df"], m["dense"]
         dense._sb = dict(counts=m["counts"], ws=m.get("ws"), kernel_size=m["ks"], layout=m["layout"], grouped=m.get("grouped"))
-        if df == 0:
+        if df >= 3:
+            results.append(m["result"])
+        elif df == 0:
             results.append((m["S"], m["T"], dense, None, None, None, None, None, None))
-        elif df in (1, 3, 5, 7):
+        elif df == 1:
             w = m["ws"]      # reachable from the dense map only: nothing in the lists points back (no reference cycle)
             results.append((m["S"], m["T"], dense, w.nbmaps, w.nbsizes, w.naddrs, w.qnaddrs, w.mapsize, w.qmapsize))
         else:
@@ -534,10 +592,14 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
             K = m["K"]
             sm = torch.empty((K, m["S"]), dtype=torch.int32, device=dev)
             tm = torch.empty((K, m["T"]), dtype=torch.int32, device=dev)
-            _lib.call("spira_b200_kmap_masks", _ptr(dense), K, m["S"], m["T"], m["Tal"], _ptr(m["tile_base"]), _ptr(sm),
-                      _ptr(tm), stream)
-            sm._sb, sm._sb_role = dense._sb, "source"
-            tm._sb, tm._sb_role = dense._sb, "target"
+            if m["half"]:
+                # submanifold map with an odd kernel volume: the first (K+1)/2 rows are ranked, the others mirror them
+                # (csrc/spira/cuda/functions/query_sorted_index.cu:516-640)
+                _lib.call("spira_b200_kmap_masks_half", _ptr(dense), _ptr(m["tile_base"]), m["rows"], K, m["S"], m["T"], m["Tal"],
+                          _ptr(sm), _ptr(tm), stream)
+            else:
+                _lib.call("spira_b200_kmap_masks", _ptr(dense), K, m["S"], m["T"], m["Tal"], _ptr(m["tile_base"]), _ptr(sm),
+                          _ptr(tm), stream)
             results.append((m["S"], m["T"], dense, sm, tm, w.nbsizes, None, None, None))
     return results
 
@@ -623,6 +685,58 @@ def _build_maps_arena(voxel_pairs, kernel_sizes, source_strides, dataflows, grou
         for (dense, _), g in zip(os_maps, group_os_maps(os_maps)):
             dense._sb["grouped"] = g
     return results
+
+
+def _build_hybrid(maps, dev, stream) -> None:
+    """Post-processing of the hybrid dataflows 3-8 (``BinarySearch_Streamed_Hybrid_{WS,GS}``,
+    csrc/spira/cuda/functions/query_sorted_index.cu:647-908, and the driver,
+    csrc/spira/torch/cuda_sparse_convolution_mapping.cu:667-892).  The searched map has its rows in L1-norm order:
+    ``dense`` leading rows for the output-stationary part, then ``K - dense`` rows of which the first half is compacted
+    into pair lists (odd dataflows) or ranked into masks (even dataflows, both halves written by mirroring).  Dataflows
+    above 4 return the leading rows as ``[T_al, dense]``; 3 and 4 (only the centre offset is dense) keep the whole map."""
+    sizes = torch.empty((len(maps), 2), dtype=torch.int32, device=dev)
+    for j, m in enumerate(maps):
+        K, nt, nd = m["K"], m["Tal"] // 128, m["n_dense"]
+        half = (K - nd) // 2
+        m["half_rows"] = half
+        m["nbsizes"] = torch.empty(max(half, 1), dtype=torch.int32, device=dev)[:half]
+        m["naddrs"] = torch.zeros(half + 1, dtype=torch.int32, device=dev)
+        m["qnaddrs"] = torch.zeros(half + 1, dtype=torch.int32, device=dev)
+        m["tile_base"] = torch.empty((max(half, 1), max(nt, 1)), dtype=torch.int32, device=dev)
+        if nt > 0 and half > 0:
+            _lib.call("spira_b200_kmap_ws_sizes", m["counts"].data_ptr() + 4 * nd * nt, half, nt, _ptr(m["nbsizes"]),
+                      _ptr(m["naddrs"]), _ptr(m["qnaddrs"]), _ptr(m["tile_base"]), _ptr(sizes[j]), stream)
+        else:
+            sizes[j].zero_()
+    host_sizes = sizes.cpu().tolist()
+    for j, m in enumerate(maps):
+        K, nd, half, S, T, Tal, df, dense = m["K"], m["n_dense"], m["half_rows"], m["S"], m["T"], m["Tal"], m["df"], m["dense"]
+        mapsize, qmapsize = host_sizes[j]
+        rows_ptr = dense.data_ptr() + 4 * nd * Tal
+        w = WsLists()
+        nbmaps = torch.empty((2, mapsize), dtype=torch.int32, device=dev)
+        if mapsize > 0:
+            _lib.call("spira_b200_kmap_ws_pairs", rows_ptr, half, Tal, _ptr(m["naddrs"]), _ptr(m["tile_base"]), _ptr(nbmaps[0]),
+                      _ptr(nbmaps[1]), stream)
+        w.nbmaps, w.in_idx, w.out_idx = nbmaps, nbmaps[0], nbmaps[1]
+        w.nbsizes, w.naddrs, w.qnaddrs = m["nbsizes"], m["naddrs"], m["qnaddrs"]
+        w.rows, w.mirror, w.mapsize, w.qmapsize = half, True, int(mapsize), int(qmapsize)
+        w.set_pointers()
+        if df > 4:
+            lead = torch.empty((Tal, nd), dtype=torch.int32, device=dev)
+            if nd > 0 and Tal > 0:
+                _lib.call("spira_b200_transpose_map", _ptr(dense), nd, Tal, _ptr(lead), stream)
+            lead._sb = dict(layout=LAYOUT_OS, ws=None, grouped=None, counts=None, kernel_size=m["ks"])
+            out_map = lead
+        else:
+            out_map = dense
+        if df % 2 == 1:
+            m["result"] = (S, T, out_map, w.nbmaps, w.nbsizes, w.naddrs, w.qnaddrs, w.mapsize, w.qmapsize)
+        else:
+            sm = torch.empty((K - nd, S), dtype=torch.int32, device=dev)
+            tm = torch.empty((K - nd, T), dtype=torch.int32, device=dev)
+            _lib.call("spira_b200_kmap_masks_half", rows_ptr, _ptr(m["tile_base"]), half, K - nd, S, T, Tal, _ptr(sm), _ptr(tm), stream)
+            m["result"] = (S, T, out_map, sm, tm, w.nbsizes, None, None, None)
 
 
 class _WsTuple(tuple):
@@ -1031,14 +1145,16 @@ def cuda_sparse_convolution_forward_os(num_sources, num_targets, out_in_map, sou
     return conv_os(num_sources, num_targets, out_in_map, sources, weights)
 
 
-def _lists_from_reference_slots(naddrs, qnaddrs, nbmaps, mapsize, qmapsize, num_sources, num_targets, K) -> WsLists:
+def _lists_from_reference_slots(naddrs, qnaddrs, nbmaps, mapsize, qmapsize, num_sources, num_targets, K, mirror=None) -> WsLists:
     w = WsLists()
     nbmaps = nbmaps.contiguous()
     w.nbmaps, w.in_idx, w.out_idx = nbmaps, nbmaps[0], nbmaps[1]
     w.naddrs, w.qnaddrs = naddrs.contiguous(), qnaddrs.contiguous()
     w.rows = naddrs.shape[0] - 1
     w.nbsizes = None
-    w.mirror = (w.rows == (K + 1) // 2) and K % 2 == 1 and num_sources == num_targets and w.rows != K
+    if mirror is None:
+        mirror = (w.rows == (K + 1) // 2) and K % 2 == 1 and num_sources == num_targets and w.rows != K
+    w.mirror = bool(mirror)
     w.mapsize, w.qmapsize = int(mapsize), int(qmapsize)
     return w.set_pointers()
 
@@ -1051,44 +1167,121 @@ def cuda_sparse_convolution_forward_ws_merged(num_sources, num_targets, sources,
     return conv_ws(num_sources, num_targets, sources, weights, lists, swap=bool(transpose))
 
 
+def lists_from_masks(source_masks: torch.Tensor, target_masks: torch.Tensor, kernel_map_sizes: torch.Tensor) -> WsLists:
+    """Pair lists of ALL mask rows from the mask format alone: ``source_masks [Km, S]``, ``target_masks [Km, T]`` and
+    the list sizes of all rows or of the first half of a mirrored map, whoever built them.  Nothing is read back: the
+    lists get the capacity ``Km * min(S, T)`` and the kernels read their sizes on the device.  The result is kept on
+    the mask tensor, so later forwards on the same map reuse it."""
+    cached = getattr(source_masks, "_sb_lists", None)
+    if cached is not None and cached[0] is target_masks and cached[1] == (source_masks._version, target_masks._version):
+        return cached[2]
+    _require_cuda(source_masks, target_masks, kernel_map_sizes)
+    if source_masks.dim() != 2 or target_masks.dim() != 2 or source_masks.shape[0] != target_masks.shape[0]:
+        raise RuntimeError("[spira_b200] source_masks and target_masks must be [K, S] and [K, T]")
+    if source_masks.dtype != torch.int32 or target_masks.dtype != torch.int32 or kernel_map_sizes.dtype != torch.int32:
+        raise RuntimeError("[spira_b200] masks and kernel_map_sizes must be int32")
+    sm, tm, sizes = source_masks.contiguous(), target_masks.contiguous(), kernel_map_sizes.contiguous()
+    Km, S = sm.shape
+    T = tm.shape[1]
+    n = sizes.shape[0]
+    if n != Km and n != (Km + 1) // 2:
+        raise RuntimeError(f"[spira_b200] kernel_map_sizes has {n} entries for {Km} mask rows (expected all rows or their first half)")
+    dev = sm.device
+    small = torch.empty(2 * (Km + 1), dtype=torch.int32, device=dev)
+    nbmaps = torch.empty((2, max(Km * min(S, T), 1)), dtype=torch.int32, device=dev)
+    w = WsLists()
+    w.nbmaps, w.in_idx, w.out_idx = nbmaps, nbmaps[0], nbmaps[1]
+    w.naddrs, w.qnaddrs, w.nbsizes = small[:Km + 1], small[Km + 1:], None
+    w.rows, w.mirror, w.mapsize, w.qmapsize = Km, False, None, None
+    w.set_pointers()
+    _lib.call("spira_b200_kmap_lists_from_masks", _ptr(sm), _ptr(tm), _ptr(sizes), n, Km, S, T, w.naddrs_ptr, w.qnaddrs_ptr,
+              w.in_ptr, w.out_ptr, _stream(dev))
+    w._keep = (sm, tm, sizes)
+    try:
+        source_masks._sb_lists = (target_masks, (source_masks._version, target_masks._version), w)
+    except Exception:
+        pass
+    return w
+
+
 def cuda_sparse_convolution_forward_ws(num_sources, num_targets, gather_tile_size, scatter_tile_size, parallel, threshold,
                                        sources, weights, source_masks, target_masks, kernel_map_sizes):
-    """Mask-format weight-stationary call (csrc/spira/torch/cuda_sparse_convolution_forward.cu:82-181).  The tile
-    sizes, GEMM parallelism and padding threshold tune the reference's gather / cuBLAS / scatter
-    pipeline and have no counterpart in the fused kernel; they are accepted and ignored."""
-    sb = getattr(source_masks, "_sb", None) or getattr(target_masks, "_sb", None)
-    if sb is None or sb.get("ws") is None:
-        raise RuntimeError("[spira_b200] mask tensors must come from this engine's build_kmap(dataflow=2)")
-    lists = sb["ws"]
-    # the masks of a transposed layer arrive exchanged (spira/nn/conv.py:353-360)
-    swap = getattr(source_masks, "_sb_role", "source") == "target"
-    return conv_ws(num_sources, num_targets, sources, weights, lists, swap=swap)
+    """Mask-format weight-stationary call (csrc/spira/torch/cuda_sparse_convolution_forward.cu:82-181,
+    csrc/spira/cuda/functions/sparse_convolution.cu:1002-1124).  The pair lists are derived from the masks themselves
+    (:func:`lists_from_masks`), so masks from any builder work; the masks of a transposed layer arrive exchanged
+    (spira/nn/conv.py:353-360) and yield the exchanged lists.  The tile sizes, GEMM parallelism and padding threshold
+    tune the reference's gather / cuBLAS / scatter pipeline and have no counterpart in the fused kernel; they are
+    accepted and ignored."""
+    if source_masks.shape[1] != num_sources or target_masks.shape[1] != num_targets:
+        raise RuntimeError(f"[spira_b200] masks of shape {tuple(source_masks.shape)} / {tuple(target_masks.shape)} do not match "
+                           f"{num_sources} sources and {num_targets} targets")
+    if weights.shape[0] != source_masks.shape[0]:
+        raise RuntimeError(f"[spira_b200] The dimension 0 of Tensor weights is expected to be {source_masks.shape[0]} but found {weights.shape[0]}")
+    lists = lists_from_masks(source_masks, target_masks, kernel_map_sizes)
+    return conv_ws(num_sources, num_targets, sources, weights, lists)
+
+
+def _identity_map(n: int, device) -> torch.Tensor:
+    """``[T_al, 1]`` output-stationary map of the centre offset of a submanifold layer: every voxel is its own neighbour."""
+    m = torch.full((_aligned(n), 1), -1, dtype=torch.int32, device=device)
+    m[:n, 0] = torch.arange(n, dtype=torch.int32, device=device)
+    return m
+
+
+def _hybrid_dense_part(num_sources, num_targets, sources, weights, out_in_map):
+    """Output-stationary part of a hybrid call: the leading ``K_os`` weights over ``out_in_map [T_al, K_os]``, or -- no
+    map given -- the centre offset alone, a plain matrix product in the reference
+    (csrc/spira/cuda/functions/sparse_convolution.cu:1368-1380)."""
+    if out_in_map is None:
+        if num_sources != num_targets:
+            raise RuntimeError("[spira_b200] a hybrid call without out_in_map is the centre offset of a submanifold layer")
+        out_in_map = _identity_map(num_targets, sources.device)
+    k_os = out_in_map.shape[1]
+    return k_os, conv_os(num_sources, num_targets, out_in_map, sources, weights[:k_os].contiguous())
 
 
 def cuda_sparse_convolution_forward_hs_merged(num_sources, num_targets, sources, weights, naddrs, qnaddrs, nbmaps, out_in_map,
                                               mapsize, qmapsize, transpose=False):
-    """Hybrid call of the reference (csrc/spira/torch/cuda_sparse_convolution_forward.cu:338-420): maps built by this
-    engine for dataflows 3/5/7 hold the complete pair lists, so the call reduces to the weight-stationary one."""
-    return cuda_sparse_convolution_forward_ws_merged(num_sources, num_targets, sources, weights, naddrs, qnaddrs, nbmaps,
-                                                     mapsize, qmapsize, transpose)
+    """Hybrid call of the reference (csrc/spira/torch/cuda_sparse_convolution_forward.cu:338-420,
+    csrc/spira/cuda/functions/sparse_convolution.cu:1299-1350): the leading ``K_os`` weights (L1-norm order,
+    scripts/models/convert_weights.py:30-55) run output-stationary over ``out_in_map``, the remaining ``2 * rows`` weights
+    weight-stationary over the half-compacted, mirrored pair lists, and the two parts are summed -- here in fp32 on top
+    of the rounded output-stationary part."""
+    _check_feats(sources, weights)
+    rows = naddrs.shape[0] - 1
+    k_os, dense_part = _hybrid_dense_part(num_sources, num_targets, sources, weights, out_in_map)
+    if weights.shape[0] != k_os + 2 * rows:
+        raise RuntimeError(f"[spira_b200] The dimension 0 of Tensor weights is expected to be {k_os + 2 * rows} but found {weights.shape[0]}")
+    if rows == 0:
+        return dense_part
+    lists = _lists_from_reference_slots(naddrs, qnaddrs, nbmaps, mapsize, qmapsize, num_sources, num_targets, 2 * rows, mirror=True)
+    return conv_ws(num_sources, num_targets, sources, weights[k_os:].contiguous(), lists, swap=bool(transpose), residual=dense_part)
 
 
 def cuda_sparse_convolution_forward_hs(num_sources, num_targets, gather_tile_size, scatter_tile_size, parallel, threshold,
                                        sources, weights, source_masks, target_masks, kernel_map_sizes, out_in_map):
-    """Hybrid mask-format call (csrc/spira/torch/cuda_sparse_convolution_forward.cu:248-336); see ``..._hs_merged``."""
-    return cuda_sparse_convolution_forward_ws(num_sources, num_targets, gather_tile_size, scatter_tile_size, parallel,
-                                              threshold, sources, weights, source_masks, target_masks, kernel_map_sizes)
+    """Hybrid mask-format call (csrc/spira/torch/cuda_sparse_convolution_forward.cu:248-336): like
+    :func:`cuda_sparse_convolution_forward_hs_merged` with the weight-stationary part given as masks over
+    ``K - K_os`` rows (both halves present, sizes for the first half)."""
+    _check_feats(sources, weights)
+    k_os, dense_part = _hybrid_dense_part(num_sources, num_targets, sources, weights, out_in_map)
+    k_ws = target_masks.shape[0]
+    if weights.shape[0] != k_os + k_ws or source_masks.shape[0] != k_ws:
+        raise RuntimeError(f"[spira_b200] The dimension 0 of Tensor weights is expected to be {k_os + k_ws} but found {weights.shape[0]}")
+    if k_ws == 0:
+        return dense_part
+    lists = lists_from_masks(source_masks, target_masks, kernel_map_sizes)
+    return conv_ws(num_sources, num_targets, sources, weights[k_os:].contiguous(), lists, residual=dense_part)
 
 
-def _time_ws(weights, source_masks, target_masks) -> float:
-    sb = getattr(source_masks, "_sb", None)
-    if sb is None or sb.get("ws") is None:
-        raise RuntimeError("[spira_b200] mask tensors must come from this engine's build_kmap(dataflow=2)")
+def _time_ws(weights, source_masks, target_masks, kernel_map_sizes) -> float:
     S, T = source_masks.shape[1], target_masks.shape[1]
-    feats = torch.zeros((S, weights.shape[1]), dtype=weights.dtype, device=weights.device)
+    lists = lists_from_masks(source_masks, target_masks, kernel_map_sizes)
+    w = weights[weights.shape[0] - source_masks.shape[0]:].contiguous()     # (a hybrid layer: the weight-stationary rows)
+    feats = torch.zeros((S, w.shape[1]), dtype=w.dtype, device=w.device)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    conv_ws(S, T, feats, weights, sb["ws"])
+    conv_ws(S, T, feats, w, lists)
     b.record()
     b.synchronize()
     return a.elapsed_time(b)
@@ -1097,17 +1290,17 @@ def _time_ws(weights, source_masks, target_masks) -> float:
 def cuda_time_gemm(parallel, threshold, is_hybrid, weights, source_masks, target_masks, kernel_map_sizes) -> float:
     """Timing probe used by the reference tuner (csrc/spira/torch/cuda_sparse_convolution_forward.cu:422-498).  The fused
     kernel has no separate GEMM stage: the time of the whole weight-stationary layer is returned."""
-    return _time_ws(weights, source_masks, target_masks)
+    return _time_ws(weights, source_masks, target_masks, kernel_map_sizes)
 
 
 def cuda_time_gather(tile_size, threshold, is_hybrid, weights, source_masks, target_masks, kernel_map_sizes) -> float:
     """See :func:`cuda_time_gemm`."""
-    return _time_ws(weights, source_masks, target_masks)
+    return _time_ws(weights, source_masks, target_masks, kernel_map_sizes)
 
 
 def cuda_time_scatter(tile_size, threshold, is_hybrid, weights, source_masks, target_masks, kernel_map_sizes) -> float:
     """See :func:`cuda_time_gemm`."""
-    return _time_ws(weights, source_masks, target_masks)
+    return _time_ws(weights, source_masks, target_masks, kernel_map_sizes)
 
 
 _option_epoch = [0]      # bumped by set_option: prepared calls re-read the options they depend on

@@ -68,6 +68,16 @@ def main(out_dir):
                 m2 = ref.cuda_binary_search(s_, t_, ks, st, 2)
                 out[f"{tag}_{name}_smask"] = m2[3].cpu().numpy()
                 out[f"{tag}_{name}_tmask"] = m2[4].cpu().numpy()
+            if name in ("sub3", "sub5"):
+                # the submanifold mask format (mirrored halves) and the hybrid dataflows: every slot of the 9-tuple
+                for df in range(2, 9):
+                    m = ref.cuda_binary_search(s_, t_, ks, st, df)
+                    out[f"{tag}_{name}_df{df}_map"] = m[2].cpu().numpy()
+                    for slot in (3, 4, 5, 6):
+                        if m[slot] is not None:
+                            out[f"{tag}_{name}_df{df}_slot{slot}"] = m[slot].cpu().numpy()
+                    if m[7] is not None:
+                        out[f"{tag}_{name}_df{df}_sizes"] = np.array([m[7], m[8]], dtype=np.int32)
             if name == "sub3" and not double:
                 nsrc = s_.shape[0]
                 feats = torch.from_numpy(rng.normal(size=(nsrc, 16)).astype(np.float16)).cuda()
@@ -76,6 +86,19 @@ def main(out_dir):
                 out["conv_os_on_os_map"] = ref.cuda_sparse_convolution_forward_os(nsrc, nsrc, m0[2], feats, w).cpu().numpy()
                 out["conv_ws_merged"] = ref.cuda_sparse_convolution_forward_ws_merged(
                     nsrc, nsrc, feats, w, m1[5], m1[6], m1[3], m1[7], m1[8], False).cpu().numpy()
+                # mask-format and hybrid forward calls on the same features and kernel tensor (each dataflow reads the
+                # kernel tensor in its own offset order)
+                for df in range(2, 9):
+                    m = ref.cuda_binary_search(s_, t_, ks, st, df)
+                    if df == 2:
+                        y = ref.cuda_sparse_convolution_forward_ws(nsrc, nsrc, 16, 16, 4, -1, feats, w, m[3], m[4], m[5])
+                    elif df % 2 == 1:
+                        y = ref.cuda_sparse_convolution_forward_hs_merged(nsrc, nsrc, feats, w, m[5], m[6], m[3],
+                                                                          None if df == 3 else m[2], m[7], m[8], False)
+                    else:
+                        y = ref.cuda_sparse_convolution_forward_hs(nsrc, nsrc, 16, 16, 4, -1, feats, w, m[3], m[4], m[5],
+                                                                   None if df == 4 else m[2])
+                    out[f"conv_df{df}"] = y.cpu().numpy()
     torch.cuda.synchronize()
     Path(out_dir).mkdir(parents=True, exist_ok=True)
     np.savez_compressed(Path(out_dir) / "reference_vectors.npz", **out)

@@ -31,7 +31,7 @@ def test_python_binding_covers_the_header(lib):
 
 def test_struct_layouts_match_the_header():
     from spira_b200 import _lib
-    assert ctypes.sizeof(_lib.KmapDesc) == 8 * 4 + 4 * 8 + 8 * 2      # 2 ptr, 2 i64, 8 i32, 2 ptr
+    assert ctypes.sizeof(_lib.KmapDesc) == 8 * 4 + 4 * 8 + 8 * 3      # 2 ptr, 2 i64, 8 i32, 3 ptr
     assert ctypes.sizeof(_lib.Epilogue) == 4 * 8 + 8
 
 

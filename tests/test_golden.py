@@ -63,6 +63,52 @@ def test_kernel_maps_and_lists(g, tag, name):
         np.testing.assert_array_equal(tm, g[f"{tag}_{name}_tmask"])
 
 
+@pytest.mark.parametrize("tag", ["u32", "u64"])
+@pytest.mark.parametrize("name", ["sub3", "sub5"])
+@pytest.mark.parametrize("df", [2, 3, 4, 5, 6, 7, 8])
+def test_mirrored_masks_and_hybrid_maps(g, tag, name, df):
+    if f"{tag}_{name}_df{df}_map" not in g.files:
+        pytest.skip("golden vectors predate the hybrid dataflows: regenerate with tests/golden/make_golden.py on a GPU box")
+    keys = u(g[f"{tag}_keys"])
+    ks = CASES[name][2]
+    ws = O.kernel_map(keys, keys, ks, (1, 1, 1), "ws")
+    n = len(keys)
+    got = {}
+    if df == 2:
+        K = ws.shape[0]
+        sm, tm, sizes = O.gs_masks_half(ws[:(K + 1) // 2], K, n, n)
+        got = {"map": ws, 3: sm, 4: tm, 5: sizes}
+    else:
+        h = O.hybrid_structures(ws, n, n, ks, df)
+        got["map"] = h["map"]
+        if df % 2 == 1:
+            got.update({3: h["nbmaps"], 4: h["nbsizes"], 5: h["naddrs"], 6: h["qnaddrs"], "sizes": h["sizes"]})
+        else:
+            got.update({3: h["smask"], 4: h["tmask"], 5: h["nbsizes"]})
+    np.testing.assert_array_equal(got["map"], g[f"{tag}_{name}_df{df}_map"])
+    for slot in (3, 4, 5, 6):
+        key = f"{tag}_{name}_df{df}_slot{slot}"
+        assert (key in g.files) == (slot in got), f"slot {slot} presence"
+        if slot in got:
+            np.testing.assert_array_equal(got[slot], g[key])
+    if "sizes" in got:
+        np.testing.assert_array_equal(got["sizes"], g[f"{tag}_{name}_df{df}_sizes"])
+
+
+@pytest.mark.parametrize("df", [2, 3, 4, 5, 6, 7, 8])
+def test_mask_and_hybrid_features(g, df):
+    if f"conv_df{df}" not in g.files:
+        pytest.skip("golden vectors predate the hybrid dataflows: regenerate with tests/golden/make_golden.py on a GPU box")
+    f, w = torch.from_numpy(g["feats"]), torch.from_numpy(g["weights"])
+    n = f.shape[0]
+    # the hybrid calls read the kernel tensor in L1-norm order, dataflow 2 in natural order
+    w_nat = w if df == 2 else O.natural_weights_from_l1(w, (3, 3, 3), df)
+    got = O.conv_ws(f, w_nat, g["u32_sub3_ws"], n).float()
+    want = torch.from_numpy(g[f"conv_df{df}"]).float()
+    # the reference sums these dataflows in fp16 (cuBLAS Hgemm outputs, fp16 scatter sums and atomics)
+    assert ((got - want).abs() <= 2e-2 + 2e-2 * want.abs()).all()
+
+
 def test_features(g):
     f, w = torch.from_numpy(g["feats"]), torch.from_numpy(g["weights"])
     n = f.shape[0]

@@ -186,7 +186,7 @@ def test_module_level_dataflows_agree(C, scene):
     torch.manual_seed(0)
     net = torch.nn.Sequential(spnn.SparseConv(32, 64, 3), spnn.SparseConv(64, 64, 3, stride=2), spnn.SparseConv(64, 32, 3, stride=2, transposed=True)).cuda().half()
     outs = {}
-    for df, force_os in ((1, False), (2, False), (1, True), (5, False), (4, False)):
+    for df, force_os in ((1, False), (2, False), (1, True), (2, True)):
         cache = spnn.KernelMapCache()
         sp.set_kernel_map_cache(net, cache)
         for layer in net:
