@@ -966,10 +966,10 @@ def run_layer(args, device, pk, pk_kind):
         ach = flops / (mean_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": round(ach, 2), "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": round(ach / pk["bf16_tflops"], 4), "traffic": None}
     kernel = _lib.KERNEL_NAMES[_lib.load().spira_b200_conv_kernel_choice(df, 27, args.cin, args.cout, n)]
-    if df == 0 and m[2]._sb.get("grouped") is not None and args.cin % 8 == 0:
+    if df == 0 and _C.grouped_twin(m[2]) is not None and args.cin % 8 == 0:
         # Bytes that cross from L2 into the SMs per launch: gathered rows + one weight chunk per visited (tile, 64-wide
         # reduction chunk) + the map.  This, not HBM, is what the output-stationary kernels move most of.
-        stats = m[2]._sb["grouped"].stats.cpu().tolist()
+        stats = _C.grouped_twin(m[2]).stats.cpu().tolist()
         tile_rows = 256 if kernel == "conv_os_n256_kernel" else 128
         visited = stats[1] if tile_rows == 256 else stats[0]              # non-empty (tile, offset) pairs of the grouped map
         xbar = nnz * args.cin * 2 + visited * (args.cin / 64.0) * args.cout * 128 + m[2].numel() * 4

@@ -1,27 +1,30 @@
 // Kernel-map construction: one launch builds the (input, output, weight-offset) maps of every
 // sparse-convolution layer of a network.
 //
-// Work decomposition: one CTA of 128 threads per tile of 128 consecutive sorted targets of one map.
-// For an xy offset o the queries tgt[t] + off[o] of a tile are monotone in t, so every match lies
-// in one contiguous window of the sorted source keys.  The CTA finds the window bounds with
-// warp-cooperative 32-ary searches (4 dependent loads instead of 17 for 120k keys), stages the
-// windows of as many offsets as fit into shared memory with coalesced loads, and every thread then
-// resolves its queries by a binary search + z walk entirely in shared memory.  Results are
-//   - written as a dense int32 map, either [K][T_al] with coalesced rows, or [T_al][K] through a
-//     shared-memory slab that is stored with 16-byte vectors, and
-//   - counted per (offset, 128-target tile) with warp ballots, which is what the compaction into
-//     weight-stationary pair lists, the mask format and the dataflow selector consume.
-// A query equals an exact lookup of the wrapped packed key; windows that would be too large (or
-// offsets whose queries wrap inside the tile) fall back to per-thread searches in global memory.
+// Work decomposition: one CTA of 256 threads per tile of 128 consecutive sorted targets of one map; a thread resolves
+// one (target, xy offset) column at a time: a lower bound for the lowest z, then a walk over the kz consecutive z
+// values (keys are z-fastest, so the kz answers are neighbours in the sorted source array).
+// The lower bound does not search the whole source array.  For a fixed x offset the queries tgt[t] + off(ix, iy) of a
+// tile grow with t and with iy, so all of them fall into ONE window of the sorted sources, whose two ends the CTA
+// finds first with warp-cooperative 32-ary searches (4 dependent loads for 120k keys instead of 17).  The per-thread
+// binary searches then run inside that window (typically a few hundred keys: ~9 steps, and the window stays in L1).
+// No shared-memory staging: the kernel keeps next to nothing per CTA, so every SM holds its full complement of warps
+// and the dependent loads of one search hide behind the others.
+// Results are
+//   - written as a dense int32 map, [K][T_al] (consecutive threads = consecutive targets of one offset: coalesced
+//     rows) or [T_al][K] (consecutive threads = consecutive xy offsets of one target: runs of nxy entries), and
+//   - counted per (offset, 128-target tile), which is what the compaction into weight-stationary pair lists, the mask
+//     format and the dataflow selector consume.
+// A query equals an exact lookup of the wrapped packed key; offsets whose queries wrap inside the tile search the
+// whole array, every z on its own.
 #include "common.cuh"
 
 namespace sb {
 
-constexpr int kTile = 128;          // targets per CTA == threads per CTA
+constexpr int kTile = 128;          // targets per CTA
+constexpr int kSearchThreads = 256;
 constexpr int kMaxXY = 64;          // kx*ky
 constexpr int kMaxK = 512;          // kx*ky*kz
-constexpr int kWindowCap = 3072;    // keys staged per offset group
-constexpr int kStageMaxBytes = 96 * 1024;
 
 template <typename KeyT>
 struct MapDesc {
@@ -34,7 +37,7 @@ struct MapDesc {
   int32_t kx, ky, kz, nxy, K;
   int32_t x0, y0, z0;  // lowest offset per axis, in units of the source stride
   int32_t sx, sy, sz;
-  int32_t layout, staged;
+  int32_t layout;
   int32_t tile_begin;
 };
 
@@ -45,12 +48,10 @@ struct SearchParams {
 };
 
 template <typename KeyT>
-__device__ __forceinline__ KeyT xy_offset(const MapDesc<KeyT> &D, int o) {
-  int ix = o / D.ky + D.x0;
-  int iy = o % D.ky + D.y0;
+__device__ __forceinline__ KeyT xy_offset(const MapDesc<KeyT> &D, int ix, int iy) {
   // wrapping arithmetic on purpose: identical to adding signed multiples of the field units
-  return static_cast<KeyT>(static_cast<int64_t>(ix) * D.sx) * (KeyT(1) << KeyShift<KeyT>::X) +
-         static_cast<KeyT>(static_cast<int64_t>(iy) * D.sy) * (KeyT(1) << KeyShift<KeyT>::Y) +
+  return static_cast<KeyT>(static_cast<int64_t>(ix + D.x0) * D.sx) * (KeyT(1) << KeyShift<KeyT>::X) +
+         static_cast<KeyT>(static_cast<int64_t>(iy + D.y0) * D.sy) * (KeyT(1) << KeyShift<KeyT>::Y) +
          static_cast<KeyT>(static_cast<int64_t>(D.z0) * D.sz);
 }
 
@@ -75,25 +76,25 @@ __device__ __forceinline__ int warp_lower_bound(const KeyT *__restrict__ a, int 
   return lo;
 }
 
+// Branch-free lower bound in a[lo, hi): the trip count depends on the window length only, so the lanes of a warp that
+// share a window stay converged.
 template <typename KeyT>
-__device__ __forceinline__ int lower_bound(const KeyT *a, int n, KeyT q) {
-  int lo = 0, hi = n;
-  while (lo < hi) {
-    int mid = (lo + hi) >> 1;
-    if (a[mid] < q) lo = mid + 1; else hi = mid;
+__device__ __forceinline__ int lower_bound(const KeyT *__restrict__ a, int lo, int hi, KeyT q) {
+  int len = hi - lo;
+  if (len <= 0) return lo;
+  while (len > 1) {
+    const int half = len >> 1;
+    lo = (__ldg(a + lo + half - 1) < q) ? lo + half : lo;
+    len -= half;
   }
-  return lo;
+  return lo + (__ldg(a + lo) < q ? 1 : 0);
 }
 
 template <typename KeyT>
-__global__ void __launch_bounds__(kTile) kmap_search_kernel(const __grid_constant__ SearchParams<KeyT> P,
-                                                             int stage_bytes) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ int s_lo[kMaxXY], s_hi[kMaxXY], s_irregular[kMaxXY];
+__global__ void __launch_bounds__(kSearchThreads) kmap_search_kernel(const __grid_constant__ SearchParams<KeyT> P) {
+  __shared__ KeyT s_tgt[kTile];
+  __shared__ int s_lo[8], s_hi[8], s_irregular[8];      // per x offset (kx <= 8)
   __shared__ int s_cnt[kMaxK];
-
-  int32_t *stage = reinterpret_cast<int32_t *>(smem_raw);
-  KeyT *win = reinterpret_cast<KeyT *>(smem_raw + stage_bytes);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int mi = 0;
@@ -101,109 +102,142 @@ __global__ void __launch_bounds__(kTile) kmap_search_kernel(const __grid_constan
   const MapDesc<KeyT> &D = P.m[mi];
   const int lt = blockIdx.x - D.tile_begin;
   const int t0 = lt * kTile;
-  const int t = t0 + tid;
   const int nvalid = min(kTile, D.T - t0);
-  const bool valid = tid < nvalid;
   const KeyT *__restrict__ src = D.src;
-  const KeyT my = valid ? D.tgt[t] : KeyT(0);
   const KeyT first = D.tgt[t0], last = D.tgt[t0 + nvalid - 1];
   const KeyT sz = static_cast<KeyT>(D.sz);
-  const int K = D.K, nxy = D.nxy, kz = D.kz;
+  const int K = D.K, nxy = D.nxy, kz = D.kz, kx = D.kx, ky = D.ky, S = D.S;
   const bool count = D.tile_counts != nullptr;
+  const bool ws = D.layout == SPIRA_B200_LAYOUT_WS;
 
-  for (int k = tid; k < K; k += kTile) s_cnt[k] = 0;
+  if (tid < kTile) s_tgt[tid] = tid < nvalid ? D.tgt[t0 + tid] : KeyT(0);
+  for (int k = tid; k < K; k += kSearchThreads) s_cnt[k] = 0;
 
-  // ---- window bounds: 2*nxy warp-cooperative searches --------------------------------------
-  for (int b = warp; b < 2 * nxy; b += kTile / 32) {
-    int o = b >> 1;
-    KeyT off = xy_offset(D, o);
-    KeyT qf = first + off, ql = last + off;
-    KeyT qmax = ql + static_cast<KeyT>(kz - 1) * sz;
-    bool irregular = !(qf <= ql && ql <= qmax) || D.S == 0;
+  // ---- one source window per x offset: 2 * kx warp-cooperative searches ----------------------------------------------
+  for (int b = warp; b < 2 * kx; b += kSearchThreads / 32) {
+    const int ix = b >> 1;
+    const KeyT off_lo = xy_offset(D, ix, 0), off_hi = xy_offset(D, ix, ky - 1);
+    const KeyT qf = first + off_lo, ql = last + off_lo, qh = last + off_hi;
+    const KeyT qmax = qh + static_cast<KeyT>(kz - 1) * sz;
+    // the queries of this x offset are ordered like (t, iy, iz) unless one of them wraps around the key range
+    const bool irregular = !(qf <= ql && ql <= qh && qh <= qmax) || S == 0;
     int r;
     if (irregular) {
-      r = (b & 1) ? D.S : 0;
+      r = (b & 1) ? S : 0;
     } else if (b & 1) {
-      r = (qmax == ~KeyT(0)) ? D.S : warp_lower_bound(src, D.S, static_cast<KeyT>(qmax + 1), lane);
+      r = (qmax == ~KeyT(0)) ? S : warp_lower_bound(src, S, static_cast<KeyT>(qmax + 1), lane);
     } else {
-      r = warp_lower_bound(src, D.S, qf, lane);
+      r = warp_lower_bound(src, S, qf, lane);
     }
     if (lane == 0) {
-      if (b & 1) s_hi[o] = r; else { s_lo[o] = r; s_irregular[o] = irregular; }
+      if (b & 1) s_hi[ix] = r; else { s_lo[ix] = r; s_irregular[ix] = irregular; }
     }
   }
   __syncthreads();
 
-  // ---- offsets in groups whose windows fit into shared memory ------------------------------
-  int o_begin = 0;
-  while (o_begin < nxy) {
-    int used = 0, o_end = o_begin;
-    while (o_end < nxy) {
-      int len = s_hi[o_end] - s_lo[o_end];
-      int need = len <= kWindowCap ? len : 0;  // oversized windows are searched in global memory
-      if (used + need > kWindowCap) break;
-      used += need;
-      ++o_end;
-    }
-    // stage
-    int base = 0;
-    for (int o = o_begin; o < o_end; ++o) {
-      int lo = s_lo[o], len = s_hi[o] - lo;
-      if (len <= kWindowCap) {
-        for (int i = tid; i < len; i += kTile) win[base + i] = src[lo + i];
-        base += len;
+  // ---- one (target, xy offset) column per thread and turn --------------------------------------------------------------
+  // One column: a lower bound for the lowest z inside the window of the column's x offset, then the kz answers by
+  // walking on (z is the fastest key field).  `row` points at the first entry of the column in the map, `step` is the
+  // distance between its z entries; hits are counted per map row.
+  auto column = [&](int tl, int o, int ix, KeyT off, int32_t *__restrict__ out, int step, int k_first, int k_step) {
+    const bool valid = tl < nvalid;
+    const int lo = s_lo[ix], hi = s_hi[ix];
+    KeyT q = s_tgt[tl] + off;
+    if (s_irregular[ix] == 0) {
+      int i = valid ? lower_bound(src, lo, hi, q) : hi;
+#pragma unroll 1
+      for (int iz = 0; iz < kz; ++iz) {
+        int r = -1;
+        KeyT v = KeyT(0);
+        while (i < hi && (v = __ldg(src + i)) < q) ++i;
+        if (i < hi && v == q) r = i;
+        out[iz * step] = r;
+        if (count) {
+          if (ws) {
+            const unsigned m = __ballot_sync(0xffffffffu, r >= 0);  // (the 32 columns of a warp share the offset)
+            if (lane == 0 && m) atomicAdd(&s_cnt[k_first + iz * k_step], __popc(m));
+          } else if (r >= 0) {
+            atomicAdd(&s_cnt[k_first + iz * k_step], 1);
+          }
+        }
+        q += sz;
       }
-    }
-    __syncthreads();
-    // search
-    base = 0;
-    for (int o = o_begin; o < o_end; ++o) {
-      const int lo = s_lo[o], len = s_hi[o] - lo;
-      const bool in_smem = len <= kWindowCap;
-      const bool irregular = s_irregular[o] != 0;
-      const KeyT *W = in_smem ? (win + base) : (src + lo);
-      if (in_smem) base += len;
-      KeyT q = my + xy_offset(D, o);
-      int i = 0;
-      if (valid && !irregular && in_smem) i = lower_bound(W, len, q);
+    } else {
+      // some query of this x offset wraps around the key range: every z is an exact lookup in the whole array
 #pragma unroll 1
       for (int iz = 0; iz < kz; ++iz) {
         int r = -1;
         if (valid) {
-          if (irregular || !in_smem) {
-            i = lower_bound(W, len, q);
-          } else {
-            while (i < len && W[i] < q) ++i;
-          }
-          if (i < len && W[i] == q) r = lo + i;
+          const int i = lower_bound(src, 0, S, q);
+          if (i < S && __ldg(src + i) == q) r = i;
         }
-        const int k_nat = kz * o + iz;
-        const int k_ws = D.row_perm ? D.row_perm[k_nat] : k_nat;     // (the output-stationary layout never carries one)
+        out[iz * step] = r;
         if (count) {
-          unsigned m = __ballot_sync(0xffffffffu, r >= 0);
-          if (lane == 0 && m) atomicAdd(&s_cnt[k_ws], __popc(m));
-        }
-        if (D.layout == SPIRA_B200_LAYOUT_WS) {
-          D.map[static_cast<int64_t>(k_ws) * D.T_al + t] = r;
-        } else if (D.staged) {
-          stage[tid * K + iz * nxy + o] = r;
-        } else {
-          D.map[static_cast<int64_t>(t) * K + iz * nxy + o] = r;
+          if (ws) {
+            const unsigned m = __ballot_sync(0xffffffffu, r >= 0);
+            if (lane == 0 && m) atomicAdd(&s_cnt[k_first + iz * k_step], __popc(m));
+          } else if (r >= 0) {
+            atomicAdd(&s_cnt[k_first + iz * k_step], 1);
+          }
         }
         q += sz;
       }
     }
-    __syncthreads();
-    o_begin = o_end;
-  }
+  };
 
-  if (D.layout == SPIRA_B200_LAYOUT_OS && D.staged) {
-    const int4 *s4 = reinterpret_cast<const int4 *>(stage);
-    int4 *d4 = reinterpret_cast<int4 *>(D.map + static_cast<int64_t>(t0) * K);
-    for (int i = tid; i < (kTile / 4) * K; i += kTile) d4[i] = s4[i];
+  if (ws) {
+    // [K][T_al]: thread = target tid % 128 of offsets tid / 128, tid / 128 + 2, ...: consecutive threads write consecutive
+    // entries of one map row.  Natural row k = kz*o + iz may be stored elsewhere (row_perm).
+    const int tl = tid & (kTile - 1);
+    int32_t *const base = D.map + t0 + tl;
+    for (int o = tid >> 7; o < nxy; o += kSearchThreads / kTile) {
+      const int ix = o / ky, iy = o - ix * ky;
+      const KeyT off = xy_offset(D, ix, iy);
+      if (D.row_perm == nullptr) {
+        column(tl, o, ix, off, base + static_cast<int64_t>(kz * o) * D.T_al, D.T_al, kz * o, 1);
+      } else {
+        // permuted rows are not equidistant: one z at a time
+        const bool valid = tl < nvalid;
+        const int lo = s_lo[ix], hi = s_hi[ix];
+        const bool irregular = s_irregular[ix] != 0;
+        KeyT q = s_tgt[tl] + off;
+        int i = (valid && !irregular) ? lower_bound(src, lo, hi, q) : hi;
+#pragma unroll 1
+        for (int iz = 0; iz < kz; ++iz) {
+          int r = -1;
+          if (valid && irregular) {
+            const int j = lower_bound(src, 0, S, q);
+            if (j < S && __ldg(src + j) == q) r = j;
+          } else {
+            KeyT v = KeyT(0);
+            while (i < hi && (v = __ldg(src + i)) < q) ++i;
+            if (i < hi && v == q) r = i;
+          }
+          const int k_ws = D.row_perm[kz * o + iz];
+          base[static_cast<int64_t>(k_ws) * D.T_al] = r;
+          if (count) {
+            const unsigned m = __ballot_sync(0xffffffffu, r >= 0);
+            if (lane == 0 && m) atomicAdd(&s_cnt[k_ws], __popc(m));
+          }
+          q += sz;
+        }
+      }
+    }
+  } else {
+    // [T_al][K]: thread = xy offset tid % nxy of targets tid / nxy, + 256 / nxy, ...: consecutive threads write runs of nxy
+    // consecutive entries (column iz*nxy + o of a row).  Offset, window and x offset are fixed per thread.
+    const int per_turn = kSearchThreads / nxy;
+    if (tid < per_turn * nxy) {
+      const int o = tid % nxy, sub = tid / nxy;
+      const int ix = o / ky, iy = o - ix * ky;
+      const KeyT off = xy_offset(D, ix, iy);
+      for (int tl = sub; tl < kTile; tl += per_turn)
+        column(tl, o, ix, off, D.map + static_cast<int64_t>(t0 + tl) * K + o, nxy, kz * o, 1);
+    }
   }
+  __syncthreads();
   if (count)
-    for (int k = tid; k < K; k += kTile) D.tile_counts[static_cast<int64_t>(k) * D.n_tiles + lt] = s_cnt[k];
+    for (int k = tid; k < K; k += kSearchThreads) D.tile_counts[static_cast<int64_t>(k) * D.n_tiles + lt] = s_cnt[k];
 }
 
 // ---- weight-stationary post-processing ------------------------------------------------------
@@ -429,7 +463,7 @@ template <typename KeyT>
 int search_impl(const spira_b200_kmap_desc *descs, int n_maps, cudaStream_t stream) {
   SearchParams<KeyT> P;
   P.n_maps = 0;
-  int tiles = 0, stage_bytes = 0;
+  int tiles = 0;
   for (int i = 0; i < n_maps; ++i) {
     const spira_b200_kmap_desc &d = descs[i];
     SB_CHECK_ARG(d.num_sources >= 0 && d.num_sources < (int64_t(1) << 31) && d.num_targets >= 0 &&
@@ -437,8 +471,8 @@ int search_impl(const spira_b200_kmap_desc *descs, int n_maps, cudaStream_t stre
                  "kmap_search: map %d has sizes out of range", i);
     const int kx = d.kernel_size[0], ky = d.kernel_size[1], kz = d.kernel_size[2];
     SB_CHECK_ARG(kx >= 1 && ky >= 1 && kz >= 1, "kmap_search: map %d has a non-positive kernel size", i);
-    SB_CHECK_ARG(kx * ky <= kMaxXY && kx * ky * kz <= kMaxK, "kmap_search: map %d kernel %dx%dx%d exceeds %d xy / %d total offsets",
-                 i, kx, ky, kz, kMaxXY, kMaxK);
+    SB_CHECK_ARG(kx <= 8 && kx * ky <= kMaxXY && kx * ky * kz <= kMaxK,
+                 "kmap_search: map %d kernel %dx%dx%d exceeds 8 in x / %d xy / %d total offsets", i, kx, ky, kz, kMaxXY, kMaxK);
     SB_CHECK_ARG(d.source_stride[0] >= 1 && d.source_stride[1] >= 1 && d.source_stride[2] >= 1,
                  "kmap_search: map %d has a non-positive stride", i);
     SB_CHECK_ARG(d.layout == SPIRA_B200_LAYOUT_OS || d.layout == SPIRA_B200_LAYOUT_WS, "kmap_search: map %d layout %d", i,
@@ -461,17 +495,11 @@ int search_impl(const spira_b200_kmap_desc *descs, int n_maps, cudaStream_t stre
     m.z0 = (kz % 2 == 1) ? -(kz / 2) : -(kz / 2) + 1;
     m.sx = d.source_stride[0]; m.sy = d.source_stride[1]; m.sz = d.source_stride[2];
     m.layout = d.layout;
-    int sb = m.K * kTile * 4;
-    m.staged = (d.layout == SPIRA_B200_LAYOUT_OS && sb <= kStageMaxBytes) ? 1 : 0;
-    if (m.staged && sb > stage_bytes) stage_bytes = sb;
     m.tile_begin = tiles;
     tiles += m.n_tiles;
   }
   if (tiles == 0) return SPIRA_B200_OK;
-  size_t smem = static_cast<size_t>(stage_bytes) + kWindowCap * sizeof(KeyT);
-  SB_CHECK_CUDA(cudaFuncSetAttribute(kmap_search_kernel<KeyT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(smem)));
-  kmap_search_kernel<KeyT><<<tiles, kTile, smem, stream>>>(P, stage_bytes);
+  kmap_search_kernel<KeyT><<<tiles, kSearchThreads, 0, stream>>>(P);
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
 }

@@ -127,7 +127,7 @@ class KernelMapCache(object):
             if sb is None or sb.get("layout") == _C.LAYOUT_WS:
                 flipped = _C.transpose_map(entry[3])
                 if sb is not None:
-                    flipped._sb = dict(sb, layout=_C.LAYOUT_OS, grouped=_C.group_os_map(flipped, entry[2]))
+                    flipped._sb = dict(sb, layout=_C.LAYOUT_OS, group_lazy=None, grouped=_C.group_os_map(flipped, entry[2]))
                 entry[3] = flipped
             entry[0] = True
 
@@ -141,7 +141,7 @@ class KernelMapCache(object):
                 inv = F.convert_transposed_os(entry[3], entry[1])
                 sb = getattr(entry[3], "_sb", None)
                 if sb is not None:
-                    inv._sb = dict(sb, ws=None, counts=None, _counts=None,
+                    inv._sb = dict(sb, ws=None, counts=None, _counts=None, group_lazy=None,
                                    grouped=_C.group_os_map(inv, entry[1]) if self._groups(key) else None)
                     self._inverse_keys.add(key)
                 self._derived_maps[dkey] = inv
@@ -234,7 +234,7 @@ class KernelMapCache(object):
                     todo.append((entry[3], entry[2]))
                 if key in self._inverse_keys and (key, "inverted") not in self._derived_maps:
                     inv = F.convert_transposed_os(entry[3], entry[1])
-                    inv._sb = dict(sb, ws=None, counts=None, _counts=None, grouped=None)
+                    inv._sb = dict(sb, ws=None, counts=None, _counts=None, group_lazy=None, grouped=None)
                     self._derived_maps[(key, "inverted")] = inv
                     todo.append((inv, entry[1]))
             for (mp, _), g in zip(todo, _C.group_os_maps(todo)):

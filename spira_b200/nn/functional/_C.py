@@ -438,6 +438,20 @@ def group_os_map(map_os: torch.Tensor, num_targets: int) -> Optional[GroupedMap]
     return group_os_maps([(map_os, int(num_targets))])[0]
 
 
+def grouped_twin(map_os: torch.Tensor) -> Optional[GroupedMap]:
+    """The grouped twin of an engine-built output-stationary map, or None.  Maps from the network-wide builder carry it
+    already; a map from the single-map call (``cuda_binary_search``) gets it here, on the first convolution that runs
+    over it -- the map build itself returns what the reference's returns and costs what a map build costs."""
+    sb = getattr(map_os, "_sb", None)
+    if sb is None:
+        return None
+    g = sb.get("grouped")
+    if g is None and sb.get("group_lazy") is not None:
+        num_targets, sb["group_lazy"] = sb["group_lazy"], None
+        g = sb["grouped"] = group_os_map(map_os, num_targets)
+    return g
+
+
 def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_sizes=True, group=True):
     """Shared implementation of the serial and the network-wide builders.
 
@@ -571,7 +585,7 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
             w.qmapsize = None if qmapsize is None else int(qmapsize)
             m["ws"] = w.set_pointers()
 
-    if group:       # else the caller groups these maps together with others of its own
+    if group is True:       # False: the caller groups these maps together with others of its own; "lazy": on first use
         os_maps = [m for m in info if m["layout"] == LAYOUT_OS]
         for m, g in zip(os_maps, group_os_maps([(m["dense"], m["T"]) for m in os_maps])):
             m["grouped"] = g
@@ -579,7 +593,8 @@ def _build_maps(voxel_pairs, kernel_sizes, source_strides, dataflows, exact_size
     results = []
     for m in info:
         df, dense = m["df"], m["dense"]
-        dense._sb = dict(counts=m["counts"], ws=m.get("ws"), kernel_size=m["ks"], layout=m["layout"], grouped=m.get("grouped"))
+        dense._sb = dict(counts=m["counts"], ws=m.get("ws"), kernel_size=m["ks"], layout=m["layout"], grouped=m.get("grouped"),
+                         group_lazy=m["T"] if (group == "lazy" and m["layout"] == LAYOUT_OS) else None)
         if df >= 3:
             results.append(m["result"])
         elif df == 0:
@@ -775,7 +790,7 @@ def map_counts(map_tensor: torch.Tensor) -> Optional[torch.Tensor]:
 
 def cuda_binary_search(sources, targets, kernel_size, source_stride, dataflow: int = 0):
     """One kernel map.  Reference: ``BinarySearch`` (csrc/spira/torch/cuda_sparse_convolution_mapping.cu:211-892)."""
-    return _build_maps([(sources.contiguous(), targets.contiguous())], [kernel_size], [source_stride], [dataflow])[0]
+    return _build_maps([(sources.contiguous(), targets.contiguous())], [kernel_size], [source_stride], [dataflow], group="lazy")[0]
 
 
 def cuda_binary_search_streamed(voxels, kernel_sizes, source_strides, dataflow, exact_sizes=True):
@@ -785,7 +800,7 @@ def cuda_binary_search_streamed(voxels, kernel_sizes, source_strides, dataflow, 
         raise RuntimeError("[spira_b200] kernel_sizes, source_strides and dataflow must have the same length")
     voxels = [v.contiguous() for v in voxels]
     pairs = [(voxels[i // 2], voxels[(i + 1) // 2]) for i in range(len(kernel_sizes))]
-    return _build_maps(pairs, kernel_sizes, source_strides, dataflow, exact_sizes)
+    return _build_maps(pairs, kernel_sizes, source_strides, dataflow, exact_sizes, group="lazy")
 
 
 def cuda_binary_search_pairs(voxel_pairs, kernel_sizes, source_strides, dataflow, exact_sizes=True, group=True):
@@ -911,9 +926,8 @@ def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None
         out_in_map = padded
     packed = None if force_simt else packed_weights(weights, _lib.load().spira_b200_get_option(b"os_pack_mode"))
     ep, keep = _epilogue(bias, scale, shift, residual, relu)
-    sb = getattr(out_in_map, "_sb", None)
-    g = sb.get("grouped") if (sb is not None and grouped and GROUP_OS) else None
-    if g is not None and (packed is not None or _stem_shape(cin, cout, K)):
+    g = grouped_twin(out_in_map) if (grouped and GROUP_OS and (packed is not None or _stem_shape(cin, cout, K))) else None
+    if g is not None:
         _lib.call("spira_b200_conv_os_grouped", _ptr(sources), _ptr(weights), _ptr(packed), C.byref(ep) if ep is not None else None, g.map_ptr,
                   g.row_of_ptr, g.tile_masks_ptr, int(num_sources), int(num_targets), K, cin, cout, _ptr(out),
                   _ptr(status_word(sources.device)), _stream(sources.device))
@@ -1036,11 +1050,15 @@ def run_conv_os(call: ConvCall, num_sources: int, num_targets: int, out_in_map: 
     out = torch.empty((num_targets, call.cout), dtype=torch.float16, device=feats.device)
     call.ep.residual = residual.data_ptr() if residual is not None else None
     sb = getattr(out_in_map, "_sb", None)
-    g = sb.get("grouped") if sb is not None else None
+    g = None
+    if sb is not None and (call.eligible or call.stem) and GROUP_OS:
+        g = sb.get("grouped")
+        if g is None and sb.get("group_lazy") is not None:
+            g = grouped_twin(out_in_map)
     mode = _pack_mode[0]
     if mode < 0:
         mode = _pack_mode[0] = _lib.load().spira_b200_get_option(b"os_pack_mode")
-    if g is not None and (call.eligible or call.stem) and GROUP_OS:
+    if g is not None:
         name, fn = "spira_b200_conv_os_grouped", call.fn_os_grouped
         args = (feats.data_ptr(), call.w_ptr, call.packed_ptr(mode), call.ep_ref, g.map_ptr, g.row_of_ptr, g.tile_masks_ptr,
                 num_sources, num_targets, call.K, call.cin, call.cout, out.data_ptr(), call.status_ptr,

@@ -205,7 +205,7 @@ def test_grouping_reorders_the_map_without_changing_it(C, scene):
     for src, tgt, stride in ((keys, keys, (1, 1, 1)), (keys, down, (1, 1, 1))):
         m = C.cuda_binary_search(keys_to_torch(src), keys_to_torch(tgt), (3, 3, 3), stride, 0)
         T = len(tgt)
-        g = m[2]._sb["grouped"]
+        g = C.grouped_twin(m[2])
         assert g is not None
         dense = m[2].cpu().numpy()
         want_map, want_rows, want_masks, want_stats = O.group_os_map(dense, T)
@@ -227,7 +227,7 @@ def test_grouped_convolution_is_bit_identical(C, scene, cin, cout):
     for src, tgt in ((keys, keys), (keys, down)):
         S, T = len(src), len(tgt)
         m = C.cuda_binary_search(keys_to_torch(src), keys_to_torch(tgt), (3, 3, 3), (1, 1, 1), 0)
-        assert m[2]._sb["grouped"] is not None
+        assert C.grouped_twin(m[2]) is not None
         f, w = tensors(S, cin, cout, 27, cin * 7 + cout)
         res = torch.from_numpy(rng.normal(size=(T, cout)).astype(np.float16)).cuda()
         scale = torch.from_numpy(rng.uniform(0.5, 1.5, cout).astype(np.float32)).cuda()

@@ -97,7 +97,7 @@ def test_grouping_is_a_row_permutation_at_full_size(C, scene):
     _, keys, _ = scene
     T = keys.shape[0]
     m = C.cuda_binary_search(keys, keys, (3, 3, 3), (1, 1, 1), 0)
-    g = m[2]._sb["grouped"]
+    g = C.grouped_twin(m[2])
     row_of = g.row_of[:T].long()
     assert torch.equal(torch.sort(row_of).values, torch.arange(T, device="cuda"))
     assert torch.equal(g.map[:T], m[2][row_of])
