@@ -567,6 +567,7 @@ def main():
     ap.add_argument("--steps", type=int, default=32)     # (scenes of ~2 ms: 32 steps keep one slow step from moving the mean)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-kernels"])
+    ap.add_argument("--no-batched", action="store_true", help="skip the B-scenes-per-launch throughput reported as batched")
     ap.add_argument("--no-batch16", action="store_true", help="skip the 16-scene sharded SECOND-style batch reported as c4_batch16")
     ap.add_argument("--workload", default="minkunet", choices=["minkunet", "indoor", "second", "layer", "kmap"])
     ap.add_argument("--no-group", action="store_true", help="output-stationary maps keep their target order (no grouping by neighbour pattern)")
@@ -717,8 +718,10 @@ def main():
             line["cpu_baseline"] = {"value": round(scenes_done / cpu_s, 5), "unit": "scenes/s", "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": f"oracle port: sort + kernel maps (numpy) + {n_done}/{len(layers)} conv layers "
                                               f"(torch-CPU gather-GEMM-scatter) per scene, {scenes_done:.2f} scenes in {cpu_s:.1f} s; BN/ReLU omitted"}
+    del engine
+    if not args.no_batched:
+        line["batched"] = run_batched(args, args.workload, wl, device, rank, n_gpus, dev, l2buf, dist_ctx)
     if not args.no_batch16:
-        del engine
         line["c4_batch16"] = run_batch16(args, device, rank, world, dist_ctx, l2buf)
     if rank == 0:
         print(json.dumps(line))
@@ -885,6 +888,26 @@ def measure(engine, host, dev, args, l2buf, dist_ctx, device):
     return {"median_ms": res["median_ms"], "mean_ms": res["mean_ms"], "steps": res["steps"], "enqueue_ms": res["enqueue_ms"],
             "e2e_median_ms": e2e["median_ms"], "e2e_mean_ms": e2e["mean_ms"], "launches": launches,
             "h2d": int(np.mean([h[0].numel() * 4 + h[1].numel() * 2 for h in host])), "d2h": int(d2h_bytes[0])}
+
+
+def run_batched(args, workload_name, wl, device, rank, n_gpus, dev, l2buf, dist_ctx):
+    """Throughput with the rank's scenes merged into ONE sparse tensor per step (``spira_b200.batch.merge_scenes``: the
+    scenes lie side by side, far enough apart never to interact), so that every launch of the step works on all of
+    them: value = scenes of all ranks per second, from the median device time of a step.  Both arms alike."""
+    from spira_b200 import batch
+    coords, feats, pitch, grid = batch.merge_scenes([c for c, _ in dev], [f for _, f in dev])
+    if coords.shape[0] % 64 == 0:          # (see load_scenes)
+        coords, feats = coords[:-1].contiguous(), feats[:-1].contiguous()
+    merged = [(coords, feats)]
+    engine, note = make_engine(args, workload_name, wl, device, merged, rank)
+    for _ in range(2):
+        engine.step(coords, feats)
+    torch.cuda.synchronize()
+    res = timed_loop(lambda i: engine.step(coords, feats), max(4, args.steps // 2), args.warmup, l2buf, dist_ctx)
+    B = len(dev)
+    return {"value": round(n_gpus * B * 1e3 / res["median_ms"], 2), "unit": "scenes/s", "scenes_per_step": B,
+            "ms_per_step": round(res["median_ms"], 4), "voxels_per_step": int(coords.shape[0]), "grid": list(grid), "pitch": pitch,
+            "dataflows": note}
 
 
 def run_batch16(args, device, rank, world, dist_ctx, l2buf):

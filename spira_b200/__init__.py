@@ -15,5 +15,6 @@ from .operators import *
 from .compat import install_as_spira
 from .fusion import fuse
 from .compile import compile_model, CompiledModel
+from . import batch
 
 __version__ = "0.1.0"

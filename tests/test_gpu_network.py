@@ -310,3 +310,36 @@ def test_two_map_builds_in_flight_keep_their_own_level_sizes(lib):
             got = cache._coordinates_cache[stride].cpu().numpy().view(np.uint32)
             assert np.array_equal(got, want), f"level {stride} of a scene with {len(host)} voxels"
     _C.check_status()
+
+
+@pytest.mark.parametrize("kind", ["second", "minkunet"])
+def test_batched_scenes_compute_what_the_scenes_compute_alone(lib, kind):
+    """Three scenes merged into one sparse tensor (``spira_b200.batch``) against the same scenes one at a time.
+    The all-convolution backbone on the output-stationary dataflow must agree bit for bit; the U-Net (library GEMMs for
+    its 1x1x1 shortcuts, whose kernel choice depends on the row count) and the weight-stationary dataflow within tolerance."""
+    import spira_b200 as sp
+    from spira_b200 import batch, models, scenes, nn as spnn
+    from spira_b200.nn.functional import _C
+    torch.manual_seed(21)
+    cin, n_down = (5, 3) if kind == "second" else (4, 4)
+    model = (models.second_backbone(5) if kind == "second" else models.minkunet18(4, 19, 3)).cuda().half().eval()
+    cache = spnn.KernelMapCache()
+    sp.set_kernel_map_cache(model, cache)
+    sched = models.map_schedule(n_down, 3, 3)
+    parts = [(scenes.lidar_scene(s)[:n], s) for s, n in ((31, 30000), (32, 17000), (33, 42000))]
+    cs = [torch.from_numpy(c).cuda() for c, _ in parts]
+    fs = [torch.from_numpy(scenes.features(len(c), cin, s)).cuda() for c, s in parts]
+    mc, mf, pitch, grid = batch.merge_scenes(cs, fs)
+    for dataflow in (0, 1):
+        alone = [run(model, cache, c, f, sched, dataflow)[0] for c, f in zip(cs, fs)]
+        y, x = run(model, cache, mc, mf, sched, dataflow)
+        stride = y._stride[0]
+        ids = batch.scene_ids(_C.cuda_unflatten(y._coordinates), pitch, grid)
+        for b, (got, want) in enumerate(zip(batch.split_rows(y._features, ids, len(cs)), alone)):
+            assert got.shape == want._features.shape, f"scene {b}: {tuple(got.shape)} rows vs {tuple(want._features.shape)}"
+            if kind == "second" and dataflow == 0:
+                assert torch.equal(got, want._features), f"scene {b} differs between the batch and its own run"
+            else:
+                scale = max(want._features.float().abs().max().item(), 1.0)
+                assert (got.float() - want._features.float()).abs().max().item() <= 2e-2 * scale
+    _C.check_status()
