@@ -87,9 +87,12 @@ int spira_b200_flatten_sort_workspace(int64_t n, int key_bytes, size_t *bytes);
 
 /* pack + ascending unsigned sort + permutation; replaces cuda_flatten_sort
  * (csrc/spira/torch/cuda_arg_sort_coordinates.cu:11-39, cuda/functions/arg_sort_coodrinates.cu:35-88).
- * sorted_keys[n], perm[n] (int32, perm[i] = original row of sorted item i). */
+ * sorted_keys[n], perm[n] (int32, perm[i] = original row of sorted item i; equal keys keep their input order).
+ * ONE cooperative launch: a stable 8-bit radix sort whose passes are separated by grid barriers and which skips the
+ * digits that are the same in every key.  The 16-byte aligned workspace is cleared by the call.  `status` (device int32,
+ * may be NULL) is set to 1 if a grid-barrier wait ran into the "wait_limit_us" option (the result is then undefined). */
 int spira_b200_flatten_sort(const int32_t *coords, int64_t n, int key_bytes, void *sorted_keys, int32_t *perm,
-                            void *workspace, size_t workspace_bytes, void *stream);
+                            void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
 
 /* rows_out[i][:] = rows_in[perm[i]][:], row_bytes a multiple of 2; the feature permutation of
  * SparseTensor.order (spira/tensors.py:55-65). */
@@ -122,7 +125,9 @@ int spira_b200_downsample(const void *keys, int64_t n, int key_bytes, int n_leve
  * key is a sum of lengths of contiguous ranges of the sorted input, found by binary searches; level l+1 is computed
  * from the output of level l, whose size stays on the device.  The reference sorts every level from scratch
  * (csrc/spira/torch/cuda_arg_sort_coordinates.cu:107-200).  Other stride sequences: SPIRA_B200_ERR_UNSUPPORTED (use
- * spira_b200_downsample).  `status` (device int32, may be NULL) is cleared by the call and set to 2 if the input turns out not to be sorted. */
+ * spira_b200_downsample).  All levels are ONE cooperative launch (rank pass, grid barrier, compaction, per level).
+ * `status` (device int32, may be NULL) is cleared by the call and set to 2 if the input turns out not to be sorted, to 1
+ * if a grid-barrier wait ran into the "wait_limit_us" option. */
 int spira_b200_downsample_sorted_workspace(int64_t n, int key_bytes, size_t *bytes);
 int spira_b200_downsample_sorted(const void *sorted_keys, int64_t n, int key_bytes, int n_levels,
                                  const int32_t *host_strides, void *const *host_out_keys, int32_t *counts,

@@ -1,7 +1,8 @@
-// Packed voxel keys: pack / unpack, sort with permutation, strided down-sampling.
+// Packed voxel keys: pack / unpack, feature permutation, strided down-sampling of UNSORTED keys.
 //
-// The radix sort and the run-length "unique" use CUB device primitives (library-class ops);
-// everything else is hand written.
+// The sort of a scene's keys and the down-sampling of sorted keys (the path every scene takes) are hand-written
+// cooperative kernels in ingest.cu; the general down-sampling here (unsorted input, arbitrary power-of-two strides)
+// uses CUB's radix sort and run-length "unique" (library-class ops).
 #include <cub/cub.cuh>
 
 #include "common.cuh"
@@ -63,15 +64,6 @@ __global__ void __launch_bounds__(256) mask_levels_kernel(const KeyT *__restrict
 }
 
 template <typename KeyT>
-size_t sort_pairs_temp(int64_t n) {
-  size_t bytes = 0;
-  cub::DoubleBuffer<KeyT> dk(nullptr, nullptr);
-  cub::DoubleBuffer<int32_t> dv(nullptr, nullptr);
-  cub::DeviceRadixSort::SortPairs(nullptr, bytes, dk, dv, static_cast<int>(n), 0, int(sizeof(KeyT) * 8));
-  return bytes;
-}
-
-template <typename KeyT>
 size_t sort_keys_temp(int64_t n) {
   size_t a = 0, b = 0;
   cub::DoubleBuffer<KeyT> dk(nullptr, nullptr);
@@ -82,33 +74,6 @@ size_t sort_keys_temp(int64_t n) {
 }
 
 inline size_t round256(size_t b) { return (b + 255) / 256 * 256; }
-
-template <typename KeyT>
-int flatten_sort_impl(const int32_t *coords, int64_t n, KeyT *sorted_keys, int32_t *perm, void *ws, size_t ws_bytes,
-                      cudaStream_t stream) {
-  // workspace: [alt keys n][alt perm n][cub temp]
-  size_t temp = sort_pairs_temp<KeyT>(n);
-  size_t need = round256(n * sizeof(KeyT)) + round256(n * sizeof(int32_t)) + temp;
-  if (ws_bytes < need) return fail(SPIRA_B200_ERR_WORKSPACE, "flatten_sort: workspace %zu < %zu bytes", ws_bytes, need);
-  char *p = static_cast<char *>(ws);
-  KeyT *alt_keys = reinterpret_cast<KeyT *>(p);
-  p += round256(n * sizeof(KeyT));
-  int32_t *alt_perm = reinterpret_cast<int32_t *>(p);
-  p += round256(n * sizeof(int32_t));
-  if (n == 0) return SPIRA_B200_OK;
-  int blocks = static_cast<int>(div_up(n, 256));
-  // pack into the user's buffers, sort with a double buffer, copy back if the result landed in scratch
-  pack_kernel<KeyT><<<blocks, 256, 0, stream>>>(coords, n, sorted_keys, perm);
-  SB_CHECK_LAUNCH();
-  cub::DoubleBuffer<KeyT> dk(sorted_keys, alt_keys);
-  cub::DoubleBuffer<int32_t> dv(perm, alt_perm);
-  SB_CHECK_CUDA(cub::DeviceRadixSort::SortPairs(p, temp, dk, dv, static_cast<int>(n), 0, int(sizeof(KeyT) * 8), stream));
-  if (dk.Current() != sorted_keys)
-    SB_CHECK_CUDA(cudaMemcpyAsync(sorted_keys, dk.Current(), n * sizeof(KeyT), cudaMemcpyDeviceToDevice, stream));
-  if (dv.Current() != perm)
-    SB_CHECK_CUDA(cudaMemcpyAsync(perm, dv.Current(), n * sizeof(int32_t), cudaMemcpyDeviceToDevice, stream));
-  return SPIRA_B200_OK;
-}
 
 template <typename KeyT>
 KeyT stride_mask(const int32_t *s) {
@@ -157,73 +122,6 @@ int downsample_impl(const KeyT *keys, int64_t n, int n_levels, const int32_t *st
   return SPIRA_B200_OK;
 }
 
-// ---- down-sampling of SORTED keys without a sort -------------------------------------------------------------------
-// Level l+1 is computed from the sorted unique keys of level l when every stride doubles or stays.  Flooring a
-// coordinate to the coarser stride keeps the order along that axis, so the coarse keys are out of order only locally:
-// the keys that fall into one coarse cell (x', y', z') come from at most 2 x values, each with at most 2 y values,
-// each a run sorted by z.  The final position of a coarse key m is the number of input keys whose coarse key is
-// smaller, and that is a sum of lengths of contiguous ranges of the sorted input:
-//     #{x' < m.x}  +  sum over the x values of the cell of  #{that x, y' < m.y}
-//                  +  sum over the (x, y) values of the cell of  #{that x, that y, z' < m.z}
-// Every term is a difference of two lower bounds, found by binary searches inside the x' block of the element.
-// All inputs with the same coarse key compute the same position and store the same value there; positions that
-// nobody writes stay unflagged, and one stream compaction of the flagged slots yields the sorted unique coarse keys.
-template <typename KeyT>
-__device__ __forceinline__ int lower_bound_range(const KeyT *__restrict__ a, int lo, int hi, KeyT v) {
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    if (a[mid] < v) lo = mid + 1; else hi = mid;
-  }
-  return lo;
-}
-
-template <typename KeyT>
-__global__ void __launch_bounds__(256) coarsen_rank_kernel(const KeyT *__restrict__ in, const int32_t *__restrict__ n_dev,
-                                                            int n_host, int sx, int sy, int sz,     // strides of `in`
-                                                            int rx, int ry, int rz,                 // 1 or 2 per axis
-                                                            KeyT *__restrict__ vals, unsigned char *__restrict__ flags,
-                                                            int32_t *__restrict__ status) {
-  using L = KeyLayout<KeyT>;
-  const int n = n_dev ? *n_dev : n_host;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const KeyT key = in[i];
-  if (i > 0 && in[i - 1] > key && status) atomicExch(status, 2);      // the input was not sorted: report, do not guess
-  constexpr KeyT XM = (KeyT(1) << L::XB) - 1, YM = (KeyT(1) << L::YB) - 1, ZM = (KeyT(1) << L::ZB) - 1;
-  const KeyT x = (key >> KeyShift<KeyT>::X) & XM, y = (key >> KeyShift<KeyT>::Y) & YM, z = key & ZM;
-  const KeyT X0 = x & ~static_cast<KeyT>(sx * rx - 1), Y0 = y & ~static_cast<KeyT>(sy * ry - 1),
-             Z0 = z & ~static_cast<KeyT>(sz * rz - 1);
-  auto pack3 = [](KeyT a, KeyT b, KeyT c) { return (a << KeyShift<KeyT>::X) | (b << KeyShift<KeyT>::Y) | c; };
-  // the x' block of this element
-  const int lo = lower_bound_range(in, 0, n, pack3(X0, 0, 0));
-  const KeyT x_end = X0 + static_cast<KeyT>(sx * rx);
-  const int hi = x_end <= XM ? lower_bound_range(in, lo, n, pack3(x_end, 0, 0)) : n;
-  int pos = lo;
-  for (int jx = 0; jx < rx; ++jx) {
-    const KeyT xc = X0 + static_cast<KeyT>(jx * sx);
-    const int a0 = jx == 0 ? lo : lower_bound_range(in, lo, hi, pack3(xc, 0, 0));
-    int a1 = lower_bound_range(in, a0, hi, pack3(xc, Y0, 0));
-    pos += a1 - a0;
-    for (int jy = 0; jy < ry; ++jy) {
-      const KeyT yc = Y0 + static_cast<KeyT>(jy * sy);
-      const int b0 = jy == 0 ? a1 : lower_bound_range(in, a1, hi, pack3(xc, yc, 0));
-      const int b1 = lower_bound_range(in, b0, hi, pack3(xc, yc, Z0));
-      pos += b1 - b0;
-      a1 = b1;      // later searches of this x start behind what was already passed
-    }
-  }
-  vals[pos] = pack3(X0, Y0, Z0);
-  flags[pos] = 1;
-}
-
-template <typename KeyT>
-size_t select_flagged_temp(int64_t n) {
-  size_t b = 0;
-  cub::DeviceSelect::Flagged(nullptr, b, (const KeyT *)nullptr, (const unsigned char *)nullptr, (KeyT *)nullptr,
-                             (int32_t *)nullptr, static_cast<int>(n));
-  return b;
-}
-
 // strides[l] must be, per axis, equal to or twice strides[l-1] (strides[-1] = 1)
 inline bool strides_double(int n_levels, const int32_t *strides) {
   int prev[3] = {1, 1, 1};
@@ -236,43 +134,13 @@ inline bool strides_double(int n_levels, const int32_t *strides) {
   return true;
 }
 
-template <typename KeyT>
-int downsample_sorted_impl(const KeyT *keys, int64_t n, int n_levels, const int32_t *strides, void *const *out_keys,
-                           int32_t *counts, void *ws, size_t ws_bytes, int32_t *status, cudaStream_t stream) {
-  // workspace: [vals n][flags n, one array per level so that ONE memset clears them all][cub temp]
-  const size_t temp = select_flagged_temp<KeyT>(n);
-  const size_t need = round256(n * sizeof(KeyT)) + SPIRA_B200_MAX_LEVELS * round256(n) + temp;
-  if (ws_bytes < need) return fail(SPIRA_B200_ERR_WORKSPACE, "downsample_sorted: workspace %zu < %zu bytes", ws_bytes, need);
-  if (n == 0) {
-    SB_CHECK_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_levels, stream));
-    return SPIRA_B200_OK;
-  }
-  char *base = static_cast<char *>(ws);
-  KeyT *vals = reinterpret_cast<KeyT *>(base);
-  unsigned char *all_flags = reinterpret_cast<unsigned char *>(base + round256(n * sizeof(KeyT)));
-  void *temp_ptr = base + round256(n * sizeof(KeyT)) + SPIRA_B200_MAX_LEVELS * round256(n);
-  int prev[3] = {1, 1, 1};
-  const KeyT *in = keys;
-  const int32_t *n_dev = nullptr;
-  if (status) SB_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
-  SB_CHECK_CUDA(cudaMemsetAsync(all_flags, 0, n_levels * round256(n), stream));
-  for (int l = 0; l < n_levels; ++l) {
-    const int32_t *s = strides + 3 * l;
-    unsigned char *flags = all_flags + l * round256(n);
-    // level sizes beyond the first are only known on the device: launch for the upper bound n
-    coarsen_rank_kernel<KeyT><<<static_cast<int>(div_up(n, 256)), 256, 0, stream>>>(
-        in, n_dev, static_cast<int>(n), prev[0], prev[1], prev[2], s[0] / prev[0], s[1] / prev[1], s[2] / prev[2], vals, flags,
-        status);
-    SB_CHECK_LAUNCH();
-    size_t t = temp;
-    SB_CHECK_CUDA(cub::DeviceSelect::Flagged(temp_ptr, t, vals, flags, static_cast<KeyT *>(out_keys[l]), counts + l,
-                                             static_cast<int>(n), stream));
-    in = static_cast<const KeyT *>(out_keys[l]);
-    n_dev = counts + l;
-    for (int a = 0; a < 3; ++a) prev[a] = s[a];
-  }
-  return SPIRA_B200_OK;
-}
+// scene ingest in cooperative launches (ingest.cu)
+size_t ingest_sort_workspace(int64_t n, int key_bytes);
+int ingest_sort(const int32_t *coords, int64_t n, int key_bytes, void *sorted_keys, int32_t *perm, void *ws, size_t ws_bytes,
+                int32_t *status, cudaStream_t stream);
+size_t ingest_coarsen_workspace(int64_t n, int key_bytes);
+int ingest_coarsen(const void *keys, int64_t n, int key_bytes, int n_levels, const int32_t *strides, void *const *out_keys,
+                   int32_t *counts, void *ws, size_t ws_bytes, int32_t *status, cudaStream_t stream);
 
 }  // namespace sb
 
@@ -316,20 +184,17 @@ extern "C" int spira_b200_unpack(const void *keys, int64_t n, int key_bytes, int
 extern "C" int spira_b200_flatten_sort_workspace(int64_t n, int key_bytes, size_t *bytes) {
   SB_CHECK_ARG(bytes != nullptr, "flatten_sort_workspace: null output");
   SB_CHECK_ARG(n >= 0 && n < (int64_t(1) << 31), "flatten_sort: n=%lld out of range", (long long)n);
-  SB_KEY_DISPATCH(key_bytes, {
-    *bytes = round256(n * sizeof(KeyT)) + round256(n * sizeof(int32_t)) + sort_pairs_temp<KeyT>(n) + 256;
-  })
+  SB_CHECK_ARG(key_bytes == 4 || key_bytes == 8, "key_bytes must be 4 or 8, got %d", key_bytes);
+  *bytes = ingest_sort_workspace(n, key_bytes);
   return SPIRA_B200_OK;
 }
 
 extern "C" int spira_b200_flatten_sort(const int32_t *coords, int64_t n, int key_bytes, void *sorted_keys,
-                                       int32_t *perm, void *workspace, size_t workspace_bytes, void *stream) {
+                                       int32_t *perm, void *workspace, size_t workspace_bytes, int32_t *status, void *stream) {
   SB_CHECK_ARG(n >= 0 && n < (int64_t(1) << 31), "flatten_sort: n=%lld out of range", (long long)n);
   SB_CHECK_ARG(n == 0 || (coords && sorted_keys && perm && workspace), "flatten_sort: null pointer");
-  SB_KEY_DISPATCH(key_bytes, {
-    return flatten_sort_impl<KeyT>(coords, n, static_cast<KeyT *>(sorted_keys), perm, workspace, workspace_bytes,
-                                   as_stream(stream));
-  })
+  SB_CHECK_ARG(key_bytes == 4 || key_bytes == 8, "key_bytes must be 4 or 8, got %d", key_bytes);
+  return ingest_sort(coords, n, key_bytes, sorted_keys, perm, workspace, workspace_bytes, status, as_stream(stream));
 }
 
 extern "C" int spira_b200_permute_rows(const void *rows_in, const int32_t *perm, int64_t n, int64_t row_bytes,
@@ -386,9 +251,8 @@ extern "C" int spira_b200_downsample(const void *keys, int64_t n, int key_bytes,
 extern "C" int spira_b200_downsample_sorted_workspace(int64_t n, int key_bytes, size_t *bytes) {
   SB_CHECK_ARG(bytes != nullptr, "downsample_sorted_workspace: null output");
   SB_CHECK_ARG(n >= 0 && n < (int64_t(1) << 31), "downsample_sorted: n=%lld out of range", (long long)n);
-  SB_KEY_DISPATCH(key_bytes, {
-    *bytes = round256(n * sizeof(KeyT)) + SPIRA_B200_MAX_LEVELS * round256(n) + select_flagged_temp<KeyT>(n) + 256;
-  })
+  SB_CHECK_ARG(key_bytes == 4 || key_bytes == 8, "key_bytes must be 4 or 8, got %d", key_bytes);
+  *bytes = ingest_coarsen_workspace(n, key_bytes);
   return SPIRA_B200_OK;
 }
 
@@ -409,8 +273,7 @@ extern "C" int spira_b200_downsample_sorted(const void *sorted_keys, int64_t n, 
   if (!strides_double(n_levels, host_strides))
     return fail(SPIRA_B200_ERR_UNSUPPORTED, "downsample_sorted: every stride must equal or double the stride of the level before");
   SB_CHECK_ARG(n == 0 || (sorted_keys && workspace), "downsample_sorted: null pointer");
-  SB_KEY_DISPATCH(key_bytes, {
-    return downsample_sorted_impl<KeyT>(static_cast<const KeyT *>(sorted_keys), n, n_levels, host_strides, host_out_keys,
-                                        counts, workspace, workspace_bytes, status, as_stream(stream));
-  })
+  SB_CHECK_ARG(key_bytes == 4 || key_bytes == 8, "key_bytes must be 4 or 8, got %d", key_bytes);
+  return ingest_coarsen(sorted_keys, n, key_bytes, n_levels, host_strides, host_out_keys, counts, workspace, workspace_bytes,
+                        status, as_stream(stream));
 }

@@ -94,7 +94,7 @@ def cuda_flatten_sort(coordinates: torch.Tensor, is_double: bool = False):
     _lib.call("spira_b200_flatten_sort_workspace", n, kb, C.byref(need))
     ws = torch.empty(need.value, dtype=torch.uint8, device=coordinates.device)
     _lib.call("spira_b200_flatten_sort", _ptr(coordinates), n, kb, _ptr(keys), _ptr(perm), _ptr(ws), need.value,
-              _stream(coordinates.device))
+              _ptr(status_word(coordinates.device)), _stream(coordinates.device))
     return keys, perm
 
 
