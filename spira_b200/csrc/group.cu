@@ -11,10 +11,13 @@
 // The sort key keeps the 19 highest mask bits beside the 5-bit count of absent offsets: 24 bits are three radix passes
 // instead of four, and on LiDAR-like scenes the processed rows per pair grow by less than 0.5 % against the full mask.
 //
+// The sort is the library's cooperative radix sort (radix_sort.cuh): the keys are generated from the map rows inside its
+// first phase, and the digits that are the same for every row are skipped, so a network's maps take three or four 8-bit
+// passes inside ONE launch.
+//
 // The reference has no counterpart: its output-stationary kernel walks the map in target order.
-#include <cub/cub.cuh>
-
 #include "common.cuh"
+#include "radix_sort.cuh"
 
 namespace sb {
 
@@ -37,23 +40,23 @@ struct GroupBatch {
 
 // Sort key of row t of map m: map index on top (the maps stay apart); below it, for K <= 27, K - popcount (fullest rows
 // first) and the 19 highest bits of the mask (rows with similar masks adjacent); for larger K the complemented mask.
-__global__ void __launch_bounds__(256) group_keys_kernel(const __grid_constant__ GroupBatch B, uint64_t *__restrict__ keys,
-                                                          int32_t *__restrict__ iota) {
-  const int64_t g = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
-  if (g >= B.row_base[B.n_maps]) return;
-  int m = 0;
-  while (m + 1 < B.n_maps && g >= B.row_base[m + 1]) ++m;
-  const int64_t t = g - B.row_base[m];
-  const int K = B.K[m];
-  const int32_t *row = B.map_os[m] + t * K;
-  uint32_t mask = 0;
-  for (int k = 0; k < K; ++k) mask |= (row[k] >= 0 ? 1u : 0u) << k;
-  const int drop = K > kGroupMaskBits ? K - kGroupMaskBits : 0;
-  const uint32_t low = (K <= 27) ? ((static_cast<uint32_t>(K - __popc(mask)) << kGroupMaskBits) | (mask >> drop)) : ~mask;
-  keys[g] = (static_cast<uint64_t>(m) << B.key_bits) | low;
-  iota[g] = static_cast<int32_t>(g);
-  if (t == 0) { B.stats[m][0] = 0; B.stats[m][1] = 0; }      // counted by the kernels that follow on the stream
-}
+// Element g of the sort is row g - row_base[m] of map m.
+struct GroupKeyGen {
+  GroupBatch B;
+  __device__ __forceinline__ uint64_t operator()(int g) const {
+    int m = 0;
+    while (m + 1 < B.n_maps && g >= B.row_base[m + 1]) ++m;
+    const int64_t t = g - B.row_base[m];
+    const int K = B.K[m];
+    const int32_t *row = B.map_os[m] + t * K;
+    uint32_t mask = 0;
+    for (int k = 0; k < K; ++k) mask |= (row[k] >= 0 ? 1u : 0u) << k;
+    const int drop = K > kGroupMaskBits ? K - kGroupMaskBits : 0;
+    const uint32_t low = (K <= 27) ? ((static_cast<uint32_t>(K - __popc(mask)) << kGroupMaskBits) | (mask >> drop)) : ~mask;
+    if (t == 0) { B.stats[m][0] = 0; B.stats[m][1] = 0; }      // counted by the kernel that follows on the stream
+    return (static_cast<uint64_t>(m) << B.key_bits) | low;
+  }
+};
 
 // One CTA per pair of 128-row tiles: gathers the rows of the map in the new order (through shared memory, so that the
 // grouped map is written with coalesced stores), ORs the presence masks of each tile and counts the non-empty
@@ -100,14 +103,6 @@ __global__ void __launch_bounds__(2 * kGroupTile) group_rows_kernel(const __grid
   }
 }
 
-static size_t sort_temp_bytes(int64_t n) {
-  size_t bytes = 0;
-  cub::DeviceRadixSort::SortPairs(nullptr, bytes, static_cast<const uint64_t *>(nullptr), static_cast<uint64_t *>(nullptr),
-                                  static_cast<const int32_t *>(nullptr), static_cast<int32_t *>(nullptr),
-                                  static_cast<int>(n));
-  return bytes;
-}
-
 static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 
 }  // namespace sb
@@ -117,7 +112,8 @@ using namespace sb;
 extern "C" int spira_b200_kmap_group_workspace(int64_t total_targets, size_t *bytes) {
   SB_CHECK_ARG(bytes != nullptr, "kmap_group_workspace: null output");
   SB_CHECK_ARG(total_targets >= 0 && total_targets < (int64_t(1) << 31) - 128, "kmap_group: total_targets out of range");
-  *bytes = 2 * round256(total_targets * 8) + 2 * round256(total_targets * 4) + round256(sort_temp_bytes(total_targets)) + 256;
+  // [sorted keys][order][workspace of the sort]
+  *bytes = round256(total_targets * 8) + round256(total_targets * 4) + sort_workspace_bytes<uint64_t>(total_targets) + 256;
   return SPIRA_B200_OK;
 }
 
@@ -158,18 +154,13 @@ extern "C" int spira_b200_kmap_group(const spira_b200_group_desc *descs, int n_m
   unsigned char *w = static_cast<unsigned char *>(workspace);
   w += (256 - reinterpret_cast<uintptr_t>(w) % 256) % 256;
   const size_t col8 = round256(rows * 8), col4 = round256(rows * 4);
-  uint64_t *keys = reinterpret_cast<uint64_t *>(w);
-  uint64_t *keys_sorted = reinterpret_cast<uint64_t *>(w + col8);
-  int32_t *iota = reinterpret_cast<int32_t *>(w + 2 * col8);
-  int32_t *order = reinterpret_cast<int32_t *>(w + 2 * col8 + col4);
-  void *temp = w + 2 * col8 + 2 * col4;
-  size_t temp_bytes = sort_temp_bytes(rows);
-  group_keys_kernel<<<static_cast<unsigned>(div_up(rows, 256)), 256, 0, st>>>(B, keys, iota);
-  SB_CHECK_LAUNCH();
-  int map_bits = 0;
-  while ((1 << map_bits) < n_maps) ++map_bits;
-  SB_CHECK_CUDA(cub::DeviceRadixSort::SortPairs(temp, temp_bytes, keys, keys_sorted, iota, order, static_cast<int>(rows), 0,
-                                                B.key_bits + map_bits, st));
+  uint64_t *keys_sorted = reinterpret_cast<uint64_t *>(w);
+  int32_t *order = reinterpret_cast<int32_t *>(w + col8);
+  const int wait_us = spira_b200_get_option("wait_limit_us");
+  int rc = radix_sort_generated<uint64_t>(GroupKeyGen{B}, rows, keys_sorted, order, w + col8 + col4, sort_workspace_bytes<uint64_t>(rows),
+                                          nullptr, static_cast<unsigned long long>(wait_us > 0 ? wait_us : 1500000) * 1000ull, st,
+                                          "kmap_group");
+  if (rc != SPIRA_B200_OK) return rc;
   group_rows_kernel<<<static_cast<unsigned>(pairs), 2 * kGroupTile, 2 * kGroupTile * max_K * sizeof(int32_t), st>>>(B, order);
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
