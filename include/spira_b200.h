@@ -312,6 +312,28 @@ int spira_b200_conv_os_grouped(const void *feats, const void *weights, const voi
                                const uint32_t *tile_masks, int64_t num_sources, int64_t num_targets, int K, int c_in,
                                int c_out, void *out, int32_t *status, void *stream);
 
+/* Output-stationary convolution of a SMALL layer with the reduction of every 128-target tile shared among `splits`
+ * CTAs (2, 4 or 8), so that a deep network level of a few thousand voxels occupies all SMs instead of one SM per tile.
+ * No reference counterpart: the reference runs such layers through its ordinary output-stationary kernel
+ * (csrc/spira/cuda/kernels/output_stat.cuh:19-189).  CTA i of a tile takes the tile's non-empty 64-wide reduction chunks
+ * i, i + splits, ...; the fp32 partial sums meet in `scratch`, each CTA then adds the partials of c_out / splits columns
+ * in the fixed order 0 .. splits-1 (deterministic; rounds differently from spira_b200_conv_os, whose single CTA adds all
+ * chunks in TMEM), applies the epilogue and writes fp16.  The kernel is launched cooperatively and the CTAs of a tile
+ * wait for one another with the bounded wait of the "wait_limit_us" option (expiry is reported through `status`; the
+ * scratch must then be cleared before its next use).
+ *   map_os / row_of / tile_masks   a plain [T_al][K] map (row_of = tile_masks = NULL) or a grouped one
+ *   scratch   caller-owned, 16-byte aligned; its first 1024 bytes are tile counters that must be ZERO on entry and are
+ *             zero again when the call completes, the rest is overwritten.  Calls that share a scratch must be ordered
+ *             on one stream.
+ * spira_b200_conv_os_split_plan reports the largest `splits` a layer takes (1: none -- more than 128 tiles, tiles x 2
+ * beyond the SM count, c_out / splits not a multiple of 8, or fewer than 4 chunks per CTA) and the scratch bytes needed
+ * at that count: 1024 + T_al * splits * c_out * 4. */
+int spira_b200_conv_os_split_plan(int64_t num_targets, int K, int c_in, int c_out, int *max_splits, size_t *scratch_bytes);
+int spira_b200_conv_os_split(const void *feats, const void *packed, const spira_b200_epilogue *epilogue,
+                             const int32_t *map_os, const int32_t *row_of, const uint32_t *tile_masks, int64_t num_sources,
+                             int64_t num_targets, int K, int c_in, int c_out, int splits, void *scratch,
+                             size_t scratch_bytes, void *out, int32_t *status, void *stream);
+
 /* Weight-stationary gather-GEMM-scatter over compacted pair lists: for row k and pair p in
  * [naddrs[k], naddrs[k+1]):  accum[out_idx[p]][:] += feats[in_idx[p]][:] @ W[k].  With
  * `mirror` != 0 (submanifold map, rows == (K+1)/2) every row k is also applied with in/out swapped

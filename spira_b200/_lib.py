@@ -89,6 +89,9 @@ SIGNATURES = {
     "spira_b200_kmap_group": [C.POINTER(GroupDesc), c_int, c_void_p, c_size_t, c_void_p],
     "spira_b200_conv_os_grouped": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_int64,
                                    c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "spira_b200_conv_os_split_plan": [c_int64, c_int, c_int, c_int, C.POINTER(c_int), C.POINTER(c_size_t)],
+    "spira_b200_conv_os_split": [c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int,
+                                 c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p],
     "spira_b200_conv_ws": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                            c_void_p, c_void_p],
@@ -135,7 +138,8 @@ KERNELS_PER_CALL = {
     "spira_b200_pack": 1, "spira_b200_unpack": 1, "spira_b200_flatten_sort": 1, "spira_b200_permute_rows": 1,
     "spira_b200_downsample": 1, "spira_b200_pointwise": 1, "spira_b200_downsample_sorted": 1, "spira_b200_kmap_search": 1, "spira_b200_kmap_ws_sizes": 2, "spira_b200_kmap_ws_pairs": 1, "spira_b200_kmap_ws_lists": 3,
     "spira_b200_kmap_masks": 1, "spira_b200_kmap_masks_half": 1, "spira_b200_kmap_lists_from_masks": 3, "spira_b200_convert_transposed_os": 1, "spira_b200_transpose_map": 1,
-    "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_os_grouped": 1, "spira_b200_kmap_group": 2,
+    "spira_b200_pack_weights": 1, "spira_b200_conv_os": 1, "spira_b200_conv_os_grouped": 1, "spira_b200_conv_os_split": 1,
+    "spira_b200_kmap_group": 2,
     "spira_b200_conv_ws": 2, "spira_b200_conv_ws_fused": 1, "spira_b200_conv_ws_static": 2,
 }
 launch_count = 0          # kernels launched through `call` since import (or since it was last reset by the caller)

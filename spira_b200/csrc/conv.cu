@@ -83,6 +83,11 @@ struct ConvParams {
   int T, n_tiles, K, c_in, c_out, R, n_chunks;  // n_chunks: OS = ceil(R/64); WS = ceil(c_in/64) per offset
   int stages, teams, slab_bufs, b_bytes, acc_stride, tmem_cols;
   int off_b, off_slab, off_flags, off_cm, off_meta, off_bar;
+  // OS, split reduction: `split` CTAs share one tile, CTA blockIdx.x % split takes every split-th non-empty chunk, the
+  // partial sums meet in split_scratch [tile][split][c_out][128] fp32 and every CTA reduces c_out / split columns
+  int split;
+  float *split_scratch;
+  unsigned *split_counters;     // [2][n_tiles]: arrivals and leavers per tile, zero between launches
   unsigned long long wait_ns;   // limit of every internal wait (mbarriers, grid barrier)
 };
 
@@ -159,8 +164,13 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // i-th tile of this CTA: the output-stationary cp.async path alternates the direction of the rounds
+  const int split = (!kWS && !kTma) ? P.split : 1;
+  const int split_rank = split > 1 ? static_cast<int>(blockIdx.x) % split : 0;
   auto tile_at = [&](int i) -> int {
-    if constexpr (!kWS && !kTma) return snake_tile(i);
+    if constexpr (!kWS && !kTma) {
+      if (split > 1) return i == 0 ? static_cast<int>(blockIdx.x) / split : 0x7fffffff;      // one tile per CTA
+      return snake_tile(i);
+    }
     return static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x);
   };
 
@@ -417,16 +427,26 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         for (int w = tid; w < n_words; w += kProducers) cmask[((tile_i + 1) & 1) * n_words + w] = 0;
         int n_chunks_tile = 0;
         for (int w = 0; w < n_words; ++w) n_chunks_tile += __popc(my_cmask[w]);
-        const bool force_first = (n_chunks_tile == 0);   // a tile always sends at least one chunk
-        if (force_first) n_chunks_tile = 1;
+        // A CTA always sends at least one chunk: a tile without neighbours, or (split reduction) a CTA whose share of the
+        // tile's chunks is empty, sends chunk 0 with all rows zero.
+        const bool force_first = (n_chunks_tile <= split_rank);
+        int my_last = 0;                                 // the last chunk number e this CTA sends
+        if (force_first) {
+          n_chunks_tile = 1;
+        } else {
+          my_last = split_rank + (n_chunks_tile - 1 - split_rank) / split * split;
+        }
         // Chunk number e (0-based, in increasing j) of the tile is pipeline item q = q_base + e and goes to stage
         // q % stages; this team owns the items with q % teams == team (teams divides stages).  All of it is tracked
         // incrementally: an integer division per chunk would dominate this latency-bound instruction stream.
+        // (Split reduction: this CTA's items are the chunks e = rank, rank + split, ...; item number (e - rank) / split.)
         int word = 0, pos = 0;                           // walks the set bits of the mask: `pos` of them are behind
         uint32_t bits = force_first ? 1u : my_cmask[0];
         int e = team - q_mod_teams;
         if (e < 0) e += teams;
-        for (; active && ok && e < n_chunks_tile; e += teams) {
+        const int e_step = teams * split;
+        if (split > 1) e = force_first ? team : split_rank + team * split;
+        for (; active && ok && e < n_chunks_tile; e += e_step) {
           while (true) {                                 // e < number of set bits, so the walk stays inside the mask
             while (bits == 0) bits = my_cmask[++word];
             if (pos == e) break;
@@ -439,7 +459,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           my_stage += teams;
           ++my_slot;
           if (my_stage >= stages) { my_stage -= stages; my_slot = 0; my_phase ^= 1; }
-          if (r == 0) post_weights(stage, j, min(kChunk, P.R - j * kChunk), e == 0, e == n_chunks_tile - 1);
+          if (r == 0) post_weights(stage, j, min(kChunk, P.R - j * kChunk), e == (force_first ? 0 : split_rank), e == my_last);
           // this thread's piece belongs to one offset k and starts at channel c of it
           const int rr = j * kChunk + piece * 8;
           const int k = __float2int_rd((static_cast<float>(rr) + 0.5f) * inv_c_in);
@@ -453,7 +473,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           // them would queue behind them in the load/store unit
           int idx[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) idx[i] = piece_valid ? col[i * 16 * P.K] : -1;
+          for (int i = 0; i < 8; ++i) idx[i] = (piece_valid && !(force_first && split > 1)) ? col[i * 16 * P.K] : -1;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const __half *src = P.feats + (idx[i] >= 0 ? (static_cast<int64_t>(idx[i]) * P.c_in + c) : 0);
@@ -525,6 +545,75 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       } else {
         const int64_t t = static_cast<int64_t>(tile) * kRows + row;
         out_row = t < P.T ? (P.row_of ? P.row_of[t] : t) : -1;
+      }
+      if constexpr (!kWS && !kTma) {
+        if (split > 1) {
+          // ---- split reduction: park this CTA's partial sums (column-major, so that a warp writes 32 consecutive rows
+          // of a column), meet the other CTAs of the tile, then reduce this CTA's share of the columns in a fixed order
+          float *part = P.split_scratch + (static_cast<int64_t>(tile) * split + split_rank) * P.c_out * kRows + row;
+          for (int c0 = 0; c0 < P.c_out; c0 += 16) {
+            uint32_t h[16];
+            tmem_ld_32x16(taddr + c0, h);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) __stcg(part + (c0 + i) * kRows, __uint_as_float(h[i]));
+          }
+          tc_fence_before();
+          mbar_arrive(bar_acc_empty(b));
+          __threadfence();
+          named_bar_sync(2, kRows);
+          if (q == 0 && lane == 0) {
+            atomicAdd(P.split_counters + tile, 1u);
+            const unsigned long long t0 = global_timer_ns();
+            int polls = 0;
+            while (*reinterpret_cast<volatile unsigned *>(P.split_counters + tile) < static_cast<unsigned>(split)) {
+              if ((++polls & 31) == 0 && global_timer_ns() - t0 > P.wait_ns) { *abort_flag = 1; break; }
+            }
+            __threadfence();
+          }
+          named_bar_sync(2, kRows);
+          if (*abort_flag != 0) break;
+          const int cw = P.c_out / split, cbase = split_rank * cw;        // cw is a multiple of 8
+          const float *all = P.split_scratch + static_cast<int64_t>(tile) * split * P.c_out * kRows + row;
+          for (int c8 = 0; c8 < cw; c8 += 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+            for (int sp = 0; sp < split; ++sp) {
+              const float *src = all + (static_cast<int64_t>(sp) * P.c_out + cbase + c8) * kRows;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] += __ldcg(src + i * kRows);
+            }
+            if (out_row >= 0) {
+              const int c = cbase + c8;
+              uint4 rv = make_uint4(0, 0, 0, 0);
+              if (P.ep.residual) rv = *reinterpret_cast<const uint4 *>(P.ep.residual + out_row * P.c_out + c);
+              const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+              uint4 pack;
+              uint32_t *pw = reinterpret_cast<uint32_t *>(&pack);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float v0 = epilogue_apply(v[2 * e], c + 2 * e, P.ep);
+                float v1 = epilogue_apply(v[2 * e + 1], c + 2 * e + 1, P.ep);
+                if (P.ep.residual) { v0 += __low2float(rh[e]); v1 += __high2float(rh[e]); }
+                if (P.ep.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
+                const __half2 hv = __floats2half2_rn(v0, v1);
+                pw[e] = *reinterpret_cast<const uint32_t *>(&hv);
+              }
+              *reinterpret_cast<uint4 *>(P.out + out_row * P.c_out + c) = pack;
+            }
+          }
+          // the last CTA to leave the tile clears its counters for the next launch
+          named_bar_sync(2, kRows);
+          if (q == 0 && lane == 0) {
+            unsigned *leavers = P.split_counters + n_tiles + tile;
+            if (atomicAdd(leavers, 1u) == static_cast<unsigned>(split) - 1u) {
+              P.split_counters[tile] = 0u;
+              *leavers = 0u;
+            }
+          }
+          continue;
+        }
       }
       for (int c0 = 0; c0 < P.c_out; c0 += 32) {
         uint32_t r[32];
@@ -1255,6 +1344,16 @@ static int launch_conv_tc(ConvParams &P, bool tma, size_t smem, int64_t num_sour
     return SPIRA_B200_OK;
   }
   if (grid <= 0) return SPIRA_B200_OK;
+  if (!kWS && P.split > 1) {
+    // the CTAs of a tile wait for one another: cooperative launch, all of them resident
+    grid = P.n_tiles * P.split;
+    SB_CHECK_CUDA(cudaFuncSetAttribute(conv_tc_kernel<kWS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    void *args[] = {&P, &tmap};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(&conv_tc_kernel<kWS, false>), dim3(grid),
+                                                dim3(kConvThreads), args, smem, st);
+    if (e != cudaSuccess) return fail(SPIRA_B200_ERR_CUDA, "conv_os_split: cooperative launch failed: %s", cudaGetErrorString(e));
+    return SPIRA_B200_OK;
+  }
   if (tma) {
     int rc = make_feats_tensor_map(&tmap, P.feats, num_sources, P.c_in);
     if (rc != SPIRA_B200_OK) return rc;
@@ -1381,9 +1480,35 @@ extern "C" int spira_b200_conv_kernel_choice(int weight_stationary, int K, int c
   return os_n256_applies(K, c_in, c_out, num_targets) ? SPIRA_B200_KERNEL_N256_OS : SPIRA_B200_KERNEL_TC_OS;
 }
 
+// Split reduction of the output-stationary kernel: the head of the caller's scratch holds the per-tile counters (arrivals,
+// leavers; zero whenever no launch is in flight), the fp32 partial sums follow.
+constexpr size_t kSplitCounterBytes = 1024;
+constexpr int kSplitMaxTiles = static_cast<int>(kSplitCounterBytes / 8);
+
+static int split_limit(int64_t num_targets, int K, int c_in, int c_out) {
+  if (!tc_eligible(K, c_in, c_out) || num_targets <= 0) return 1;
+  const int64_t n_tiles = align128(num_targets) / kRows;
+  if (n_tiles > kSplitMaxTiles) return 1;
+  const int64_t chunks = div_up(static_cast<int64_t>(K) * c_in, kChunk);
+  for (int s = 8; s >= 2; s >>= 1)
+    if (n_tiles * s <= sm_count() && c_out % (8 * s) == 0 && chunks >= 4 * s) return s;
+  return 1;
+}
+
+extern "C" int spira_b200_conv_os_split_plan(int64_t num_targets, int K, int c_in, int c_out, int *max_splits,
+                                             size_t *scratch_bytes) {
+  SB_CHECK_ARG(max_splits && scratch_bytes, "conv_os_split_plan: null output");
+  SB_CHECK_ARG(K >= 1 && c_in >= 1 && c_out >= 1 && num_targets >= 0, "conv_os_split_plan: K=%d c_in=%d c_out=%d", K, c_in, c_out);
+  const int s = split_limit(num_targets, K, c_in, c_out);
+  *max_splits = s;
+  *scratch_bytes = s > 1 ? kSplitCounterBytes + static_cast<size_t>(align128(num_targets)) * s * c_out * sizeof(float) : 0;
+  return SPIRA_B200_OK;
+}
+
 static int conv_os_impl(const void *feats, const void *weights, const void *packed, const spira_b200_epilogue *epilogue,
                         const int32_t *map_os, const int32_t *row_of, const uint32_t *tile_masks, int64_t num_sources,
-                        int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status, void *stream) {
+                        int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status, void *stream,
+                        int splits = 1, void *split_scratch = nullptr, size_t split_scratch_bytes = 0) {
   SB_CHECK_ARG(num_sources >= 0 && num_targets >= 0 && num_targets < (int64_t(1) << 31) - 128 &&
                    num_sources < (int64_t(1) << 31),
                "conv_os: sizes out of range");
@@ -1422,9 +1547,18 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
                    reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(map_os) % 16 == 0 &&
                    (ep.residual == nullptr || reinterpret_cast<uintptr_t>(ep.residual) % 16 == 0),
                "conv_os: feats, packed, out, map and residual must be 16-byte aligned");
+  if (splits > 1) {
+    SB_CHECK_ARG(packed != nullptr, "conv_os_split: needs a packed weight image");
+    SB_CHECK_ARG((splits == 2 || splits == 4 || splits == 8) && splits <= split_limit(num_targets, K, c_in, c_out),
+                 "conv_os_split: %d splits not possible for %lld targets, K=%d, c_in=%d, c_out=%d (see spira_b200_conv_os_split_plan)",
+                 splits, static_cast<long long>(num_targets), K, c_in, c_out);
+    SB_CHECK_ARG(split_scratch && reinterpret_cast<uintptr_t>(split_scratch) % 16 == 0 &&
+                     split_scratch_bytes >= kSplitCounterBytes + static_cast<size_t>(align128(num_targets)) * splits * c_out * sizeof(float),
+                 "conv_os_split: scratch missing, misaligned or too small");
+  }
   // On grouped maps both kernels run at the speed of the row gathers; the 256-target tiles then only pay off for the
   // wider layers (measured: 32 channels 20 % slower, 64 equal, 96 5 % faster than 128-target tiles).
-  if (os_n256_applies(K, c_in, c_out, num_targets)) {
+  if (splits <= 1 && os_n256_applies(K, c_in, c_out, num_targets)) {
     ConvN2Params Q{};
     Q.feats = static_cast<const __half *>(feats);
     Q.packed = static_cast<const unsigned char *>(packed);
@@ -1463,7 +1597,12 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
   P.n_tiles = static_cast<int>(align128(num_targets) / kRows);
   P.K = K; P.c_in = c_in; P.c_out = c_out;
   P.wait_ns = wait_limit_ns();
-  const bool tma = g_gather_tma != 0 && num_sources > 0 && K <= 512;
+  const bool tma = g_gather_tma != 0 && num_sources > 0 && K <= 512 && splits <= 1;
+  P.split = splits > 1 ? splits : 1;
+  if (splits > 1) {
+    P.split_counters = static_cast<unsigned *>(split_scratch);
+    P.split_scratch = reinterpret_cast<float *>(static_cast<unsigned char *>(split_scratch) + kSplitCounterBytes);
+  }
   P.R = K * c_in;
   // TMA gather: every offset owns ceil(c_in/64) chunks (PACK_WS image); cp.async: 64-wide chunks over the whole reduction
   P.n_chunks = tma ? static_cast<int>(div_up(c_in, kChunk)) : static_cast<int>(div_up(P.R, kChunk));
@@ -1489,6 +1628,17 @@ extern "C" int spira_b200_conv_os_grouped(const void *feats, const void *weights
   SB_CHECK_ARG(K <= 32, "conv_os_grouped: K=%d, grouped maps have at most 32 offsets", K);
   return conv_os_impl(feats, weights, packed, epilogue, grouped_map, row_of, tile_masks, num_sources, num_targets, K, c_in,
                       c_out, out, status, stream);
+}
+
+extern "C" int spira_b200_conv_os_split(const void *feats, const void *packed, const spira_b200_epilogue *epilogue,
+                                        const int32_t *map_os, const int32_t *row_of, const uint32_t *tile_masks,
+                                        int64_t num_sources, int64_t num_targets, int K, int c_in, int c_out, int splits,
+                                        void *scratch, size_t scratch_bytes, void *out, int32_t *status, void *stream) {
+  SB_CHECK_ARG((row_of == nullptr) == (tile_masks == nullptr), "conv_os_split: row_of and tile_masks come together");
+  SB_CHECK_ARG(row_of == nullptr || K <= 32, "conv_os_split: K=%d, grouped maps have at most 32 offsets", K);
+  SB_CHECK_ARG(splits >= 1, "conv_os_split: splits=%d", splits);
+  return conv_os_impl(feats, nullptr, packed, epilogue, map_os, row_of, tile_masks, num_sources, num_targets, K, c_in, c_out,
+                      out, status, stream, splits, scratch, scratch_bytes);
 }
 
 static int conv_ws_impl(const void *feats, const void *weights, const void *packed, const spira_b200_epilogue *epilogue,

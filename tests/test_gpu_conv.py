@@ -233,11 +233,68 @@ def test_grouped_convolution_is_bit_identical(C, scene, cin, cout):
         scale = torch.from_numpy(rng.uniform(0.5, 1.5, cout).astype(np.float32)).cuda()
         shift = torch.from_numpy(rng.normal(size=cout).astype(np.float32)).cuda()
         for kw in ({}, dict(scale=scale, shift=shift, residual=res, relu=True)):
-            a = C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=True, **kw)
-            b = C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=False, **kw)
+            a = C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=True, splits=1, **kw)
+            b = C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=False, splits=1, **kw)
             assert torch.equal(a, b)
         assert_features_close(C.conv_os(S, T, m[2], f.cuda(), w.cuda()), O.conv_os(f, w, m[2].cpu().numpy(), T))
     C.check_status()
+
+
+@pytest.mark.parametrize("n", [1, 700, 2000, 9000])
+@pytest.mark.parametrize("cin,cout", [(64, 64), (128, 128), (256, 256), (96, 48)])
+def test_split_output_stationary_agrees_and_is_deterministic(C, n, cin, cout):
+    """Tiles shared among 2, 4 or 8 CTAs: same sums as one CTA per tile up to the order of the fp32 additions
+    (compared with the oracle and with the unsplit call at the usual tolerance), the same bits on every run, tile
+    counters back at zero."""
+    keys, _ = O.flat_sort(surface(n + 3, n))
+    n = len(keys)
+    down = O.downsample(keys, (2, 2, 2))
+    rng = np.random.default_rng(n + cin)
+    for src, tgt, ks in ((keys, keys, (3, 3, 3)), (keys, down, (2, 2, 2))):
+        S, T = len(src), len(tgt)
+        K = ks[0] ** 3
+        m = C.cuda_binary_search(keys_to_torch(src), keys_to_torch(tgt), ks, (1, 1, 1), 0)
+        limit, _ = C.os_split_plan(T, K, cin, cout)
+        f, w = tensors(S, cin, cout, K, cin + cout + n)
+        res = torch.from_numpy(rng.normal(size=(T, cout)).astype(np.float16)).cuda()
+        scale = torch.from_numpy(rng.uniform(0.5, 1.5, cout).astype(np.float32)).cuda()
+        shift = torch.from_numpy(rng.normal(size=cout).astype(np.float32)).cuda()
+        bias = torch.from_numpy(rng.normal(size=cout).astype(np.float16)).cuda()
+        want = O.conv_os(f, w, m[2].cpu().numpy(), T)
+        for splits in (2, 4, 8):
+            if splits > limit:
+                with pytest.raises(RuntimeError):
+                    C.conv_os(S, T, m[2], f.cuda(), w.cuda(), splits=splits)
+                continue
+            for grouped in (True, False):
+                got = C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=grouped, splits=splits)
+                assert_features_close(got, want)
+                assert torch.equal(got, C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=grouped, splits=splits))
+                kw = dict(bias=bias, scale=scale, shift=shift, residual=res, relu=True)
+                a = C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=grouped, splits=splits, **kw)
+                b = C.conv_os(S, T, m[2], f.cuda(), w.cuda(), grouped=grouped, splits=1, **kw)
+                assert_features_close(a, b.float().cpu())
+                assert float((ulp_distance(a, b) <= 1).float().mean()) > 0.99      # (cancellation against the residual aside)
+            scratch = C.split_scratch(torch.device("cuda", 0), 1024)
+            assert int(scratch[:1024].max()) == 0
+        if limit >= 4:      # the opt-in default: the largest split the layer takes
+            C.OS_SPLIT = True
+            try:
+                auto = C.cuda_sparse_convolution_forward_os(S, T, m[2], f.cuda(), w.cuda())
+            finally:
+                C.OS_SPLIT = False
+            assert torch.equal(auto, C.conv_os(S, T, m[2], f.cuda(), w.cuda(), splits=limit))
+    C.check_status()
+
+
+def test_split_plan_limits(C):
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert C.os_split_plan(128 * (sms // 8), 27, 256, 256)[0] == 8
+    assert C.os_split_plan(128 * (sms // 8) + 1, 27, 256, 256)[0] == 4
+    assert C.os_split_plan(128 * (sms // 2) + 1, 27, 256, 256)[0] == 1
+    assert C.os_split_plan(1000, 27, 96, 48) == (2, 1024 + 1024 * 2 * 48 * 4)       # 48 / 4 is not a multiple of 8
+    assert C.os_split_plan(1000, 27, 4, 32)[0] == 1                                  # not tensor-core eligible
+    assert C.os_split_plan(1000, 1, 64, 64)[0] == 1                                  # one chunk: nothing to share
 
 
 def test_grouping_rejects_wide_kernels(C, lib):
