@@ -535,17 +535,27 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     int tile_i = 0;
     for (int tile = tile_at(0); tile < n_tiles; tile = tile_at(++tile_i)) {
       const int b = tile_i & 1;
+      int64_t out_row = -1;
+      uint4 res_next[4];          // residual of the next 32 columns: requested before the wait for the accumulator / the TMEM load
+      auto fetch_residual = [&](int c0) {
+        if (out_row >= 0 && P.ep.residual && c0 < P.c_out) {
+          const __half *src = P.ep.residual + out_row * P.c_out + c0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (c0 + 8 * i < P.c_out) res_next[i] = *reinterpret_cast<const uint4 *>(src + 8 * i);
+        }
+      };
+      if constexpr (!kWS) {
+        // the output row and the first residual values are on their way while the tile's MMAs are still running
+        const int64_t t = static_cast<int64_t>(tile) * kRows + row;
+        out_row = t < P.T ? (P.row_of ? P.row_of[t] : t) : -1;
+        if (split <= 1) fetch_residual(0);
+      }
       if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag, P.wait_ns)) break;
       acc_phase ^= 1u << b;
       tc_fence_after();
       const uint32_t taddr = tmem_base + b * P.acc_stride + (static_cast<uint32_t>(q * 32) << 16);
-      int64_t out_row;
-      if constexpr (kWS) {
-        out_row = slab[kRows + (tile_i & (kScatterRing - 1)) * kRows + row];
-      } else {
-        const int64_t t = static_cast<int64_t>(tile) * kRows + row;
-        out_row = t < P.T ? (P.row_of ? P.row_of[t] : t) : -1;
-      }
+      if constexpr (kWS) out_row = slab[kRows + (tile_i & (kScatterRing - 1)) * kRows + row];
       if constexpr (!kWS && !kTma) {
         if (split > 1) {
           // ---- split reduction: park this CTA's partial sums (column-major, so that a warp writes 32 consecutive rows
@@ -638,14 +648,13 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
                                __uint_as_float(r[i + 3]));
           } else {
             __half *dst = P.out + out_row * P.c_out + c0;
-            const __half *res = P.ep.residual ? P.ep.residual + out_row * P.c_out + c0 : nullptr;
+            const bool res = P.ep.residual != nullptr;
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               if (i < width) {
                 uint4 pack;
                 uint32_t *pw = reinterpret_cast<uint32_t *>(&pack);
-                uint4 rv = make_uint4(0, 0, 0, 0);
-                if (res) rv = *reinterpret_cast<const uint4 *>(res + i);
+                const uint4 rv = res_next[i >> 3];
                 const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -659,6 +668,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
                 *reinterpret_cast<uint4 *>(dst + i) = pack;
               }
             }
+            fetch_residual(c0 + 32);      // (the accumulator registers are free again: no pressure from the values in flight)
           }
         }
       }
@@ -985,19 +995,37 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     uint32_t *tr = reinterpret_cast<uint32_t *>(smem + P.off_tr) + q * (32 * 17);
     uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
+    const bool has_res = P.ep.residual != nullptr;
     for (int tile = snake_tile(0); tile < P.n_tiles; tile = snake_tile(++tile_i)) {
       const int b = tile_i & 1;
+      const int64_t t0 = static_cast<int64_t>(tile) * kN2Rows;
+      // Output rows and residual values do not depend on the accumulator: under the load of the row gathers a dependent
+      // global load takes ~2 k cycles, so they are fetched ahead -- the output rows two blocks of 32 targets ahead, the
+      // residual one block ahead, the first ones while the tile's MMAs are still running.
+      auto orow_of = [&](int jb) -> int {      // output row of target jb * 32 + lane (-1: none)
+        const int64_t t = t0 + jb * 32 + lane;
+        return (jb < kN2Rows / 32 && t < P.T) ? (P.row_of ? P.row_of[t] : static_cast<int>(t)) : -1;
+      };
+      uint4 res[2][2];
+      auto fetch_residual = [&](int orow_lane, int h) {      // (all lanes take part in the shuffle)
+        const int orow = __shfl_sync(0xffffffffu, orow_lane, 16 * h + tl);
+        if (has_res && orow >= 0 && ch0 < n_valid) {
+          const __half *src = P.ep.residual + static_cast<int64_t>(orow) * P.c_out + q * 32 + ch0;
+          res[h][0] = *reinterpret_cast<const uint4 *>(src);
+          res[h][1] = *reinterpret_cast<const uint4 *>(src + 8);
+        }
+      };
+      int orow_cur = orow_of(0), orow_next = orow_of(1);
+      fetch_residual(orow_cur, 0);
+      fetch_residual(orow_cur, 1);
       if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag, P.wait_ns)) break;
       acc_phase ^= 1u << b;
       tc_fence_after();
       if (n_valid > 0) {
         const uint32_t taddr = tmem_base + b * kN2Rows + (static_cast<uint32_t>(q * 32) << 16);
-        const int64_t t0 = static_cast<int64_t>(tile) * kN2Rows;
         for (int jb = 0; jb < kN2Rows / 32; ++jb) {
           if (t0 + jb * 32 >= P.T) break;                       // warp-uniform: no target left in this block
-          // output row of target jb*32 + lane (-1: none); the transposed halves fetch theirs with a shuffle
-          const int64_t t = t0 + jb * 32 + lane;
-          const int orow_lane = t < P.T ? (P.row_of ? P.row_of[t] : static_cast<int>(t)) : -1;
+          const int orow_after = orow_of(jb + 2);
           uint32_t v[32];
           tmem_ld_32x32(taddr + jb * 32, v);
           tmem_ld_wait();
@@ -1007,23 +1035,23 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
             for (int i = 0; i < 16; ++i)
               tr[lane * 17 + i] = __float_as_uint((__uint_as_float(v[16 * h + i]) + bias) * scale + shift);
             __syncwarp();
-            const int orow = __shfl_sync(0xffffffffu, orow_lane, 16 * h + tl);
+            const int orow = __shfl_sync(0xffffffffu, orow_cur, 16 * h + tl);
             float x[16];
 #pragma unroll
             for (int m = 0; m < 16; ++m) x[m] = __uint_as_float(tr[(ch0 + m) * 17 + tl]);
             __syncwarp();
-            if (orow >= 0 && ch0 < n_valid) {
-              const int64_t base = static_cast<int64_t>(orow) * P.c_out + q * 32 + ch0;
-              if (P.ep.residual) {
-                const uint4 r0 = *reinterpret_cast<const uint4 *>(P.ep.residual + base);
-                const uint4 r1 = *reinterpret_cast<const uint4 *>(P.ep.residual + base + 8);
-                const __half2 *rh0 = reinterpret_cast<const __half2 *>(&r0), *rh1 = reinterpret_cast<const __half2 *>(&r1);
+            const bool mine = orow >= 0 && ch0 < n_valid;
+            if (mine && has_res) {
+              const __half2 *rh0 = reinterpret_cast<const __half2 *>(&res[h][0]), *rh1 = reinterpret_cast<const __half2 *>(&res[h][1]);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  x[2 * e] += __low2float(rh0[e]); x[2 * e + 1] += __high2float(rh0[e]);
-                  x[8 + 2 * e] += __low2float(rh1[e]); x[8 + 2 * e + 1] += __high2float(rh1[e]);
-                }
+              for (int e = 0; e < 4; ++e) {
+                x[2 * e] += __low2float(rh0[e]); x[2 * e + 1] += __high2float(rh0[e]);
+                x[8 + 2 * e] += __low2float(rh1[e]); x[8 + 2 * e + 1] += __high2float(rh1[e]);
               }
+            }
+            fetch_residual(orow_next, h);                       // the same half of the next block
+            if (mine) {
+              const int64_t base = static_cast<int64_t>(orow) * P.c_out + q * 32 + ch0;
               uint32_t y[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
@@ -1036,6 +1064,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
               *reinterpret_cast<uint4 *>(P.out + base + 8) = make_uint4(y[4], y[5], y[6], y[7]);
             }
           }
+          orow_cur = orow_next;
+          orow_next = orow_after;
         }
       }
       tc_fence_before();
