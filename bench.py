@@ -581,6 +581,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dataflow", default="auto", choices=["auto", "0", "1"], help="auto = per-group selector (tune); 0/1 = uniform")
     ap.add_argument("--no-compile", action="store_true", help="run the eager module path instead of the recorded tape (ours arm)")
+    ap.add_argument("--tape", default="auto", choices=["auto", "native", "replay"],
+                    help="forward replay of the ours arm: the library's tape executor, the Python replay, or whichever runs whole steps faster on this box")
+    ap.add_argument("--no-native-tape", action="store_true", help="replay the recorded tape operator by operator from Python instead of one spira_b200_run_tape call per scene (ours arm)")
     ap.add_argument("--no-fuse", action="store_true", help="keep BatchNorm / ReLU / residual adds as separate passes (ours arm)")
     ap.add_argument("--dump-layers", default=None, help="write the per-layer timing table of the profiled step to this JSON file")
     args = ap.parse_args()
@@ -673,7 +676,9 @@ def main():
                    "setup": "tune / compile, then every scene once untimed (allocator priming), then the W warm-up steps",
                    "dataflows": chosen_note, "sharding": "independent scenes per GPU, no collective",
                    "fused_epilogue": bool(args.impl == "ours" and not args.no_fuse),
-                   "recorded_tape": bool(args.impl == "ours" and not args.no_compile)},
+                   "recorded_tape": bool(args.impl == "ours" and not args.no_compile),
+                   "native_tape": bool(getattr(getattr(engine, "compiled", None), "use_native", False)),
+                   "tape_choice_ms": getattr(engine, "tape_choice", None)},
         "e2e": {"value": round(n_gpus * 1e3 / m["e2e_median_ms"], 3), "unit": "scenes/s", "ms_per_step": round(m["e2e_median_ms"], 4),
                 "mean_ms_per_step": round(m["e2e_mean_ms"], 4), "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"]},
         "mean_ms_per_step": round(m["mean_ms"], 4),
@@ -805,7 +810,29 @@ def make_engine(args, workload_name, wl, device, dev, rank):
             ref_mod.cuda_reset_error()
             engine.set_uniform_dataflow(best[0])
     if args.impl == "ours" and not args.no_compile:
+        if args.no_native_tape:
+            import spira_b200.compile as spc
+            spc.NATIVE_TAPE = False
         engine.compile(*dev[0])
+        engine.tape_choice = None
+        if engine.compiled.native is not None and args.tape == "auto":
+            # part of the setup, like the dataflow selection: whole steps timed with the forward replayed from Python and
+            # through the library's tape executor; the faster one stays (which one that is depends on the host)
+            took = {}
+            for mode in (True, False, True, False):
+                engine.compiled.use_native = mode
+                for i in range(3):
+                    engine.step(*dev[i % len(dev)])
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for i in range(12):
+                    engine.step(*dev[i % len(dev)])
+                torch.cuda.synchronize()
+                took.setdefault(mode, []).append((time.perf_counter() - t0) / 12 * 1e3)
+            engine.compiled.use_native = min(took[True]) <= min(took[False])
+            engine.tape_choice = {"native_ms": round(min(took[True]), 4), "replay_ms": round(min(took[False]), 4)}
+        elif engine.compiled.native is not None:
+            engine.compiled.use_native = args.tape == "native"
     return engine, chosen_note
 
 

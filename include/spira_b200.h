@@ -334,6 +334,103 @@ int spira_b200_conv_os_split(const void *feats, const void *packed, const spira_
                              int64_t num_targets, int K, int c_in, int c_out, int splits, void *scratch,
                              size_t scratch_bytes, void *out, int32_t *status, void *stream);
 
+/* One convolution from a descriptor: the tensor-core paths of spira_b200_conv_os / _os_grouped / _os_split (dataflow 0) and
+ * spira_b200_conv_ws_fused (dataflow 1) behind one call, plus two forms the positional entry points do not have:
+ *   two sources   the input rows are the channel concatenation of two tensors that share the map, never materialised:
+ *                 channels [0, c_in_a) of source row s come from feats[s][0..c_in_a), channels [c_in_a, c_in) from
+ *                 feats_b[s][0..c_in - c_in_a).  The weights stay [K][c_in][c_out].  c_in_a must be a multiple of 8.
+ *                 (The reference concatenates first: spira/operators.py:11-13 -- one more read and write of both tensors.)
+ *   identity map  dataflow 0 with K == 1 and map_os == NULL: target t reads source t (a 1x1x1 layer: the reference runs it
+ *                 as a dense matrix product, spira/nn/conv.py:312-316).
+ * `packed` is the SPIRA_B200_PACK_OS image for dataflow 0 and the SPIRA_B200_PACK_WS image for dataflow 1.  A layer
+ * outside the tensor-core kernels (spira_b200_tensor_core_eligible == 0) passes packed = NULL and its plain `weights`
+ * instead: dataflow 0 only, one source, no identity map, and a grouped map only for the narrow-input shapes
+ * spira_b200_conv_os_grouped takes without an image.  Everything else -- epilogue, status word, scratch contracts,
+ * stream binding of dataflow 1 -- is as documented for the positional calls. */
+typedef struct spira_b200_conv_desc {
+  int32_t dataflow;            /* 0 output-stationary, 1 weight-stationary (single fused launch) */
+  int32_t K, c_in, c_out;
+  int32_t c_in_a;              /* channels taken from `feats`; 0 or c_in: one source */
+  int32_t rows, mirror, swap;  /* dataflow 1: as for spira_b200_conv_ws */
+  int32_t splits;              /* dataflow 0: CTAs per tile (0 or 1: one), as for spira_b200_conv_os_split */
+  int32_t reserved;
+  int64_t num_sources, num_targets;
+  int64_t num_tiles128;        /* dataflow 1: qnaddrs[rows] / 128, or -1 */
+  const void *feats, *feats_b;
+  const void *packed;
+  const void *weights;         /* fp16 [K][c_in][c_out]; read only when packed == NULL */
+  const spira_b200_epilogue *epilogue;   /* may be NULL */
+  const int32_t *map_os;       /* dataflow 0: [T_al][K], plain or grouped; NULL = identity (K == 1) */
+  const int32_t *row_of;       /* dataflow 0, grouped map: with tile_masks, else both NULL */
+  const uint32_t *tile_masks;
+  const int32_t *in_idx, *out_idx, *naddrs, *qnaddrs;   /* dataflow 1 */
+  float *zeroed_accum;         /* dataflow 1: the always-zero scratch of spira_b200_conv_ws_fused */
+  void *split_scratch;         /* dataflow 0, splits > 1 */
+  size_t split_scratch_bytes;
+  void *out;                   /* fp16 [num_targets][c_out] */
+} spira_b200_conv_desc;
+int spira_b200_conv(const spira_b200_conv_desc *desc, int32_t *status, void *stream);
+
+/* A whole network forward as ONE call: the operators of a recorded forward pass, executed in order on `stream`.  No
+ * reference counterpart (its forward is eager PyTorch, one Python call chain per layer: spira/nn/conv.py:310-419); the
+ * host cost of a scene drops from one interpreter round trip per layer to one per scene.
+ *   ops     the static part: operator kinds, shapes, weight images, epilogue constants, and which SLOT (feature tensor
+ *           of the forward pass) each operator reads and writes
+ *   maps    the kernel maps of THIS scene, indexed by spira_b200_tape_op.map
+ *   slots   per slot its row count for this scene, its channel count, and its address: slots with a non-NULL `ptr`
+ *           (the network input, the outputs the caller wants to keep) are used as given, the others are placed in
+ *           `arena` -- slots that share a `buffer` number share storage (the caller assigns the numbers from the
+ *           lifetimes of the recorded pass); `ptr` is filled in for every slot on return
+ *   arena   caller-owned device memory, 256-byte aligned; if `arena_bytes` is too small the call launches nothing,
+ *           stores the size it needs in *arena_needed and returns SPIRA_B200_ERR_UNSUPPORTED
+ * Operator kinds:
+ *   SPIRA_B200_TAPE_CONV       spira_b200_conv on maps[op.map]: dataflow 0 uses its output-stationary form (the grouped
+ *                              one if op.grouped != 0 and the map has it; transposed != 0: the inverted forms `*_t`
+ *                              with sources and targets exchanged), dataflow 1 its pair lists (transposed != 0: swap)
+ *   SPIRA_B200_TAPE_IDENTITY   a 1x1x1 layer through the identity map (rows of in_a)
+ *   SPIRA_B200_TAPE_POINTWISE  spira_b200_pointwise (1x1x1 layer with at most 32 output channels)
+ * The residual slot of an operator, if any, replaces epilogue.residual. */
+#define SPIRA_B200_TAPE_CONV 0
+#define SPIRA_B200_TAPE_IDENTITY 1
+#define SPIRA_B200_TAPE_POINTWISE 2
+typedef struct spira_b200_tape_map {
+  int64_t num_sources, num_targets;
+  const int32_t *map_os;       /* [T_al][K] in target order, or NULL when the scene built only the lists */
+  const int32_t *grouped_map;  /* its grouped twin with row_of and tile_masks, or all three NULL */
+  const int32_t *row_of;
+  const uint32_t *tile_masks;
+  const int32_t *map_os_t;     /* inverted map [S_al][K] for transposed layers run output-stationary, else NULL */
+  const int32_t *grouped_map_t;
+  const int32_t *row_of_t;
+  const uint32_t *tile_masks_t;
+  const int32_t *in_idx, *out_idx, *naddrs, *qnaddrs;
+  int32_t rows, mirror;
+  int64_t num_tiles128;
+} spira_b200_tape_map;
+typedef struct spira_b200_tape_op {
+  int32_t kind;
+  int32_t dataflow, transposed;
+  int32_t map;                 /* index into maps (TAPE_CONV) */
+  int32_t in_a, in_b;          /* input slots; in_b = -1: one source */
+  int32_t residual;            /* slot or -1 */
+  int32_t out;                 /* output slot */
+  int32_t K, c_in, c_in_a, c_out;
+  int32_t grouped;             /* dataflow 0: run over the grouped twin of the map where it exists */
+  int32_t reserved;
+  const void *packed;          /* TAPE_CONV / TAPE_IDENTITY: weight image of the operator's dataflow, or NULL */
+  const void *weights;         /* TAPE_POINTWISE: fp16 [c_in][c_out]; TAPE_CONV with packed == NULL: fp16 [K][c_in][c_out] */
+  spira_b200_epilogue epilogue;   /* bias / scale / shift / relu of the operator (residual is taken from the slot) */
+} spira_b200_tape_op;
+typedef struct spira_b200_tape_slot {
+  int64_t rows;
+  int32_t channels;
+  int32_t buffer;              /* arena buffer number, -1 with a caller-given ptr */
+  void *ptr;
+} spira_b200_tape_slot;
+int spira_b200_run_tape(const spira_b200_tape_op *ops, int n_ops, const spira_b200_tape_map *maps, int n_maps,
+                        spira_b200_tape_slot *slots, int n_slots, void *arena, size_t arena_bytes, size_t *arena_needed,
+                        float *zeroed_accum, size_t zeroed_accum_floats, int32_t *status, void *stream);
+
 /* Weight-stationary gather-GEMM-scatter over compacted pair lists: for row k and pair p in
  * [naddrs[k], naddrs[k+1]):  accum[out_idx[p]][:] += feats[in_idx[p]][:] @ W[k].  With
  * `mirror` != 0 (submanifold map, rows == (K+1)/2) every row k is also applied with in/out swapped

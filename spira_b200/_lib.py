@@ -43,6 +43,40 @@ class Epilogue(C.Structure):
                 ("relu", c_int32), ("reserved", c_int32)]
 
 
+class ConvDesc(C.Structure):
+    """Mirror of ``spira_b200_conv_desc`` (include/spira_b200.h)."""
+    _fields_ = [("dataflow", c_int32), ("K", c_int32), ("c_in", c_int32), ("c_out", c_int32), ("c_in_a", c_int32),
+                ("rows", c_int32), ("mirror", c_int32), ("swap", c_int32), ("splits", c_int32), ("reserved", c_int32),
+                ("num_sources", c_int64), ("num_targets", c_int64), ("num_tiles128", c_int64),
+                ("feats", c_void_p), ("feats_b", c_void_p), ("packed", c_void_p), ("weights", c_void_p), ("epilogue", C.POINTER(Epilogue)),
+                ("map_os", c_void_p), ("row_of", c_void_p), ("tile_masks", c_void_p),
+                ("in_idx", c_void_p), ("out_idx", c_void_p), ("naddrs", c_void_p), ("qnaddrs", c_void_p),
+                ("zeroed_accum", c_void_p), ("split_scratch", c_void_p), ("split_scratch_bytes", c_size_t), ("out", c_void_p)]
+
+
+class TapeMap(C.Structure):
+    """Mirror of ``spira_b200_tape_map`` (include/spira_b200.h)."""
+    _fields_ = [("num_sources", c_int64), ("num_targets", c_int64),
+                ("map_os", c_void_p), ("grouped_map", c_void_p), ("row_of", c_void_p), ("tile_masks", c_void_p),
+                ("map_os_t", c_void_p), ("grouped_map_t", c_void_p), ("row_of_t", c_void_p), ("tile_masks_t", c_void_p),
+                ("in_idx", c_void_p), ("out_idx", c_void_p), ("naddrs", c_void_p), ("qnaddrs", c_void_p),
+                ("rows", c_int32), ("mirror", c_int32), ("num_tiles128", c_int64)]
+
+
+class TapeOp(C.Structure):
+    """Mirror of ``spira_b200_tape_op`` (include/spira_b200.h)."""
+    _fields_ = [("kind", c_int32), ("dataflow", c_int32), ("transposed", c_int32), ("map", c_int32),
+                ("in_a", c_int32), ("in_b", c_int32), ("residual", c_int32), ("out", c_int32),
+                ("K", c_int32), ("c_in", c_int32), ("c_in_a", c_int32), ("c_out", c_int32),
+                ("grouped", c_int32), ("reserved", c_int32), ("packed", c_void_p), ("weights", c_void_p), ("epilogue", Epilogue)]
+
+
+class TapeSlot(C.Structure):
+    """Mirror of ``spira_b200_tape_slot`` (include/spira_b200.h)."""
+    _fields_ = [("rows", c_int64), ("channels", c_int32), ("buffer", c_int32), ("ptr", c_void_p)]
+
+
+TAPE_CONV, TAPE_IDENTITY, TAPE_POINTWISE = 0, 1, 2
 LAYOUT_OS, LAYOUT_WS = 0, 1
 KERNEL_NAMES = {0: "conv_os_simt_kernel", 1: "conv_os_stem_kernel", 2: "conv_tc_kernel<OS>", 3: "conv_os_n256_kernel",
                 4: "conv_tc_kernel<WS>", 5: "conv_ws_simt_kernel"}
@@ -92,6 +126,9 @@ SIGNATURES = {
     "spira_b200_conv_os_split_plan": [c_int64, c_int, c_int, c_int, C.POINTER(c_int), C.POINTER(c_size_t)],
     "spira_b200_conv_os_split": [c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int,
                                  c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p],
+    "spira_b200_conv": [C.POINTER(ConvDesc), c_void_p, c_void_p],
+    "spira_b200_run_tape": [C.POINTER(TapeOp), c_int, C.POINTER(TapeMap), c_int, C.POINTER(TapeSlot), c_int, c_void_p, c_size_t,
+                            C.POINTER(c_size_t), c_void_p, c_size_t, c_void_p, c_void_p],
     "spira_b200_conv_ws": [c_void_p, c_void_p, c_void_p, C.POINTER(Epilogue), c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int64, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                            c_void_p, c_void_p],

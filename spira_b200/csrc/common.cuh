@@ -56,4 +56,7 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// One convolution from its descriptor (the body of spira_b200_conv; the tape executor calls it per operator).
+int conv_run(const spira_b200_conv_desc &desc, int32_t *status, void *stream);
+
 }  // namespace sb

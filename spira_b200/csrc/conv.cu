@@ -64,7 +64,12 @@ __device__ __forceinline__ int snake_tile(int i) {
 }
 
 struct ConvParams {
+  // Input rows may come from two tensors that share the map (a channel concatenation that is never materialised):
+  // channels [0, c_a) of a row from feats (row pitch c_a), channels [c_a, c_in) from feats_b (row pitch c_in - c_a).
+  // One source: c_a == c_in.  A 16-byte piece (8 channels) never straddles the two: c_a is a multiple of 8.
   const __half *feats;
+  const __half *feats_b;
+  int c_a;
   const unsigned char *packed;
   __half *out;      // OS
   float *accum;     // WS
@@ -83,6 +88,10 @@ struct ConvParams {
   int T, n_tiles, K, c_in, c_out, R, n_chunks;  // n_chunks: OS = ceil(R/64); WS = ceil(c_in/64) per offset
   int stages, teams, slab_bufs, b_bytes, acc_stride, tmem_cols;
   int off_b, off_slab, off_flags, off_cm, off_meta, off_bar;
+  int off_ep;                   // per-channel epilogue constants as fp32: bias[256], scale[256], shift[256]
+  // OS, 1x1x1 layer through the identity map: all weight chunks are fetched once and stay in shared memory
+  // (chunk j at off_b + j * b_bytes) instead of travelling with every pipeline stage
+  int resident;
   // OS, split reduction: `split` CTAs share one tile, CTA blockIdx.x % split takes every split-th non-empty chunk, the
   // partial sums meet in split_scratch [tile][split][c_out][128] fp32 and every CTA reduces c_out / split columns
   int split;
@@ -141,6 +150,15 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     }
   }
 
+  // The epilogue applies (acc + bias[c]) * scale[c] + shift[c] with one thread per ROW, i.e. every thread needs the
+  // constants of every channel: they are staged once as fp32 (identity values where the caller gave none) and read
+  // back as shared-memory broadcasts instead of three global loads per element.
+  float *s_bias = reinterpret_cast<float *>(smem + P.off_ep), *s_scale = s_bias + 256, *s_shift = s_bias + 512;
+  for (int c = tid; c < P.c_out; c += kConvThreads) {
+    s_bias[c] = P.ep.bias ? __half2float(P.ep.bias[c]) : 0.f;
+    s_scale[c] = P.ep.scale ? P.ep.scale[c] : 1.f;
+    s_shift[c] = P.ep.scale ? P.ep.shift[c] : 0.f;
+  }
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(bar_full(s), kTma ? 1 : kRows + 1);
@@ -150,6 +168,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       mbar_init(bar_acc_full(b), 1);
       mbar_init(bar_acc_empty(b), 128);
     }
+    mbar_init(bar0 + 8u * (2 * kMaxStages + 5), 1);   // resident weights (one bulk copy)
     mbar_init(bar0 + 8u * (2 * kMaxStages + 6), 1);   // map slab buffers (bulk copies)
     mbar_init(bar0 + 8u * (2 * kMaxStages + 7), 1);
     *abort_flag = 0;
@@ -299,7 +318,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     bool ok = true;
     int tile_i = 0;
     auto post_weights = [&](int stage, int chunk_id, int valid, bool first, bool last) {
-      meta[stage] = ((valid + 15) >> 4) | (first << 8) | (last << 9);
+      meta[stage] = ((valid + 15) >> 4) | (first << 8) | (last << 9) | (chunk_id << 16);
+      if (!kWS && P.resident) {
+        mbar_arrive(bar_full(stage));      // the chunk is in shared memory already
+        return;
+      }
       mbar_arrive_expect_tx(bar_full(stage), P.b_bytes);
       bulk_g2s(sbase + P.off_b + stage * P.b_bytes, P.packed + static_cast<int64_t>(chunk_id) * P.b_bytes, P.b_bytes,
                bar_full(stage));
@@ -345,10 +368,13 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         if (r == 0) post_weights(stage, w_row * cpo + jj, min(kChunk, P.c_in - jj * kChunk), jj == 0, jj == cpo - 1);
         const uint32_t dst = sbase + stage * kABytes + dst_off;
         const int c = jj * kChunk + piece * 8;
+        const bool second = c >= P.c_a;
+        const __half *fbase = second ? P.feats_b + (c - P.c_a) : P.feats + c;
+        const int64_t pitch = second ? P.c_in - P.c_a : P.c_a;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const bool take = idx[i] >= 0 && c < P.c_in;
-          cp_async_16(dst + i * 2048, take ? P.feats + static_cast<int64_t>(idx[i]) * P.c_in + c : P.feats, take ? 16u : 0u);
+          cp_async_16(dst + i * 2048, take ? fbase + idx[i] * pitch : P.feats, take ? 16u : 0u);
         }
         cp_async_mbar_arrive_noinc(bar_full(stage));
         my_stage += teams;
@@ -372,27 +398,46 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       // place i of stage slot * teams + team holds zeros, so the zero-fill for a missing neighbour (most of them are
       // missing) is skipped when the place is zero already.  stages / teams <= 4 slots.
       uint32_t zero_rows = 0;
-      if (tid == 0 && P.slab_bufs == 2 && tile_at(0) < n_tiles) {
+      // P.map == nullptr: the identity map of a 1x1x1 layer (K == 1, two slab buffers): row t gathers row t, and the
+      // producers write the 128 entries of a tile themselves instead of fetching them
+      const bool identity = P.map == nullptr;
+      if (tid == 0 && P.resident) {
+        const uint32_t bar_wres = bar0 + 8u * (2 * kMaxStages + 5);
+        mbar_arrive_expect_tx(bar_wres, static_cast<uint32_t>(P.n_chunks) * P.b_bytes);
+        bulk_g2s(sbase + P.off_b, P.packed, static_cast<uint32_t>(P.n_chunks) * P.b_bytes, bar_wres);
+      }
+      if (tid == 0 && P.slab_bufs == 2 && tile_at(0) < n_tiles && !identity) {
         mbar_arrive_expect_tx(bar_slab0, slab_bytes);
         bulk_g2s(sbase + P.off_slab, P.map + static_cast<int64_t>(tile_at(0)) * kRows * P.K, slab_bytes, bar_slab0);
       }
       for (int w = tid; w < 2 * n_words; w += kProducers) cmask[w] = 0;
       // grouped maps come with the offsets present in each tile; the mask of the next tile is fetched a tile ahead
       uint32_t tile_mask = (P.tile_masks && tile_at(0) < n_tiles) ? P.tile_masks[tile_at(0)] : 0u;
+      const bool have_masks = P.tile_masks != nullptr || identity;      // (identity: every tile has its one offset)
+      if (identity) tile_mask = 1u;
       // Every thread runs the same sequence of named barriers; a failed wait only takes effect through the
       // OR-reduction of those barriers, so that all producer warps leave the loop in the same iteration.
       for (int tile = tile_at(0); tile < n_tiles; tile = tile_at(++tile_i)) {
         const int next = tile_at(tile_i + 1);
         const uint32_t this_mask = tile_mask;
         if (P.tile_masks && next < n_tiles) tile_mask = P.tile_masks[next];
+        if (identity) tile_mask = 1u;
         const int buf = (P.slab_bufs == 2) ? (tile_i & 1) : 0;
         const int32_t *my_slab = slab + buf * kRows * P.K;
         uint32_t *my_cmask = cmask + (tile_i & 1) * n_words;
         if (P.slab_bufs == 2) {
-          if (!mbar_wait(bar_slab0 + 8u * buf, (tile_i >> 1) & 1, abort_flag, P.wait_ns)) ok = false;
+          if (identity) {
+            // (this buffer was last read two tiles ago, and every warp has passed the barrier of the tile in between)
+            if (tid < kRows) {
+              const int64_t t = static_cast<int64_t>(tile) * kRows + tid;
+              slab[buf * kRows + tid] = t < P.T ? static_cast<int32_t>(t) : -1;
+            }
+          } else if (!mbar_wait(bar_slab0 + 8u * buf, (tile_i >> 1) & 1, abort_flag, P.wait_ns)) {
+            ok = false;
+          }
           // all warps have issued their share of the previous tile: the other slab and chunk mask are free
           if (named_bar_red_or(1, kProducers, !ok || *abort_flag != 0)) break;
-          if (tid == 0 && next < n_tiles) {
+          if (tid == 0 && next < n_tiles && !identity) {
             mbar_arrive_expect_tx(bar_slab0 + 8u * (buf ^ 1), slab_bytes);
             bulk_g2s(sbase + P.off_slab + (buf ^ 1) * slab_bytes, P.map + static_cast<int64_t>(next) * kRows * P.K, slab_bytes,
                      bar_slab0 + 8u * (buf ^ 1));
@@ -411,7 +456,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           const int k_lo = __float2int_rd((static_cast<float>(j * kChunk) + 0.5f) * inv_c_in);
           const int k_hi = min(__float2int_rd((static_cast<float>(j * kChunk + kChunk - 8) + 0.5f) * inv_c_in), P.K - 1);
           bool any;
-          if (P.tile_masks) {
+          if (have_masks) {
             any = (this_mask & ((0xffffffffu >> (31 - (k_hi - k_lo))) << k_lo)) != 0;    // K <= 32 for grouped maps
           } else {
             int v = -1;
@@ -474,9 +519,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           int idx[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) idx[i] = (piece_valid && !(force_first && split > 1)) ? col[i * 16 * P.K] : -1;
+          const bool second = c >= P.c_a;
+          const __half *fbase = second ? P.feats_b + (c - P.c_a) : P.feats + c;
+          const int64_t pitch = second ? P.c_in - P.c_a : P.c_a;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const __half *src = P.feats + (idx[i] >= 0 ? (static_cast<int64_t>(idx[i]) * P.c_in + c) : 0);
+            const __half *src = idx[i] >= 0 ? fbase + idx[i] * pitch : P.feats;
             // a missing neighbour needs zeros: nothing to do if the previous fill of this stage left zeros there
             if (idx[i] >= 0 || !((was_zero >> i) & 1u)) cp_async_16(dst + i * 2048, src, idx[i] >= 0 ? 16u : 0u);
             now_zero |= (idx[i] >= 0 ? 0u : 1u) << i;
@@ -499,6 +547,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
       bool ok = true;
       int tile_i = 0;
+      const bool resident = !kWS && !kTma && P.resident;
+      if (resident && tile_at(0) < n_tiles) ok = mbar_wait(bar0 + 8u * (2 * kMaxStages + 5), 0, abort_flag, P.wait_ns);
       for (int tile = tile_at(0); ok && tile < n_tiles; tile = tile_at(++tile_i)) {
         const int b = tile_i & 1;
         if (!mbar_wait(bar_acc_empty(b), ((acc_phase >> b) & 1u) ^ 1u, abort_flag, P.wait_ns)) break;
@@ -514,7 +564,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           const bool first = (m >> 8) & 1, last = (m >> 9) & 1;
           // descriptors of the first 16-wide K step; each further step is 32 bytes (2 units of 16 bytes) on
           const uint64_t a_desc = smem_desc_k_sw128(sbase + stage * kABytes);
-          const uint64_t b_desc = smem_desc_k_sw128(sbase + P.off_b + stage * P.b_bytes);
+          const uint64_t b_desc = smem_desc_k_sw128(sbase + P.off_b + (resident ? (m >> 16) : stage) * P.b_bytes);
           for (int ks = 0; ks < nk; ++ks)
             mma_f16_ss(d_tmem, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (first && ks == 0) ? 0u : 1u);
           mma_commit(bar_empty(stage));
@@ -531,6 +581,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     // =========================== epilogue ===========================
     const int q = warp & 3;
     const int row = q * 32 + lane;
+    const bool out_v8 = (reinterpret_cast<uintptr_t>(P.out) & 31) == 0;      // rows are multiples of 32 bytes (c_out % 16 == 0)
     uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
     for (int tile = tile_at(0); tile < n_tiles; tile = tile_at(++tile_i)) {
@@ -650,22 +701,33 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
             __half *dst = P.out + out_row * P.c_out + c0;
             const bool res = P.ep.residual != nullptr;
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
+            for (int i = 0; i < 32; i += 16) {
               if (i < width) {
-                uint4 pack;
-                uint32_t *pw = reinterpret_cast<uint32_t *>(&pack);
-                const uint4 rv = res_next[i >> 3];
-                const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+                uint4 pack[2];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float v0 = epilogue_apply(__uint_as_float(r[i + 2 * e]), c0 + i + 2 * e, P.ep);
-                  float v1 = epilogue_apply(__uint_as_float(r[i + 2 * e + 1]), c0 + i + 2 * e + 1, P.ep);
-                  if (res) { v0 += __low2float(rh[e]); v1 += __high2float(rh[e]); }
-                  if (P.ep.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
-                  __half2 hv = __floats2half2_rn(v0, v1);
-                  pw[e] = *reinterpret_cast<uint32_t *>(&hv);
+                for (int hh = 0; hh < 2; ++hh) {
+                  uint32_t *pw = reinterpret_cast<uint32_t *>(&pack[hh]);
+                  const uint4 rv = res_next[(i >> 3) + hh];
+                  const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int cc = c0 + i + 8 * hh + 2 * e;
+                    float v0 = (__uint_as_float(r[i + 8 * hh + 2 * e]) + s_bias[cc]) * s_scale[cc] + s_shift[cc];
+                    float v1 = (__uint_as_float(r[i + 8 * hh + 2 * e + 1]) + s_bias[cc + 1]) * s_scale[cc + 1] + s_shift[cc + 1];
+                    if (res) { v0 += __low2float(rh[e]); v1 += __high2float(rh[e]); }
+                    if (P.ep.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
+                    __half2 hv = __floats2half2_rn(v0, v1);
+                    pw[e] = *reinterpret_cast<uint32_t *>(&hv);
+                  }
                 }
-                *reinterpret_cast<uint4 *>(dst + i) = pack;
+                // 16 channels = one 32-byte sector: a single 256-bit store where the output allows it (two 16-byte
+                // stores of a thread reach L2 as two partial-sector writes and cost two transactions)
+                if (out_v8) {
+                  st_global_v8(dst + i, pack[0], pack[1]);
+                } else {
+                  *reinterpret_cast<uint4 *>(dst + i) = pack[0];
+                  *reinterpret_cast<uint4 *>(dst + i + 8) = pack[1];
+                }
               }
             }
             fetch_residual(c0 + 32);      // (the accumulator registers are free again: no pressure from the values in flight)
@@ -760,7 +822,9 @@ constexpr int kN2Rows = 256;                 // targets per tile (MMA N)
 constexpr int kN2FeatBytes = kN2Rows * 128;  // one feature stage
 
 struct ConvN2Params {
-  const __half *feats;
+  const __half *feats;          // channels [0, c_a) of an input row, row pitch c_a
+  const __half *feats_b;        // channels [c_a, c_in), row pitch c_in - c_a (one source: c_a == c_in)
+  int c_a;
   const unsigned char *packed;
   __half *out;
   Epilogue ep;
@@ -926,9 +990,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
         int idx[kRowsPerThread];
 #pragma unroll
         for (int i = 0; i < kRowsPerThread; ++i) idx[i] = piece_valid ? col[i * kRowStep * P.K] : -1;
+        const bool second = c >= P.c_a;
+        const __half *fbase = second ? P.feats_b + (c - P.c_a) : P.feats + c;
+        const int64_t pitch = second ? P.c_in - P.c_a : P.c_a;
 #pragma unroll
         for (int i = 0; i < kRowsPerThread; ++i) {
-          const __half *src = P.feats + (idx[i] >= 0 ? (static_cast<int64_t>(idx[i]) * P.c_in + c) : 0);
+          const __half *src = idx[i] >= 0 ? fbase + idx[i] * pitch : P.feats;
           // a missing neighbour needs zeros: nothing to do if the previous fill of this stage left zeros there
           if (idx[i] >= 0 || !((was_zero >> i) & 1u)) cp_async_16(dst + i * (kRowStep * 128), src, idx[i] >= 0 ? 16u : 0u);
           now_zero |= (idx[i] >= 0 ? 0u : 1u) << i;
@@ -996,6 +1063,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
     const bool has_res = P.ep.residual != nullptr;
+    const bool out_v8 = (reinterpret_cast<uintptr_t>(P.out) & 31) == 0;      // 16 channels of a row are one aligned 32-byte sector
     for (int tile = snake_tile(0); tile < P.n_tiles; tile = snake_tile(++tile_i)) {
       const int b = tile_i & 1;
       const int64_t t0 = static_cast<int64_t>(tile) * kN2Rows;
@@ -1060,8 +1128,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
                 const __half2 hv = __floats2half2_rn(a0, a1);       // the single rounding
                 y[e] = *reinterpret_cast<const uint32_t *>(&hv);
               }
-              *reinterpret_cast<uint4 *>(P.out + base) = make_uint4(y[0], y[1], y[2], y[3]);
-              *reinterpret_cast<uint4 *>(P.out + base + 8) = make_uint4(y[4], y[5], y[6], y[7]);
+              if (out_v8) {
+                st_global_v8(P.out + base, make_uint4(y[0], y[1], y[2], y[3]), make_uint4(y[4], y[5], y[6], y[7]));
+              } else {
+                *reinterpret_cast<uint4 *>(P.out + base) = make_uint4(y[0], y[1], y[2], y[3]);
+                *reinterpret_cast<uint4 *>(P.out + base + 8) = make_uint4(y[4], y[5], y[6], y[7]);
+              }
             }
           }
           orow_cur = orow_next;
@@ -1398,7 +1470,8 @@ static int launch_conv_tc(ConvParams &P, bool tma, size_t smem, int64_t num_sour
 }
 
 // Fills the shared-memory plan of ConvParams; returns the dynamic shared memory size or 0 if it does not fit.
-static size_t plan_smem(ConvParams &P, bool ws) {
+constexpr int kEpilogueBytes = 3 * 256 * 4;
+static size_t plan_smem(ConvParams &P, bool ws, bool resident = false) {
   P.b_bytes = P.c_out * 128;
   int acc = 32;
   while (acc < P.c_out) acc <<= 1;
@@ -1410,22 +1483,28 @@ static size_t plan_smem(ConvParams &P, bool ws) {
   int n_words = ws ? 1 : (P.n_chunks + 31) / 32;
   // weight-stationary: the list offsets of all rows (naddrs, qnaddrs: rows + 1 entries each) are staged in shared memory
   const int rowtab_bytes = ws ? 2 * round16((P.rows + 1) * 4) : round16(P.K * 4);
-  int fixed = slab_bytes + rowtab_bytes + round16(2 * n_words * 4) + round16(kMaxStages * 4) + 8 * (2 * kMaxStages + 8) + 16;
+  int fixed = slab_bytes + rowtab_bytes + round16(2 * n_words * 4) + round16(kMaxStages * 4) + kEpilogueBytes + 8 * (2 * kMaxStages + 8) + 16;
   int per_stage = kABytes + P.b_bytes;
+  if (resident) {           // all weight chunks stay, the stages hold feature rows only
+    per_stage = kABytes;
+    fixed += P.n_chunks * P.b_bytes;
+    if (fixed >= kSmemBudget) return 0;
+  }
   int stages = (kSmemBudget - fixed) / per_stage;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 2) return 0;
+  if (stages < (resident ? 4 : 2)) return 0;
   // producer teams: stage s is filled by team s % teams, so the stage count is a multiple of the team count
   if (stages == 7) stages = 6;
   if (stages == 5) stages = 4;
   P.teams = (stages % 4 == 0) ? 4 : (stages % 3 == 0) ? 3 : 2;
   P.stages = stages;
   P.off_b = stages * kABytes;
-  P.off_slab = P.off_b + stages * P.b_bytes;
+  P.off_slab = P.off_b + (resident ? P.n_chunks : stages) * P.b_bytes;
   P.off_flags = P.off_slab + slab_bytes;
   P.off_cm = P.off_flags + rowtab_bytes;
   P.off_meta = P.off_cm + round16(2 * n_words * 4);
-  P.off_bar = P.off_meta + round16(kMaxStages * 4);
+  P.off_ep = P.off_meta + round16(kMaxStages * 4);
+  P.off_bar = P.off_ep + kEpilogueBytes;
   return static_cast<size_t>(P.off_bar) + 8 * (2 * kMaxStages + 8) + 16 + 1024;
 }
 
@@ -1538,15 +1617,25 @@ extern "C" int spira_b200_conv_os_split_plan(int64_t num_targets, int K, int c_i
 static int conv_os_impl(const void *feats, const void *weights, const void *packed, const spira_b200_epilogue *epilogue,
                         const int32_t *map_os, const int32_t *row_of, const uint32_t *tile_masks, int64_t num_sources,
                         int64_t num_targets, int K, int c_in, int c_out, void *out, int32_t *status, void *stream,
-                        int splits = 1, void *split_scratch = nullptr, size_t split_scratch_bytes = 0) {
+                        int splits = 1, void *split_scratch = nullptr, size_t split_scratch_bytes = 0,
+                        const void *feats_b = nullptr, int c_in_a = 0, bool identity = false) {
   SB_CHECK_ARG(num_sources >= 0 && num_targets >= 0 && num_targets < (int64_t(1) << 31) - 128 &&
                    num_sources < (int64_t(1) << 31),
                "conv_os: sizes out of range");
   SB_CHECK_ARG(K >= 1 && c_in >= 1 && c_out >= 1, "conv_os: K=%d c_in=%d c_out=%d", K, c_in, c_out);
   if (num_targets == 0) return SPIRA_B200_OK;
-  SB_CHECK_ARG(map_os && out && (feats || num_sources == 0), "conv_os: null pointer");
+  SB_CHECK_ARG((map_os || identity) && out && (feats || num_sources == 0), "conv_os: null pointer");
   Epilogue ep = make_epilogue(epilogue);
   SB_CHECK_ARG((ep.scale == nullptr) == (ep.shift == nullptr), "conv_os: scale and shift must be given together");
+  const bool two = feats_b != nullptr && c_in_a > 0 && c_in_a < c_in;
+  if (two)
+    SB_CHECK_ARG(packed != nullptr && !g_gather_tma && c_in_a % 8 == 0 && reinterpret_cast<uintptr_t>(feats_b) % 16 == 0,
+                 "conv_os: two sources need a packed weight image, the cp.async producers, c_in_a %% 8 == 0 (got %d) and a "
+                 "16-byte aligned second tensor", c_in_a);
+  if (identity)
+    SB_CHECK_ARG(packed != nullptr && !g_gather_tma && K == 1 && map_os == nullptr && row_of == nullptr && splits <= 1 &&
+                     num_sources >= num_targets,
+                 "conv_os: the identity map is for 1x1x1 layers with a packed weight image (K=%d)", K);
   if (packed == nullptr) {
     SB_CHECK_ARG(weights != nullptr, "conv_os: neither weights nor a packed image given");
     const size_t stem_smem = static_cast<size_t>(K) * c_in * c_out * 4 + static_cast<size_t>(128) * K * 4;
@@ -1577,6 +1666,7 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
                    reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(map_os) % 16 == 0 &&
                    (ep.residual == nullptr || reinterpret_cast<uintptr_t>(ep.residual) % 16 == 0),
                "conv_os: feats, packed, out, map and residual must be 16-byte aligned");
+  const int c_a = two ? c_in_a : c_in;
   if (splits > 1) {
     SB_CHECK_ARG(packed != nullptr, "conv_os_split: needs a packed weight image");
     SB_CHECK_ARG((splits == 2 || splits == 4 || splits == 8) && splits <= split_limit(num_targets, K, c_in, c_out),
@@ -1588,9 +1678,11 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
   }
   // On grouped maps both kernels run at the speed of the row gathers; the 256-target tiles then only pay off for the
   // wider layers (measured: 32 channels 20 % slower, 64 equal, 96 5 % faster than 128-target tiles).
-  if (splits <= 1 && os_n256_applies(K, c_in, c_out, num_targets)) {
+  if (splits <= 1 && !identity && os_n256_applies(K, c_in, c_out, num_targets)) {
     ConvN2Params Q{};
     Q.feats = static_cast<const __half *>(feats);
+    Q.feats_b = static_cast<const __half *>(feats_b);
+    Q.c_a = c_a;
     Q.packed = static_cast<const unsigned char *>(packed);
     Q.out = static_cast<__half *>(out);
     Q.ep = ep;
@@ -1616,6 +1708,8 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
   }
   ConvParams P{};
   P.feats = static_cast<const __half *>(feats);
+  P.feats_b = static_cast<const __half *>(feats_b);
+  P.c_a = c_a;
   P.packed = static_cast<const unsigned char *>(packed);
   P.out = static_cast<__half *>(out);
   P.ep = ep;
@@ -1636,7 +1730,12 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
   P.R = K * c_in;
   // TMA gather: every offset owns ceil(c_in/64) chunks (PACK_WS image); cp.async: 64-wide chunks over the whole reduction
   P.n_chunks = tma ? static_cast<int>(div_up(c_in, kChunk)) : static_cast<int>(div_up(P.R, kChunk));
-  size_t smem = plan_smem(P, false);
+  size_t smem = 0;
+  if (identity) {
+    smem = plan_smem(P, false, true);
+    P.resident = smem != 0 ? 1 : 0;
+  }
+  if (smem == 0) smem = plan_smem(P, false);
   if (smem == 0) return fail(SPIRA_B200_ERR_UNSUPPORTED, "conv_os: K=%d c_out=%d does not fit the shared-memory plan", K, c_out);
   return launch_conv_tc<false>(P, tma, smem, num_sources, as_stream(stream));
 }
@@ -1674,7 +1773,8 @@ extern "C" int spira_b200_conv_os_split(const void *feats, const void *packed, c
 static int conv_ws_impl(const void *feats, const void *weights, const void *packed, const spira_b200_epilogue *epilogue,
                         const int32_t *in_idx, const int32_t *out_idx, const int32_t *naddrs, const int32_t *qnaddrs, int rows,
                         int64_t num_tiles128, int mirror, int swap, int64_t num_sources, int64_t num_targets, int K, int c_in,
-                        int c_out, float *accum, void *out, int32_t *status, void *stream, bool fused) {
+                        int c_out, float *accum, void *out, int32_t *status, void *stream, bool fused,
+                        const void *feats_b = nullptr, int c_in_a = 0) {
   SB_CHECK_ARG(num_sources >= 0 && num_targets >= 0 && num_targets < (int64_t(1) << 31) && num_sources < (int64_t(1) << 31),
                "conv_ws: sizes out of range");
   SB_CHECK_ARG(K >= 1 && c_in >= 1 && c_out >= 1 && rows >= 1 && rows <= K, "conv_ws: K=%d c_in=%d c_out=%d rows=%d", K, c_in,
@@ -1690,6 +1790,11 @@ static int conv_ws_impl(const void *feats, const void *weights, const void *pack
   if (!fused) SB_CHECK_CUDA(cudaMemsetAsync(accum, 0, sizeof(float) * n_out, st));
   const int32_t *gi = swap ? out_idx : in_idx;
   const int32_t *go = swap ? in_idx : out_idx;
+  const bool two = feats_b != nullptr && c_in_a > 0 && c_in_a < c_in;
+  if (two)
+    SB_CHECK_ARG(packed != nullptr && !g_gather_tma && c_in_a % 8 == 0 && reinterpret_cast<uintptr_t>(feats_b) % 16 == 0,
+                 "conv_ws: two sources need a packed weight image, the cp.async producers, c_in_a %% 8 == 0 (got %d) and a "
+                 "16-byte aligned second tensor", c_in_a);
   if (fused) {
     SB_CHECK_ARG(packed != nullptr && tc_eligible(K, c_in, c_out) && !g_gather_tma,
                  "conv_ws_fused: needs a tensor-core eligible layer with its packed weights and the cp.async producers");
@@ -1712,6 +1817,8 @@ static int conv_ws_impl(const void *feats, const void *weights, const void *pack
                    "conv_ws: feats, packed and accum must be 16-byte aligned");
       ConvParams P{};
       P.feats = static_cast<const __half *>(feats);
+      P.feats_b = static_cast<const __half *>(feats_b);
+      P.c_a = two ? c_in_a : c_in;
       P.packed = static_cast<const unsigned char *>(packed);
       P.accum = accum;
       P.out = static_cast<__half *>(out);
@@ -1765,6 +1872,31 @@ extern "C" int spira_b200_conv_ws_fused(const void *feats, const void *packed, c
                                         float *zeroed_accum, void *out, int32_t *status, void *stream) {
   return conv_ws_impl(feats, nullptr, packed, epilogue, in_idx, out_idx, naddrs, qnaddrs, rows, num_tiles128, mirror, swap,
                       num_sources, num_targets, K, c_in, c_out, zeroed_accum, out, status, stream, true);
+}
+
+int sb::conv_run(const spira_b200_conv_desc &d, int32_t *status, void *stream) {
+  SB_CHECK_ARG(d.dataflow == 0 || d.dataflow == 1, "conv: dataflow %d (0: output-stationary, 1: weight-stationary)", d.dataflow);
+  SB_CHECK_ARG(d.packed != nullptr || (d.weights != nullptr && d.dataflow == 0),
+               "conv: a packed weight image, or plain weights for an output-stationary layer outside the tensor-core kernels");
+  SB_CHECK_ARG(d.c_in_a >= 0 && d.c_in_a <= d.c_in, "conv: c_in_a=%d outside [0, c_in=%d]", d.c_in_a, d.c_in);
+  const bool two = d.c_in_a > 0 && d.c_in_a < d.c_in;
+  SB_CHECK_ARG(!two || d.feats_b != nullptr, "conv: c_in_a=%d of c_in=%d channels but no second tensor", d.c_in_a, d.c_in);
+  if (d.dataflow == 0) {
+    const bool identity = d.map_os == nullptr && d.K == 1;
+    SB_CHECK_ARG((d.row_of == nullptr) == (d.tile_masks == nullptr), "conv: row_of and tile_masks come together");
+    SB_CHECK_ARG(d.row_of == nullptr || d.K <= 32, "conv: K=%d, grouped maps have at most 32 offsets", d.K);
+    return conv_os_impl(d.feats, d.packed ? nullptr : d.weights, d.packed, d.epilogue, d.map_os, d.row_of, d.tile_masks, d.num_sources, d.num_targets,
+                        d.K, d.c_in, d.c_out, d.out, status, stream, d.splits > 1 ? d.splits : 1, d.split_scratch,
+                        d.split_scratch_bytes, two ? d.feats_b : nullptr, d.c_in_a, identity);
+  }
+  return conv_ws_impl(d.feats, nullptr, d.packed, d.epilogue, d.in_idx, d.out_idx, d.naddrs, d.qnaddrs, d.rows, d.num_tiles128,
+                      d.mirror, d.swap, d.num_sources, d.num_targets, d.K, d.c_in, d.c_out, d.zeroed_accum, d.out, status,
+                      stream, true, two ? d.feats_b : nullptr, d.c_in_a);
+}
+
+extern "C" int spira_b200_conv(const spira_b200_conv_desc *desc, int32_t *status, void *stream) {
+  SB_CHECK_ARG(desc != nullptr, "conv: null descriptor");
+  return sb::conv_run(*desc, status, stream);
 }
 
 extern "C" int spira_b200_set_option(const char *name, int value) {

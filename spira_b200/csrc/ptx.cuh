@@ -114,6 +114,19 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, uint64_t tmap, int x, 
 
 // Barrier + OR-reduction of a predicate over the participating threads: used to leave loops TOGETHER when a
 // bounded wait expired somewhere (a plain barrier would wait forever for a thread that already left).
+// 256-bit global accesses (sm_100): one instruction moves a whole 32-byte sector per thread.  The address must be
+// 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void *p, const uint4 &a, const uint4 &b) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x),
+               "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
+}
+__device__ __forceinline__ void ld_global_v8(const void *p, uint4 &a, uint4 &b) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+               : "l"(p));
+}
+
 __device__ __forceinline__ bool named_bar_red_or(int id, int threads, bool pred) {
   uint32_t r;
   asm volatile(

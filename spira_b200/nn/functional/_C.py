@@ -910,13 +910,63 @@ def _check_feats(sources, weights):
         raise RuntimeError("[spira_b200] features and weights must be float16 (fp16 in/out, fp32 accumulate)")
 
 
+def _check_second_source(sources, sources_b, weights):
+    """Two-source form: the rows of ``sources`` and ``sources_b`` side by side are the input rows (a channel
+    concatenation that is never materialised)."""
+    _require_cuda(sources_b)
+    if sources_b.dim() != 2 or sources_b.shape[0] != sources.shape[0] or sources_b.dtype != torch.float16:
+        raise RuntimeError("[spira_b200] the second source must be float16 with the rows of the first")
+    if sources.shape[1] + sources_b.shape[1] != weights.shape[1]:
+        raise RuntimeError(f"[spira_b200] the sources hold {sources.shape[1]} + {sources_b.shape[1]} channels, the weights expect {weights.shape[1]}")
+    if sources.shape[1] % 8 != 0 or sources_b.shape[1] % 8 != 0:
+        raise RuntimeError("[spira_b200] both sources of a two-source convolution need a multiple of 8 channels")
+
+
+def conv_desc_call(desc: "_lib.ConvDesc", device) -> None:
+    """``spira_b200_conv`` on the current stream of ``device``."""
+    _lib.call("spira_b200_conv", C.byref(desc), _ptr(status_word(device)), _stream(device))
+
+
+def conv_identity(sources, weights, *, sources_b=None, bias=None, scale=None, shift=None, residual=None, relu=False) -> torch.Tensor:
+    """1x1x1 layer ``[sources | sources_b] @ weights[0]`` with the fused epilogue, on the tensor-core output-stationary
+    kernel through the identity map (no map tensor).  ``weights`` is ``[1, c_in, c_out]``."""
+    if sources_b is None:
+        _check_feats(sources, weights)
+    else:
+        _require_cuda(sources, weights)
+        _check_second_source(sources, sources_b, weights)
+        sources_b = sources_b.contiguous()
+    sources, weights = sources.contiguous(), weights.contiguous()
+    K, cin, cout = weights.shape
+    if K != 1:
+        raise RuntimeError("[spira_b200] conv_identity is for 1x1x1 layers")
+    packed = packed_weights(weights, PACK_OS)
+    if packed is None:
+        raise RuntimeError(f"[spira_b200] a 1x1x1 layer {cin} -> {cout} is outside the tensor-core kernels")
+    n = sources.shape[0]
+    out = torch.empty((n, cout), dtype=torch.float16, device=sources.device)
+    ep, keep = _epilogue(bias, scale, shift, residual, relu)
+    d = _lib.ConvDesc(dataflow=0, K=1, c_in=cin, c_out=cout, c_in_a=sources.shape[1], num_sources=n, num_targets=n,
+                      feats=_ptr(sources), feats_b=_ptr(sources_b), packed=_ptr(packed), out=_ptr(out))
+    if ep is not None:
+        d.epilogue = C.pointer(ep)
+    conv_desc_call(d, sources.device)
+    return out
+
+
 def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None, scale=None, shift=None, residual=None,
-            relu=False, force_simt=False, grouped=True, splits=None) -> torch.Tensor:
+            relu=False, force_simt=False, grouped=True, splits=None, sources_b=None) -> torch.Tensor:
     """Output-stationary forward with the optional fused epilogue.  An engine-built map that carries a grouped twin
     (rows sorted by neighbour pattern) runs over the twin unless ``grouped=False``; the result is the same.
     ``splits`` (2, 4 or 8; default: ``os_splits`` decides) shares the reduction of every tile among that many CTAs; the
-    fp32 partial sums are added in a fixed order, so the result is deterministic but rounds differently from one CTA's."""
-    _check_feats(sources, weights)
+    fp32 partial sums are added in a fixed order, so the result is deterministic but rounds differently from one CTA's.
+    ``sources_b``: second source tensor, see :func:`conv_ws`."""
+    if sources_b is None:
+        _check_feats(sources, weights)
+    else:
+        _require_cuda(sources, weights)
+        _check_second_source(sources, sources_b, weights)
+        sources_b = sources_b.contiguous()
     sources, weights, out_in_map = sources.contiguous(), weights.contiguous(), out_in_map.contiguous()
     K, cin, cout = weights.shape
     if out_in_map.dim() != 2 or out_in_map.shape[1] != K or out_in_map.shape[0] < num_targets:
@@ -932,6 +982,23 @@ def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None
     g = grouped_twin(out_in_map) if (grouped and GROUP_OS and (packed is not None or _stem_shape(cin, cout, K))) else None
     if splits is None:
         splits = os_splits(num_targets, K, cin, cout) if packed is not None else 1
+    if sources_b is not None:
+        if packed is None:
+            raise RuntimeError(f"[spira_b200] two sources need a layer the tensor-core kernels take (K={K}, {cin} -> {cout})")
+        d = _lib.ConvDesc(dataflow=0, K=K, c_in=cin, c_out=cout, c_in_a=sources.shape[1], splits=int(splits),
+                          num_sources=int(num_sources), num_targets=int(num_targets), feats=_ptr(sources), feats_b=_ptr(sources_b),
+                          packed=_ptr(packed), out=_ptr(out))
+        if g is not None:
+            d.map_os, d.row_of, d.tile_masks = g.map_ptr, g.row_of_ptr, g.tile_masks_ptr
+        else:
+            d.map_os = _ptr(out_in_map)
+        if splits > 1:
+            scratch = split_scratch(sources.device, 1024 + _aligned(num_targets) * splits * cout * 4)
+            d.split_scratch, d.split_scratch_bytes = _ptr(scratch), scratch.numel()
+        if ep is not None:
+            d.epilogue = C.pointer(ep)
+        conv_desc_call(d, sources.device)
+        return out
     if splits > 1:
         scratch = split_scratch(sources.device, 1024 + _aligned(num_targets) * splits * cout * 4)
         _lib.call("spira_b200_conv_os_split", _ptr(sources), _ptr(packed), C.byref(ep) if ep is not None else None,
@@ -951,11 +1018,19 @@ def conv_os(num_sources, num_targets, out_in_map, sources, weights, *, bias=None
 
 
 def conv_ws(num_sources, num_targets, sources, weights, lists: WsLists, *, swap=False, bias=None, scale=None, shift=None,
-            residual=None, relu=False, force_simt=False, fused=None) -> torch.Tensor:
+            residual=None, relu=False, force_simt=False, fused=None, sources_b=None) -> torch.Tensor:
     """Weight-stationary forward over compacted pair lists with the optional fused epilogue.  ``fused`` (default:
     ``WS_FUSED`` where it applies) selects the single cooperative launch over the persistent zero scratch; the sums are
-    the same (the order of the fp32 reductions varies from run to run on either path)."""
-    _check_feats(sources, weights)
+    the same (the order of the fp32 reductions varies from run to run on either path).
+    ``sources_b``: a second source tensor with the rows of ``sources``; the layer then convolves the channel
+    concatenation ``[sources | sources_b]`` without building it (the reference concatenates first:
+    ``spira/operators.py:11-13``).  Tensor-core eligible layers only, fused call only."""
+    if sources_b is None:
+        _check_feats(sources, weights)
+    else:
+        _require_cuda(sources, weights)
+        _check_second_source(sources, sources_b, weights)
+        sources_b = sources_b.contiguous()
     sources, weights = sources.contiguous(), weights.contiguous()
     K, cin, cout = weights.shape
     out = torch.empty((num_targets, cout), dtype=torch.float16, device=sources.device)
@@ -968,6 +1043,18 @@ def conv_ws(num_sources, num_targets, sources, weights, lists: WsLists, *, swap=
     can_fuse = packed is not None and num_targets > 0 and get_option("gather_tma") == 0
     if fused is None:
         fused = WS_FUSED
+    if sources_b is not None:
+        if not can_fuse:
+            raise RuntimeError(f"[spira_b200] two sources need a layer the tensor-core kernels take (K={K}, {cin} -> {cout})")
+        accum = zero_scratch(sources.device, num_targets * cout)
+        d = _lib.ConvDesc(dataflow=1, K=K, c_in=cin, c_out=cout, c_in_a=sources.shape[1], rows=lists.rows, mirror=1 if mirror else 0,
+                          swap=1 if swap else 0, num_sources=int(num_sources), num_targets=int(num_targets), num_tiles128=n_tiles,
+                          feats=_ptr(sources), feats_b=_ptr(sources_b), packed=_ptr(packed), in_idx=lists.in_ptr, out_idx=lists.out_ptr,
+                          naddrs=lists.naddrs_ptr, qnaddrs=lists.qnaddrs_ptr, zeroed_accum=_ptr(accum), out=_ptr(out))
+        if ep is not None:
+            d.epilogue = C.pointer(ep)
+        conv_desc_call(d, sources.device)
+        return out
     if fused and can_fuse:
         accum = zero_scratch(sources.device, num_targets * cout)
         _lib.call("spira_b200_conv_ws_fused", _ptr(sources), _ptr(packed), C.byref(ep) if ep is not None else None,

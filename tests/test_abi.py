@@ -33,6 +33,10 @@ def test_struct_layouts_match_the_header():
     from spira_b200 import _lib
     assert ctypes.sizeof(_lib.KmapDesc) == 8 * 4 + 4 * 8 + 8 * 3      # 2 ptr, 2 i64, 8 i32, 3 ptr
     assert ctypes.sizeof(_lib.Epilogue) == 4 * 8 + 8
+    assert ctypes.sizeof(_lib.ConvDesc) == 10 * 4 + 3 * 8 + 16 * 8         # the library static_asserts the same sizes
+    assert ctypes.sizeof(_lib.TapeMap) == 2 * 8 + 12 * 8 + 2 * 4 + 8
+    assert ctypes.sizeof(_lib.TapeOp) == 14 * 4 + 2 * 8 + ctypes.sizeof(_lib.Epilogue)
+    assert ctypes.sizeof(_lib.TapeSlot) == 8 + 4 + 4 + 8
 
 
 def test_argument_errors_without_a_gpu(lib):

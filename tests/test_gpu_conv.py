@@ -287,6 +287,69 @@ def test_split_output_stationary_agrees_and_is_deterministic(C, n, cin, cout):
     C.check_status()
 
 
+@pytest.mark.parametrize("ca,cb,cout", [(32, 32, 64), (64, 32, 96), (96, 32, 96), (128, 64, 128), (256, 128, 256), (8, 24, 32)])
+def test_two_sources_equal_the_convolution_of_the_concatenation(C, scene, ca, cb, cout):
+    """[a | b] read as two sources: bit-identical to the same kernel on torch.cat (output-stationary: same order of
+    additions), within tolerance of the oracle; weight-stationary within tolerance (its fp32 reductions are unordered)."""
+    keys, down = scene
+    rng = np.random.default_rng(ca * 100 + cb)
+    for src, tgt, ks in ((keys, keys, (3, 3, 3)), (keys, down, (2, 2, 2))):
+        S, T = len(src), len(tgt)
+        K = ks[0] ** 3
+        f, w = tensors(S, ca + cb, cout, K, ca + cb + cout)
+        fa, fb = f[:, :ca].contiguous().cuda(), f[:, ca:].contiguous().cuda()
+        res = torch.from_numpy(rng.normal(size=(T, cout)).astype(np.float16)).cuda()
+        scale = torch.from_numpy(rng.uniform(0.5, 1.5, cout).astype(np.float32)).cuda()
+        shift = torch.from_numpy(rng.normal(size=cout).astype(np.float32)).cuda()
+        kw = dict(scale=scale, shift=shift, residual=res, relu=True)
+        m0 = C.cuda_binary_search(keys_to_torch(src), keys_to_torch(tgt), ks, (1, 1, 1), 0)
+        want = O.conv_os(f, w, m0[2].cpu().numpy(), T)
+        for grouped in (True, False):
+            got = C.conv_os(S, T, m0[2], fa, w.cuda(), sources_b=fb, grouped=grouped, splits=1)
+            assert torch.equal(got, C.conv_os(S, T, m0[2], f.cuda(), w.cuda(), grouped=grouped, splits=1))
+            assert_features_close(got, want)
+            got = C.conv_os(S, T, m0[2], fa, w.cuda(), sources_b=fb, grouped=grouped, splits=1, **kw)
+            assert torch.equal(got, C.conv_os(S, T, m0[2], f.cuda(), w.cuda(), grouped=grouped, splits=1, **kw))
+        m1 = C.cuda_binary_search(keys_to_torch(src), keys_to_torch(tgt), ks, (1, 1, 1), 1)
+        w_nat = w.cuda()
+        got = C.conv_ws(S, T, fa, w_nat, m1[2]._sb["ws"], sources_b=fb)
+        assert_features_close(got, C.conv_ws(S, T, f.cuda(), w_nat, m1[2]._sb["ws"]).float().cpu())
+    C.check_status()
+
+
+@pytest.mark.parametrize("n", [1, 127, 128, 5000, 40001])
+@pytest.mark.parametrize("ca,cb,cout", [(64, 0, 128), (128, 64, 128), (256, 128, 256), (96, 32, 96), (32, 0, 64)])
+def test_identity_map_layer_matches_the_matrix_product(C, n, ca, cb, cout):
+    """A 1x1x1 layer through the identity map (no map tensor), one or two sources, with the fused epilogue, against the
+    fp32 matrix product."""
+    rng = np.random.default_rng(n + ca)
+    f = torch.from_numpy(rng.normal(size=(n, ca + cb)).astype(np.float16))
+    w = torch.from_numpy((rng.normal(size=(1, ca + cb, cout)) / np.sqrt(ca + cb)).astype(np.float16))
+    bias = torch.from_numpy(rng.normal(size=cout).astype(np.float16))
+    res = torch.from_numpy(rng.normal(size=(n, cout)).astype(np.float16))
+    want = f.float() @ w[0].float() + bias.float()
+    fa = f[:, :ca].contiguous().cuda()
+    fb = f[:, ca:].contiguous().cuda() if cb else None
+    got = C.conv_identity(fa, w.cuda(), sources_b=fb, bias=bias.cuda())
+    assert_features_close(got, want)
+    got = C.conv_identity(fa, w.cuda(), sources_b=fb, bias=bias.cuda(), residual=res.cuda(), relu=True)
+    assert_features_close(got, torch.relu(want + res.float()))
+    C.check_status()
+
+
+def test_two_sources_are_checked(C, scene):
+    keys, _ = scene
+    n = len(keys)
+    m0 = C.cuda_binary_search(keys_to_torch(keys), keys_to_torch(keys), (3, 3, 3), (1, 1, 1), 0)
+    f, w = tensors(n, 64, 64, 27, 1)
+    with pytest.raises(RuntimeError):       # 60 + 4 channels: not multiples of 8
+        C.conv_os(n, n, m0[2], f[:, :60].contiguous().cuda(), w.cuda(), sources_b=f[:, 60:].contiguous().cuda())
+    with pytest.raises(RuntimeError):       # channel counts do not add up
+        C.conv_os(n, n, m0[2], f[:, :32].contiguous().cuda(), w.cuda(), sources_b=f[:, :16].contiguous().cuda())
+    with pytest.raises(RuntimeError):       # rows differ
+        C.conv_os(n, n, m0[2], f[:, :32].contiguous().cuda(), w.cuda(), sources_b=f[:100, 32:].contiguous().cuda())
+
+
 def test_split_plan_limits(C):
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     assert C.os_split_plan(128 * (sms // 8), 27, 256, 256)[0] == 8

@@ -165,18 +165,56 @@ def test_compiled_replay_matches_eager(lib):
                 model(x0)
             for h in hooks:
                 h.remove()
+        import spira_b200.compile as spc
         x = prepare(30000, 1, dataflows)
-        compiled = sp.compile_model(model, x, cache)
+        spc.NATIVE_TAPE = False
+        try:
+            replay = sp.compile_model(model, x, cache)        # operator by operator from Python
+        finally:
+            spc.NATIVE_TAPE = True
+        native = sp.compile_model(model, x, cache)            # one spira_b200_run_tape call per scene
+        assert replay.native is None and native.native is not None, native.native_error
         for n, seed in ((30000, 1), (52000, 2), (17000, 3)):
             x = prepare(n, seed, dataflows)
             with torch.no_grad():
                 want = model(x)
-            got = compiled(x)
-            assert got._stride == want._stride and got._features.shape == want._features.shape
             scale = want._features.float().abs().max().item()
+            got = replay(x)
+            assert got._stride == want._stride and got._features.shape == want._features.shape
             tol = 0.0 if not any(dataflows) else 2e-2 * max(scale, 1.0)     # OS is deterministic; WS sums with atomics
             assert (got._features.float() - want._features.float()).abs().max().item() <= tol
+            # the native tape runs the 1x1x1 shortcuts on the engine's own kernel instead of the library GEMM (one
+            # rounding instead of two) and reads concatenations as two sources: equal up to those roundings
+            got = native(x)
+            assert got._stride == want._stride and got._features.shape == want._features.shape
+            tol = (5e-3 if not any(dataflows) else 2e-2) * max(scale, 1.0)
+            assert (got._features.float() - want._features.float()).abs().max().item() <= tol
+            again = native(x)
+            if not any(dataflows):
+                assert torch.equal(again._features, got._features)
     _C.check_status()
+
+
+def test_native_tape_declines_what_it_does_not_cover(lib):
+    """A pass with an operator outside the tape executor (an unfused BatchNorm) replays from Python, with the reason kept."""
+    import spira_b200 as sp
+    from spira_b200 import models, scenes, nn as spnn
+    torch.manual_seed(0)
+    model = models.minkunet18(4, 19, 3).cuda().half().eval()            # not fused: BatchNorm / ReLU stay torch operators
+    cache = spnn.KernelMapCache()
+    sp.set_kernel_map_cache(model, cache)
+    sched = models.map_schedule(4, 3, 3)
+    c = scenes.lidar_scene(2)[:20000]
+    x = sp.SparseTensor(torch.from_numpy(c).cuda(), torch.from_numpy(scenes.features(len(c), 4, 0)).cuda()).order()
+    cache.add_all_kernel_maps(x._coordinates, *sched, (1, 1, 1), [0] * 9)
+    for m in model.modules():
+        if hasattr(m, "_tunable_config"):
+            m._tunable_config["map_dataflow"] = 0
+    compiled = sp.compile_model(model, x, cache)
+    assert compiled.native is None and "torch operator" in compiled.native_error
+    with torch.no_grad():
+        want = model(x)
+    assert torch.equal(compiled(x)._features, want._features)
 
 
 @pytest.mark.parametrize("dataflow", [0, 1, 2])
