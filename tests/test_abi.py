@@ -75,3 +75,47 @@ def test_more_argument_errors_without_a_gpu(lib):
     assert lib.spira_b200_set_option(b"no_such_option", 1) != 0 and lib.spira_b200_get_option(b"no_such_option") == -1
     assert lib.spira_b200_get_option(b"wait_limit_us") == 1500000 and lib.spira_b200_get_option(b"os_n256") == 1
     assert lib.spira_b200_read_back(None, None, 4, None, None, None) != 0
+
+
+def test_tape_and_descriptor_argument_checks_without_a_gpu(lib):
+    """spira_b200_run_tape places its slots and validates the tables before anything is launched; the descriptor call
+    rejects what it cannot run.  None of these reaches the device."""
+    from spira_b200 import _lib
+    need = ctypes.c_size_t(123)
+    assert lib.spira_b200_run_tape(None, 0, None, 0, None, 0, None, 0, ctypes.byref(need), None, 0, None, None) == 0
+    assert need.value == 0
+    slots = (_lib.TapeSlot * 3)()
+    for i, (rows, ch, buf) in enumerate(((1000, 64, -1), (1000, 96, 0), (500, 96, 0))):
+        slots[i].rows, slots[i].channels, slots[i].buffer = rows, ch, buf
+    slots[0].ptr = 4096
+    # the arena is too small: nothing runs, the size it needs comes back (the two slots share buffer 0: the larger wins)
+    rc = lib.spira_b200_run_tape(None, 0, None, 0, slots, 3, None, 0, ctypes.byref(need), None, 0, None, None)
+    assert rc != 0
+    assert need.value == 1000 * 96 * 2 and b"arena" in lib.spira_b200_last_error()
+    # with an arena the slots get their addresses (same buffer, same address)
+    rc = lib.spira_b200_run_tape(None, 0, None, 0, slots, 3, ctypes.c_void_p(1 << 20), 1 << 20, ctypes.byref(need), None, 0, None, None)
+    assert rc == 0 and slots[1].ptr == slots[2].ptr == 1 << 20 and slots[0].ptr == 4096
+    rc = lib.spira_b200_run_tape(None, 0, None, 0, slots, 3, ctypes.c_void_p((1 << 20) + 16), 1 << 20, ctypes.byref(need), None, 0, None, None)
+    assert rc == 0      # (addresses already assigned: nothing left to place)
+    slots[1].ptr = None
+    rc = lib.spira_b200_run_tape(None, 0, None, 0, slots, 3, ctypes.c_void_p((1 << 20) + 16), 1 << 20, ctypes.byref(need), None, 0, None, None)
+    assert rc != 0 and b"256-byte" in lib.spira_b200_last_error()
+    # operators naming slots that do not exist, or whose channel counts do not match
+    ops = (_lib.TapeOp * 1)()
+    ops[0].kind, ops[0].in_a, ops[0].in_b, ops[0].residual, ops[0].out = _lib.TAPE_CONV, 0, -1, -1, 7
+    rc = lib.spira_b200_run_tape(ops, 1, None, 0, slots, 3, ctypes.c_void_p(1 << 20), 1 << 20, ctypes.byref(need), None, 0, None, None)
+    assert rc != 0 and b"slot" in lib.spira_b200_last_error()
+    ops[0].out, ops[0].c_in, ops[0].c_out, ops[0].K = 1, 64, 32, 27
+    rc = lib.spira_b200_run_tape(ops, 1, None, 0, slots, 3, ctypes.c_void_p(1 << 20), 1 << 20, ctypes.byref(need), None, 0, None, None)
+    assert rc != 0 and b"channels" in lib.spira_b200_last_error()
+    ops[0].c_out, ops[0].map = 96, 3
+    rc = lib.spira_b200_run_tape(ops, 1, None, 0, slots, 3, ctypes.c_void_p(1 << 20), 1 << 20, ctypes.byref(need), None, 0, None, None)
+    assert rc != 0 and b"map" in lib.spira_b200_last_error()
+    # descriptor call
+    d = _lib.ConvDesc(dataflow=5)
+    assert lib.spira_b200_conv(ctypes.byref(d), None, None) != 0 and b"dataflow" in lib.spira_b200_last_error()
+    d = _lib.ConvDesc(dataflow=0, K=27, c_in=64, c_out=64, c_in_a=32, packed=4096, feats=4096)
+    assert lib.spira_b200_conv(ctypes.byref(d), None, None) != 0 and b"second tensor" in lib.spira_b200_last_error()
+    assert lib.spira_b200_conv(None, None, None) != 0
+    n, b = ctypes.c_int(0), ctypes.c_size_t(0)
+    assert lib.spira_b200_conv_os_split_plan(1000, 27, 64, 64, None, None) != 0
