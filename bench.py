@@ -1095,7 +1095,8 @@ def run_kmap(args, device, pk, pk_kind):
                        "l2": "256 MiB buffer rewritten between timed steps"},
             "maps": out,
             "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(ach / pk["hbm_gbs"], 4),
-                         "traffic": None, "kernel": "kmap_search_kernel<u32>, 5^3 map of scene 0", "peak_source": f"of {pk_kind}",
+                         "traffic": captured_traffic("kmap_search_kernel<u32>", "kernel maps only, 4 LiDAR-like scenes ~125k voxels each"),
+                         "kernel": "kmap_search_kernel<u32>, 5^3 map of scene 0", "peak_source": f"of {pk_kind}",
                          "algorithmic_bytes": byts5, "kernel_ms": round(k_ms, 5), "kernel_min_ms": round(k_min, 5)},
             "gpu_launches": args.steps * 4 * 4}
 
