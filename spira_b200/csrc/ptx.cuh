@@ -213,6 +213,9 @@ __device__ __forceinline__ uint32_t idesc_f16_m128(uint32_t n) {
   return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
+__device__ __forceinline__ void red_add_f32(float *addr, float a) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
+}
 __device__ __forceinline__ void red_add_v4_f32(float *addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }

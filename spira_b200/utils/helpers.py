@@ -67,9 +67,9 @@ _GROUPED_REDUNDANCY = (1.2, 1.3)   # rows visited per real pair once the map row
 _IMBALANCE = (1.3, 1.3)        # heaviest CTA over the mean (128- / 256-row tiles)
 _TILE_OVERHEAD_CHUNKS = (3.0, 6.0)   # per-tile prologue and epilogue, in units of one stage (128- / 256-row tiles)
 _HEAVIEST_TILE = 0.75          # share of all offsets present in the fullest tile of a grouped map
-_ATOMIC_BYTES_PER_US = 4.2e6   # fp32 vector reductions into the weight-stationary scratch
+_ATOMIC_BYTES_PER_US = 7.0e6   # fp32 vector reductions into the weight-stationary scratch (eight lanes per output row)
 _STREAM_BYTES_PER_US = 1.0e7   # in-kernel conversion pass over the scratch (read fp32, write fp16, write zeros)
-_WS_FIXED_US = 14.0            # launch, pipeline fill, grid barrier of the single cooperative launch
+_WS_FIXED_US = 9.0             # launch, pipeline fill, grid barrier of the single cooperative launch
 _OS_FIXED_US = 14.0
 _INVERT_US = (150.0, 3.0e6)    # output-stationary map of a transposed layer: inverse, its rows in the grouping sort, its own
                                # grouped copy (measured end to end: the step gets slower unless the layer saves more than that)
