@@ -584,6 +584,7 @@ def main():
     ap.add_argument("--tape", default="auto", choices=["auto", "native", "replay"],
                     help="forward replay of the ours arm: the library's tape executor, the Python replay, or whichever runs whole steps faster on this box")
     ap.add_argument("--no-native-tape", action="store_true", help="replay the recorded tape operator by operator from Python instead of one spira_b200_run_tape call per scene (ours arm)")
+    ap.add_argument("--no-pdl", action="store_true", help="launch every kernel the ordinary way (no programmatic dependent launch)")
     ap.add_argument("--no-fuse", action="store_true", help="keep BatchNorm / ReLU / residual adds as separate passes (ours arm)")
     ap.add_argument("--dump-layers", default=None, help="write the per-layer timing table of the profiled step to this JSON file")
     args = ap.parse_args()
@@ -651,6 +652,8 @@ def main():
         from spira_b200 import build, _lib
         build.build()
         _lib.load()
+        if args.no_pdl:
+            _lib.call("spira_b200_set_option", b"pdl", 0)
 
     host, dev = load_scenes(wl, [s + 100 * rank for s in wl["seeds"]], device)
     n_vox = [len(h[0]) for h in host]

@@ -28,6 +28,10 @@ int sm_count() {
   return cached[dev];
 }
 
+static bool g_pdl = true;
+bool pdl_enabled() { return g_pdl; }
+void set_pdl_enabled(bool on) { g_pdl = on; }
+
 }  // namespace sb
 
 extern "C" int spira_b200_version(void) { return 100; }

@@ -56,6 +56,32 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Programmatic dependent launch.  A kernel launched through launch_dependent() may be scheduled while its predecessor on
+// the stream is still draining: its CTAs take the SMs the predecessor's CTAs leave, run their set-up, and block in
+// pdl_wait() (device side, ptx.cuh) until the predecessor grid has completed and its writes are visible.  That hides the
+// 2-3 us between two dependent launches of one-CTA-per-SM kernels (measured: 3.1 -> 0.7 us).  Rules for a kernel launched
+// this way: every thread executes pdl_wait() before its first access to global memory that an earlier kernel may have
+// written or may still read; nothing is written before it.  `pdl_enabled()` is the "pdl" option (default on).
+bool pdl_enabled();
+void set_pdl_enabled(bool on);
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pdl_enabled()) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // One convolution from its descriptor (the body of spira_b200_conv; the tape executor calls it per operator).
 int conv_run(const spira_b200_conv_desc &desc, int32_t *status, void *stream);
 

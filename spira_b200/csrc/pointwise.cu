@@ -35,12 +35,15 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_kernel(const __half *__r
   __half *s_out = reinterpret_cast<__half *>(s_bias + 8 * NT);                         // [warps][16 * c_out]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // (programmatic dependent launch: see common.cuh)
   for (int i = tid; i < 8 * NT * ldw; i += kPwThreads) {
     const int col = i / ldw, k = i - col * ldw;
     s_wt[i] = (col < c_out && k < c_in) ? w[k * c_out + col] : __float2half(0.f);
   }
   if (tid < 8 * NT) s_bias[tid] = (bias != nullptr && tid < c_out) ? __half2float(bias[tid]) : 0.f;
   __syncthreads();
+  asm volatile("griddepcontrol.wait;" ::: "memory");      // weights and bias are the layer's own; the rows come from the kernel before
+
   const int k_steps = k_pad / 16;
   const uint32_t *wt32 = reinterpret_cast<const uint32_t *>(s_wt);
   __half *my_out = s_out + warp * 16 * c_out;
@@ -106,8 +109,8 @@ static int launch_pointwise(const __half *feats, const __half *w, const __half *
   int64_t blocks = div_up(div_up(n, 16), kPwWarps);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
   if (blocks > cap) blocks = cap;
-  pointwise_kernel<NT><<<static_cast<unsigned>(blocks), kPwThreads, smem, st>>>(feats, w, bias, n, c_in, c_out, out);
-  SB_CHECK_LAUNCH();
+  SB_CHECK_CUDA(launch_dependent(pointwise_kernel<NT>, dim3(static_cast<unsigned>(blocks)), dim3(kPwThreads), smem, st, feats, w, bias, n,
+                                 c_in, c_out, out));
   return SPIRA_B200_OK;
 }
 
