@@ -82,6 +82,12 @@ inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 bl
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Device side of the programmatic dependent launch: pdl_trigger() lets the next kernel on the stream be scheduled as this
+// grid's CTAs leave, pdl_wait() blocks until the previous grid has completed and its writes are visible.  Both are no-ops
+// for a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // One convolution from its descriptor (the body of spira_b200_conv; the tape executor calls it per operator).
 int conv_run(const spira_b200_conv_desc &desc, int32_t *status, void *stream);
 

@@ -66,6 +66,8 @@ __global__ void __launch_bounds__(2 * kGroupTile) group_rows_kernel(const __grid
   extern __shared__ int32_t s_rows[];   // [256][K]
   __shared__ uint32_t s_mask[2];
   const int tid = threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
   int m = 0;
   while (m + 1 < B.n_maps && static_cast<int>(blockIdx.x) >= B.pair_base[m + 1]) ++m;
   const int tile0 = 2 * (blockIdx.x - B.pair_base[m]);
@@ -161,7 +163,8 @@ extern "C" int spira_b200_kmap_group(const spira_b200_group_desc *descs, int n_m
                                           nullptr, static_cast<unsigned long long>(wait_us > 0 ? wait_us : 1500000) * 1000ull, st,
                                           "kmap_group");
   if (rc != SPIRA_B200_OK) return rc;
-  group_rows_kernel<<<static_cast<unsigned>(pairs), 2 * kGroupTile, 2 * kGroupTile * max_K * sizeof(int32_t), st>>>(B, order);
+  SB_CHECK_CUDA(launch_dependent(group_rows_kernel, dim3(static_cast<unsigned>(pairs)), dim3(2 * kGroupTile),
+                                 2 * kGroupTile * max_K * sizeof(int32_t), st, B, order));
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
 }

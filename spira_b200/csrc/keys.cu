@@ -38,6 +38,8 @@ __global__ void __launch_bounds__(256) unpack_kernel(const KeyT *__restrict__ ke
 template <typename VecT>
 __global__ void __launch_bounds__(256) permute_rows_kernel(const VecT *__restrict__ in, const int32_t *__restrict__ perm,
                                                             int64_t n, int vecs_per_row, VecT *__restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   int64_t g = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
   int64_t row = g / vecs_per_row;
   int v = static_cast<int>(g - row * vecs_per_row);
@@ -207,12 +209,13 @@ extern "C" int spira_b200_permute_rows(const void *rows_in, const int32_t *perm,
                (reinterpret_cast<uintptr_t>(rows_out) % 16 == 0);
   if (vec16) {
     int vpr = static_cast<int>(row_bytes / 16);
-    permute_rows_kernel<uint4><<<static_cast<unsigned>(div_up(n * vpr, 256)), 256, 0, as_stream(stream)>>>(
-        static_cast<const uint4 *>(rows_in), perm, n, vpr, static_cast<uint4 *>(rows_out));
+    SB_CHECK_CUDA(launch_dependent(permute_rows_kernel<uint4>, dim3(static_cast<unsigned>(div_up(n * vpr, 256))), dim3(256), 0,
+                                   as_stream(stream), static_cast<const uint4 *>(rows_in), perm, n, vpr, static_cast<uint4 *>(rows_out)));
   } else {
     int vpr = static_cast<int>(row_bytes / 2);
-    permute_rows_kernel<uint16_t><<<static_cast<unsigned>(div_up(n * vpr, 256)), 256, 0, as_stream(stream)>>>(
-        static_cast<const uint16_t *>(rows_in), perm, n, vpr, static_cast<uint16_t *>(rows_out));
+    SB_CHECK_CUDA(launch_dependent(permute_rows_kernel<uint16_t>, dim3(static_cast<unsigned>(div_up(n * vpr, 256))), dim3(256), 0,
+                                   as_stream(stream), static_cast<const uint16_t *>(rows_in), perm, n, vpr,
+                                   static_cast<uint16_t *>(rows_out)));
   }
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;

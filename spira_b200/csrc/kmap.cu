@@ -97,6 +97,8 @@ __global__ void __launch_bounds__(kSearchThreads) kmap_search_kernel(const __gri
   __shared__ int s_cnt[kMaxK];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_trigger();
+  pdl_wait();
   int mi = 0;
   while (mi + 1 < P.n_maps && static_cast<int>(blockIdx.x) >= P.m[mi + 1].tile_begin) ++mi;
   const MapDesc<KeyT> &D = P.m[mi];
@@ -341,17 +343,23 @@ struct WsBatch {
 };
 
 __global__ void __launch_bounds__(256) ws_row_scan_batched_kernel(const __grid_constant__ WsBatch B) {
+  pdl_trigger();
+  pdl_wait();
   int m = 0;
   while (m + 1 < B.n_maps && static_cast<int>(blockIdx.x) >= B.scan_base[m + 1]) ++m;
   ws_row_scan_body(B.tile_counts[m], B.T_al[m] / kTile, B.tile_base[m], B.nbsizes[m], blockIdx.x - B.scan_base[m]);
 }
 
 __global__ void ws_addr_batched_kernel(const __grid_constant__ WsBatch B) {
+  pdl_trigger();
+  pdl_wait();
   const int m = blockIdx.x;
   if (threadIdx.x == 0) ws_addr_body(B.nbsizes[m], B.rows[m], B.naddrs[m], B.qnaddrs[m], B.sizes[m]);
 }
 
 __global__ void __launch_bounds__(kTile) ws_pairs_batched_kernel(const __grid_constant__ WsBatch B) {
+  pdl_trigger();
+  pdl_wait();
   int m = 0;
   while (m + 1 < B.n_maps && static_cast<int>(blockIdx.x) >= B.pairs_base[m + 1]) ++m;
   const int local = blockIdx.x - B.pairs_base[m];
@@ -436,6 +444,8 @@ __global__ void __launch_bounds__(256) lists_from_masks_kernel(const int32_t *__
 
 __global__ void __launch_bounds__(256) invert_os_kernel(const int32_t *__restrict__ map_os, int64_t n, int K,
                                                          int32_t *__restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
   if (i >= n) return;
   int v = map_os[i];
@@ -499,7 +509,7 @@ int search_impl(const spira_b200_kmap_desc *descs, int n_maps, cudaStream_t stre
     tiles += m.n_tiles;
   }
   if (tiles == 0) return SPIRA_B200_OK;
-  kmap_search_kernel<KeyT><<<tiles, kSearchThreads, 0, stream>>>(P);
+  SB_CHECK_CUDA(launch_dependent(kmap_search_kernel<KeyT>, dim3(tiles), dim3(kSearchThreads), 0, stream, P));
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
 }
@@ -572,11 +582,11 @@ extern "C" int spira_b200_kmap_ws_lists(const spira_b200_ws_desc *descs, int n_m
   B.scan_base[n_maps] = static_cast<int32_t>(scan); B.pairs_base[n_maps] = static_cast<int32_t>(pairs);
   B.n_maps = n_maps;
   cudaStream_t st = as_stream(stream);
-  ws_row_scan_batched_kernel<<<static_cast<unsigned>(scan), 256, 0, st>>>(B);
+  SB_CHECK_CUDA(launch_dependent(ws_row_scan_batched_kernel, dim3(static_cast<unsigned>(scan)), dim3(256), 0, st, B));
   SB_CHECK_LAUNCH();
-  ws_addr_batched_kernel<<<n_maps, 32, 0, st>>>(B);
+  SB_CHECK_CUDA(launch_dependent(ws_addr_batched_kernel, dim3(n_maps), dim3(32), 0, st, B));
   SB_CHECK_LAUNCH();
-  ws_pairs_batched_kernel<<<static_cast<unsigned>(pairs), kTile, 0, st>>>(B);
+  SB_CHECK_CUDA(launch_dependent(ws_pairs_batched_kernel, dim3(static_cast<unsigned>(pairs)), dim3(kTile), 0, st, B));
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
 }
@@ -650,7 +660,7 @@ extern "C" int spira_b200_convert_transposed_os(const int32_t *map_os, int64_t a
   int64_t n = aligned_targets * K;
   if (n == 0) return SPIRA_B200_OK;
   SB_CHECK_ARG(map_os != nullptr, "convert_transposed_os: null input");
-  invert_os_kernel<<<static_cast<unsigned>(div_up(n, 256)), 256, 0, as_stream(stream)>>>(map_os, n, K, out);
+  SB_CHECK_CUDA(launch_dependent(invert_os_kernel, dim3(static_cast<unsigned>(div_up(n, 256))), dim3(256), 0, as_stream(stream), map_os, n, K, out));
   SB_CHECK_LAUNCH();
   return SPIRA_B200_OK;
 }

@@ -35,14 +35,14 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_kernel(const __half *__r
   __half *s_out = reinterpret_cast<__half *>(s_bias + 8 * NT);                         // [warps][16 * c_out]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // (programmatic dependent launch: see common.cuh)
+  pdl_trigger();
   for (int i = tid; i < 8 * NT * ldw; i += kPwThreads) {
     const int col = i / ldw, k = i - col * ldw;
     s_wt[i] = (col < c_out && k < c_in) ? w[k * c_out + col] : __float2half(0.f);
   }
   if (tid < 8 * NT) s_bias[tid] = (bias != nullptr && tid < c_out) ? __half2float(bias[tid]) : 0.f;
   __syncthreads();
-  asm volatile("griddepcontrol.wait;" ::: "memory");      // weights and bias are the layer's own; the rows come from the kernel before
+  pdl_wait();      // weights and bias are the layer's own; the rows come from the kernel before
 
   const int k_steps = k_pad / 16;
   const uint32_t *wt32 = reinterpret_cast<const uint32_t *>(s_wt);

@@ -114,12 +114,6 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, uint64_t tmap, int x, 
 
 // Barrier + OR-reduction of a predicate over the participating threads: used to leave loops TOGETHER when a
 // bounded wait expired somewhere (a plain barrier would wait forever for a thread that already left).
-// Programmatic dependent launch (see launch_dependent() in common.cuh): pdl_trigger() lets the next kernel on the stream
-// be scheduled as this grid's CTAs leave, pdl_wait() blocks until the previous grid has completed and its writes are
-// visible.  Both are no-ops for a kernel that was launched the ordinary way.
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 // 256-bit global accesses (sm_100): one instruction moves a whole 32-byte sector per thread.  The address must be
 // 32-byte aligned.
 __device__ __forceinline__ void st_global_v8(void *p, const uint4 &a, const uint4 &b) {
