@@ -62,6 +62,14 @@ int spira_b200_read_back(const void *device_src, void *pinned_dst, size_t bytes,
  *   "wait_limit_us"     limit, in microseconds, of every wait inside the tensor-core kernels (mbarriers, the grid
  *                       barrier of spira_b200_conv_ws_fused); default 1500000.  A kernel whose wait runs out sets its
  *                       `status` word, lets its copies land, releases its tensor memory and returns
+ *   "pdl"               1 (default): kernels are launched as programmatic dependents of their predecessor on the
+ *                       stream -- their CTAs may be scheduled while the predecessor drains and block, before their first
+ *                       access to global data, until it has completed and its writes are visible; what the caller
+ *                       observes on the stream is unchanged.  0: ordinary launches
+ *   "ws_cooperative_launch"  0 (default): spira_b200_conv_ws_fused is an ordinary dependent launch of at most one CTA per
+ *                       SM (its grid barrier only waits for CTAs of its own grid, which become resident as earlier
+ *                       kernels drain; the wait is bounded).  1: cudaLaunchCooperativeKernel, which guarantees the
+ *                       residency -- for hosts that run other barrier kernels on other streams of the same GPU
  *   "ws_barrier_skew_once"  test aid: added to the grid-barrier target of the NEXT spira_b200_conv_ws_fused launch only,
  *                       so that its barrier cannot be met and the wait limit is exercised without any fault
  * get_option additionally answers "os_pack_mode": the SPIRA_B200_PACK_* image spira_b200_conv_os expects under
@@ -450,8 +458,9 @@ int spira_b200_conv_ws(const void *feats, const void *weights, const void *packe
                        void *out, int32_t *status, void *stream);
 
 /* spira_b200_conv_ws with the zero-fill and the final conversion inside the convolution kernel (one launch instead of
- * three; tensor-core eligible layers only, `packed` required).  No reference counterpart.  The kernel is launched
- * cooperatively: after their last tile the CTAs meet at a grid barrier (bounded wait, reported through `status`), then
+ * three; tensor-core eligible layers only, `packed` required).  No reference counterpart.  The grid has at most one
+ * CTA per SM (see the "ws_cooperative_launch" option for how it is launched): after their last tile the CTAs meet at a
+ * grid barrier (bounded wait, reported through `status`), then
  * every CTA converts its slice of the scratch to fp16 with the epilogue applied and writes zeros back.  Contract:
  *   zeroed_accum[0 .. num_targets * c_out) holds zeros on entry and holds zeros again when the call has completed;
  *   calls on one device must be ordered on one stream (they share the arrival counter of the grid barrier): the first

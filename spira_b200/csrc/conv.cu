@@ -46,7 +46,8 @@ static_assert(kProducerWarps % 4 == 0, "epilogue warps must start at a multiple 
 constexpr int kConvThreads = (kMmaWarp + 1) * 32;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 220 * 1024;
-constexpr int kScatterRing = 32;        // WS: scatter-row lists kept for tiles in flight (producers run < 16 tiles ahead)
+constexpr int kScatterRing = 16;        // WS: scatter-row lists kept for tiles in flight (producers run at most kMaxStages tiles ahead of
+                                        // the MMA, the MMA two tiles ahead of the epilogue)
 
 struct Epilogue {
   const __half *bias;
@@ -157,9 +158,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
   // constants of every channel: they are staged once as fp32 (identity values where the caller gave none) and read
   // back as shared-memory broadcasts instead of three global loads per element.
   float4 *s_ep = reinterpret_cast<float4 *>(smem + P.off_ep);      // {bias, scale, shift, -} per channel: one 16-byte read
-  for (int c = tid; c < P.c_out; c += kConvThreads)
-    s_ep[c] = make_float4(P.ep.bias ? __half2float(P.ep.bias[c]) : 0.f, P.ep.scale ? P.ep.scale[c] : 1.f,
-                          P.ep.scale ? P.ep.shift[c] : 0.f, 0.f);
+  if constexpr (!kWS) {      // (weight-stationary: the conversion pass applies the epilogue, the region does not exist)
+    for (int c = tid; c < P.c_out; c += kConvThreads)
+      s_ep[c] = make_float4(P.ep.bias ? __half2float(P.ep.bias[c]) : 0.f, P.ep.scale ? P.ep.scale[c] : 1.f,
+                            P.ep.scale ? P.ep.shift[c] : 0.f, 0.f);
+  }
   const bool has_affine = P.ep.bias != nullptr || P.ep.scale != nullptr;
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -1538,7 +1541,8 @@ static size_t plan_smem(ConvParams &P, bool ws, bool resident = false) {
   // weight-stationary: the list offsets of all rows (naddrs, qnaddrs: rows + 1 entries each) are staged in shared memory
   const int rowtab_bytes = ws ? 2 * round16((P.rows + 1) * 4) : round16(P.K * 4);
   const int tr_bytes = ws ? 4 * 32 * 36 * 4 : 0;
-  int fixed = slab_bytes + rowtab_bytes + round16(2 * n_words * 4) + round16(kMaxStages * 4) + kEpilogueBytes + tr_bytes + 8 * (2 * kMaxStages + 8) + 16;
+  const int ep_bytes = ws ? 0 : kEpilogueBytes;
+  int fixed = slab_bytes + rowtab_bytes + round16(2 * n_words * 4) + round16(kMaxStages * 4) + ep_bytes + tr_bytes + 8 * (2 * kMaxStages + 8) + 16;
   int per_stage = kABytes + P.b_bytes;
   if (resident) {           // all weight chunks stay, the stages hold feature rows only
     per_stage = kABytes;
@@ -1559,7 +1563,7 @@ static size_t plan_smem(ConvParams &P, bool ws, bool resident = false) {
   P.off_cm = P.off_flags + rowtab_bytes;
   P.off_meta = P.off_cm + round16(2 * n_words * 4);
   P.off_ep = P.off_meta + round16(kMaxStages * 4);
-  P.off_tr = P.off_ep + kEpilogueBytes;
+  P.off_tr = P.off_ep + ep_bytes;
   P.off_bar = P.off_tr + tr_bytes;
   return static_cast<size_t>(P.off_bar) + 8 * (2 * kMaxStages + 8) + 16 + 1024;
 }
