@@ -41,11 +41,15 @@ constexpr int kChunk = 64;              // fp16 elements of the reduction per pi
 constexpr int kABytes = kRows * 128;    // one A stage
 constexpr int kProducers = 512;          // cp.async producers: teams of 128 (or 256 / 512) threads, 8 lanes per tile row
 constexpr int kProducerWarps = kProducers / 32;
-constexpr int kMmaWarp = kProducerWarps + 4;         // warps kProducerWarps .. +3 are the epilogue (warp % 4 = TMEM lane quarter)
+// Epilogue: warps kProducerWarps .. +7.  A warp can only read the TMEM lane quarter warp % 4, so two warps share each
+// quarter and take alternate 32-column blocks (256-target kernel: alternate blocks of 32 targets): an epilogue warp is a
+// serial chain of a few hundred instructions per block, and the last tile's epilogue of every launch is exposed.
+constexpr int kEpilogueWarps = 8;
+constexpr int kMmaWarp = kProducerWarps + kEpilogueWarps;
 static_assert(kProducerWarps % 4 == 0, "epilogue warps must start at a multiple of 4");
 constexpr int kConvThreads = (kMmaWarp + 1) * 32;
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 220 * 1024;
+constexpr int kSmemBudget = 224 * 1024;
 constexpr int kScatterRing = 16;        // WS: scatter-row lists kept for tiles in flight (producers run at most kMaxStages tiles ahead of
                                         // the MMA, the MMA two tiles ahead of the epilogue)
 
@@ -91,6 +95,7 @@ struct ConvParams {
   int off_b, off_slab, off_flags, off_cm, off_meta, off_bar;
   int off_ep;                   // per-channel epilogue constants as fp32: {bias, scale, shift, -}[256]
   int off_tr;                   // WS: per epilogue warp a 32 x 36-word tile for the transposition of the accumulator
+  int ws_epilogue_warps;        // WS: 8 (two warps per lane quarter) where the tiles fit beside four stages, else 4
   // OS, 1x1x1 layer through the identity map: all weight chunks are fetched once and stay in shared memory
   // (chunk j at off_b + j * b_bytes) instead of travelling with every pipeline stage
   int resident;
@@ -171,7 +176,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full(b), 1);
-      mbar_init(bar_acc_empty(b), 128);
+      mbar_init(bar_acc_empty(b), 32 * kEpilogueWarps);
     }
     mbar_init(bar0 + 8u * (2 * kMaxStages + 5), 1);   // resident weights (one bulk copy)
     mbar_init(bar0 + 8u * (2 * kMaxStages + 6), 1);   // map slab buffers (bulk copies)
@@ -588,6 +593,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
   } else {
     // =========================== epilogue ===========================
     const int q = warp & 3;
+    const int half = (warp - kProducerWarps) >> 2;      // which of the two warps of this lane quarter
     const int row = q * 32 + lane;
     uint32_t *tr_ws = reinterpret_cast<uint32_t *>(smem + P.off_tr);
     const bool out_v8 = (reinterpret_cast<uintptr_t>(P.out) & 31) == 0;      // rows are multiples of 32 bytes (c_out % 16 == 0)
@@ -609,7 +615,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
         // the output row and the first residual values are on their way while the tile's MMAs are still running
         const int64_t t = static_cast<int64_t>(tile) * kRows + row;
         out_row = t < P.T ? (P.row_of ? P.row_of[t] : t) : -1;
-        if (split <= 1) fetch_residual(0);
+        if (split <= 1) fetch_residual(32 * half);
       }
       if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag, P.wait_ns)) break;
       acc_phase ^= 1u << b;
@@ -617,6 +623,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
       const uint32_t taddr = tmem_base + b * P.acc_stride + (static_cast<uint32_t>(q * 32) << 16);
       if constexpr (kWS) out_row = slab[kRows + (tile_i & (kScatterRing - 1)) * kRows + row];
       if constexpr (!kWS && !kTma) {
+        if (split > 1 && half == 1) {      // (the split reduction is the work of one warp per lane quarter)
+          tc_fence_before();
+          mbar_arrive(bar_acc_empty(b));
+          continue;
+        }
         if (split > 1) {
           // ---- split reduction: park this CTA's partial sums (column-major, so that a warp writes 32 consecutive rows
           // of a column), meet the other CTAs of the tile, then reduce this CTA's share of the columns in a fixed order
@@ -685,7 +696,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           continue;
         }
       }
-      for (int c0 = 0; c0 < P.c_out; c0 += 32) {
+      const bool both_halves = !kWS || P.ws_epilogue_warps == kEpilogueWarps;
+      for (int c0 = both_halves ? 32 * half : (half == 0 ? 0 : P.c_out); c0 < P.c_out; c0 += both_halves ? 64 : 32) {
         uint32_t r[32];
         const bool full = c0 + 32 <= P.c_out;
         if (full) {
@@ -704,7 +716,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
           // with eight lanes per row: one instruction then covers 4 rows x 128 contiguous bytes (4 wavefronts) with the
           // same sixteen-byte reductions.  (Scalar reductions of 32 consecutive channels per instruction were measured
           // 1.5x slower: the L2 performs one operation per reduction, whatever its width.)
-          uint32_t *tile = tr_ws + q * (32 * 36);
+          uint32_t *tile = tr_ws + (warp - kProducerWarps) * (32 * 36);
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
             *reinterpret_cast<uint4 *>(tile + lane * 36 + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
@@ -761,7 +773,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
                 }
               }
             }
-            fetch_residual(c0 + 32);      // (the accumulator registers are free again: no pressure from the values in flight)
+            fetch_residual(c0 + 64);      // (the accumulator registers are free again: no pressure from the values in flight)
           }
         }
       }
@@ -904,7 +916,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full(b), 1);
-      mbar_init(bar_acc_empty(b), 128);
+      mbar_init(bar_acc_empty(b), 32 * kEpilogueWarps);
     }
     mbar_init(bar_slab, 1);
     *abort_flag = 0;
@@ -1092,7 +1104,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
     const float shift = (has_channel && P.ep.shift) ? P.ep.shift[c] : 0.f;
     const bool relu = P.ep.relu != 0;
     const int tl = lane & 15, ch0 = (lane >> 4) * 16;       // second half of a pass: this thread's target and first channel
-    uint32_t *tr = reinterpret_cast<uint32_t *>(smem + P.off_tr) + q * (32 * 17);
+    const int half = (warp - kProducerWarps) >> 2;          // the two warps of a lane quarter take alternate blocks of 32 targets
+    uint32_t *tr = reinterpret_cast<uint32_t *>(smem + P.off_tr) + (warp - kProducerWarps) * (32 * 17);
     uint32_t acc_phase = 0;   // bit b: phase of accumulator buffer b
     int tile_i = 0;
     const bool has_res = P.ep.residual != nullptr;
@@ -1116,7 +1129,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
           res[h][1] = *reinterpret_cast<const uint4 *>(src + 8);
         }
       };
-      int orow_cur = orow_of(0), orow_next = orow_of(1);
+      int orow_cur = orow_of(half), orow_next = orow_of(half + 2);
       fetch_residual(orow_cur, 0);
       fetch_residual(orow_cur, 1);
       if (!mbar_wait(bar_acc_full(b), (acc_phase >> b) & 1u, abort_flag, P.wait_ns)) break;
@@ -1124,9 +1137,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_os_n256_kernel(const __g
       tc_fence_after();
       if (n_valid > 0) {
         const uint32_t taddr = tmem_base + b * kN2Rows + (static_cast<uint32_t>(q * 32) << 16);
-        for (int jb = 0; jb < kN2Rows / 32; ++jb) {
+        for (int jb = half; jb < kN2Rows / 32; jb += 2) {
           if (t0 + jb * 32 >= P.T) break;                       // warp-uniform: no target left in this block
-          const int orow_after = orow_of(jb + 2);
+          const int orow_after = orow_of(jb + 4);
           uint32_t v[32];
           tmem_ld_32x32(taddr + jb * 32, v);
           tmem_ld_wait();
@@ -1540,8 +1553,17 @@ static size_t plan_smem(ConvParams &P, bool ws, bool resident = false) {
   int n_words = ws ? 1 : (P.n_chunks + 31) / 32;
   // weight-stationary: the list offsets of all rows (naddrs, qnaddrs: rows + 1 entries each) are staged in shared memory
   const int rowtab_bytes = ws ? 2 * round16((P.rows + 1) * 4) : round16(P.K * 4);
-  const int tr_bytes = ws ? 4 * 32 * 36 * 4 : 0;
+  int tr_bytes = ws ? kEpilogueWarps * 32 * 36 * 4 : 0;
   const int ep_bytes = ws ? 0 : kEpilogueBytes;
+  P.ws_epilogue_warps = kEpilogueWarps;
+  if (ws) {
+    // eight transposition tiles must not cost the pipeline its fourth stage
+    const int fixed8 = slab_bytes + rowtab_bytes + round16(2 * n_words * 4) + round16(kMaxStages * 4) + tr_bytes + 8 * (2 * kMaxStages + 8) + 16;
+    if ((kSmemBudget - fixed8) / (kABytes + P.b_bytes) < 4) {
+      tr_bytes /= 2;
+      P.ws_epilogue_warps = 4;
+    }
+  }
   int fixed = slab_bytes + rowtab_bytes + round16(2 * n_words * 4) + round16(kMaxStages * 4) + ep_bytes + tr_bytes + 8 * (2 * kMaxStages + 8) + 16;
   int per_stage = kABytes + P.b_bytes;
   if (resident) {           // all weight chunks stay, the stages hold feature rows only
@@ -1574,7 +1596,7 @@ static size_t plan_smem_n256(ConvN2Params &P, int teams) {
   P.w_stride = (P.w_bytes + 1023) / 1024 * 1024;
   const int slab_bytes = kN2Rows * P.K * 4;
   const int n_words = (P.n_chunks + 31) / 32;
-  const int tr_bytes = 4 * 32 * 17 * 4;             // per epilogue warp: 32 channels x 16 fp16 pairs, padded rows
+  const int tr_bytes = kEpilogueWarps * 32 * 17 * 4;   // per epilogue warp: 32 channels x 16 targets in fp32, padded rows
   const int fixed = slab_bytes + tr_bytes + round16(2 * n_words * 4) + round16(kMaxStages * 4) + 8 * (2 * kMaxStages + 8) + 16;
   const int per_stage = P.w_stride + kN2FeatBytes;
   int stages = (kSmemBudget - fixed) / per_stage;
