@@ -447,13 +447,17 @@ def profile_kernels(engine, scene):
 
 
 def kernel_source_sha() -> str:
-    """Hash of the CUDA sources of the library: a captured DRAM-traffic figure is only valid for the kernels it was
-    captured from."""
+    """Hash of the CUDA sources of the library, comments and white space excluded: a captured DRAM-traffic figure is only
+    valid for the code it was captured from."""
     import hashlib
+    import re
     h = hashlib.sha256()
     for f in sorted((ROOT / "spira_b200" / "csrc").glob("*.cu*")):
+        text = f.read_text()
+        text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)       # block comments
+        text = re.sub(r"//[^\n]*", " ", text)                     # line comments (no string literal of the sources holds "//")
         h.update(f.name.encode())
-        h.update(f.read_bytes())
+        h.update(" ".join(text.split()).encode())
     return h.hexdigest()[:16]
 
 

@@ -8,18 +8,18 @@
 //     so there are no atomics and the result is deterministic.
 //   weight-stationary (WS): a tile is 128 compacted (in, out) pairs of ONE offset, so every MMA
 //     row is a real pair.  The 128 x c_out product is added into an fp32 scratch with vector
-//     reductions; a second small kernel applies the epilogue and rounds to fp16.
+//     reductions; the same launch (after a grid barrier) or a second small kernel applies the epilogue and rounds to fp16.
 //
-// Roles inside a CTA (672 threads, one CTA per SM):
+// Roles inside a CTA (800 threads, one CTA per SM):
 //   warps 0-15 producers: gather feature rows with 16-byte cp.async (zero-fill for missing rows)
 //              into a 128-byte-swizzled K-major A tile and let the copies arrive on the stage's
 //              mbarrier asynchronously (no thread waits for its own data); one thread bulk-copies
 //              the matching pre-packed weight chunk (already an MMA-ready image) and posts its bytes;
-//   warp  20   one elected thread issues tcgen05.mma (M=128, N=c_out, K=16) into one of two
+//   warp  24   one elected thread issues tcgen05.mma (M=128, N=c_out, K=16) into one of two
 //              TMEM accumulator buffers and commits stage / accumulator barriers;
-//   warps 16-19 epilogue: tcgen05.ld the finished accumulator (one row per thread), apply the
-//              fused epilogue, store fp16 rows (OS) or issue fp32 vector reductions (WS) while the
-//              next tile is already being multiplied.
+//   warps 16-23 epilogue, two per TMEM lane quarter: tcgen05.ld the finished accumulator (one row per thread,
+//              alternate 32-column blocks), apply the fused epilogue, store fp16 rows (OS) or issue fp32 vector
+//              reductions (WS) while the next tile is already being multiplied.
 // All mbarrier waits are bounded; on expiry the kernel raises a status word and drains.
 //
 // Channel counts the tensor-core path cannot tile (c_in % 8 != 0, c_out % 16 != 0, c_out > 256)
