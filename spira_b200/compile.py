@@ -136,8 +136,17 @@ class CompiledModel:
             if inputs._stride not in cache._coords:
                 cache._coords[inputs._stride] = inputs._coordinates
         if self.native is not None and self.use_native:
-            return self._build(self.outputs, self.native.run(inputs._features))
-        for op in self.ops:
+            # The layers on the level-0 map (built before the level sizes are known) are enqueued first, operator by
+            # operator: the GPU works on them while the host waits for the sizes inside cache.finish().  The rest of the
+            # pass is one call into the library.
+            self._replay(self.ops[:self.native.prefix], slots)
+            return self._build(self.outputs, self.native.run(slots))
+        self._replay(self.ops, slots)
+        return self._build(self.outputs, slots)
+
+    def _replay(self, ops, slots):
+        cache = self.cache
+        for op in ops:
             kind = op[0]
             if kind == 0:
                 _, module, i, r, o, in_stride, out_stride, os_flow, dataflow, force_os, key, fast = op
@@ -188,7 +197,6 @@ class CompiledModel:
                 slots[op[2]] = torch.cat([slots[j] for j in op[1]], dim=1)
             else:
                 slots[op[3]] = slots[op[1]] + slots[op[2]]
-        return self._build(self.outputs, slots)
 
 
 class _NotNative(Exception):
@@ -217,6 +225,14 @@ class _NativeTape:
         ops = compiled.ops
         n_slots = compiled.n_slots
         out_slots = set(_output_slots(compiled.outputs, []))
+        # leading layers that share the map of the first one: they run before the other maps exist (see __call__)
+        prefix = 0
+        if ops and ops[0][0] == 0 and not ops[0][1]._trivial and ops[0][11]:
+            while prefix < len(ops) and ops[prefix][0] == 0 and not ops[prefix][1]._trivial and ops[prefix][11] \
+                    and ops[prefix][10] == ops[0][10] and not ops[prefix][1].transposed:
+                prefix += 1
+        self.prefix = prefix
+        self.prefix_slots = {op[4]: op[1].out_channels for op in ops[:prefix]}      # produced by the prefix: external to the tape
         # ---- concatenations: (a | b) read only by convolutions -> two-source convolutions
         other_reads = set()     # slots read as a residual or by a concatenation
         for op in ops:
@@ -241,8 +257,9 @@ class _NativeTape:
         table = []          # (TapeOp fields dict, module)
         map_keys = []       # cache key per map index
         slot_channels = {0: None}
+        slot_channels.update(self.prefix_slots)
         slot_stride = dict(compiled_strides(compiled))
-        for op in ops:
+        for op in ops[prefix:]:
             if op[0] == 2:
                 continue
             _, module, i, r, o, in_stride, out_stride, os_flow, dataflow, force_os, key, fast = op
@@ -367,7 +384,7 @@ class _NativeTape:
             self.slots[sl].channels = slot_channels.get(sl) or 0
             self.slots[sl].buffer = buffer_of.get(sl, -1)
         self.arena_slots = [sl for sl in range(n_slots) if sl in buffer_of]
-        self.used_slots = sorted(set(self.arena_slots) | out_slots | {0})
+        self.used_slots = sorted(set(self.arena_slots) | out_slots | {0} | set(self.prefix_slots))
         self.maps = (_lib.TapeMap * max(len(map_keys), 1))()
         self.ws_outputs = [(f["out"], f["c_out"]) for f, _ in table if f["kind"] == _lib.TAPE_CONV and f["dataflow"] == 1]
         self.needs = {}     # map index -> (needs the output-stationary form, needs its inverse, needs the lists)
@@ -385,7 +402,10 @@ class _NativeTape:
         self.needed = C.c_size_t(0)
         self.fn = _lib.load().spira_b200_run_tape
 
-    def run(self, feats: torch.Tensor):
+    def run(self, given):
+        """``given``: the slot list of the pass with the network input in slot 0 and the outputs of the prefix layers in
+        theirs; returns the list with the model's outputs filled in."""
+        feats = given[0]
         cache = self.cache
         cache.finish()
         for module, stamp in zip(self.modules, self.stamps):
@@ -449,8 +469,14 @@ class _NativeTape:
             slots[0].channels = feats.shape[1]
         result = [None] * self.n_slots
         result[0] = feats
+        for sl in self.prefix_slots:
+            t = given[sl]
+            if not t.is_contiguous():
+                t = given[sl] = t.contiguous()
+            result[sl] = t
+            slots[sl].ptr = t.data_ptr()
         for sl in self.out_slots:
-            if sl == 0:
+            if sl == 0 or sl in self.prefix_slots:
                 continue
             t = result[sl] = torch.empty((slots[sl].rows, slots[sl].channels), dtype=torch.float16, device=device)
             slots[sl].ptr = t.data_ptr()

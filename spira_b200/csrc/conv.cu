@@ -1813,7 +1813,7 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
   // TMA gather: every offset owns ceil(c_in/64) chunks (PACK_WS image); cp.async: 64-wide chunks over the whole reduction
   P.n_chunks = tma ? static_cast<int>(div_up(c_in, kChunk)) : static_cast<int>(div_up(P.R, kChunk));
   size_t smem = 0;
-  if (identity) {
+  if (identity && P.n_tiles > sm_count()) {      // (with one tile per CTA the whole image would only delay the first MMA)
     smem = plan_smem(P, false, true);
     P.resident = smem != 0 ? 1 : 0;
   }
