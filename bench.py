@@ -318,6 +318,16 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([v.strip() for v in line.split(",")])
 
+    def wait_first(self, timeout_s: float = 5.0):
+        """Blocks until nvidia-smi has delivered its first sample (it needs a few hundred ms to come up)."""
+        t_end = time.time() + timeout_s
+        while self.proc is not None and not self.rows and time.time() < t_end:
+            time.sleep(0.01)
+        self.rows.clear()          # (that sample was taken on an idle device)
+
+    def n_samples(self) -> int:
+        return len(self.rows)
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -334,7 +344,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm),
+                "window": "timed loops, then the same steps until three samples (one per 100 ms) were taken under load"}
 
 
 def flush_l2(buf):
@@ -668,7 +679,16 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.wait_first()
     m = measure(engine, host, dev, args, l2buf, dist_ctx, device)
+    if rank == 0:
+        # the timed loops are a few tens of milliseconds: the same steps keep running until the sampler (one sample
+        # per 100 ms) has seen the device under this load at least three times
+        t_end, i = time.time() + 3.0, 0
+        while sampler.n_samples() < 3 and time.time() < t_end:
+            engine.step(*dev[i % len(dev)])
+            i += 1
+        torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
 
     line = {
