@@ -388,6 +388,8 @@ def timed_loop(step_fn, n_steps, warmup, l2buf, dist_ctx, drain_fn=None):
     per_step = [a.elapsed_time(b) for a, b in evs]
     dev_ = torch.device("cuda")
     return {"median_ms": sharding.max_over_ranks(statistics.median(per_step), dev_),
+            "rank_median_ms": [round(v, 4) for v in sharding.all_ranks(statistics.median(per_step), dev_)],
+            "rank_enqueue_ms": [round(v, 4) for v in sharding.all_ranks(enqueue * 1e3 / n_steps, dev_)],
             "mean_ms": sharding.max_over_ranks(sum(per_step) / len(per_step), dev_),
             "steps": per_step, "enqueue_ms": wall[1] * 1e3 / n_steps, "wall_s": wall[0]}
 
@@ -711,6 +713,7 @@ def main():
         "mean_ms_per_step": round(m["mean_ms"], 4),
         "gpu_launches": m["launches"] if args.impl == "ours" else 0,
         "host_enqueue_ms_per_step": round(m["enqueue_ms"], 4),
+        "ms_per_step_per_rank": m["rank_median_ms"], "host_enqueue_ms_per_rank": m["rank_enqueue_ms"],
         "step_ms_min_median_max": [round(min(m["steps"]), 4), round(statistics.median(m["steps"]), 4), round(max(m["steps"]), 4)],
         "step_ms_first": [round(v, 4) for v in m["steps"][:8]],
         "clocks": clocks,
@@ -940,6 +943,7 @@ def measure(engine, host, dev, args, l2buf, dist_ctx, device):
     launches = _lib.launch_count - launches0
     e2e = timed_loop(step_e2e, args.steps, args.warmup, l2buf, dist_ctx, drain_e2e)
     return {"median_ms": res["median_ms"], "mean_ms": res["mean_ms"], "steps": res["steps"], "enqueue_ms": res["enqueue_ms"],
+            "rank_median_ms": res["rank_median_ms"], "rank_enqueue_ms": res["rank_enqueue_ms"],
             "e2e_median_ms": e2e["median_ms"], "e2e_mean_ms": e2e["mean_ms"], "launches": launches,
             "h2d": int(np.mean([h[0].numel() * 4 + h[1].numel() * 2 for h in host])), "d2h": int(d2h_bytes[0])}
 

@@ -28,6 +28,16 @@ def max_over_ranks(value: float, device: Optional[torch.device] = None) -> float
     return float(t.item())
 
 
+def all_ranks(value: float, device: Optional[torch.device] = None) -> list:
+    """The value of every rank, in rank order (a one-element list without a process group)."""
+    if not (torch.distributed.is_available() and torch.distributed.is_initialized()):
+        return [float(value)]
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    out = [torch.zeros_like(t) for _ in range(torch.distributed.get_world_size())]
+    torch.distributed.all_gather(out, t)
+    return [float(v.item()) for v in out]
+
+
 def job_throughput(local_ms: float, scenes_per_rank: Sequence[int], device: Optional[torch.device] = None) -> float:
     """Whole-job scenes/s: all ranks' scenes divided by the slowest rank's time."""
     worst = max_over_ranks(local_ms, device)

@@ -20,6 +20,7 @@ def test_assignment_partitions_the_scenes():
 
 def test_single_process_needs_no_group():
     assert sharding.max_over_ranks(3.5) == 3.5
+    assert sharding.all_ranks(3.5) == [3.5]
     assert sharding.job_throughput(500.0, [4]) == pytest.approx(8.0)
 
 
@@ -30,7 +31,7 @@ def _worker(rank, world, port, out):
         mine = sharding.assign_scenes(7, world, rank)
         local_ms = 100.0 * (rank + 1)                      # rank 1 is the slow one
         counts = [len(sharding.assign_scenes(7, world, r)) for r in range(world)]
-        out[rank] = (mine, sharding.max_over_ranks(local_ms), sharding.job_throughput(local_ms, counts))
+        out[rank] = (mine, sharding.max_over_ranks(local_ms), sharding.job_throughput(local_ms, counts), sharding.all_ranks(local_ms))
     finally:
         torch.distributed.destroy_process_group()
 
@@ -46,3 +47,4 @@ def test_two_ranks_gloo():
     for r in (0, 1):
         assert out[r][1] == 200.0                           # the slowest rank's time, on every rank
         assert out[r][2] == pytest.approx(7 / 0.2)
+        assert out[r][3] == [100.0, 200.0]                  # every rank's value, in rank order
