@@ -60,8 +60,8 @@ int sm_count();
 // the stream is still draining: its CTAs take the SMs the predecessor's CTAs leave, run their set-up, and block in
 // pdl_wait() (device side, ptx.cuh) until the predecessor grid has completed and its writes are visible.  That hides the
 // 2-3 us between two dependent launches of one-CTA-per-SM kernels (measured: 3.1 -> 0.7 us).  Rules for a kernel launched
-// this way: every thread executes pdl_wait() before its first access to global memory that an earlier kernel may have
-// written or may still read; nothing is written before it.  `pdl_enabled()` is the "pdl" option (default on).
+// this way: every thread executes pdl_wait() before its FIRST access to global memory -- also to weights and other
+// constants, which a kernel enqueued just before may have written -- and nothing is written before it.  `pdl_enabled()` is the "pdl" option (default on).
 bool pdl_enabled();
 void set_pdl_enabled(bool on);
 

@@ -141,7 +141,29 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int stages = P.stages;
   pdl_trigger();
-  if constexpr (kWS) pdl_wait();      // (the list offsets staged below come from the map build)
+  // ---- set-up that touches no global memory: it may overlap the drain of the kernel before this one
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar_full(s), kTma ? 1 : kRows + 1);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), 32 * kEpilogueWarps);
+    }
+    mbar_init(bar0 + 8u * (2 * kMaxStages + 5), 1);   // resident weights (one bulk copy)
+    mbar_init(bar0 + 8u * (2 * kMaxStages + 6), 1);   // map slab buffers (bulk copies)
+    mbar_init(bar0 + 8u * (2 * kMaxStages + 7), 1);
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_slot), P.tmem_cols);
+    tmem_relinquish();
+  }
+  // ---- everything the kernel reads from global memory (maps, lists, features, but also weights and epilogue constants,
+  // which an earlier kernel on the stream may just have written) comes after this point
+  pdl_wait();
   // tile counts: given by the host, or (weight-stationary lists whose sizes never left the device) read here
   int n_tiles = P.n_tiles, n_tiles_plain = P.n_tiles_plain;
   // weight-stationary: list offsets of all rows, staged once (finding the row of a tile is a walk over them, and a walk
@@ -169,32 +191,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv_tc_kernel(const __grid_c
                             P.ep.scale ? P.ep.shift[c] : 0.f, 0.f);
   }
   const bool has_affine = P.ep.bias != nullptr || P.ep.scale != nullptr;
-  if (tid == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(bar_full(s), kTma ? 1 : kRows + 1);
-      mbar_init(bar_empty(s), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar_acc_full(b), 1);
-      mbar_init(bar_acc_empty(b), 32 * kEpilogueWarps);
-    }
-    mbar_init(bar0 + 8u * (2 * kMaxStages + 5), 1);   // resident weights (one bulk copy)
-    mbar_init(bar0 + 8u * (2 * kMaxStages + 6), 1);   // map slab buffers (bulk copies)
-    mbar_init(bar0 + 8u * (2 * kMaxStages + 7), 1);
-    *abort_flag = 0;
-    mbar_init_fence();
-  }
-  if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(tmem_slot), P.tmem_cols);
-    tmem_relinquish();
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // everything above touched only shared memory, TMEM and the layer's constants; from here on the kernel reads what
-  // earlier kernels on the stream wrote
-  if constexpr (!kWS) pdl_wait();
   // i-th tile of this CTA: the output-stationary cp.async path alternates the direction of the rounds
   const int split = (!kWS && !kTma) ? P.split : 1;
   const int split_rank = split > 1 ? static_cast<int>(blockIdx.x) % split : 0;
@@ -1281,6 +1281,7 @@ __global__ void __launch_bounds__(128) conv_os_stem_kernel(const __half *__restr
   int32_t *slab = reinterpret_cast<int32_t *>(stem_smem + static_cast<size_t>(K) * c_in * COUT * 4);   // [128][K]
   const int tid = threadIdx.x;
   pdl_trigger();
+  pdl_wait();      // (before the first global read: also the weights may have been written by the kernel before this one)
   if (reinterpret_cast<uintptr_t>(w) % 16 == 0) {                               // (COUT is a multiple of 16: whole 8-value groups)
     for (int i = tid; i < K * c_in * COUT / 8; i += 128) {
       const uint4 v = __ldg(reinterpret_cast<const uint4 *>(w) + i);
@@ -1295,7 +1296,6 @@ __global__ void __launch_bounds__(128) conv_os_stem_kernel(const __half *__restr
   } else {
     for (int i = tid; i < K * c_in * COUT; i += 128) ws[i] = __half2float(w[i]);
   }
-  pdl_wait();      // the weights above are the layer's own; map and features come from earlier kernels on the stream
   // the map has T_al rows (T rounded up to 128): every block finds its 128 rows
   const int64_t t0 = static_cast<int64_t>(blockIdx.x) * 128;
   const int4 *s4 = reinterpret_cast<const int4 *>(map + t0 * K);

@@ -36,13 +36,13 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_kernel(const __half *__r
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   pdl_trigger();
+  pdl_wait();      // (before the first global read: also the weights may have been written by the kernel before this one)
   for (int i = tid; i < 8 * NT * ldw; i += kPwThreads) {
     const int col = i / ldw, k = i - col * ldw;
     s_wt[i] = (col < c_out && k < c_in) ? w[k * c_out + col] : __float2half(0.f);
   }
   if (tid < 8 * NT) s_bias[tid] = (bias != nullptr && tid < c_out) ? __half2float(bias[tid]) : 0.f;
   __syncthreads();
-  pdl_wait();      // weights and bias are the layer's own; the rows come from the kernel before
 
   const int k_steps = k_pad / 16;
   const uint32_t *wt32 = reinterpret_cast<const uint32_t *>(s_wt);
