@@ -602,6 +602,7 @@ def main():
                     help="forward replay of the ours arm: the library's tape executor, the Python replay, or whichever runs whole steps faster on this box")
     ap.add_argument("--no-native-tape", action="store_true", help="replay the recorded tape operator by operator from Python instead of one spira_b200_run_tape call per scene (ours arm)")
     ap.add_argument("--no-pdl", action="store_true", help="launch every kernel the ordinary way (no programmatic dependent launch)")
+    ap.add_argument("--no-identity-tma", action="store_true", help="1x1x1 layers of the native tape run on the output-stationary kernel through the identity map instead of the dense TMA kernel")
     ap.add_argument("--no-fuse", action="store_true", help="keep BatchNorm / ReLU / residual adds as separate passes (ours arm)")
     ap.add_argument("--dump-layers", default=None, help="write the per-layer timing table of the profiled step to this JSON file")
     args = ap.parse_args()
@@ -671,6 +672,8 @@ def main():
         _lib.load()
         if args.no_pdl:
             _lib.call("spira_b200_set_option", b"pdl", 0)
+        if args.no_identity_tma:
+            _lib.call("spira_b200_set_option", b"identity_tma", 0)
 
     host, dev = load_scenes(wl, [s + 100 * rank for s in wl["seeds"]], device)
     n_vox = [len(h[0]) for h in host]

@@ -70,6 +70,10 @@ int spira_b200_read_back(const void *device_src, void *pinned_dst, size_t bytes,
  *                       SM (its grid barrier only waits for CTAs of its own grid, which become resident as earlier
  *                       kernels drain; the wait is bounded).  1: cudaLaunchCooperativeKernel, which guarantees the
  *                       residency -- for hosts that run other barrier kernels on other streams of the same GPU
+ *   "identity_tma"      1 (default): a 1x1x1 layer through the identity map whose sources hold whole groups of 32 channels
+ *                       (c_in_a and c_in - c_in_a multiples of 32) runs on the dense kernel: TMA moves 128-row boxes of
+ *                       the feature tensors, no producer threads, no map.  0: every identity-map layer runs on the
+ *                       output-stationary kernel (the results are equal)
  *   "ws_barrier_skew_once"  test aid: added to the grid-barrier target of the NEXT spira_b200_conv_ws_fused launch only,
  *                       so that its barrier cannot be met and the wait limit is exercised without any fault
  * get_option additionally answers "os_pack_mode": the SPIRA_B200_PACK_* image spira_b200_conv_os expects under
@@ -349,7 +353,8 @@ int spira_b200_conv_os_split(const void *feats, const void *packed, const spira_
  *                 feats_b[s][0..c_in - c_in_a).  The weights stay [K][c_in][c_out].  c_in_a must be a multiple of 8.
  *                 (The reference concatenates first: spira/operators.py:11-13 -- one more read and write of both tensors.)
  *   identity map  dataflow 0 with K == 1 and map_os == NULL: target t reads source t (a 1x1x1 layer: the reference runs it
- *                 as a dense matrix product, spira/nn/conv.py:312-316).
+ *                 as a dense matrix product, spira/nn/conv.py:312-316).  With sources of whole 32-channel groups the
+ *                 layer runs on a kernel of its own whose input tiles are TMA boxes ("identity_tma" option).
  * `packed` is the SPIRA_B200_PACK_OS image for dataflow 0 and the SPIRA_B200_PACK_WS image for dataflow 1.  A layer
  * outside the tensor-core kernels (spira_b200_tensor_core_eligible == 0) passes packed = NULL and its plain `weights`
  * instead: dataflow 0 only, one source, no identity map, and a grouped map only for the narrow-input shapes

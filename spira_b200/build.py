@@ -14,7 +14,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libspira_b200.so"
-SOURCES = ["api.cu", "keys.cu", "ingest.cu", "kmap.cu", "group.cu", "pointwise.cu", "conv.cu", "tape.cu"]
+SOURCES = ["api.cu", "keys.cu", "ingest.cu", "kmap.cu", "group.cu", "pointwise.cu", "conv.cu", "dense.cu", "tape.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-I", str(INCLUDE), "-I", str(CSRC)]
 

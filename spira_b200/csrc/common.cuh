@@ -91,4 +91,11 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // One convolution from its descriptor (the body of spira_b200_conv; the tape executor calls it per operator).
 int conv_run(const spira_b200_conv_desc &desc, int32_t *status, void *stream);
 
+// 1x1x1 layers (identity map) as dense tiles moved by TMA (dense.cu).  dense_applies: channel counts in whole 32-channel
+// boxes (c_a = channels of the first source, c_in - c_a of the second), c_out a multiple of 16 up to 256, 16-byte aligned
+// tensors, and a driver that encodes tensor maps.  `packed` is the K = 1 image of spira_b200_pack_weights.
+bool dense_applies(int64_t n, int c_in, int c_a, int c_out, const void *feats, const void *feats_b, const void *packed);
+int dense_run(const void *feats, const void *feats_b, int c_a, const void *packed, const spira_b200_epilogue *epilogue, int64_t n,
+              int c_in, int c_out, void *out, int32_t *status, unsigned long long wait_ns, cudaStream_t st);
+
 }  // namespace sb

@@ -1420,6 +1420,7 @@ static int round16(int x) { return (x + 15) / 16 * 16; }
 
 // ---- run-time options -----------------------------------------------------------------------------
 static int g_gather_tma = 0;      // 1: producers use TMA gather4, 0: cp.async
+static int g_identity_tma = 1;    // 1: 1x1x1 layers whose channel counts allow it run on the dense TMA kernel
 static int g_wait_limit_us = kDefaultWaitLimitUs;   // limit of every wait inside the tensor-core kernels
 static int g_ws_barrier_skew_once = 0;              // added to the grid-barrier target of the NEXT fused launch only
 
@@ -1718,6 +1719,9 @@ static int conv_os_impl(const void *feats, const void *weights, const void *pack
     SB_CHECK_ARG(packed != nullptr && !g_gather_tma && K == 1 && map_os == nullptr && row_of == nullptr && splits <= 1 &&
                      num_sources >= num_targets,
                  "conv_os: the identity map is for 1x1x1 layers with a packed weight image (K=%d)", K);
+  if (identity && g_identity_tma && dense_applies(num_targets, c_in, two ? c_in_a : c_in, c_out, feats, two ? feats_b : nullptr, packed))
+    return dense_run(feats, two ? feats_b : nullptr, two ? c_in_a : c_in, packed, epilogue, num_targets, c_in, c_out, out, status,
+                     wait_limit_ns(), as_stream(stream));
   if (packed == nullptr) {
     SB_CHECK_ARG(weights != nullptr, "conv_os: neither weights nor a packed image given");
     const size_t stem_smem = static_cast<size_t>(K) * c_in * c_out * 4 + static_cast<size_t>(128) * K * 4;
@@ -1985,6 +1989,7 @@ extern "C" int spira_b200_set_option(const char *name, int value) {
   SB_CHECK_ARG(name != nullptr, "set_option: null name");
   if (std::strcmp(name, "gather_tma") == 0) { g_gather_tma = value ? 1 : 0; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_n256") == 0) { g_os_n256 = value ? 1 : 0; return SPIRA_B200_OK; }
+  if (std::strcmp(name, "identity_tma") == 0) { g_identity_tma = value ? 1 : 0; return SPIRA_B200_OK; }
   if (std::strcmp(name, "pdl") == 0) { set_pdl_enabled(value != 0); return SPIRA_B200_OK; }
   if (std::strcmp(name, "ws_cooperative_launch") == 0) { g_ws_cooperative_launch = value ? 1 : 0; return SPIRA_B200_OK; }
   if (std::strcmp(name, "os_n256_min_targets") == 0) { g_os_n256_min_targets = value < 0 ? 0 : value; return SPIRA_B200_OK; }
@@ -2014,6 +2019,7 @@ extern "C" int spira_b200_get_option(const char *name) {
   if (name == nullptr) return -1;
   if (std::strcmp(name, "gather_tma") == 0) return g_gather_tma;
   if (std::strcmp(name, "os_n256") == 0) return g_os_n256;
+  if (std::strcmp(name, "identity_tma") == 0) return g_identity_tma;
   if (std::strcmp(name, "pdl") == 0) return pdl_enabled() ? 1 : 0;
   if (std::strcmp(name, "ws_cooperative_launch") == 0) return g_ws_cooperative_launch;
   if (std::strcmp(name, "wait_limit_us") == 0) return g_wait_limit_us;

@@ -78,6 +78,9 @@ def test_more_argument_errors_without_a_gpu(lib):
     assert lib.spira_b200_get_option(b"pdl") == 1 and lib.spira_b200_get_option(b"ws_cooperative_launch") == 0
     assert lib.spira_b200_set_option(b"pdl", 0) == 0 and lib.spira_b200_get_option(b"pdl") == 0
     assert lib.spira_b200_set_option(b"pdl", 1) == 0
+    assert lib.spira_b200_get_option(b"identity_tma") == 1
+    assert lib.spira_b200_set_option(b"identity_tma", 0) == 0 and lib.spira_b200_get_option(b"identity_tma") == 0
+    assert lib.spira_b200_set_option(b"identity_tma", 1) == 0
 
 
 def test_tape_and_descriptor_argument_checks_without_a_gpu(lib):

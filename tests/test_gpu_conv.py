@@ -318,22 +318,39 @@ def test_two_sources_equal_the_convolution_of_the_concatenation(C, scene, ca, cb
 
 
 @pytest.mark.parametrize("n", [1, 127, 128, 5000, 40001])
-@pytest.mark.parametrize("ca,cb,cout", [(64, 0, 128), (128, 64, 128), (256, 128, 256), (96, 32, 96), (32, 0, 64)])
+@pytest.mark.parametrize("ca,cb,cout", [(64, 0, 128), (128, 64, 128), (256, 128, 256), (96, 32, 96), (32, 0, 64), (96, 0, 48),
+                                        (160, 32, 240), (40, 24, 64)])
 def test_identity_map_layer_matches_the_matrix_product(C, n, ca, cb, cout):
     """A 1x1x1 layer through the identity map (no map tensor), one or two sources, with the fused epilogue, against the
-    fp32 matrix product."""
+    fp32 matrix product: on the dense TMA kernel (channel counts in whole 32-channel boxes; the last case is not) and,
+    with that kernel switched off, on the output-stationary kernel.  The two kernels add the same products in the same
+    order, so their results are equal."""
     rng = np.random.default_rng(n + ca)
     f = torch.from_numpy(rng.normal(size=(n, ca + cb)).astype(np.float16))
     w = torch.from_numpy((rng.normal(size=(1, ca + cb, cout)) / np.sqrt(ca + cb)).astype(np.float16))
     bias = torch.from_numpy(rng.normal(size=cout).astype(np.float16))
+    scale = torch.from_numpy(rng.uniform(0.5, 1.5, cout).astype(np.float32))
+    shift = torch.from_numpy(rng.normal(size=cout).astype(np.float32))
     res = torch.from_numpy(rng.normal(size=(n, cout)).astype(np.float16))
     want = f.float() @ w[0].float() + bias.float()
     fa = f[:, :ca].contiguous().cuda()
     fb = f[:, ca:].contiguous().cuda() if cb else None
-    got = C.conv_identity(fa, w.cuda(), sources_b=fb, bias=bias.cuda())
-    assert_features_close(got, want)
-    got = C.conv_identity(fa, w.cuda(), sources_b=fb, bias=bias.cuda(), residual=res.cuda(), relu=True)
-    assert_features_close(got, torch.relu(want + res.float()))
+    results = []
+    assert C.get_option("identity_tma") == 1
+    for tma in (1, 0):
+        C.set_option("identity_tma", tma)
+        try:
+            got = [C.conv_identity(fa, w.cuda(), sources_b=fb, bias=bias.cuda()),
+                   C.conv_identity(fa, w.cuda(), sources_b=fb, bias=bias.cuda(), residual=res.cuda(), relu=True),
+                   C.conv_identity(fa, w.cuda(), sources_b=fb, scale=scale.cuda(), shift=shift.cuda(), relu=True)]
+        finally:
+            C.set_option("identity_tma", 1)
+        assert_features_close(got[0], want)
+        assert_features_close(got[1], torch.relu(want + res.float()))
+        assert_features_close(got[2], torch.relu((f.float() @ w[0].float()) * scale + shift))
+        results.append(got)
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
     C.check_status()
 
 
