@@ -594,6 +594,7 @@ def main():
     ap.add_argument("--gather", default="default", choices=["default", "tma", "cpasync"], help="row-gather engine of the tensor-core kernels")
     ap.add_argument("--cin", type=int, default=64)
     ap.add_argument("--cout", type=int, default=64)
+    ap.add_argument("--ksize", type=int, default=3, choices=[3, 1], help="layer workload: 3 = submanifold 3^3 layer, 1 = 1x1x1 layer (no map)")
     ap.add_argument("--scene", default="c0", choices=["c0", "lidar"], help="layer workload: 50k-voxel plane/sphere scene or a LiDAR scene")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dataflow", default="auto", choices=["auto", "0", "1"], help="auto = per-group selector (tune); 0/1 = uniform")
@@ -652,6 +653,8 @@ def main():
         from spira_b200 import build, _lib
         build.build()
         _lib.load()
+        if args.no_identity_tma:
+            _lib.call("spira_b200_set_option", b"identity_tma", 0)
         line = {"layer": run_layer, "kmap": run_kmap}[args.workload](args, device, pk, pk_kind)
         line["n_gpus"] = n_gpus
         if rank == 0:
@@ -1019,6 +1022,62 @@ def _time_calls(fn, steps, warmup, l2buf):
     return sum(t) / len(t), min(t)
 
 
+def run_pointwise_layer(args, device, pk, pk_kind, n, feats, rng):
+    """Single 1x1x1 layer c_in -> c_out over the voxels of the scene (no kernel map: row t of the output reads row t of
+    the input), with a BatchNorm-style epilogue.  The layer is bound by HBM: it reads n*c_in*2 and writes n*c_out*2 bytes.
+    A launch takes ~15 us, less than the Python wrapper needs to prepare one, so a timed step is one pass of prepared
+    descriptor calls over SIX input / output sets (together larger than the L2: every launch reads rows that left the
+    cache several launches ago); the figures are per launch."""
+    import ctypes
+    from spira_b200 import _lib
+    from spira_b200.nn.functional import _C
+    w = torch.from_numpy((rng.normal(size=(1, args.cin, args.cout)) / np.sqrt(args.cin)).astype(np.float16)).to(device)
+    scale = torch.from_numpy(rng.uniform(0.5, 1.5, args.cout).astype(np.float32)).to(device)
+    shift = torch.from_numpy(rng.normal(size=args.cout).astype(np.float32)).to(device)
+    l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+    packed = _C.packed_weights(w, _C.PACK_OS)
+    if packed is None:
+        raise RuntimeError(f"a 1x1x1 layer {args.cin} -> {args.cout} is outside the tensor-core kernels")
+    ep, keep = _C._epilogue(None, scale, shift, None, False)
+    n_sets = 6
+    sets = []
+    for i in range(n_sets):
+        f = feats if i == 0 else feats.clone()
+        out = torch.empty((n, args.cout), dtype=torch.float16, device=device)
+        d = _lib.ConvDesc(dataflow=0, K=1, c_in=args.cin, c_out=args.cout, c_in_a=args.cin, num_sources=n, num_targets=n,
+                          feats=f.data_ptr(), packed=packed.data_ptr(), out=out.data_ptr())
+        d.epilogue = ctypes.pointer(ep)
+        sets.append((f, out, d))
+
+    def one_pass():
+        for _, _, d in sets:
+            _C.conv_desc_call(d, device)
+
+    pass_ms, pass_min_ms = _time_calls(one_pass, args.steps, args.warmup, l2buf)
+    mean_ms, min_ms = pass_ms / n_sets, pass_min_ms / n_sets
+    _C.check_status()
+    want = torch.mm(feats, w[0]).float() * scale + shift
+    err = (sets[-1][1].float() - want).abs().max().item()
+    if not err <= 2e-2 * max(1.0, want.abs().max().item()):
+        raise RuntimeError(f"1x1x1 layer: result differs from the matrix product by {err}")
+    flops = 2.0 * n * args.cin * args.cout
+    byts = n * args.cin * 2 + args.cin * args.cout * 2 + n * args.cout * 2
+    ach = byts / (mean_ms * 1e-3) / 1e9
+    dense = _C.get_option("identity_tma") == 1 and args.cin % 32 == 0
+    kernel = "dense_tc_kernel" if dense else "conv_tc_kernel<OS>"
+    workload_label = f"single 1x1x1 layer {args.cin}->{args.cout}, {n} voxels ({args.scene})"
+    roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(ach / pk["hbm_gbs"], 4),
+            "traffic": captured_traffic(kernel, workload_label), "kernel": kernel, "peak_source": f"of {pk_kind}",
+            "algorithmic_bytes": int(byts), "algorithmic_flops": int(flops),
+            "fastest_pass": {"ms_per_launch": round(min_ms, 5), "gbs": round(byts / (min_ms * 1e-3) / 1e9, 1)}}
+    return {"metric": "1x1x1 layer GB/s (bytes = n*(c_in + c_out)*2 + weights)", "value": round(ach, 1), "unit": "GB/s",
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(mean_ms, 5), "min_ms": round(min_ms, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": workload_label, "launches_per_step": n_sets,
+                       "l2": "six input/output sets (340 MB at 128->96 over 127 k voxels) visited in turn, and a 256 MiB buffer rewritten between timed steps"},
+            "roofline": roof, "gpu_launches": args.steps * n_sets}
+
+
 def run_layer(args, device, pk, pk_kind):
     """Single-layer workload: one submanifold 3^3 layer, c_in -> c_out, 50,000 voxels in a 512^3 grid (64-bit keys)."""
     from spira_b200 import scenes as sc, _lib
@@ -1031,6 +1090,8 @@ def run_layer(args, device, pk, pk_kind):
     keys, perm = _C.cuda_flatten_sort(torch.from_numpy(c).to(device), double)
     feats = torch.from_numpy(sc.features(n, args.cin, 0)).to(device)
     rng = np.random.default_rng(0)
+    if args.ksize == 1:
+        return run_pointwise_layer(args, device, pk, pk_kind, n, feats, rng)
     w = torch.from_numpy((rng.normal(size=(27, args.cin, args.cout)) / np.sqrt(27 * args.cin)).astype(np.float16)).to(device)
     df = 1 if args.dataflow == "1" else 0
     m = _C.cuda_binary_search(keys, keys, (3, 3, 3), (1, 1, 1), df)
@@ -1160,6 +1221,32 @@ def run_layer_reference(args, device, pk, pk_kind):
     keys = _padded(keys)
     feats = torch.from_numpy(sc.features(n, args.cin, 0)).to(device)
     rng = np.random.default_rng(0)
+    if args.ksize == 1:
+        # the reference's 1x1x1 layer is torch.mm (spira/nn/conv.py:312-316) followed by its BatchNorm module as a pass of its own
+        w1 = torch.from_numpy((rng.normal(size=(1, args.cin, args.cout)) / np.sqrt(args.cin)).astype(np.float16)).to(device)
+        gamma = torch.from_numpy(rng.uniform(0.5, 1.5, args.cout).astype(np.float16)).to(device)
+        beta = torch.from_numpy(rng.normal(size=args.cout).astype(np.float16)).to(device)
+        mean, var = torch.zeros(args.cout, dtype=torch.float16, device=device), torch.ones(args.cout, dtype=torch.float16, device=device)
+        l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+        inputs = [feats] + [feats.clone() for _ in range(5)]      # six sets visited in turn, as in this engine's leg
+        keep = [None] * len(inputs)
+
+        def one_pass():
+            for i, f in enumerate(inputs):
+                keep[i] = torch.nn.functional.batch_norm(torch.mm(f, w1[0]), mean, var, gamma, beta, False, 0.0, 1e-5)
+
+        pass_ms, pass_min_ms = _time_calls(one_pass, args.steps, args.warmup, l2buf)
+        mean_ms, min_ms = pass_ms / len(inputs), pass_min_ms / len(inputs)
+        byts = n * args.cin * 2 + args.cin * args.cout * 2 + n * args.cout * 2
+        v = round(byts / (mean_ms * 1e-3) / 1e9, 1)
+        return {"metric": "1x1x1 layer GB/s (bytes = n*(c_in + c_out)*2 + weights)", "value": v, "unit": "GB/s", "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": round(mean_ms, 5), "min_ms": round(min_ms, 5), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": {"workload": f"single 1x1x1 layer {args.cin}->{args.cout}, {n} voxels ({args.scene}), torch.mm + BatchNorm pass as in the reference",
+                           "l2": "256 MiB buffer rewritten between timed steps"},
+                "cpu_baseline": {"value": v, "unit": "GB/s", "cores": 0, "kind": "reference",
+                                 "sample": "the reference's own path on the GPU (library GEMM + BatchNorm kernel): it has no CPU path"},
+                "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     w = torch.from_numpy((rng.normal(size=(27, args.cin, args.cout)) / np.sqrt(27 * args.cin)).astype(np.float16)).to(device)
     l2buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
     gt, st_ = min(args.cin, 16), min(args.cout, 16)
