@@ -10,10 +10,10 @@
 // csrc/spira/cuda/functions/arg_sort_coodrinates.cu:35-88): least-significant-digit radix sort with 8-bit digits,
 // stable, so equal keys keep their input order like the reference's.  A first pass over the input packs the keys and
 // finds which bits differ between keys at all (AND / OR of all keys): digits whose bits are constant are skipped, which
-// removes e.g. five of the eight passes of a 64-bit key in a 512^3 grid.  A pass is: per-CTA digit histogram of the
-// CTA's contiguous chunk -> grid barrier -> every CTA sums the histogram columns of the CTAs before it (its base
-// position per digit) and scatters its chunk in order, ranking equal digits inside a warp with match_any and across
-// warps with a per-warp count table -> grid barrier.
+// removes e.g. five of the eight passes of a 64-bit key in a 512^3 grid.  A pass is: every CTA sums the per-CTA digit
+// histograms of the CTAs before it (its base position per digit) and scatters its contiguous chunk in order, ranking
+// equal digits inside a warp with match_any and across warps with a per-warp count table, and counts the NEXT digit of
+// every key it moves for the chunk the key lands in -> grid barrier (one per pass).
 //
 // Down-sampling of sorted keys (csrc/spira/torch/cuda_arg_sort_coordinates.cu:107-200 sorts every level from scratch):
 // flooring the coordinates to a stride twice as coarse disturbs the order only inside a coarse cell, so the final

@@ -5,10 +5,13 @@
 // pass over ~10^5 keys is a few microseconds of work and a chain of launches would spend its time on launch latencies.
 // A first phase generates the keys of the CTA's contiguous chunk (gen(i) for element i), writes the identity
 // permutation, builds the histogram of the lowest digit and finds which bits differ between keys at all (AND / OR of all
-// keys): digits whose bits are the same in every key are skipped.  A pass is: per-CTA digit histogram of the chunk ->
-// grid barrier -> every CTA sums the histogram columns of the CTAs before it (its base position per digit) and scatters
-// its chunk in order, ranking equal digits inside a warp with match_any and across warps with a per-warp count table ->
-// grid barrier.
+// keys): digits whose bits are the same in every key are skipped.  A pass is: every CTA sums the histogram columns of the
+// CTAs before it (its base position per digit) and scatters its chunk in order, ranking equal digits inside a warp with
+// match_any and across warps with a per-warp count table -> grid barrier.  The per-CTA histograms of the NEXT pass are
+// built during the scatter: the thread that moves a key knows the chunk it lands in and adds one to that chunk's count
+// of the key's next digit (a global reduction), so a pass needs ONE grid barrier and no histogram phase of its own.
+// Three histogram tables rotate: pass p reads table p % 3, adds into table (p + 1) % 3 and clears its own row of table
+// (p + 2) % 3, which every CTA finished reading before the barrier of pass p - 1.
 #pragma once
 
 #include "common.cuh"
@@ -26,7 +29,7 @@ struct SortParams {
   int32_t *vals_a;            // result (permutation)
   KeyT *keys_b;               // scratch
   int32_t *vals_b;
-  uint32_t *ghist;            // [gridDim.x][256]
+  uint32_t *ghist;            // [3][gridDim.x][256]
   KeyT *bits;                 // [2]: AND and OR of all keys (initialised to ~0 and 0)
   unsigned *barrier;
   int32_t *status;
@@ -81,7 +84,10 @@ __global__ void __launch_bounds__(kIngestThreads) sort_keys_kernel(const __grid_
     for (int w = 1; w < kIngestWarps; ++w) { k_and &= s_red[w]; k_or |= s_red[kIngestWarps + w]; }
     atomic_and_or(P.bits, k_and, k_or);
   }
-  if (tid < 256) P.ghist[b * 256 + tid] = s_hist[tid];
+  if (tid < 256) {
+    P.ghist[b * 256 + tid] = s_hist[tid];
+    P.ghist[(G + b) * 256 + tid] = 0u;      // this CTA's row of the table the first pass adds into
+  }
   if (!grid_sync(gb)) return;
   // bits in which at least two keys differ; the lowest digit always gets its pass (its histogram is on its way already:
   // a pass over a constant digit moves nothing)
@@ -91,18 +97,16 @@ __global__ void __launch_bounds__(kIngestThreads) sort_keys_kernel(const __grid_
   const int32_t *v_in = P.vals_a;
   KeyT *k_out = P.keys_b;
   int32_t *v_out = P.vals_b;
-  for (int shift = 0; shift < static_cast<int>(sizeof(KeyT)) * 8; shift += 8) {
+  constexpr int kKeyBits = static_cast<int>(sizeof(KeyT)) * 8;
+  int pass = 0;
+  for (int shift = 0; shift < kKeyBits; shift += 8) {
     if (((varying >> shift) & KeyT(0xff)) == 0) continue;            // every key has the same digit here: nothing moves
-    // ---- histogram of the chunk (the first pass got its histogram while packing) -------------------------------------------
-    if (shift > 0) {
-      if (tid < 256) s_hist[tid] = 0;
-      __syncthreads();
-      // (keys written by other CTAs in the pass before: read them past the L1, which is not coherent across SMs)
-      for (int i = c0 + tid; i < c1; i += kIngestThreads) atomicAdd(&s_hist[static_cast<uint32_t>(__ldcg(k_in + i) >> shift) & 0xffu], 1u);
-      __syncthreads();
-      if (tid < 256) P.ghist[b * 256 + tid] = s_hist[tid];
-      if (!grid_sync(gb)) return;
-    }
+    int next_shift = shift + 8;                                      // the digit of the next pass, if there is one
+    while (next_shift < kKeyBits && ((varying >> next_shift) & KeyT(0xff)) == 0) next_shift += 8;
+    const bool more = next_shift < kKeyBits;
+    const uint32_t *hist_cur = P.ghist + static_cast<size_t>(pass % 3) * G * 256;
+    uint32_t *hist_next = P.ghist + static_cast<size_t>((pass + 1) % 3) * G * 256;
+    if (tid < 256) P.ghist[(static_cast<size_t>((pass + 2) % 3) * G + b) * 256 + tid] = 0u;
     // ---- base position of every digit for this CTA: digits before it, and the same digit in the CTAs before it ---------------
     {
       // four threads per digit, each over a quarter of the CTAs, sixteen loads in flight: the sums are latency, not work
@@ -114,12 +118,12 @@ __global__ void __launch_bounds__(kIngestThreads) sort_keys_kernel(const __grid_
       for (; c + 16 <= ce; c += 16) {
         uint32_t v[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) v[e] = __ldcg(&P.ghist[(c + e) * 256 + d]);
+        for (int e = 0; e < 16; ++e) v[e] = __ldcg(&hist_cur[(c + e) * 256 + d]);
 #pragma unroll
         for (int e = 0; e < 16; ++e) { total += v[e]; before += (c + e) < b ? v[e] : 0u; }
       }
       for (; c < ce; ++c) {
-        const uint32_t v = __ldcg(&P.ghist[c * 256 + d]);
+        const uint32_t v = __ldcg(&hist_cur[c * 256 + d]);
         total += v;
         before += c < b ? v : 0u;
       }
@@ -174,6 +178,8 @@ __global__ void __launch_bounds__(kIngestThreads) sort_keys_kernel(const __grid_
         const uint32_t pos = s_wcount[warp][digit] + rank;
         k_out[pos] = key;
         v_out[pos] = val;
+        // the key lands in chunk pos / chunk: that CTA's histogram of the next digit
+        if (more) atomicAdd(&hist_next[(pos / static_cast<uint32_t>(chunk)) * 256 + (static_cast<uint32_t>(key >> next_shift) & 0xffu)], 1u);
       }
       __syncthreads();
       if (tid < 256) {
@@ -185,6 +191,7 @@ __global__ void __launch_bounds__(kIngestThreads) sort_keys_kernel(const __grid_
     if (!grid_sync(gb)) return;
     const KeyT *tk = k_in; k_in = k_out; k_out = const_cast<KeyT *>(tk);
     const int32_t *tv = v_in; v_in = v_out; v_out = const_cast<int32_t *>(tv);
+    ++pass;
   }
   // an odd number of passes leaves the result in the scratch buffers
   if (k_in != P.keys_a) {
@@ -201,8 +208,8 @@ inline int sort_grid() { return sm_count(); }
 
 template <typename KeyT>
 size_t sort_workspace_bytes(int64_t n) {
-  // [control 256][ghist G*256*4][alt keys][alt values]
-  return 256 + sort_round256(static_cast<size_t>(sort_grid()) * 256 * 4) + sort_round256(n * sizeof(KeyT)) + sort_round256(n * sizeof(int32_t));
+  // [control 256][ghist 3*G*256*4][alt keys][alt values]
+  return 256 + sort_round256(static_cast<size_t>(sort_grid()) * 3 * 256 * 4) + sort_round256(n * sizeof(KeyT)) + sort_round256(n * sizeof(int32_t));
 }
 
 // Sorts n generated keys into sorted_keys / order (order[i] = element of sorted position i).  The 16-byte aligned
@@ -225,7 +232,7 @@ int radix_sort_generated(const Gen &gen, int64_t n, KeyT *sorted_keys, int32_t *
   P.barrier = reinterpret_cast<unsigned *>(p);
   P.bits = reinterpret_cast<KeyT *>(p + 16);
   P.ghist = reinterpret_cast<uint32_t *>(p + 256);
-  char *q = p + 256 + sort_round256(static_cast<size_t>(sort_grid()) * 256 * 4);
+  char *q = p + 256 + sort_round256(static_cast<size_t>(sort_grid()) * 3 * 256 * 4);
   P.keys_b = reinterpret_cast<KeyT *>(q);
   P.vals_b = reinterpret_cast<int32_t *>(q + sort_round256(n * sizeof(KeyT)));
   P.status = status;
