@@ -72,3 +72,36 @@ def test_grouping_is_weighed_against_its_cost():
     assert estimate_layer_us(96, 96, 27, 127363, 1042915, 25985, grouped=False)[0] > estimate_layer_us(96, 96, 27, 127363, 1042915, 25985)[0]
     # kernels wider than 32 offsets are never grouped: the flag changes nothing
     assert estimate_layer_us(64, 64, 125, 50000, 900000, 40000, grouped=True) == estimate_layer_us(64, 64, 125, 50000, 900000, 40000, grouped=False)
+
+
+def test_concurrent_builds_never_expose_a_partial_library(tmp_path):
+    """Several ranks of one node call build() at the same moment.  With a stand-in compiler that writes its output in
+    two halves, the library path must only ever hold a complete file, and every process must return successfully."""
+    import os
+    import subprocess
+    import sys
+    import time
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    fake = tmp_path / "fake_nvcc"
+    fake.write_text("#!/bin/sh\n"
+                    "out=\"\"; shared=0\n"
+                    "while [ $# -gt 0 ]; do case \"$1\" in -o) out=\"$2\"; shift;; -shared) shared=1;; esac; shift; done\n"
+                    "if [ $shared = 1 ]; then printf FIRSTHALF > \"$out\"; sleep 0.3; printf SECONDHALF >> \"$out\"; else printf obj > \"$out\"; fi\n")
+    fake.chmod(0o755)
+    lib = tmp_path / "libfake.so"
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from pathlib import Path\n"
+            "from spira_b200 import build\n"
+            "build.build(force=True, lib=Path(%r), objdir=Path(%r))\n" % (str(root), str(lib), str(tmp_path / "obj")))
+    env = dict(os.environ, NVCC=str(fake))
+    procs = [subprocess.Popen([sys.executable, "-c", code], env=env) for _ in range(4)]
+    seen = set()
+    while any(p.poll() is None for p in procs):
+        if lib.exists():
+            seen.add(lib.read_bytes())
+        time.sleep(0.01)
+    assert all(p.returncode == 0 for p in procs)
+    assert lib.read_bytes() == b"FIRSTHALFSECONDHALF"
+    assert seen <= {b"FIRSTHALFSECONDHALF"}
+    assert not list(tmp_path.glob("*.tmp"))
